@@ -1,0 +1,319 @@
+"""Hot ops of the framework.
+
+Each op has two implementations: the in-tree sm_100a CUDA kernel (``nanotron_b200.ops.native``, C ABI in
+``csrc/``) used for CUDA tensors, and the PyTorch fp32 oracle (``nanotron_b200.ops.reference``) used on CPU and
+in tests.  On a CUDA device a missing extension is an error, never a silent fallback; the oracle can be forced
+with ``ops.set_mode("torch")``.
+"""
+from __future__ import annotations
+
+import math
+import os
+from contextlib import contextmanager
+from typing import Optional, Tuple
+
+import torch
+
+from nanotron_b200.ops import reference as ref
+
+_MODE = os.environ.get("NTB_OPS", "auto")  # auto | torch
+_GEMM = os.environ.get("NTB_GEMM", "auto")  # auto | cublas | tcgen05
+_ATTN = os.environ.get("NTB_ATTN", "auto")  # auto | native | sdpa
+LAUNCH_COUNTER = {"n": 0}
+
+
+def set_mode(mode: str):
+    global _MODE
+    assert mode in ("auto", "torch")
+    _MODE = mode
+
+
+def set_gemm(mode: str):
+    global _GEMM
+    assert mode in ("auto", "cublas", "tcgen05")
+    _GEMM = mode
+
+
+def set_attention(mode: str):
+    global _ATTN
+    assert mode in ("auto", "native", "sdpa")
+    _ATTN = mode
+
+
+def get_mode() -> str:
+    return _MODE
+
+
+@contextmanager
+def mode(m: str):
+    global _MODE
+    old = _MODE
+    set_mode(m)
+    try:
+        yield
+    finally:
+        _MODE = old
+
+
+def native_launches() -> int:
+    """Number of in-tree kernel launches issued by this process so far."""
+    return LAUNCH_COUNTER["n"]
+
+
+def _use_native(t: torch.Tensor) -> bool:
+    if _MODE == "torch" or not t.is_cuda:
+        return False
+    from nanotron_b200.ops import native
+
+    native.lib()  # raises when the extension is missing: no silent fallback on GPU
+    return True
+
+
+# ============================================================================ GEMM
+def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+    if _GEMM == "cublas" or not a.is_cuda or _MODE == "torch":
+        return False
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        return False
+    from nanotron_b200.ops import native
+
+    return native.gemm_supported(a, b, force=_GEMM == "tcgen05")
+
+
+def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[M,N] = x2[M,K] @ weight[N,K]^T (+ bias)."""
+    if _tcgen05_ok(x2, weight):
+        from nanotron_b200.ops import native
+
+        y = native.gemm_nt(x2, weight)
+        return y if bias is None else y + bias
+    return torch.nn.functional.linear(x2, weight, bias)
+
+
+def linear_dgrad(go2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """dx[M,K] = go2[M,N] @ weight[N,K]."""
+    if _tcgen05_ok(go2, weight):
+        from nanotron_b200.ops import native
+
+        return native.gemm_nn(go2, weight)
+    return go2.matmul(weight)
+
+
+def linear_wgrad(go2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+    """dW[N,K] = go2[M,N]^T @ x2[M,K].  When the weight carries an fp32 ``main_grad`` buffer the product is
+    accumulated into it and ``None`` is returned (autograd then leaves ``weight.grad`` unset)."""
+    main_grad = getattr(weight, "main_grad", None)
+    if main_grad is not None:
+        if _tcgen05_ok(go2, x2):
+            from nanotron_b200.ops import native
+
+            native.gemm_tn_accum_fp32(go2, x2, main_grad)
+        else:
+            gw = go2.t().matmul(x2)
+            main_grad.add_(gw)
+        weight.grad_added_to_main_grad = True
+        return None
+    if _tcgen05_ok(go2, x2):
+        from nanotron_b200.ops import native
+
+        return native.gemm_tn(go2, x2)
+    return go2.t().matmul(x2)
+
+
+# ============================================================================ norms
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, residual):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        r2 = residual.reshape(-1, shape[-1]) if residual is not None else None
+        if _use_native(x):
+            from nanotron_b200.ops import native
+
+            y, pre, rstd = native.rmsnorm_fwd(x2.contiguous(), r2.contiguous() if r2 is not None else None, weight, eps)
+        else:
+            y, pre, rstd = ref.rms_norm_fwd(x2, weight, eps, r2)
+        ctx.save_for_backward(pre, weight, rstd)
+        ctx.has_residual = residual is not None
+        ctx.shape = shape
+        if residual is not None:
+            return y.view(shape), pre.view(shape)
+        return y.view(shape), None
+
+    @staticmethod
+    def backward(ctx, dy, dpre):
+        pre, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, ctx.shape[-1]).contiguous()
+        dres = dpre.reshape(-1, ctx.shape[-1]).contiguous() if dpre is not None else None
+        if _use_native(dy2):
+            from nanotron_b200.ops import native
+
+            dx, dw = native.rmsnorm_bwd(dy2, pre, weight, rstd, dres)
+        else:
+            dx, dw = ref.rms_norm_bwd(dy2, pre, weight, rstd, dres)
+        dx = dx.view(ctx.shape)
+        return dx, dw.to(weight.dtype), None, (dx if ctx.has_residual else None)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
+    """Returns ``y`` (no residual) or ``(y, x + residual)``: the fused residual-add + norm used between blocks."""
+    y, pre = _RMSNorm.apply(x, weight, eps, residual)
+    return y if residual is None else (y, pre)
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, residual):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        r2 = residual.reshape(-1, shape[-1]) if residual is not None else None
+        if _use_native(x):
+            from nanotron_b200.ops import native
+
+            y, pre, mean, rstd = native.layernorm_fwd(x2.contiguous(), r2.contiguous() if r2 is not None else None, weight, bias, eps)
+        else:
+            y, pre, mean, rstd = ref.layer_norm_fwd(x2, weight, bias, eps, r2)
+        ctx.save_for_backward(pre, weight, mean, rstd)
+        ctx.has_residual, ctx.has_bias, ctx.shape = residual is not None, bias is not None, shape
+        return y.view(shape), (pre.view(shape) if residual is not None else None)
+
+    @staticmethod
+    def backward(ctx, dy, dpre):
+        pre, weight, mean, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, ctx.shape[-1]).contiguous()
+        dres = dpre.reshape(-1, ctx.shape[-1]).contiguous() if dpre is not None else None
+        if _use_native(dy2):
+            from nanotron_b200.ops import native
+
+            dx, dw, db = native.layernorm_bwd(dy2, pre, weight, mean, rstd, dres, ctx.has_bias)
+        else:
+            dx, dw, db = ref.layer_norm_bwd(dy2, pre, weight, mean, rstd, dres, ctx.has_bias)
+        dx = dx.view(ctx.shape)
+        return dx, dw.to(weight.dtype), (db.to(weight.dtype) if ctx.has_bias else None), None, (dx if ctx.has_residual else None)
+
+
+def layer_norm(x, weight, bias, eps: float, residual=None):
+    y, pre = _LayerNorm.apply(x, weight, bias, eps, residual)
+    return y if residual is None else (y, pre)
+
+
+# ============================================================================ rotary
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, interleaved, inplace):
+        ctx.save_for_backward(cos, sin)
+        ctx.interleaved = interleaved
+        if _use_native(x):
+            from nanotron_b200.ops import native
+
+            out = native.rope(x, cos, sin, interleaved, inverse=False, inplace=inplace)
+            if inplace:
+                ctx.mark_dirty(x)
+            return out
+        return ref.rope_apply(x, cos, sin, interleaved)
+
+    @staticmethod
+    def backward(ctx, dout):
+        cos, sin = ctx.saved_tensors
+        if _use_native(dout):
+            from nanotron_b200.ops import native
+
+            return native.rope(dout.contiguous() if dout.stride(-1) != 1 else dout, cos, sin, ctx.interleaved, inverse=True, inplace=False), None, None, None, None
+        return ref.rope_apply(dout, cos, sin, ctx.interleaved, inverse=True), None, None, None, None
+
+
+def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool = False, inplace: bool = False) -> torch.Tensor:
+    """x: [T, H, D] (may be a strided view into a fused qkv buffer, last dim contiguous); cos/sin: [T, D/2] fp32."""
+    return _Rope.apply(x, cos, sin, interleaved, inplace)
+
+
+# ============================================================================ SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        if _use_native(gate_up):
+            from nanotron_b200.ops import native
+
+            return native.swiglu_fwd(gate_up.contiguous())
+        return ref.swiglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gate_up,) = ctx.saved_tensors
+        if _use_native(dout):
+            from nanotron_b200.ops import native
+
+            return native.swiglu_bwd(gate_up.contiguous(), dout.contiguous())
+        return ref.swiglu_bwd(gate_up, dout)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for the fused [gate | up] projection output; the product is recomputed in backward."""
+    return _SwiGLU.apply(gate_up)
+
+
+# ============================================================================ cross entropy pieces
+def ce_partials(logits2: torch.Tensor, target: torch.Tensor, vocab_start: int):
+    if _use_native(logits2):
+        from nanotron_b200.ops import native
+
+        return native.ce_partials(logits2.contiguous(), target.contiguous(), vocab_start)
+    return ref.ce_partials(logits2, target, vocab_start)
+
+
+def ce_backward(logits2, target, logz, grad_loss, grad_z, vocab_start: int):
+    if _use_native(logits2):
+        from nanotron_b200.ops import native
+
+        return native.ce_backward(logits2, target, logz.contiguous(), grad_loss, grad_z, vocab_start)
+    return ref.ce_backward(logits2, target, logz, grad_loss, grad_z, vocab_start)
+
+
+# ============================================================================ attention
+class _FlashAttnVarlen(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, window):
+        from nanotron_b200.ops import native
+
+        out, lse = native.flash_attn_fwd(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, window)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.cfg = (max_q, max_k, causal, scale, window)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from nanotron_b200.ops import native
+
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        max_q, max_k, causal, scale, window = ctx.cfg
+        dq, dk, dv = native.flash_attn_bwd(dout.contiguous(), q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale, window)
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
+def _sdpa_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, window):
+    """Library attention for CUDA tensors when the in-tree kernel does not cover the case."""
+    B = cu_q.numel() - 1
+    Tq, Hq, D = q.shape
+    if B * max_q == Tq and B * max_k == k.shape[0] and window is None:
+        qb = q.view(B, max_q, Hq, D).transpose(1, 2)
+        kb = k.view(B, max_k, k.shape[1], D).transpose(1, 2)
+        vb = v.view(B, max_k, v.shape[1], D).transpose(1, 2)
+        o = torch.nn.functional.scaled_dot_product_attention(qb, kb, vb, is_causal=causal and max_q == max_k, scale=scale, enable_gqa=Hq != k.shape[1])
+        return o.transpose(1, 2).reshape(Tq, Hq, D)
+    return ref.attention_varlen(q, k, v, cu_q, cu_k, causal=causal, softmax_scale=scale, window=window)
+
+
+def flash_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, causal: bool = True, softmax_scale: Optional[float] = None, window: Optional[int] = None) -> torch.Tensor:
+    """Variable-length attention over packed sequences.  q: [Tq,Hq,D]; k,v: [Tk,Hkv,D]; cu_seqlens int32 [B+1]."""
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and _MODE != "torch":
+        from nanotron_b200.ops import native
+
+        if _ATTN != "sdpa" and native.flash_attn_supported(q, k, v, window):
+            return _FlashAttnVarlen.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
+        return _sdpa_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
+    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=scale, window=window)
+
+
+from nanotron_b200.ops import tp_fused  # noqa: E402,F401

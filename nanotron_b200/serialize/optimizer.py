@@ -1,0 +1,205 @@
+"""Optimizer / LR-scheduler checkpoints (format parity: reference src/nanotron/serialize/optimizer.py:27-370).
+
+``optimizer/optimizer_config.json`` records the optimizer type, the topology it was saved under and, for ZeRO-1, the
+per-parameter dp-rank offsets and original shapes.  State dicts are ``torch.save``d per (pp, [dp,] tp, exp) rank.
+Loading supports the same topology (fast path), a different dp size under ZeRO-1 (merge dp shards, re-slice) and a
+different tp size (merge + re-shard each state tensor through the parameters' slice maps).
+"""
+from __future__ import annotations
+
+import json
+import warnings
+from pathlib import Path
+from typing import Dict, Optional, Tuple
+
+import torch
+from torch import nn
+
+from nanotron_b200 import distributed as dist
+from nanotron_b200 import optim
+from nanotron_b200.logging import get_logger, log_rank
+from nanotron_b200.optim.zero import ZeroDistributedOptimizer, extract_parallel_ranks_from_shard_path, merge_dp_shard_in_zero1_optimizer
+from nanotron_b200.parallel import ParallelContext
+from nanotron_b200.parallel.parameters import NanotronParameter
+from nanotron_b200.serialize.metadata import TensorMetadata
+from nanotron_b200.serialize.utils import ObjectType, merge_and_shard_tp_tensors
+
+logger = get_logger(__name__)
+
+
+def _ep(parallel_context):
+    size = parallel_context.expert_parallel_size
+    return (dist.get_rank(parallel_context.ep_pg) if size > 1 else 0), size
+
+
+def optimizer_filename(parallel_context: ParallelContext, is_zero: bool) -> str:
+    ep_rank, ep_size = _ep(parallel_context)
+    pp, tp, dp = parallel_context.pp_pg, parallel_context.tp_pg, parallel_context.dp_pg
+    if is_zero:
+        return f"{ObjectType.OPTIMIZER.value}_pp-{dist.get_rank(pp)}-of-{pp.size()}_dp-{dist.get_rank(dp)}-of-{dp.size()}_tp-{dist.get_rank(tp)}-of-{tp.size()}_exp-{ep_rank}-of-{ep_size}.pt"
+    return f"{ObjectType.OPTIMIZER.value}_pp-{dist.get_rank(pp)}-of-{pp.size()}_tp-{dist.get_rank(tp)}-of-{tp.size()}_exp-{ep_rank}-of-{ep_size}.pt"
+
+
+def lr_scheduler_filename(parallel_context: ParallelContext, is_zero: bool) -> str:
+    return optimizer_filename(parallel_context, is_zero).replace(ObjectType.OPTIMIZER.value + "_", ObjectType.LR_SCHEDULER.value + "_", 1)
+
+
+def save_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelContext, root_folder: Path):
+    if not optimizer.inherit_from(ZeroDistributedOptimizer) and dist.get_rank(parallel_context.dp_cp_pg) > 0:
+        return  # identical on every dp replica: only the first writes
+    if optimizer.inherit_from(ZeroDistributedOptimizer) and dist.get_rank(parallel_context.cp_pg) > 0:
+        return
+    root_folder = Path(root_folder) / "optimizer"
+    root_folder.mkdir(exist_ok=True, parents=True)
+    if dist.get_rank(parallel_context.world_pg) == 0:
+        cfg = {
+            "type": str(optimizer.__class__.__name__),
+            "parallelism": {
+                "tp_size": str(parallel_context.tp_pg.size()),
+                "dp_size": str(parallel_context.dp_pg.size()),
+                "pp_size": str(parallel_context.pp_pg.size()),
+                "expert_parallel_size": str(parallel_context.expert_parallel_size),
+            },
+            "configs": {},
+        }
+        if isinstance(optimizer, ZeroDistributedOptimizer):
+            cfg["configs"]["param_name_to_dp_rank_offsets"] = {n: {str(r): list(v) for r, v in per.items()} for n, per in optimizer.param_name_to_dp_rank_offsets.items()}
+            cfg["configs"]["orig_param_shapes"] = {n: list(p.shape) for g in optimizer.zero_named_param_groups for n, p in g["named_params"]}
+        with open(root_folder / "optimizer_config.json", "w") as fo:
+            json.dump(cfg, fo)
+    torch.save(optimizer.state_dict(), root_folder / optimizer_filename(parallel_context, is_zero=optimizer.inherit_from(ZeroDistributedOptimizer)))
+
+
+def save_lr_scheduler(lr_scheduler, is_zero, parallel_context: ParallelContext, root_folder: Path):
+    if not is_zero and dist.get_rank(parallel_context.dp_cp_pg) > 0:
+        return
+    if is_zero and dist.get_rank(parallel_context.cp_pg) > 0:
+        return
+    root_folder = Path(root_folder) / "lr_scheduler"
+    root_folder.mkdir(exist_ok=True, parents=True)
+    torch.save(lr_scheduler.state_dict(), root_folder / lr_scheduler_filename(parallel_context, is_zero))
+
+
+def _reshard_state_tensor(full_unsharded: torch.Tensor, param: NanotronParameter) -> torch.Tensor:
+    """Cut this rank's shard of an unsharded state tensor following the parameter's slice map."""
+    if not (isinstance(param, NanotronParameter) and param.is_sharded):
+        return full_unsharded
+    info = param.get_sharded_info()
+    out = torch.empty(tuple(param.shape) if param.dim() > 0 else (), dtype=full_unsharded.dtype)
+    for sp in info.local_global_slices_pairs:
+        out[sp.local_slices] = full_unsharded[sp.global_slices]
+    return out
+
+
+@torch.no_grad()
+def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelContext, root_folder: Path, map_location: Optional[str] = None, param_shard_metadata: Optional[Dict[str, Dict[Tuple[str, str], TensorMetadata]]] = None, model: Optional[nn.Module] = None):
+    root_folder = Path(root_folder) / "optimizer"
+    with open(root_folder / "optimizer_config.json") as fi:
+        ckp_cfg = json.load(fi)
+    ckp_pp = int(ckp_cfg["parallelism"]["pp_size"])
+    ckp_tp = int(ckp_cfg["parallelism"]["tp_size"])
+    ckp_dp = int(ckp_cfg["parallelism"]["dp_size"])
+    is_zero_ckp = "ZeroDistributedOptimizer" in ckp_cfg["type"]
+    is_zero_now = optimizer.inherit_from(ZeroDistributedOptimizer)
+    same_topology = ckp_pp == parallel_context.pp_pg.size() and ckp_tp == parallel_context.tp_pg.size() and (not is_zero_ckp or ckp_dp == parallel_context.dp_pg.size()) and is_zero_ckp == is_zero_now
+    if same_topology:
+        state_dict = torch.load(root_folder / optimizer_filename(parallel_context, is_zero=is_zero_now), map_location=map_location, weights_only=False)
+        optimizer.load_state_dict(state_dict, map_location=map_location)
+        return
+    if ckp_pp != parallel_context.pp_pg.size():
+        warnings.warn("You are resuming in a different PP size, so optimizer states need to be checked. Feel free to open a PR if you work on this!")
+    assert model is not None, "loading optimizer states under a different topology needs the model (for the parameters' slice maps)"
+    # 1) unshard over dp (ZeRO) -> {(pp, tp): state dict with full-shard tensors}
+    if is_zero_ckp:
+        shard_paths = sorted(root_folder.glob(f"{ObjectType.OPTIMIZER.value}_pp-*-of-{ckp_pp}_dp-*-of-{ckp_dp}_tp-*-of-{ckp_tp}_exp-*.pt"))
+        per_pp_tp = merge_dp_shard_in_zero1_optimizer(model, ckp_cfg, shard_paths, parallel_context, map_location="cpu")
+    else:
+        per_pp_tp = {}
+        for p in sorted(root_folder.glob(f"{ObjectType.OPTIMIZER.value}_pp-*-of-{ckp_pp}_tp-*-of-{ckp_tp}_exp-*.pt")):
+            per_pp_tp[extract_parallel_ranks_from_shard_path(p, is_zero1=False)] = torch.load(p, map_location="cpu", weights_only=False)
+    # 2) gather each named state across the checkpoint's tp ranks into unsharded tensors
+    name_to_param = dict(model.get_named_params_with_correct_tied()) if hasattr(model, "get_named_params_with_correct_tied") else dict(model.named_parameters())
+    new_sd = optimizer.state_dict()
+    new_names = new_sd["names"]
+    state_keys = ["exp_avg", "exp_avg_sq"]
+    new_state = {}
+    my_dp = dist.get_rank(parallel_context.dp_pg)
+    for idx, name in new_names.items():
+        param = name_to_param[name]
+        shards = []
+        step = None
+        for (pp_rank, tp_rank), sd in per_pp_tp.items():
+            ckp_idx = next((k for k, v in sd["names"].items() if v == name), None)
+            if ckp_idx is None:
+                continue
+            shards.append((tp_rank, sd["state"][ckp_idx]))
+            step = sd["state"][ckp_idx]["step"]
+        assert shards, f"optimizer state of {name} not found in checkpoint"
+        entry = {"step": step}
+        for sk in state_keys:
+            if isinstance(param, NanotronParameter) and param.is_sharded and ckp_tp != parallel_context.tp_pg.size():
+                assert param_shard_metadata is not None and name in param_shard_metadata or True
+                info = param.get_sharded_info()
+                unsharded = torch.zeros(tuple(info.unsharded_shape), dtype=torch.float32)
+                # slice maps of the checkpoint shards were collected while loading the weights
+                metas = (param_shard_metadata or {}).get(name, {})
+                for tp_rank, st in shards:
+                    meta = next((m for (pp_s, tp_s), m in metas.items() if int(tp_s) == int(tp_rank)), None)
+                    assert meta is not None, f"missing slice map of {name} tp shard {tp_rank}; load the weights first with param_shard_metadata"
+                    shard_t = st[sk].float()
+                    for sp in meta.local_global_slices_pairs:
+                        unsharded[sp.global_slices] = shard_t.view(_local_shape(meta))[sp.local_slices]
+                local = _reshard_state_tensor(unsharded, param)
+            else:
+                local = shards[0][1][sk].float().view(param.shape)
+            if is_zero_now:
+                rng = optimizer.param_name_to_dp_rank_offsets[name].get(my_dp)
+                local = local.reshape(-1)[rng[0] : rng[1]] if rng is not None else local.reshape(-1)[0:0]
+            entry[sk] = local.clone()
+        new_state[idx] = entry
+    new_sd["state"] = new_state
+    if "gradient_accumulator" in new_sd:
+        ga = {}
+        for name in new_sd["gradient_accumulator"]:
+            param = name_to_param[name]
+            src = None
+            for sd in per_pp_tp.values():
+                if "gradient_accumulator" in sd and name in sd["gradient_accumulator"]:
+                    src = sd["gradient_accumulator"][name]
+                    break
+            if src is None or ckp_tp != parallel_context.tp_pg.size():
+                # masters can always be rebuilt from the (already loaded) parameters
+                full = param.detach().float().cpu()
+            else:
+                full = src.float().view(param.shape)
+            if is_zero_now:
+                rng = optimizer.param_name_to_dp_rank_offsets[name].get(my_dp)
+                full = full.reshape(-1)[rng[0] : rng[1]] if rng is not None else full.reshape(-1)[0:0]
+            ga[name] = full
+        new_sd["gradient_accumulator"] = ga
+    optimizer.load_state_dict(new_sd, map_location=map_location)
+
+
+def _local_shape(meta: TensorMetadata):
+    shape = []
+    first = meta.local_global_slices_pairs
+    ndim = len(meta.unsharded_shape)
+    for d in range(ndim):
+        stops = [sp.local_slices[d].stop for sp in first]
+        if any(s is None for s in stops):
+            shape.append(meta.unsharded_shape[d])
+        else:
+            shape.append(max(stops))
+    return tuple(shape)
+
+
+def load_lr_scheduler(lr_scheduler, is_zero, parallel_context: ParallelContext, root_folder: Path):
+    root_folder = Path(root_folder) / "lr_scheduler"
+    path = root_folder / lr_scheduler_filename(parallel_context, is_zero)
+    if not path.exists():
+        candidates = sorted(root_folder.glob(f"{ObjectType.LR_SCHEDULER.value}_*.pt"))
+        assert candidates, f"no lr scheduler state in {root_folder}"
+        path = candidates[0]
+    state_dict = torch.load(path, weights_only=False)
+    lr_scheduler.load_state_dict(state_dict)
+    lr_scheduler._initial_step()
