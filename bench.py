@@ -1,0 +1,232 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B pre-training throughput (tokens/s, whole job) on N B200s of one node.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 bench.py --gpus 8
+    python bench.py --impl reference ...      # the unmodified reference installed under baseline/_ref
+
+What is timed: full training steps (forward, backward, gradient reduction, clipping, AdamW on fp32 masters, bf16
+parameter refresh) of a random-init Llama-3-8B (32 layers, hidden 4096, ffn 14336, 32/8 heads, vocab 128256) on
+uniform-random tokens, sequence 4096, bf16 compute with fp32 gradient accumulation and fp32 master weights,
+data-parallel over N GPUs with ZeRO-1 (weak scaling: every GPU processes the same number of tokens per step).
+Timing: CUDA events around exactly K steps, barrier + synchronize on both sides, max over ranks.  The working set
+of a step (tens of GB) is far larger than L2, so no explicit L2 flush is done between steps.
+A second number ("e2e") times the same steps through ``DistributedTrainer.training_step`` with the inputs built in
+pinned host memory and copied to the device every micro-batch, and the loss read back to the host every step.
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+# reference's published best single-node MFU for its 8.86B model (45.22 % of 989 TFLOPs on H100) expressed as tokens/s/GPU
+BASELINE_TOK_S_PER_GPU = 7900.0
+
+MODELS = {
+    "llama3-8b": dict(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0, max_position_embeddings=4096, rms_norm_eps=1e-5, tie_word_embeddings=False),
+    "llama3.2-1b": dict(hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, vocab_size=128256, rope_theta=500000.0, max_position_embeddings=4096, rms_norm_eps=1e-5, tie_word_embeddings=True),
+    "tiny": dict(hidden_size=512, intermediate_size=1536, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=4, vocab_size=32000, rope_theta=10000.0, max_position_embeddings=4096, rms_norm_eps=1e-5, tie_word_embeddings=False),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._proc = None
+        self._thread = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            if self._stop.is_set():
+                break
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except Exception:
+                pass
+        clocks, reasons, max_mhz = [], set(), None
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                max_mhz = float(s[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def build_config(args, world: int):
+    import nanotron_b200.config as c
+
+    mc = c.LlamaConfig(**MODELS[args.model])
+    zero = 1 if world > 1 else 0
+    return c.Config(
+        general=c.GeneralArgs(project="bench", run="bench", seed=42, ignore_sanity_checks=True),
+        parallelism=c.ParallelismArgs(dp=world, pp=1, tp=1, pp_engine="1f1b", tp_mode="reduce_scatter", tp_linear_async_communication=False, recompute_layer=args.recompute),
+        model=c.ModelArgs(model_config=mc, init_method=c.RandomInit(std=0.02), dtype="bfloat16"),
+        tokenizer=c.TokenizerArgs(),
+        checkpoints=c.CheckpointsArgs(checkpoints_path="/tmp/ntb_bench_ckpt", checkpoint_interval=10**9, save_final_state=False),
+        logging=c.LoggingArgs(log_level="warning", log_level_replica="error", iteration_step_info_interval=10**9),
+        tokens=c.TokensArgs(sequence_length=args.seq, train_steps=10**6, micro_batch_size=args.mbs, batch_accumulation_per_replica=args.accum),
+        optimizer=c.OptimizerArgs(
+            optimizer_factory=c.AdamWOptimizerArgs(adam_eps=1e-8, adam_beta1=0.9, adam_beta2=0.95, torch_adam_is_fused=True),
+            zero_stage=zero, weight_decay=0.01, clip_grad=1.0, accumulate_grad_in_fp32=True,
+            learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=3e-4, lr_warmup_steps=2, lr_decay_style="cosine", min_decay_lr=3e-5),
+        ),
+        data_stages=[c.DatasetStageArgs(name="bench", start_training_step=1, data=c.DataArgs(dataset=None, seed=42, num_loading_workers=0))],
+    )
+
+
+def run_native(args):
+    import torch
+
+    import nanotron_b200.distributed as dist
+    from nanotron_b200 import ops
+    from nanotron_b200.data.dataloader import dummy_infinite_data_generator
+    from nanotron_b200.models.qwen import get_flops
+    from nanotron_b200.trainer import DistributedTrainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    os.environ.setdefault("RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1"), os.environ.setdefault("LOCAL_RANK", "0")
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    cfg = build_config(args, world)
+    trainer = DistributedTrainer(cfg)
+    trainer.prepare_training()
+    ctx = trainer.parallel_context
+    mc = trainer.model_config
+
+    def gen(host_pinned: bool):
+        return dummy_infinite_data_generator(
+            micro_batch_size=args.mbs, sequence_length=args.seq, input_pp_rank=0, output_pp_rank=0, vocab_size=mc.vocab_size,
+            seed=42, parallel_context=ctx, use_position_ids=False, host_pinned=host_pinned,
+        )()
+
+    def timed(loader, steps, read_loss: bool):
+        dist.barrier(ctx.world_pg)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = ops.native_launches()
+        start.record()
+        last = None
+        for _ in range(steps):
+            _, loss, _ = trainer.training_step(loader)
+            trainer.iteration_step += 1
+            if read_loss:
+                last = float(loss.item())  # device -> host read of the step result
+            else:
+                last = loss
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier(ctx.world_pg)
+        ms = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=ctx.world_pg)
+        return float(ms.item()), ops.native_launches() - launches0, last
+
+    dev_loader, host_loader = gen(False), gen(True)
+    timed(dev_loader, args.warmup, read_loss=False)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms, launches, loss = timed(dev_loader, args.steps, read_loss=False)
+    clocks = sampler.stop()
+    loss_val = float(loss.item())
+    timed(host_loader, 1, read_loss=True)
+    e2e_ms, _, _ = timed(host_loader, args.steps, read_loss=True)
+
+    tokens_per_step = args.mbs * args.seq * args.accum * world
+    value = tokens_per_step / (ms / args.steps / 1000.0)
+    e2e_value = tokens_per_step / (e2e_ms / args.steps / 1000.0)
+    flops, _ = get_flops(num_layers=mc.num_hidden_layers, hidden_size=mc.hidden_size, num_heads=mc.num_attention_heads, num_key_value_heads=mc.num_key_value_heads, vocab_size=mc.vocab_size, seq_len=args.seq, ffn_hidden_size=mc.intermediate_size, batch_size=1)
+    tflops_per_gpu = flops / args.seq * value / world / 1e12
+    peaks = {}
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    peak = peaks.get("bf16_tflops_sustained", 1400.0)
+    if rank == 0:
+        out = {
+            "metric": "Llama-3-8B training tokens/sec (whole job), bf16, seq 4096" if args.model == "llama3-8b" else f"{args.model} training tokens/sec",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if args.model == "llama3-8b" else None,
+            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "tokens_per_sec_per_gpu": value / world, "model_tflops_per_gpu": tflops_per_gpu, "mfu_of_measured_sustained_peak": tflops_per_gpu / peak,
+            "loss": loss_val, "impl": "nanotron_b200",
+            "config": {
+                "model": args.model, "global_batch": args.mbs * args.accum * world, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
+                "parallelism": f"dp{world}" + ("+zero1" if world > 1 else ""), "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
+                "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush",
+                "gemm": ops._GEMM, "attention": ops._ATTN,
+            },
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * args.mbs * args.seq * 8 * args.accum, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
+        }
+        print(json.dumps(out), flush=True)
+    dist.barrier(ctx.world_pg)
+    ctx.destroy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default="llama3-8b", choices=sorted(MODELS))
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--mbs", type=int, default=1)
+    ap.add_argument("--accum", type=int, default=8)
+    ap.add_argument("--recompute", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        from baseline.run_reference import run_reference
+
+        return run_reference(args)
+    run_native(args)
+
+
+if __name__ == "__main__":
+    main()

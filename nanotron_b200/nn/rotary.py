@@ -41,10 +41,11 @@ class RotaryEmbedding(nn.Module):
 
     def forward(self, q: torch.Tensor, k: Optional[torch.Tensor], positions: torch.Tensor, inplace: bool = False, max_position: Optional[int] = None):
         """q: [T, Hq, D], k: [T, Hkv, D] (views are fine); positions: [T]."""
-        cos, sin = self.get_cos_sin(positions, max_position)
-        q = ops.apply_rotary(q, cos, sin, self.interleaved, inplace)
+        self._ensure_tables(max_position if max_position is not None else self.max_seq_len, positions.device)
+        pos = positions.reshape(-1)
+        q = ops.apply_rotary(q, self.cos_table, self.sin_table, self.interleaved, inplace, positions=pos)
         if k is not None:
-            k = ops.apply_rotary(k, cos, sin, self.interleaved, inplace)
+            k = ops.apply_rotary(k, self.cos_table, self.sin_table, self.interleaved, inplace, positions=pos)
         return q, k
 
 

@@ -200,31 +200,37 @@ def layer_norm(x, weight, bias, eps: float, residual=None):
 # ============================================================================ rotary
 class _Rope(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, cos, sin, interleaved, inplace):
-        ctx.save_for_backward(cos, sin)
+    def forward(ctx, x, cos, sin, interleaved, inplace, positions):
+        ctx.save_for_backward(cos, sin, positions)
         ctx.interleaved = interleaved
         if _use_native(x):
             from nanotron_b200.ops import native
 
-            out = native.rope(x, cos, sin, interleaved, inverse=False, inplace=inplace)
+            out = native.rope(x, cos, sin, interleaved, inverse=False, inplace=inplace, positions=positions)
             if inplace:
                 ctx.mark_dirty(x)
             return out
+        if positions is not None:
+            cos, sin = cos.index_select(0, positions.long()), sin.index_select(0, positions.long())
         return ref.rope_apply(x, cos, sin, interleaved)
 
     @staticmethod
     def backward(ctx, dout):
-        cos, sin = ctx.saved_tensors
+        cos, sin, positions = ctx.saved_tensors
         if _use_native(dout):
             from nanotron_b200.ops import native
 
-            return native.rope(dout.contiguous() if dout.stride(-1) != 1 else dout, cos, sin, ctx.interleaved, inverse=True, inplace=False), None, None, None, None
-        return ref.rope_apply(dout, cos, sin, ctx.interleaved, inverse=True), None, None, None, None
+            d = dout if dout.stride(-1) == 1 and dout.stride(0) % 8 == 0 and dout.stride(1) % 8 == 0 else dout.contiguous()
+            return native.rope(d, cos, sin, ctx.interleaved, inverse=True, inplace=False, positions=positions), None, None, None, None, None
+        if positions is not None:
+            cos, sin = cos.index_select(0, positions.long()), sin.index_select(0, positions.long())
+        return ref.rope_apply(dout, cos, sin, ctx.interleaved, inverse=True), None, None, None, None, None
 
 
-def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool = False, inplace: bool = False) -> torch.Tensor:
-    """x: [T, H, D] (may be a strided view into a fused qkv buffer, last dim contiguous); cos/sin: [T, D/2] fp32."""
-    return _Rope.apply(x, cos, sin, interleaved, inplace)
+def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool = False, inplace: bool = False, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x: [T, H, D] (may be a strided view into a fused qkv buffer, last dim contiguous).  cos/sin fp32: either
+    per-token rows [T, D/2], or whole tables [P, D/2] indexed by ``positions`` [T] inside the kernel."""
+    return _Rope.apply(x, cos, sin, interleaved, inplace, positions)
 
 
 # ============================================================================ SwiGLU

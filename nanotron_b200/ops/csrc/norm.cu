@@ -1,0 +1,208 @@
+// RMSNorm / LayerNorm forward and backward with optional fused residual add (sm_100a).
+//
+// Forward: one CTA per row; the row is staged once in shared memory (fp32) so DRAM sees exactly one read of x
+// (and of the residual) and one write of y (and of the new residual).  Statistics are fp32.
+// Backward: a persistent grid; each CTA walks rows with a grid stride, keeps per-column partial sums of dW (and dB)
+// in shared memory, and writes them to a [gridDim.x, cols] fp32 scratch that a second small kernel reduces.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NORM_THREADS = 256;
+
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ w,
+                                                               const T* __restrict__ b, T* __restrict__ y, T* __restrict__ pre_out,
+                                                               float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols, float eps) {
+  extern __shared__ float srow[];  // cols floats
+  __shared__ float scratch[32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const T* xr = x + (size_t)row * cols;
+  const T* rr = residual ? residual + (size_t)row * cols : nullptr;
+  float sum = 0.f, sumsq = 0.f;
+  for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
+    Vec8<T> v;
+    float f[8];
+    v.load(xr + c);
+    v.to_float(f);
+    if (rr) {
+      Vec8<T> r;
+      float g[8];
+      r.load(rr + c);
+      r.to_float(g);
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] += g[i];
+      // the residual stream is kept in the activation dtype: round once, and normalise the rounded value so that
+      // backward (which only sees the stored tensor) is consistent with forward
+      Vec8<T> o;
+      o.from_float(f);
+      o.store(pre_out + (size_t)row * cols + c);
+      o.to_float(f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) { srow[c + i] = f[i]; sum += f[i]; sumsq += f[i] * f[i]; }
+  }
+  float mean = 0.f, var;
+  if (RMS) {
+    var = block_sum(sumsq, scratch) / cols;
+  } else {
+    mean = block_sum(sum, scratch) / cols;
+    // second pass over the staged row for a numerically safe variance
+    float d2 = 0.f;
+    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) { float d = srow[c + i] - mean; d2 += d * d; }
+    }
+    var = block_sum(d2, scratch) / cols;
+  }
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0) {
+    rstd_out[row] = rstd;
+    if (!RMS) mean_out[row] = mean;
+  }
+  T* yr = y + (size_t)row * cols;
+  for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
+    Vec8<T> wv, o;
+    float wf[8], f[8];
+    wv.load(w + c);
+    wv.to_float(wf);
+#pragma unroll
+    for (int i = 0; i < 8; i++) f[i] = (srow[c + i] - mean) * rstd * wf[i];
+    if (!RMS && b) {
+      Vec8<T> bv;
+      float bf[8];
+      bv.load(b + c);
+      bv.to_float(bf);
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] += bf[i];
+    }
+    o.from_float(f);
+    o.store(yr + c);
+  }
+}
+
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const T* __restrict__ w,
+                                                               const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                                               const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ dw_partial,
+                                                               float* __restrict__ db_partial, int rows, int cols) {
+  extern __shared__ float smem[];  // [cols] dw acc, [cols] db acc (LN only), [cols] wdy stage, [cols] xhat stage
+  __shared__ float scratch[32];
+  float* dw_acc = smem;
+  float* db_acc = RMS ? nullptr : smem + cols;
+  float* s_wdy = smem + (RMS ? 1 : 2) * cols;
+  float* s_xhat = s_wdy + cols;
+  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+    dw_acc[c] = 0.f;
+    if (!RMS) db_acc[c] = 0.f;
+  }
+  __syncthreads();
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    const float mean = RMS ? 0.f : mean_in[row];
+    const T* dyr = dy + (size_t)row * cols;
+    const T* xr = pre + (size_t)row * cols;
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
+      Vec8<T> a, bv, wv;
+      float fdy[8], fx[8], fw[8];
+      a.load(dyr + c); a.to_float(fdy);
+      bv.load(xr + c); bv.to_float(fx);
+      wv.load(w + c); wv.to_float(fw);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float xhat = (fx[i] - mean) * rstd;
+        const float wdy = fdy[i] * fw[i];
+        s_wdy[c + i] = wdy;
+        s_xhat[c + i] = xhat;
+        s1 += wdy * xhat;
+        s2 += wdy;
+        dw_acc[c + i] += fdy[i] * xhat;  // this thread is the only writer of these columns
+        if (!RMS) db_acc[c + i] += fdy[i];
+      }
+    }
+    const float c1 = block_sum(s1, scratch) / cols;
+    const float c2 = RMS ? 0.f : block_sum(s2, scratch) / cols;
+    T* dxr = dx + (size_t)row * cols;
+    const T* drr = dres ? dres + (size_t)row * cols : nullptr;
+    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] = (s_wdy[c + i] - s_xhat[c + i] * c1 - c2) * rstd;
+      if (drr) {
+        Vec8<T> r;
+        float g[8];
+        r.load(drr + c);
+        r.to_float(g);
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] += g[i];
+      }
+      Vec8<T> o;
+      o.from_float(f);
+      o.store(dxr + c);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+    dw_partial[(size_t)blockIdx.x * cols + c] = dw_acc[c];
+    if (!RMS) db_partial[(size_t)blockIdx.x * cols + c] = db_acc[c];
+  }
+}
+
+// out[c] = sum_p partial[p, c]
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * cols + c];
+  out[c] = s;
+}
+
+}  // namespace
+
+// Number of CTAs the backward kernels use (== rows of the partial scratch the caller must provide).
+NTB_EXPORT int ntb_norm_bwd_num_partials(int rows) {
+  int n = 148 * 2;
+  return rows < n ? rows : n;
+}
+
+NTB_EXPORT int ntb_norm_fwd(int is_rms, int dtype, const void* x, const void* residual, const void* w, const void* b, void* y, void* pre_out,
+                            float* mean_out, float* rstd_out, int rows, int cols, float eps, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || cols > 32768) return NTB_ERR_ARG;
+  if (residual && !pre_out) return NTB_ERR_ARG;
+  const size_t smem = (size_t)cols * sizeof(float);
+  NTB_DISPATCH_DTYPE(dtype, {
+    if (is_rms) {
+      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_fwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      norm_fwd_kernel<T, true><<<rows, NORM_THREADS, smem, stream>>>((const T*)x, (const T*)residual, (const T*)w, (const T*)b, (T*)y, (T*)pre_out, mean_out, rstd_out, rows, cols, eps);
+    } else {
+      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_fwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      norm_fwd_kernel<T, false><<<rows, NORM_THREADS, smem, stream>>>((const T*)x, (const T*)residual, (const T*)w, (const T*)b, (T*)y, (T*)pre_out, mean_out, rstd_out, rows, cols, eps);
+    }
+  });
+  return ntb_check_launch();
+}
+
+// dw_partial / db_partial: fp32 [ntb_norm_bwd_num_partials(rows), cols]; dw_out / db_out: fp32 [cols].
+NTB_EXPORT int ntb_norm_bwd(int is_rms, int dtype, const void* dy, const void* pre, const void* w, const float* mean, const float* rstd,
+                            const void* dres, void* dx, float* dw_partial, float* db_partial, float* dw_out, float* db_out, int rows, int cols,
+                            cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || cols > 12288) return NTB_ERR_ARG;
+  const int nparts = ntb_norm_bwd_num_partials(rows);
+  const size_t smem = (size_t)cols * sizeof(float) * (is_rms ? 3 : 4);
+  NTB_DISPATCH_DTYPE(dtype, {
+    if (is_rms) {
+      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      norm_bwd_kernel<T, true><<<nparts, NORM_THREADS, smem, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres, (T*)dx, dw_partial, db_partial, rows, cols);
+    } else {
+      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      norm_bwd_kernel<T, false><<<nparts, NORM_THREADS, smem, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres, (T*)dx, dw_partial, db_partial, rows, cols);
+    }
+  });
+  int rc = ntb_check_launch();
+  if (rc) return rc;
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw_out, nparts, cols);
+  if (!is_rms && db_out) reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(db_partial, db_out, nparts, cols);
+  return ntb_check_launch();
+}

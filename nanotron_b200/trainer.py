@@ -299,6 +299,13 @@ class DistributedTrainer:
                 self.save_checkpoint()
         self.post_training()
 
+    def prepare_training(self):
+        """Set up what ``train`` sets up before its loop, for callers that drive ``training_step`` themselves."""
+        self.pipeline_engine: PipelineEngine = self.config.parallelism.pp_engine
+        self.pipeline_engine.nb_microbatches = self.n_micro_batches_per_batch
+        self.initial_iter_step = self.metadata.last_train_step + 1
+        self.iteration_step = self.initial_iter_step
+
     def training_step(self, dataloader: Iterator[Dict[str, Union[torch.Tensor, TensorPointer]]]):
         before_tbi_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator, self.lr_scheduler)
         if self.iteration_step < self.initial_iter_step + 5:
@@ -392,9 +399,61 @@ class DistributedTrainer:
                 dist.all_reduce_coalesced(experts, op=dist.ReduceOp.SUM, group=ctx.cp_pg)
             torch._foreach_div_(experts, ctx.dp_cp_pg.size())
 
+    def _clip_gradients_fused(self):
+        """CUDA fast path: one flat sum-of-squares kernel over the fp32 gradient buffer (this rank's shard under
+        ZeRO-1), reduced over model-parallel (and dp when sharded) groups; the clip coefficient stays on the device
+        and is applied inside the AdamW kernel instead of a separate pass over all gradients."""
+        from nanotron_b200.ops import native
+        from nanotron_b200.optim.fused_adamw import FusedAdamW
+
+        ctx = self.parallel_context
+        acc = self.grad_accumulator
+        zero = self.optimizer.inherit_from(ZeroDistributedOptimizer)
+        buf = acc._contiguous_fp32_grad_buffer
+        if zero and ctx.dp_pg.size() > 1:
+            s, e = acc.flat_shard_range
+            view = buf[s:e]
+        else:
+            view = buf
+        total = native.sumsq(view)
+        # tied parameters are counted once: ranks other than the first of a tie group remove their copy
+        world_rank = dist.get_rank(ctx.world_pg)
+        me = dist.get_rank(ctx.dp_pg)
+        for n, p in self.unwrapped_model.get_named_params_with_correct_tied():
+            if not (p.requires_grad and p.is_tied):
+                continue
+            ranks = sorted(p.get_tied_info().global_ranks)
+            if len(ranks) > 1 and world_rank != ranks[0]:
+                g = acc.get_grad_buffer(n).view(-1)
+                if zero and ctx.dp_pg.size() > 1:
+                    rng = self.optimizer.param_name_to_dp_rank_offsets[n].get(me)
+                    if rng is None:
+                        continue
+                    g = g[rng[0] : rng[1]]
+                total = total - g.float().pow(2).sum()
+        dist.all_reduce(total, group=ctx.mp_pg, op=dist.ReduceOp.SUM)
+        if zero and ctx.dp_pg.size() > 1:
+            dist.all_reduce(total, group=ctx.dp_pg, op=dist.ReduceOp.SUM)
+        norm = total.sqrt()
+        coef = torch.clamp(self.config.optimizer.clip_grad / (norm + 1e-6), max=1.0)
+        self.optimizer.get_base_optimizer().grad_scale = coef
+        return norm.squeeze()
+
+    def _can_fuse_clip(self) -> bool:
+        from nanotron_b200 import ops
+        from nanotron_b200.optim.fused_adamw import FusedAdamW
+
+        return (
+            self.grad_accumulator is not None and self.parallel_context.device.type == "cuda" and ops.get_mode() != "torch"
+            and isinstance(self.optimizer.get_base_optimizer(), FusedAdamW) and self.parallel_context.expert_parallel_size == 1
+            and not self.optimizer.get_base_optimizer()._flat_failed
+        )
+
     def _clip_gradients(self):
         ctx = self.parallel_context
         zero = self.optimizer.inherit_from(ZeroDistributedOptimizer)
+        if self._can_fuse_clip():
+            return self._clip_gradients_fused()
         named = [(n, p) for n, p in self.unwrapped_model.get_named_params_with_correct_tied() if p.requires_grad]
         if zero and self.grad_accumulator is not None and ctx.dp_pg.size() > 1:
             # gradients are only valid on this rank's shard: norm over the owned slices, summed over dp as well

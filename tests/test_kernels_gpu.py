@@ -1,0 +1,184 @@
+"""Numerics of every in-tree CUDA kernel against the PyTorch fp32 oracle (small shapes incl. ragged edges)."""
+import math
+
+import pytest
+import torch
+
+from nanotron_b200 import ops
+from nanotron_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, what=""):
+    torch.testing.assert_close(a.float(), b.float(), atol=atol, rtol=rtol, msg=lambda m: f"{what}: {m}")
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 64), (33, 1024), (128, 4096), (5, 8192)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(rows, cols, dtype, with_res):
+    from nanotron_b200.ops import native
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, cols, device=DEV, dtype=dtype)
+    r = torch.randn(rows, cols, device=DEV, dtype=dtype) if with_res else None
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(dtype)
+    y, pre, rstd = native.rmsnorm_fwd(x, r, w, 1e-5)
+    y0, pre0, rstd0 = ref.rms_norm_fwd(x, w, 1e-5, r)
+    tol = dict(atol=2e-2, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+    _close(y, y0, what="y", **tol)
+    _close(pre, pre0, what="pre", **tol)
+    _close(rstd, rstd0, atol=1e-4, rtol=1e-4, what="rstd")
+    dy = torch.randn(rows, cols, device=DEV, dtype=dtype)
+    dres = torch.randn(rows, cols, device=DEV, dtype=dtype) if with_res else None
+    dx, dw = native.rmsnorm_bwd(dy, pre, w, rstd, dres)
+    dx0, dw0 = ref.rms_norm_bwd(dy, pre0, w, rstd0, dres)
+    _close(dx, dx0, what="dx", **tol)
+    _close(dw, dw0, atol=5e-2 if dtype == torch.bfloat16 else 1e-3, rtol=2e-2, what="dw")
+
+
+@pytest.mark.parametrize("rows,cols", [(9, 128), (64, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layernorm(rows, cols, dtype):
+    from nanotron_b200.ops import native
+
+    torch.manual_seed(1)
+    x = torch.randn(rows, cols, device=DEV, dtype=dtype) + 0.5
+    r = torch.randn(rows, cols, device=DEV, dtype=dtype)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(dtype)
+    b = (0.1 * torch.randn(cols, device=DEV)).to(dtype)
+    y, pre, mean, rstd = native.layernorm_fwd(x, r, w, b, 1e-5)
+    y0, pre0, mean0, rstd0 = ref.layer_norm_fwd(x, w, b, 1e-5, r)
+    tol = dict(atol=3e-2, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-5)
+    _close(y, y0, what="y", **tol)
+    dy = torch.randn(rows, cols, device=DEV, dtype=dtype)
+    dx, dw, db = native.layernorm_bwd(dy, pre, w, mean, rstd, None, True)
+    dx0, dw0, db0 = ref.layer_norm_bwd(dy, pre0, w, mean0, rstd0, None, True)
+    _close(dx, dx0, what="dx", **tol)
+    _close(dw, dw0, atol=5e-2 if dtype == torch.bfloat16 else 1e-3, rtol=2e-2, what="dw")
+    _close(db, db0, atol=5e-2 if dtype == torch.bfloat16 else 1e-3, rtol=2e-2, what="db")
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_strided_views(interleaved, dtype):
+    torch.manual_seed(2)
+    T, Hq, Hkv, D = 37, 4, 2, 64
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV, dtype=dtype)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    pos = torch.randint(0, 100, (T,), device=DEV)
+    cos_t, sin_t = ref.rope_cos_sin(torch.arange(128, device=DEV), D, 10000.0)
+    cos, sin = cos_t[pos], sin_t[pos]
+    for x in (q, k):
+        out = ops.apply_rotary(x, cos_t.contiguous(), sin_t.contiguous(), interleaved, False, positions=pos)
+        exp = ref.rope_apply(x, cos, sin, interleaved)
+        _close(out, exp, atol=2e-2 if dtype == torch.bfloat16 else 1e-5, rtol=1e-2, what="rope fwd")
+    # backward is the inverse rotation
+    xg = q.clone().requires_grad_(True)
+    out = ops.apply_rotary(xg, cos_t.contiguous(), sin_t.contiguous(), interleaved, False, positions=pos)
+    g = torch.randn_like(out)
+    out.backward(g)
+    exp = ref.rope_apply(g, cos, sin, interleaved, inverse=True)
+    _close(xg.grad, exp, atol=2e-2 if dtype == torch.bfloat16 else 1e-5, rtol=1e-2, what="rope bwd")
+
+
+@pytest.mark.parametrize("rows,inter", [(5, 64), (130, 1408), (64, 14336)])
+def test_swiglu(rows, inter):
+    torch.manual_seed(3)
+    gu = torch.randn(rows, 2 * inter, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = ops.swiglu(gu)
+    _close(out, ref.swiglu_fwd(gu), atol=2e-2, rtol=2e-2, what="swiglu fwd")
+    d = torch.randn_like(out)
+    out.backward(d)
+    _close(gu.grad, ref.swiglu_bwd(gu, d), atol=3e-2, rtol=3e-2, what="swiglu bwd")
+
+
+@pytest.mark.parametrize("rows,vocab,start", [(4, 256, 0), (19, 32064, 32064), (8, 128256, 0)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_pieces(rows, vocab, start, dtype):
+    from nanotron_b200.ops import native
+
+    torch.manual_seed(4)
+    logits = (3 * torch.randn(rows, vocab, device=DEV)).to(dtype)
+    tgt = torch.randint(0, 2 * vocab, (rows,), device=DEV)
+    m, s, t = native.ce_partials(logits, tgt, start)
+    m0, s0, t0 = ref.ce_partials(logits, tgt, start)
+    _close(m, m0, atol=1e-6, rtol=0, what="max")
+    _close(s, s0, atol=1e-2, rtol=1e-3, what="sumexp")
+    _close(t, t0, atol=1e-6, rtol=0, what="target logit")
+    logz = m0 + torch.log(s0)
+    g = torch.rand(rows, device=DEV)
+    gz = 0.01 * torch.rand(rows, device=DEV)
+    exp = ref.ce_backward(logits, tgt, logz, g, gz, start)
+    got = native.ce_backward(logits.clone(), tgt, logz, g, gz, start, inplace=True)
+    _close(got, exp, atol=1e-2 if dtype == torch.bfloat16 else 1e-5, rtol=2e-2, what="dlogits")
+
+
+def test_sharded_cross_entropy_matches_torch():
+    from nanotron_b200.parallel.tensor_parallel.functional import sharded_cross_entropy
+
+    torch.manual_seed(5)
+    logits = torch.randn(64, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    tgt = torch.randint(0, 1024, (64,), device=DEV)
+    ref_logits = logits.detach().float().requires_grad_(True)
+    loss = sharded_cross_entropy(logits, tgt, group=None).mean()
+    exp = torch.nn.functional.cross_entropy(ref_logits, tgt)
+    _close(loss, exp, atol=1e-3, rtol=1e-3, what="loss")
+    loss.backward()
+    exp.backward()
+    _close(logits.grad, ref_logits.grad, atol=1e-4, rtol=5e-2, what="grad")
+
+
+def test_adamw_flat_matches_torch():
+    from nanotron_b200.optim.fused_adamw import FusedAdamW
+
+    torch.manual_seed(6)
+    sizes = [(128, 64), (384,), (256, 8)]
+    total = sum(math.prod(s) for s in sizes)
+    master = torch.randn(total, device=DEV)
+    grads = torch.randn(total, device=DEV)
+    half = torch.zeros(total, device=DEV, dtype=torch.bfloat16)
+    params, refs, off = [], [], 0
+    opt_groups = []
+    for i, s in enumerate(sizes):
+        n = math.prod(s)
+        p = torch.nn.Parameter(master[off : off + n].view(s))
+        p.grad = grads[off : off + n].view(s)
+        params.append(p)
+        refs.append(torch.nn.Parameter(p.detach().clone()))
+        refs[-1].grad = p.grad.clone()
+        off += n
+    wds = [0.1, 0.0, 0.1]
+    opt = FusedAdamW([{"params": [p], "weight_decay": wd} for p, wd in zip(params, wds)], lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    off = 0
+    for p in params:
+        opt.set_half_target(p, half[off : off + p.numel()])
+        off += p.numel()
+    scale = torch.tensor(0.5, device=DEV)
+    opt.grad_scale = scale
+    tref = torch.optim.AdamW([{"params": [p], "weight_decay": wd} for p, wd in zip(refs, wds)], lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    for _ in range(3):
+        for r in refs:
+            r.grad = r.grad * 0 + grads[: 0].new_tensor(0)  # placeholder overwritten below
+        off = 0
+        for r in refs:
+            r.grad = grads[off : off + r.numel()].view(r.shape) * 0.5
+            off += r.numel()
+        opt.step()
+        tref.step()
+    assert opt._flat is not None, "expected the single-launch flat path"
+    for p, r in zip(params, refs):
+        _close(p, r, atol=1e-5, rtol=1e-5, what="param")
+    _close(half, master, atol=1e-2, rtol=1e-2, what="bf16 copy")
+
+
+def test_sumsq():
+    from nanotron_b200.ops import native
+
+    x = torch.randn(1_000_003, device=DEV)
+    xa = torch.empty(1_000_004, device=DEV)[:1_000_003].copy_(x)
+    got = native.sumsq(xa)
+    _close(got.squeeze(), x.double().pow(2).sum().float(), atol=0, rtol=1e-4, what="sumsq")
