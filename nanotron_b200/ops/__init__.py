@@ -70,10 +70,15 @@ def _use_native(t: torch.Tensor) -> bool:
 
 
 # ============================================================================ GEMM
-def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
+def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor, kind: str) -> bool:
+    """Which GEMMs run on the in-tree tcgen05 kernel.  "auto": the weight-gradient product with fp32 accumulation
+    (a fused op the library does not offer: it would need a bf16 product plus a separate fp32 add) always does;
+    plain forward / dgrad products go to the library.  "tcgen05": everything the kernel supports.  "cublas": nothing."""
     if _GEMM == "cublas" or not a.is_cuda or _MODE == "torch":
         return False
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        return False
+    if _GEMM == "auto" and kind != "wgrad_accum":
         return False
     from nanotron_b200.ops import native
 
@@ -82,7 +87,7 @@ def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor) -> bool:
 
 def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[M,N] = x2[M,K] @ weight[N,K]^T (+ bias)."""
-    if _tcgen05_ok(x2, weight):
+    if _tcgen05_ok(x2, weight, "fwd"):
         from nanotron_b200.ops import native
 
         y = native.gemm_nt(x2, weight)
@@ -92,7 +97,7 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
 
 def linear_dgrad(go2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """dx[M,K] = go2[M,N] @ weight[N,K]."""
-    if _tcgen05_ok(go2, weight):
+    if _tcgen05_ok(go2, weight, "dgrad"):
         from nanotron_b200.ops import native
 
         return native.gemm_nn(go2, weight)
@@ -104,16 +109,15 @@ def linear_wgrad(go2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> O
     accumulated into it and ``None`` is returned (autograd then leaves ``weight.grad`` unset)."""
     main_grad = getattr(weight, "main_grad", None)
     if main_grad is not None:
-        if _tcgen05_ok(go2, x2):
+        if _tcgen05_ok(go2, x2, "wgrad_accum"):
             from nanotron_b200.ops import native
 
             native.gemm_tn_accum_fp32(go2, x2, main_grad)
         else:
             gw = go2.t().matmul(x2)
             main_grad.add_(gw)
-        weight.grad_added_to_main_grad = True
         return None
-    if _tcgen05_ok(go2, x2):
+    if _tcgen05_ok(go2, x2, "wgrad"):
         from nanotron_b200.ops import native
 
         return native.gemm_tn(go2, x2)

@@ -1,0 +1,138 @@
+"""Micro-benchmarks of the in-tree kernels against their roofline (run on a B200).
+
+    python -m nanotron_b200.ops.bench_kernels gemm            # tcgen05 GEMM vs the library GEMM on Llama-3-8B shapes
+    python -m nanotron_b200.ops.bench_kernels elementwise     # HBM-bound kernels vs measured copy bandwidth
+    python -m nanotron_b200.ops.bench_kernels attention
+
+Timing: CUDA events, 3 warm-up + 10 timed launches; operands are rotated through several buffers so that consecutive
+launches do not find their inputs in L2 (total footprint > 126 MB).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "_fallback": True}
+
+
+def time_fn(fn, n_warm=3, n_iter=10) -> float:
+    """Milliseconds per call."""
+    for _ in range(n_warm):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(n_iter):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / n_iter
+
+
+def bench_gemm(small: bool = False):
+    from nanotron_b200.ops import native, native_gemm as g
+
+    native.lib()
+    peak = _peaks()["bf16_tflops"]
+    shapes = [("qkv", 4096, 6144, 4096), ("o", 4096, 4096, 4096), ("gate_up", 4096, 28672, 4096), ("down", 4096, 4096, 14336), ("lm_head", 4096, 128256, 4096)]
+    if small:
+        shapes = [("qkv", 4096, 6144, 4096)]
+    for name, M, N, K in shapes:
+        nbuf = max(2, int(300e6 // ((M * K + N * K) * 2)) + 1)
+        xs = [torch.randn(M, K, device="cuda", dtype=torch.bfloat16) for _ in range(nbuf)]
+        ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(nbuf)]
+        dys = [torch.randn(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        acc = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+        i = [0]
+
+        def nxt():
+            i[0] = (i[0] + 1) % nbuf
+            return i[0]
+
+        flops = 2.0 * M * N * K
+        rows = {}
+        rows["fwd  tcgen05"] = time_fn(lambda: g.gemm_nt(xs[nxt()], ws[i[0]]))
+        rows["fwd  library"] = time_fn(lambda: torch.nn.functional.linear(xs[nxt()], ws[i[0]]))
+        rows["dgrad tcgen05"] = time_fn(lambda: g.gemm_nn(dys[nxt() % 2], ws[i[0]]))
+        rows["dgrad library"] = time_fn(lambda: dys[nxt() % 2].matmul(ws[i[0]]))
+        rows["wgrad tcgen05 (+= fp32)"] = time_fn(lambda: g.gemm_tn_accum_fp32(dys[nxt() % 2], xs[i[0]], acc))
+        rows["wgrad library (bf16 out, then fp32 add)"] = time_fn(lambda: acc.add_(dys[nxt() % 2].t().matmul(xs[i[0]])))
+        for k, ms in rows.items():
+            tf = flops / ms / 1e9
+            print(f"{name:8s} M={M} N={N} K={K}  {k:42s} {ms:8.3f} ms  {tf:7.1f} TFLOP/s  {tf / peak:5.2f} of measured peak", flush=True)
+        g.check_status("cuda")
+        del xs, ws, dys, acc
+        torch.cuda.empty_cache()
+
+
+def bench_elementwise():
+    from nanotron_b200 import ops
+    from nanotron_b200.ops import native
+
+    native.lib()
+    bw = _peaks()["hbm_gbs"]
+    T, H, I, V = 8192, 4096, 14336, 128256
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn_like(x)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    y, pre, rstd = native.rmsnorm_fwd(x, r, w, 1e-5)
+    cases = [
+        ("rmsnorm fwd (+residual)", lambda: native.rmsnorm_fwd(x, r, w, 1e-5), 4 * T * H * 2),
+        ("rmsnorm bwd (+residual)", lambda: native.rmsnorm_bwd(y, pre, w, rstd, r), 4 * T * H * 2),
+    ]
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
+    cases += [
+        ("swiglu fwd", lambda: native.swiglu_fwd(gu), 3 * T * I * 2),
+        ("swiglu bwd", lambda: native.swiglu_bwd(gu, do), 5 * T * I * 2),
+    ]
+    qkv = torch.randn(T, 6144, device="cuda", dtype=torch.bfloat16)
+    q = qkv[:, :4096].view(T, 32, 128)
+    from nanotron_b200.ops import reference as ref
+
+    cos, sin = ref.rope_cos_sin(torch.arange(T, device="cuda"), 128, 500000.0)
+    pos = torch.arange(T, device="cuda")
+    cases.append(("rope (q, 32 heads, in place)", lambda: native.rope(q, cos, sin, False, False, True, positions=pos), 2 * T * 4096 * 2))
+    logits = torch.randn(4096, V, device="cuda", dtype=torch.bfloat16)
+    tgt = torch.randint(0, V, (4096,), device="cuda")
+    m, s, t = native.ce_partials(logits, tgt, 0)
+    logz = m + torch.log(s)
+    gl = torch.ones(4096, device="cuda")
+    cases += [
+        ("cross-entropy partials", lambda: native.ce_partials(logits, tgt, 0), 4096 * V * 2),
+        ("cross-entropy backward (in place)", lambda: native.ce_backward(logits, tgt, logz, gl, None, 0, inplace=True), 2 * 4096 * V * 2),
+    ]
+    n = 256 * 1024 * 1024
+    p, g_, m_, v_ = (torch.zeros(n, device="cuda") for _ in range(4))
+    p16 = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    seg_end = torch.tensor([n], dtype=torch.int64, device="cuda")
+    seg_lr = torch.tensor([1e-3], device="cuda")
+    seg_wd = torch.tensor([0.01], device="cuda")
+    cases.append(("adamw flat (fp32 master + bf16 write-back)", lambda: native.adamw_flat(p, g_, m_, v_, p16, seg_end, seg_lr, seg_wd, 0.9, 0.95, 1e-8, 1.0), n * (4 * 4 + 3 * 4 + 2)))
+    cases.append(("sum of squares (grad norm)", lambda: native.sumsq(g_), n * 4))
+    for name, fn, nbytes in cases:
+        ms = time_fn(fn)
+        gbs = nbytes / ms / 1e6
+        print(f"{name:46s} {ms:8.3f} ms  {gbs:8.1f} GB/s  {gbs / bw:5.2f} of measured copy bandwidth", flush=True)
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    if what == "gemm":
+        bench_gemm(small="--small" in sys.argv)
+    elif what == "elementwise":
+        bench_elementwise()
+    elif what == "attention":
+        from nanotron_b200.ops.bench_attention import main
+
+        main()

@@ -1,0 +1,331 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), persistent and warp-specialised (sm_100a).
+//
+//   D[M,N] (=|+=) sum_k A(m,k) * B(n,k)
+//
+// Operand storage is selected per operand, so the three products of a linear layer need no transposed copies:
+//   K-major  : element (m,k) at  ptr[m*ld + k]   (reduction index contiguous)   -- forward:  x[M,K], W[N,K]
+//   MN-major : element (m,k) at  ptr[k*ld + m]   (output index contiguous)      -- dgrad: B = W[N_red, K_out];  wgrad: both
+// Output modes: bf16 store, fp32 store, fp32 accumulate (TMA reduce-add into the fp32 main-gradient buffer).
+//
+// One CTA per SM walks output tiles of 128 x 256.  Warp roles:
+//   warp 0     : TMA producer  (one elected lane; 4-stage ring of {A 128x64, B 256x64} bf16 tiles, 128-byte swizzle)
+//   warp 1     : MMA issuer    (one elected lane; tcgen05.mma 128x256x16, fp32 accumulators in TMEM, double buffered:
+//                               2 x 256 columns, so the epilogue of tile i overlaps the main loop of tile i+1)
+//   warps 2..5 : epilogue      (tcgen05.ld 32 lanes x 32 columns at a time -> convert -> swizzled smem staging ->
+//                               TMA store / reduce-add, double buffered per warp)
+// Synchronisation is mbarrier-only (full/empty per stage, tmem_full/tmem_empty per accumulator).  All waits are bounded;
+// on expiry the kernel raises a flag in `status`, drains what it issued, frees TMEM and returns.
+// TMA clips stores and zero-fills loads at the M/N/K edges, so any M, N and K are accepted as long as the row pitches are
+// multiples of 16 bytes (and 128 bytes for MN-major operands).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 256;
+constexpr int BLOCK_K = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
+constexpr int B_TILE_BYTES = BLOCK_N * BLOCK_K * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 128 bytes per warp per buffer
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACCUM = 2 };
+
+struct TileCoord {
+  int m_blk, n_blk;
+};
+
+// Tiles are visited in column-major order inside bands of 8 tile-rows so that CTAs running at the same time share B
+// tiles (and a few A tiles) through L2.
+__device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n) {
+  constexpr int BAND = 8;
+  const int band_size = BAND * tiles_n;
+  const int band = t / band_size;
+  const int first_m = band * BAND;
+  const int rows = min(BAND, tiles_m - first_m);
+  const int r = t - band * band_size;
+  return {first_m + r % rows, r / rows};
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
+                    int M, int N, int K, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + EPI_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;      // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+  const int tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      ptx::mbar_init(&tmem_full[b], 1);
+      ptx::mbar_init(&tmem_empty[b], EPI_WARPS);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+    ptx::prefetch_tmap(&tmap_d);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_base_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          ptx::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          if (A_MN) ptx::tma_load_3d(sa, &tmap_a, &full_bar[s], 0, kb * BLOCK_K, tc.m_blk * (BLOCK_M / 64));
+          else      ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BLOCK_K, tc.m_blk * BLOCK_M);
+          if (B_MN) ptx::tma_load_3d(sb, &tmap_b, &full_bar[s], 0, kb * BLOCK_K, tc.n_blk * (BLOCK_N / 64));
+          else      ptx::tma_load_2d(sb, &tmap_b, &full_bar[s], kb * BLOCK_K, tc.n_blk * BLOCK_N);
+        }
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA's shared memory goes away (bounded by the same limit)
+        const uint64_t t0 = ptx::globaltimer();
+        for (int s = 0; s < STAGES; s++) {
+          const int last = it - 1 - ((it - 1 - s) % STAGES + STAGES) % STAGES;  // last iteration that used stage s
+          if (it == 0 || last < 0) continue;
+          const uint32_t ph = (last / STAGES) & 1;
+          while (!ptx::mbar_try_wait(&full_bar[s], ph) && ptx::globaltimer() - t0 < NTB_WAIT_LIMIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
+      int it = 0, tile_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_it++) {
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!ptx::mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; k++) {
+            const uint64_t adesc = A_MN ? ptx::make_smem_desc(sa + k * UMMA_K * 128, BLOCK_K * 128, 1024) : ptx::make_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+            const uint64_t bdesc = B_MN ? ptx::make_smem_desc(sb + k * UMMA_K * 128, BLOCK_K * 128, 1024) : ptx::make_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+            ptx::umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) ptx::umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* my_epi = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
+    constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;  // 128 bytes of output per row
+    constexpr int CHUNKS = BLOCK_N / CHUNK_COLS;
+    int tile_it = 0, buf = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_it++) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1;
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+      const int row0 = tc.m_blk * BLOCK_M + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; c++) {
+        uint8_t* stage_buf = my_epi + buf * EPI_BUF_BYTES;
+        // the TMA store that last read this staging buffer must be done reading it
+        if (lane == 0) ptx::tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* my_row = stage_buf + lane * 128;
+        if (OUT == OUT_BF16) {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32(taddr + c * 64, r0);
+          ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++) {  // 8 x 16 bytes = 64 bf16
+            const uint32_t* src = (j < 4) ? &r0[j * 8] : &r1[(j - 4) * 8];
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = pk;  // 128-byte swizzle
+          }
+        } else {
+          uint32_t r0[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r0);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++) {  // 8 x 16 bytes = 32 fp32
+            uint4 pk = make_uint4(r0[j * 4], r0[j * 4 + 1], r0[j * 4 + 2], r0[j * 4 + 3]);
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = pk;
+          }
+        }
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          const int x = tc.n_blk * BLOCK_N + c * CHUNK_COLS;
+          if (x < N && row0 < M) {
+            if (OUT == OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
+            else ptx::tma_store_2d(&tmap_d, stage_buf, x, row0);
+          }
+          ptx::tma_commit_group();
+        }
+        buf ^= 1;
+      }
+      // accumulator fully read: hand it back to the MMA warp
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+    }
+    if (lane == 0) ptx::tma_wait_group<0>();  // all stores complete before the CTA exits
+    __syncwarp();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, NTB_ERR_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// K-major operand [rows, k] with pitch ld (elements): 2-D map {k, rows}, box {64, box_rows}.
+bool make_map_kmajor(CUtensorMap* m, const void* ptr, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t es[2] = {1, 1};
+  return get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// MN-major operand stored [k, mn] with pitch ld: 3-D map {64, k, mn/64} so one copy lands as [mn/64][k][64] in shared memory.
+bool make_map_mnmajor(CUtensorMap* m, const void* ptr, int64_t mn, int64_t k, int64_t ld, int box_mn) {
+  cuuint64_t dims[3] = {64, (cuuint64_t)k, (cuuint64_t)((mn + 63) / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)BLOCK_K, (cuuint32_t)(box_mn / 64)};
+  cuuint32_t es[3] = {1, 1, 1};
+  return get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld, bool f32) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : 64), 32};
+  cuuint32_t es[2] = {1, 1};
+  return get_encode()(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, es,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream) {
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
+  }
+  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status);
+  return ntb_check_launch();
+}
+
+}  // namespace
+
+// a_mn / b_mn: 0 = K-major ([rows, K] row-major), 1 = MN-major ([K, rows] row-major).  lda / ldb / ldd are row pitches in
+// elements.  out_mode: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate.  `status` (device int, may be null) receives
+// NTB_ERR_TIMEOUT if a bounded wait expired.
+NTB_EXPORT int ntb_gemm_bf16(const void* a, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn, int b_mn,
+                             int out_mode, int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !get_encode()) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
+  if (a_mn ? (lda % 64 || M % 64) : (lda % 8)) return NTB_ERR_ARG;
+  if (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) return NTB_ERR_ARG;
+  if (out_mode == OUT_BF16 ? (ldd % 8) : (ldd % 4)) return NTB_ERR_ARG;
+  if (num_sms <= 0) num_sms = 148;
+  CUtensorMap ta, tb, td;
+  bool ok = a_mn ? make_map_mnmajor(&ta, a, M, K, lda, BLOCK_M) : make_map_kmajor(&ta, a, M, K, lda, BLOCK_M);
+  ok = ok && (b_mn ? make_map_mnmajor(&tb, b, N, K, ldb, BLOCK_N) : make_map_kmajor(&tb, b, N, K, ldb, BLOCK_N));
+  ok = ok && make_map_out(&td, d, M, N, ldd, out_mode != OUT_BF16);
+  if (!ok) return NTB_ERR_ARG;
+#define NTB_GEMM_CASE(AM, BM, OM) \
+  if (a_mn == AM && b_mn == BM && out_mode == OM) return launch<AM != 0, BM != 0, OM>(ta, tb, td, M, N, K, status, num_sms, stream);
+  NTB_GEMM_CASE(0, 0, 0) NTB_GEMM_CASE(0, 0, 1) NTB_GEMM_CASE(0, 0, 2)
+  NTB_GEMM_CASE(0, 1, 0) NTB_GEMM_CASE(0, 1, 1) NTB_GEMM_CASE(0, 1, 2)
+  NTB_GEMM_CASE(1, 1, 0) NTB_GEMM_CASE(1, 1, 1) NTB_GEMM_CASE(1, 1, 2)
+  NTB_GEMM_CASE(1, 0, 0) NTB_GEMM_CASE(1, 0, 1) NTB_GEMM_CASE(1, 0, 2)
+#undef NTB_GEMM_CASE
+  return NTB_ERR_ARG;
+}

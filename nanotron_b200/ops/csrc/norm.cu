@@ -82,88 +82,130 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_fwd_kernel(const T* __restr
   }
 }
 
-template <typename T, bool RMS>
+// Backward.  Thread t owns columns {(it*NORM_THREADS + t)*8 .. +7 : it < ITERS}: the row slice, its dW (and dB) partial
+// sums all live in registers, so a row costs one pass over dy / x (/ dres) and one block reduction.
+template <typename T, bool RMS, int ITERS>
 __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ pre, const T* __restrict__ w,
                                                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                                                const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ dw_partial,
                                                                float* __restrict__ db_partial, int rows, int cols) {
-  extern __shared__ float smem[];  // [cols] dw acc, [cols] db acc (LN only), [cols] wdy stage, [cols] xhat stage
-  __shared__ float scratch[32];
-  float* dw_acc = smem;
-  float* db_acc = RMS ? nullptr : smem + cols;
-  float* s_wdy = smem + (RMS ? 1 : 2) * cols;
-  float* s_xhat = s_wdy + cols;
-  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
-    dw_acc[c] = 0.f;
-    if (!RMS) db_acc[c] = 0.f;
+  __shared__ float scratch[2][32];
+  float fw[ITERS][8], dw_acc[ITERS][8], db_acc[RMS ? 1 : ITERS][8];
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+    if (c < cols) {
+      Vec8<T> wv;
+      wv.load(w + c);
+      wv.to_float(fw[it]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      dw_acc[it][i] = 0.f;
+      if (!RMS) db_acc[it][i] = 0.f;
+    }
   }
-  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rstd = rstd_in[row];
     const float mean = RMS ? 0.f : mean_in[row];
     const T* dyr = dy + (size_t)row * cols;
     const T* xr = pre + (size_t)row * cols;
+    float wdy[ITERS][8], xhat[ITERS][8];
     float s1 = 0.f, s2 = 0.f;
-    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
-      Vec8<T> a, bv, wv;
-      float fdy[8], fx[8], fw[8];
-      a.load(dyr + c); a.to_float(fdy);
-      bv.load(xr + c); bv.to_float(fx);
-      wv.load(w + c); wv.to_float(fw);
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const float xhat = (fx[i] - mean) * rstd;
-        const float wdy = fdy[i] * fw[i];
-        s_wdy[c + i] = wdy;
-        s_xhat[c + i] = xhat;
-        s1 += wdy * xhat;
-        s2 += wdy;
-        dw_acc[c + i] += fdy[i] * xhat;  // this thread is the only writer of these columns
-        if (!RMS) db_acc[c + i] += fdy[i];
+    for (int it = 0; it < ITERS; it++) {
+      const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+      if (c < cols) {
+        Vec8<T> a, bv;
+        float fdy[8], fx[8];
+        a.load(dyr + c);
+        bv.load(xr + c);
+        a.to_float(fdy);
+        bv.to_float(fx);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          xhat[it][i] = (fx[i] - mean) * rstd;
+          wdy[it][i] = fdy[i] * fw[it][i];
+          s1 += wdy[it][i] * xhat[it][i];
+          s2 += wdy[it][i];
+          dw_acc[it][i] += fdy[i] * xhat[it][i];
+          if (!RMS) db_acc[it][i] += fdy[i];
+        }
       }
     }
-    const float c1 = block_sum(s1, scratch) / cols;
-    const float c2 = RMS ? 0.f : block_sum(s2, scratch) / cols;
+    // one block reduction for both sums (parity-indexed scratch: no barrier needed before the next row's write)
+    s1 = warp_sum(s1);
+    if (!RMS) s2 = warp_sum(s2);
+    float* sc = scratch[0];
+    __syncthreads();
+    if (lane == 0) { sc[warp] = s1; scratch[1][warp] = s2; }
+    __syncthreads();
+    float r1 = (lane < NORM_THREADS / 32) ? sc[lane] : 0.f;
+    float r2 = (!RMS && lane < NORM_THREADS / 32) ? scratch[1][lane] : 0.f;
+    const float c1 = warp_sum(r1) / cols;
+    const float c2 = RMS ? 0.f : warp_sum(r2) / cols;
     T* dxr = dx + (size_t)row * cols;
     const T* drr = dres ? dres + (size_t)row * cols : nullptr;
-    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8) {
-      float f[8];
 #pragma unroll
-      for (int i = 0; i < 8; i++) f[i] = (s_wdy[c + i] - s_xhat[c + i] * c1 - c2) * rstd;
-      if (drr) {
-        Vec8<T> r;
-        float g[8];
-        r.load(drr + c);
-        r.to_float(g);
+    for (int it = 0; it < ITERS; it++) {
+      const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+      if (c < cols) {
+        float f[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) f[i] += g[i];
+        for (int i = 0; i < 8; i++) f[i] = (wdy[it][i] - xhat[it][i] * c1 - c2) * rstd;
+        if (drr) {
+          Vec8<T> r;
+          float g[8];
+          r.load(drr + c);
+          r.to_float(g);
+#pragma unroll
+          for (int i = 0; i < 8; i++) f[i] += g[i];
+        }
+        Vec8<T> o;
+        o.from_float(f);
+        o.store(dxr + c);
       }
-      Vec8<T> o;
-      o.from_float(f);
-      o.store(dxr + c);
     }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
-    dw_partial[(size_t)blockIdx.x * cols + c] = dw_acc[c];
-    if (!RMS) db_partial[(size_t)blockIdx.x * cols + c] = db_acc[c];
+#pragma unroll
+  for (int it = 0; it < ITERS; it++) {
+    const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+    if (c < cols) {
+      float* dst = dw_partial + (size_t)blockIdx.x * cols + c;
+      *reinterpret_cast<float4*>(dst) = make_float4(dw_acc[it][0], dw_acc[it][1], dw_acc[it][2], dw_acc[it][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dw_acc[it][4], dw_acc[it][5], dw_acc[it][6], dw_acc[it][7]);
+      if (!RMS) {
+        float* d2 = db_partial + (size_t)blockIdx.x * cols + c;
+        *reinterpret_cast<float4*>(d2) = make_float4(db_acc[it][0], db_acc[it][1], db_acc[it][2], db_acc[it][3]);
+        *reinterpret_cast<float4*>(d2 + 4) = make_float4(db_acc[it][4], db_acc[it][5], db_acc[it][6], db_acc[it][7]);
+      }
+    }
   }
 }
 
-// out[c] = sum_p partial[p, c]
+// out[c] = sum_p partial[p, c].  Block = 32 columns x 8 part-lanes; coalesced 128-byte rows.
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * cols + c];
-  out[c] = s;
+  if (c < cols)
+    for (int p = threadIdx.y; p < nparts; p += 8) s += partial[(size_t)p * cols + c];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) t += sm[k][threadIdx.x];
+    out[c] = t;
+  }
 }
 
 }  // namespace
 
 // Number of CTAs the backward kernels use (== rows of the partial scratch the caller must provide).
 NTB_EXPORT int ntb_norm_bwd_num_partials(int rows) {
-  int n = 148 * 2;
+  int n = 148 * 4;
   return rows < n ? rows : n;
 }
 
@@ -188,21 +230,29 @@ NTB_EXPORT int ntb_norm_fwd(int is_rms, int dtype, const void* x, const void* re
 NTB_EXPORT int ntb_norm_bwd(int is_rms, int dtype, const void* dy, const void* pre, const void* w, const float* mean, const float* rstd,
                             const void* dres, void* dx, float* dw_partial, float* db_partial, float* dw_out, float* db_out, int rows, int cols,
                             cudaStream_t stream) {
-  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || cols > 12288) return NTB_ERR_ARG;
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0 || cols > NORM_THREADS * 8 * 8) return NTB_ERR_ARG;
   const int nparts = ntb_norm_bwd_num_partials(rows);
-  const size_t smem = (size_t)cols * sizeof(float) * (is_rms ? 3 : 4);
+  const int iters = (cols + NORM_THREADS * 8 - 1) / (NORM_THREADS * 8);
+#define NTB_NORM_BWD(IT)                                                                                                                             \
+  {                                                                                                                                                  \
+    if (is_rms)                                                                                                                                      \
+      norm_bwd_kernel<T, true, IT><<<nparts, NORM_THREADS, 0, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres, (T*)dx, \
+                                                                         dw_partial, db_partial, rows, cols);                                       \
+    else                                                                                                                                             \
+      norm_bwd_kernel<T, false, IT><<<nparts, NORM_THREADS, 0, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres,       \
+                                                                          (T*)dx, dw_partial, db_partial, rows, cols);                               \
+  }
   NTB_DISPATCH_DTYPE(dtype, {
-    if (is_rms) {
-      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_bwd_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      norm_bwd_kernel<T, true><<<nparts, NORM_THREADS, smem, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres, (T*)dx, dw_partial, db_partial, rows, cols);
-    } else {
-      if (smem > 32 * 1024) cudaFuncSetAttribute(norm_bwd_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      norm_bwd_kernel<T, false><<<nparts, NORM_THREADS, smem, stream>>>((const T*)dy, (const T*)pre, (const T*)w, mean, rstd, (const T*)dres, (T*)dx, dw_partial, db_partial, rows, cols);
-    }
+    if (iters <= 1) NTB_NORM_BWD(1)
+    else if (iters <= 2) NTB_NORM_BWD(2)
+    else if (iters <= 4) NTB_NORM_BWD(4)
+    else NTB_NORM_BWD(8)
   });
+#undef NTB_NORM_BWD
   int rc = ntb_check_launch();
   if (rc) return rc;
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw_out, nparts, cols);
-  if (!is_rms && db_out) reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(db_partial, db_out, nparts, cols);
+  dim3 rb(32, 8);
+  reduce_partials_kernel<<<(cols + 31) / 32, rb, 0, stream>>>(dw_partial, dw_out, nparts, cols);
+  if (!is_rms && db_out) reduce_partials_kernel<<<(cols + 31) / 32, rb, 0, stream>>>(db_partial, db_out, nparts, cols);
   return ntb_check_launch();
 }

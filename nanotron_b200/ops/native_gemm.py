@@ -1,30 +1,111 @@
-"""Bindings of the tcgen05 GEMM kernels (``csrc/gemm_tcgen05.cu``)."""
+"""Bindings of the tcgen05 GEMM kernel (``csrc/gemm_tcgen05.cu``).
+
+Three products of a linear layer, none of which needs a transposed copy:
+  gemm_nt : y[M,N]  = x[M,K] @ w[N,K]^T        (forward)
+  gemm_nn : dx[M,K] = dy[M,N] @ w[N,K]          (dgrad; w is read as an MN-major operand)
+  gemm_tn : dw[N,K] = dy[M,N]^T @ x[M,K]        (wgrad; both operands MN-major), optionally accumulated in fp32
+"""
 from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_int64, c_void_p
+from typing import Optional
 
 import torch
 
 _HAS = {"gemm": False}
+_STATUS = {}
+_SMS = {}
 
 
 def declare(L):
     _HAS["gemm"] = hasattr(L, "ntb_gemm_bf16")
+    if _HAS["gemm"]:
+        L.ntb_gemm_bf16.restype = c_int
+        L.ntb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+
+
+def status_word(device) -> torch.Tensor:
+    """Device int that a kernel sets when one of its bounded waits expired (0 = fine)."""
+    key = str(device)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device) -> None:
+    """Host-side check (synchronises): raises if any tcgen05 kernel reported a timed-out wait since the last check."""
+    from nanotron_b200.ops.native import NativeKernelError
+
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise NativeKernelError(f"a tensor-core kernel gave up waiting on a barrier (status {v})")
+
+
+def _sms(device) -> int:
+    key = str(device)
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SMS[key]
+
+
+def _ok2d(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.data_ptr() % 16 == 0 and t.dtype == torch.bfloat16
 
 
 def gemm_supported(a: torch.Tensor, b: torch.Tensor, force: bool = False) -> bool:
-    return False
+    """The kernel covers bf16 row-major operands with 16-byte aligned rows; tiny problems stay on the library."""
+    if not _HAS["gemm"] and not force:
+        from nanotron_b200.ops import native
+
+        native.lib()
+    if not _HAS["gemm"]:
+        return False
+    if not (_ok2d(a) and _ok2d(b)):
+        return False
+    if a.stride(0) % 64 or b.stride(0) % 64 or a.shape[1] % 64 or b.shape[1] % 64 or a.shape[0] % 64 or b.shape[0] % 64:
+        return False  # keeps every (nt, nn, tn) use of the same tensors legal
+    if not force and a.shape[0] * a.shape[1] < 512 * 512:
+        return False
+    return True
 
 
-def gemm_nt(a, b):
-    raise NotImplementedError
+def _launch(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode):
+    from nanotron_b200.ops import native
+
+    dev = a.device
+    with torch.cuda.device(dev):
+        rc = native.lib().ntb_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(dev).data_ptr(), _sms(dev), torch.cuda.current_stream(dev).cuda_stream)
+    native._check(rc, "gemm_tcgen05")
+    return d
 
 
-def gemm_nn(a, b):
-    raise NotImplementedError
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    M, K = x.shape
+    N = w.shape[0]
+    d = out if out is not None else torch.empty((M, N), dtype=out_dtype, device=x.device)
+    return _launch(x, w, d, M, N, K, x.stride(0), w.stride(0), d.stride(0), 0, 0, 0 if d.dtype == torch.bfloat16 else 1)
 
 
-def gemm_tn(a, b):
-    raise NotImplementedError
+def gemm_nn(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    M, N = dy.shape
+    K = w.shape[1]
+    d = out if out is not None else torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
+    return _launch(dy, w, d, M, K, N, dy.stride(0), w.stride(0), d.stride(0), 0, 1, 0 if d.dtype == torch.bfloat16 else 1)
 
 
-def gemm_tn_accum_fp32(a, b, out):
-    raise NotImplementedError
+def gemm_tn(dy: torch.Tensor, x: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    M, N = dy.shape
+    K = x.shape[1]
+    d = torch.empty((N, K), dtype=out_dtype, device=dy.device)
+    return _launch(dy, x, d, N, K, M, dy.stride(0), x.stride(0), d.stride(0), 1, 1, 0 if out_dtype == torch.bfloat16 else 1)
+
+
+def gemm_tn_accum_fp32(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[N,K] (fp32) += dy[M,N]^T @ x[M,K]."""
+    M, N = dy.shape
+    K = x.shape[1]
+    assert out.dtype == torch.float32 and out.shape == (N, K) and out.stride(1) == 1
+    return _launch(dy, x, out, N, K, M, dy.stride(0), x.stride(0), out.stride(0), 1, 1, 2)

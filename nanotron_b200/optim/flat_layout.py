@@ -80,11 +80,18 @@ def flatten_parameters(named_params: List[Tuple[str, torch.nn.Parameter]], layou
     buffers = {}
     for dtype, items in by_dtype.items():
         device = items[0][1].device
+        existing = getattr(items[0][1], "_ntb_flat_buffer", None)
+        if existing is not None and existing.numel() == layout.total and all(
+            getattr(p, "_ntb_flat_buffer", None) is existing and p.data_ptr() == existing.data_ptr() + layout.offsets[name] * existing.element_size() for name, p in items
+        ):
+            buffers[dtype] = existing  # already flattened with this layout
+            continue
         buf = torch.zeros(layout.total, dtype=dtype, device=device)
         with torch.no_grad():
             for name, p in items:
                 v = layout.view(buf, name, p.shape)
                 v.copy_(p.data)
                 p.data = v
+                p._ntb_flat_buffer = buf
         buffers[dtype] = buf
     return buffers

@@ -22,7 +22,7 @@ from typing import Callable, Dict, Iterator, Optional, Tuple
 import torch
 
 import nanotron_b200.distributed as dist
-from nanotron_b200.optim.flat_layout import ALIGN, FlatLayout, _round_up
+from nanotron_b200.optim.flat_layout import ALIGN, FlatLayout, _round_up, flatten_parameters
 from nanotron_b200.parallel.parameters import NanotronParameter
 
 
@@ -90,6 +90,11 @@ class FP32GradientAccumulator(GradientAccumulator):
         self.fp32_grad_buffers, self._contiguous_fp32_grad_buffer = self.build_grad_buffers(grad_buckets_named_params, self.layout)
         self.flat_shard_range = None
         self._grad_offsets = {n: d["offset"] for n, d in self.fp32_grad_buffers.items()}
+        # half-precision parameters live in one flat buffer with the same layout, so the optimizer can write them back
+        # (and ZeRO can all-gather them) as one contiguous range
+        self._contiguous_half_buffers = {}
+        if grad_buckets_named_params and len({p.dtype for _, p in grad_buckets_named_params}) == 1:
+            self._contiguous_half_buffers = flatten_parameters(grad_buckets_named_params, self.layout)
         # ---- masters (whole parameters until assign_param_offsets narrows them)
         self.parameters: Dict[str, Dict[str, torch.Tensor]] = {}
         self._build_masters({n: (0, p.numel()) for n, p in named_parameters})

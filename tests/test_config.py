@@ -1,0 +1,63 @@
+import pytest
+import torch
+
+import nanotron_b200.config as c
+from helpers import make_config, tiny_llama_config, tiny_qwen_config
+
+
+def test_yaml_round_trip(tmp_path):
+    cfg = make_config(tiny_llama_config(), tp=1, pp=1, dp=1, pp_engine="1f1b", tp_mode="reduce_scatter")
+    path = tmp_path / "cfg.yaml"
+    cfg.save_as_yaml(path)
+    back = c.get_config_from_file(str(path))
+    assert isinstance(back.model.model_config, c.LlamaConfig)
+    assert back.parallelism.tp_mode.name == "REDUCE_SCATTER"
+    assert type(back.parallelism.pp_engine).__name__ == "OneForwardOneBackwardPipelineEngine"
+    assert back.model.dtype == torch.float32
+    assert c.serialize(back) == c.serialize(cfg)
+
+
+def test_qwen_moe_config_round_trip(tmp_path):
+    mc = tiny_qwen_config(moe_config=c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=32, enable_shared_expert=True, shared_expert_intermediate_size=64))
+    cfg = make_config(mc)
+    path = tmp_path / "cfg.yaml"
+    cfg.save_as_yaml(path)
+    back = c.get_config_from_file(str(path))
+    assert isinstance(back.model.model_config, c.Qwen2Config)
+    assert back.model.model_config.moe_config.layers == [0, 1]
+    assert back.model.model_config.is_moe_model
+
+
+def test_strict_loader_rejects_unknown_keys(tmp_path):
+    cfg = make_config(tiny_llama_config())
+    d = c.serialize(cfg)
+    d["tokens"]["not_a_field"] = 1
+    with pytest.raises(ValueError):
+        c.get_config_from_dict(d)
+
+
+def test_cross_field_validation():
+    with pytest.raises(AssertionError):
+        make_config(tiny_llama_config(num_attention_heads=4, num_key_value_heads=4), tp=3, dp=1)
+    cfg = make_config(tiny_llama_config(), mbs=2, accum=3, dp=1)
+    assert cfg.global_batch_size == 6
+    cfg.data_stages.append(c.DatasetStageArgs(name="stable", start_training_step=5, data=c.DataArgs(dataset=None, seed=1)))
+    with pytest.raises(ValueError):
+        cfg.__post_init__()
+
+
+def test_lr_scheduler_shapes():
+    from nanotron_b200.helpers import lr_scheduler_builder
+
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = torch.optim.SGD([p], lr=1.0)
+    args = c.LRSchedulerArgs(learning_rate=1.0, lr_warmup_steps=2, lr_warmup_style="linear", lr_decay_style="cosine", lr_decay_steps=4, min_decay_lr=0.1)
+    sched = lr_scheduler_builder(opt, args, total_training_steps=10)
+    lrs = []
+    for _ in range(9):
+        lrs.append(opt.param_groups[0]["lr"])
+        opt.step()
+        sched.step()
+    assert lrs[0] == 0.0 and abs(lrs[1] - 0.5) < 1e-9 and abs(lrs[2] - 1.0) < 1e-9
+    assert abs(lrs[4] - 0.55) < 1e-9  # halfway through the cosine
+    assert abs(lrs[6] - 0.1) < 1e-9 and abs(lrs[8] - 0.1) < 1e-9

@@ -1,0 +1,231 @@
+"""Multi-rank behaviour on CPU/gloo: process-group topology, TP layers vs an unsharded oracle, ZeRO-1 vs plain
+data parallelism, pipeline engines vs a single stage, checkpoint round trip across topologies."""
+import os
+
+import pytest
+import torch
+
+from helpers import dummy_dataloader, make_config, run_distributed, tiny_llama_config, tiny_qwen_config
+
+
+# --------------------------------------------------------------------------- topology
+def _check_context(tp, pp, dp, cp, ep):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.parallel import ParallelContext
+
+    ctx = ParallelContext(tensor_parallel_size=tp, pipeline_parallel_size=pp, data_parallel_size=dp, context_parallel_size=cp, expert_parallel_size=ep)
+    rank = dist.get_rank(ctx.world_pg)
+    assert ctx.tp_pg.size() == tp and ctx.pp_pg.size() == pp and ctx.dp_pg.size() == dp and ctx.cp_pg.size() == cp and ctx.ep_pg.size() == ep
+    local = ctx.get_local_ranks(rank)
+    assert ctx.get_global_rank(ep_rank=local["ep"], pp_rank=local["pp"], dp_rank=local["dp"], cp_rank=local["cp"], tp_rank=local["tp"]) == rank
+    # tp ranks are adjacent
+    assert dist.get_global_ranks(ctx.tp_pg) == tuple(range(rank - local["tp"], rank - local["tp"] + tp))
+    assert ctx.expert_dp_pg.size() == dp // ep
+    assert local["ep"] == dist.get_rank(ctx.ep_pg)
+    ctx.destroy()
+
+
+@pytest.mark.parametrize("tp,pp,dp,cp,ep", [(2, 1, 2, 1, 1), (1, 2, 2, 1, 2), (2, 2, 1, 1, 1), (1, 1, 2, 2, 1), (1, 1, 4, 1, 2)])
+def test_parallel_context(tp, pp, dp, cp, ep):
+    run_distributed(_check_context, tp * pp * dp * cp, tp=tp, pp=pp, dp=dp, cp=cp, ep=ep)
+
+
+# --------------------------------------------------------------------------- TP layers
+def _check_tp_linear(mode, async_comm):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.parallel import ParallelContext
+    from nanotron_b200.parallel.tensor_parallel.enum import TensorParallelLinearMode
+    from nanotron_b200.parallel.tensor_parallel.nn import TensorParallelColumnLinear, TensorParallelEmbedding, TensorParallelRowLinear
+
+    ctx = ParallelContext(tensor_parallel_size=2, pipeline_parallel_size=1, data_parallel_size=1)
+    tp_mode = TensorParallelLinearMode[mode]
+    rank = dist.get_rank(ctx.tp_pg)
+    torch.manual_seed(0)
+    H, F, T = 8, 12, 6
+    w1 = torch.randn(F, H, dtype=torch.float64)
+    w2 = torch.randn(H, F, dtype=torch.float64)
+    x_full = torch.randn(T, H, dtype=torch.float64)
+    col = TensorParallelColumnLinear(H, F, pg=ctx.tp_pg, mode=tp_mode, bias=False, dtype=torch.float64, async_communication=async_comm, contiguous_chunks=(8, 4))
+    row = TensorParallelRowLinear(F, H, pg=ctx.tp_pg, mode=tp_mode, bias=False, dtype=torch.float64, async_communication=False)
+    with torch.no_grad():
+        shard = torch.cat([w1[0:8].chunk(2)[rank], w1[8:12].chunk(2)[rank]])
+        col.weight.copy_(shard)
+        cols = torch.cat([torch.arange(0, 8).chunk(2)[rank], torch.arange(8, 12).chunk(2)[rank]])
+        row.weight.copy_(w2[:, cols])
+    x_in = x_full.chunk(2)[rank].clone().requires_grad_(True) if tp_mode is TensorParallelLinearMode.REDUCE_SCATTER else x_full.clone().requires_grad_(True)
+    y = row(torch.tanh(col(x_in)))
+    # oracle
+    xo = x_full.clone().requires_grad_(True)
+    w1o, w2o = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True)
+    yo = torch.tanh(xo @ w1o.t()) @ w2o.t()
+    y_exp = yo.chunk(2)[rank] if tp_mode is TensorParallelLinearMode.REDUCE_SCATTER else yo
+    torch.testing.assert_close(y, y_exp)
+    g = torch.randn_like(yo)
+    yo.backward(g)
+    y.backward(g.chunk(2)[rank] if tp_mode is TensorParallelLinearMode.REDUCE_SCATTER else g)
+    torch.testing.assert_close(x_in.grad, xo.grad.chunk(2)[rank] if tp_mode is TensorParallelLinearMode.REDUCE_SCATTER else xo.grad)
+    torch.testing.assert_close(col.weight.grad, torch.cat([w1o.grad[0:8].chunk(2)[rank], w1o.grad[8:12].chunk(2)[rank]]))
+    torch.testing.assert_close(row.weight.grad, w2o.grad[:, cols])
+    # embedding
+    emb = TensorParallelEmbedding(10, 4, pg=ctx.tp_pg, mode=tp_mode, dtype=torch.float64)
+    table = torch.randn(10, 4, dtype=torch.float64)
+    with torch.no_grad():
+        emb.weight.copy_(table.chunk(2)[rank])
+    ids = torch.tensor([0, 9, 4, 5, 5, 2])
+    out = emb(ids)
+    exp = table[ids]
+    torch.testing.assert_close(out, exp.chunk(2)[rank] if tp_mode is TensorParallelLinearMode.REDUCE_SCATTER else exp)
+    ctx.destroy()
+
+
+@pytest.mark.parametrize("mode,async_comm", [("ALL_REDUCE", False), ("REDUCE_SCATTER", False), ("REDUCE_SCATTER", True)])
+def test_tp_layers_match_unsharded(mode, async_comm):
+    run_distributed(_check_tp_linear, 2, mode=mode, async_comm=async_comm)
+
+
+def _check_sharded_ce():
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.parallel import ParallelContext
+    from nanotron_b200.parallel.tensor_parallel.functional import sharded_cross_entropy_with_z_loss
+
+    ctx = ParallelContext(tensor_parallel_size=2, pipeline_parallel_size=1, data_parallel_size=1)
+    rank = dist.get_rank(ctx.tp_pg)
+    torch.manual_seed(0)
+    logits = torch.randn(5, 16)
+    tgt = torch.randint(0, 16, (5,))
+    local = logits.chunk(2, dim=-1)[rank].clone().requires_grad_(True)
+    ce, z = sharded_cross_entropy_with_z_loss(local, tgt, group=ctx.tp_pg, z_loss_coef=1e-2)
+    (ce + z).mean().backward()
+    full = logits.clone().requires_grad_(True)
+    lz = torch.logsumexp(full, -1)
+    exp = torch.nn.functional.cross_entropy(full, tgt, reduction="none")
+    (exp + 1e-2 * lz**2).mean().backward()
+    torch.testing.assert_close(ce, exp, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(local.grad, full.grad.chunk(2, dim=-1)[rank], atol=1e-6, rtol=1e-4)
+    ctx.destroy()
+
+
+def test_vocab_parallel_cross_entropy():
+    run_distributed(_check_sharded_ce, 2)
+
+
+# --------------------------------------------------------------------------- trainer-level equivalences
+def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123):
+    """The same global batch for every topology: ``total_mbs`` sequences per step, this rank takes its dp slice."""
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.parallel.pipeline_parallel.tensor_pointer import TensorPointer
+
+    ctx = trainer.parallel_context
+    g = torch.Generator().manual_seed(seed)
+    dp, dp_rank = ctx.dp_pg.size(), dist.get_rank(ctx.dp_pg)
+    pp_rank = dist.get_rank(ctx.pp_pg)
+    per_rank = total_mbs // dp
+    mbs = trainer.micro_batch_size
+    out = []
+    for _ in range(n):
+        tokens = torch.randint(0, vocab, (total_mbs, seq + 1), generator=g)
+        mine = tokens[dp_rank * per_rank : (dp_rank + 1) * per_rank]
+        for i in range(0, per_rank, mbs):
+            t = mine[i : i + mbs]
+            b = {}
+            if pp_rank == trainer.unwrapped_model.input_pp_rank:
+                b["input_ids"] = t[:, :-1].contiguous()
+                if uses_mask:
+                    b["input_mask"] = torch.ones(mbs, seq, dtype=torch.bool)
+                else:
+                    b["position_ids"] = torch.arange(seq).unsqueeze(0).expand(mbs, -1).contiguous()
+            else:
+                b["input_ids"] = TensorPointer(trainer.unwrapped_model.input_pp_rank)
+                b["input_mask" if uses_mask else "position_ids"] = TensorPointer(trainer.unwrapped_model.input_pp_rank)
+            if pp_rank == trainer.unwrapped_model.output_pp_rank:
+                b["label_ids"] = t[:, 1:].contiguous()
+                b["label_mask"] = torch.ones(mbs, seq, dtype=torch.bool)
+            else:
+                b["label_ids"] = TensorPointer(trainer.unwrapped_model.output_pp_rank)
+                b["label_mask"] = TensorPointer(trainer.unwrapped_model.output_pp_rank)
+            out.append(b)
+    return out
+
+
+def _deterministic_init(model):
+    """Every topology gets the same unsharded weights: values depend only on the parameter's canonical name and on
+    the element's position in the unsharded tensor."""
+    import zlib
+
+    with torch.no_grad():
+        for name, p in model.get_named_params_with_correct_tied():
+            shape = tuple(p.get_sharded_info().unsharded_shape) if p.is_sharded else tuple(p.shape)
+            g = torch.Generator().manual_seed(zlib.crc32(name.encode()))
+            full = torch.randn(shape, generator=g, dtype=torch.float32) * 0.05
+            if "layernorm" in name or "layer_norm" in name or "ln_" in name:
+                full = 1.0 + full
+            if p.is_sharded:
+                for sp in p.get_sharded_info().local_global_slices_pairs:
+                    p[sp.local_slices] = full[sp.global_slices].to(p.dtype)
+            else:
+                p.copy_(full.to(p.dtype))
+
+
+def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.trainer import DistributedTrainer as _Base
+
+    class DistributedTrainer(_Base):
+        def _load_model_checkpoint(self, model):
+            _deterministic_init(model)
+            return model
+
+    dp = topology.get("dp", 1)
+    mbs = topology.pop("mbs", 1)
+    accum = total_mbs // (dp * mbs)
+    mc = tiny_llama_config() if model == "llama" else tiny_qwen_config()
+    cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
+    t = DistributedTrainer(cfg)
+    t.prepare_training()
+    batches = iter(_fixed_batches(t, steps, total_mbs, 16, mc.vocab_size, uses_mask=(model == "llama")))
+    losses = []
+    for _ in range(steps):
+        _, loss, _ = t.training_step(batches)
+        t.iteration_step += 1
+        if loss is not None:
+            losses.append(float(loss))
+    if dist.get_rank(t.parallel_context.world_pg) == t.logger_ranks[0]:
+        torch.save(losses, out_file)
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def _losses_for(tmp_path, world, name, **kw):
+    f = str(tmp_path / f"{name}.pt")
+    run_distributed(_train_losses, world, out_file=f, **kw)
+    return torch.load(f)
+
+
+def test_topologies_agree_on_loss_curve(tmp_path):
+    """dp / zero-1 / tp (both modes) / pp (both engines) give the same loss curve as one process on the same data."""
+    base = _losses_for(tmp_path, 1, "base")
+    assert base[-1] < base[0]
+    cases = {
+        "dp2": dict(dp=2),
+        "dp2_zero1": dict(dp=2, zero=1),
+        "tp2_ar": dict(tp=2, tp_mode="all_reduce"),
+        "tp2_sp": dict(tp=2, tp_mode="reduce_scatter"),
+        "tp2_sp_async": dict(tp=2, tp_mode="reduce_scatter", async_tp=True),
+        "pp2_afab": dict(pp=2, pp_engine="afab"),
+        "pp2_1f1b": dict(pp=2, pp_engine="1f1b"),
+    }
+    for name, kw in cases.items():
+        world = kw.get("dp", 1) * kw.get("tp", 1) * kw.get("pp", 1)
+        got = _losses_for(tmp_path, world, name, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-4, (name, got, base)
+
+
+def test_3d_and_qwen_topologies(tmp_path):
+    base = _losses_for(tmp_path, 1, "qbase", model="qwen")
+    got = _losses_for(tmp_path, 4, "q3d", model="qwen", dp=2, tp=2, tp_mode="reduce_scatter", zero=1)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-4, (got, base)
+    got = _losses_for(tmp_path, 4, "qpp", model="qwen", pp=2, tp=2, pp_engine="1f1b")
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-4, (got, base)

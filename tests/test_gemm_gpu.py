@@ -1,0 +1,67 @@
+"""tcgen05 GEMM against an fp32 PyTorch product: every operand layout, every output mode, edge tiles."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(got, exp):
+    return ((got.float() - exp).abs().max() / exp.abs().max().clamp(min=1e-6)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (192, 320, 448), (1024, 1536, 1024), (4096, 6144, 4096)])
+def test_gemm_nt(M, N, K):
+    from nanotron_b200.ops import native_gemm as g
+    from nanotron_b200.ops import native
+
+    native.lib()
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    exp = x.float() @ w.float().t()
+    got = g.gemm_nt(x, w)
+    g.check_status(DEV)
+    assert _rel_err(got, exp) < 1e-2
+    got32 = g.gemm_nt(x, w, out_dtype=torch.float32)
+    assert _rel_err(got32, exp) < 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (320, 192, 448), (2048, 1024, 3072)])
+def test_gemm_nn_and_tn(M, N, K):
+    from nanotron_b200.ops import native_gemm as g
+    from nanotron_b200.ops import native
+
+    native.lib()
+    torch.manual_seed(1)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    dx = g.gemm_nn(dy, w)
+    assert _rel_err(dx, dy.float() @ w.float()) < 1e-2
+    dw = g.gemm_tn(dy, x)
+    exp_dw = dy.float().t() @ x.float()
+    assert _rel_err(dw, exp_dw) < 1e-2
+    acc = torch.randn(N, K, device=DEV, dtype=torch.float32)
+    base = acc.clone()
+    g.gemm_tn_accum_fp32(dy, x, acc)
+    g.gemm_tn_accum_fp32(dy, x, acc)
+    g.check_status(DEV)
+    assert _rel_err(acc - base, 2 * exp_dw) < 1e-3
+
+
+def test_linear_ops_route_to_tcgen05():
+    from nanotron_b200 import ops
+
+    ops.set_gemm("tcgen05")
+    try:
+        torch.manual_seed(2)
+        x = torch.randn(512, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        lin = torch.nn.Linear(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16)
+        n0 = ops.native_launches()
+        y = ops.linear_forward(x, lin.weight)
+        assert ops.native_launches() == n0 + 1
+        exp = torch.nn.functional.linear(x.float(), lin.weight.float())
+        assert _rel_err(y, exp) < 1e-2
+    finally:
+        ops.set_gemm("auto")
