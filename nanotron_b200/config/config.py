@@ -334,6 +334,9 @@ class OptimizerArgs:
     accumulate_grad_in_fp32: bool
     learning_rate_scheduler: LRSchedulerArgs
     weight_decay_exclude_named_params: Optional[List[str]] = None
+    # None: use the in-kernel NVLink reduce-scatter + AdamW + all-gather step whenever it applies (CUDA, dp > 1 inside one
+    # node, fp32 accumulation, AdamW).  False: always the NCCL collectives.
+    fused_zero_comm: Optional[bool] = None
 
     def __post_init__(self):
         if self.weight_decay_exclude_named_params is None:

@@ -118,3 +118,60 @@ def dummy_infinite_data_generator(
             yield batch
 
     return data_generator
+
+
+def get_dataloader_worker_init(dp_rank: int):
+    """Distinct numpy / python seeds per (dp rank, worker)."""
+
+    def dataloader_worker_init(worker_id):
+        import random
+
+        seed = 2**32 - 1 - (dp_rank * 1000 + worker_id)
+        np.random.seed(seed % (2**32))
+        random.seed(seed)
+
+    return dataloader_worker_init
+
+
+def get_train_dataloader(
+    train_dataset,
+    sequence_length: int,
+    parallel_context: ParallelContext,
+    input_pp_rank: int,
+    output_pp_rank: int,
+    micro_batch_size: int,
+    consumed_train_samples: int,
+    dataloader_num_workers: int,
+    seed_worker: int,
+    dataloader_drop_last: bool = True,
+    dataloader_pin_memory: bool = True,
+    use_loop_to_round_batch_size: bool = False,
+    use_position_ids: bool = False,
+    use_doc_masking: bool = True,
+    sampler_shuffle: bool = False,
+) -> DataLoader:
+    """Standard map-style dataloader: dp-sharded sampler (resumable), CLM collator, pinned memory.
+    Pipeline ranks that need no data iterate an empty dataset of the same length."""
+    from nanotron_b200.data.clm_collator import DataCollatorForCLM, DataCollatorForCLMWithPositionIds
+    from nanotron_b200.data.samplers import EmptyInfiniteDataset, get_sampler
+
+    if not isinstance(train_dataset, torch.utils.data.Dataset) and not hasattr(train_dataset, "__getitem__"):
+        raise ValueError(f"training requires a map-style dataset, got {type(train_dataset)}")
+    pp_rank = dist.get_rank(parallel_context.pp_pg)
+    if pp_rank not in (input_pp_rank, output_pp_rank):
+        train_dataset = EmptyInfiniteDataset(length=len(train_dataset))
+        dataloader_num_workers = 0
+    elif hasattr(train_dataset, "with_format"):
+        train_dataset = train_dataset.with_format(type="numpy", columns=["input_ids"] + (["positions"] if "positions" in getattr(train_dataset, "column_names", []) else []), output_all_columns=False)
+    if use_position_ids:
+        collator = DataCollatorForCLMWithPositionIds(sequence_length=sequence_length, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank, parallel_context=parallel_context, use_doc_masking=use_doc_masking)
+    else:
+        collator = DataCollatorForCLM(sequence_length=sequence_length, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank, parallel_context=parallel_context)
+    dp_size = parallel_context.dp_pg.size()
+    dp_rank = dist.get_rank(parallel_context.dp_pg)
+    sampler = get_sampler(dl_rank=dp_rank, dl_ranks_size=dp_size, train_dataset=train_dataset, seed=seed_worker, use_loop_to_round_batch_size=use_loop_to_round_batch_size, micro_batch_size=micro_batch_size, drop_last=dataloader_drop_last, consumed_train_samples=consumed_train_samples, shuffle=sampler_shuffle)
+    return DataLoader(
+        train_dataset, batch_size=micro_batch_size, sampler=sampler, collate_fn=collator, drop_last=dataloader_drop_last,
+        num_workers=dataloader_num_workers, pin_memory=dataloader_pin_memory and torch.cuda.is_available(),
+        worker_init_fn=get_dataloader_worker_init(dp_rank=dp_rank),
+    )

@@ -51,8 +51,16 @@ def _declare(L):
     L.ntb_adamw_flat.argtypes = [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int] + [c_float] * 5 + [c_void_p, c_void_p]
     L.ntb_sumsq_num_partials.restype = c_int
     L.ntb_sumsq.argtypes = [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p]
-    for name in dir(L):
-        pass
+    if hasattr(L, "ntb_symm_barrier"):
+        c_uint32, c_ull = ctypes.c_uint32, ctypes.c_ulonglong
+        L.ntb_comm_max_ranks.restype = c_int
+        L.ntb_dp_num_partials.restype = c_int
+        L.ntb_symm_barrier.restype = c_int
+        L.ntb_symm_barrier.argtypes = [c_void_p, c_int, c_int, c_uint32, c_ull, c_void_p, c_void_p]
+        L.ntb_dp_reduce_scatter.restype = c_int
+        L.ntb_dp_reduce_scatter.argtypes = [c_void_p, c_int, c_int, c_int64, c_int64, c_float, c_int, c_void_p, c_void_p, c_void_p]
+        L.ntb_dp_adamw_allgather.restype = c_int
+        L.ntb_dp_adamw_allgather.argtypes = [c_void_p] * 5 + [c_int, c_int, c_int64, c_int64] + [c_void_p] * 3 + [c_int] + [c_float] * 5 + [c_void_p, c_void_p]
     for fn in ("ntb_norm_fwd", "ntb_norm_bwd", "ntb_rope", "ntb_swiglu_fwd", "ntb_swiglu_bwd", "ntb_ce_partials", "ntb_ce_backward", "ntb_adamw_flat", "ntb_sumsq"):
         getattr(L, fn).restype = c_int
     from nanotron_b200.ops import native_gemm, native_attn  # noqa: F401  (declare their symbols when present)

@@ -71,6 +71,22 @@ class FlatLayout:
         return v.view(shape) if shape is not None else v
 
 
+_BUFFER_ALLOCATOR = None
+
+
+def set_buffer_allocator(fn):
+    """``fn(numel, dtype, device) -> zero-filled 1-D tensor`` used for every flat buffer (None: ``torch.zeros``).
+    The trainer installs a symmetric-memory allocator here so peers can address the buffers directly."""
+    global _BUFFER_ALLOCATOR
+    _BUFFER_ALLOCATOR = fn
+
+
+def alloc_flat(numel: int, dtype: torch.dtype, device) -> torch.Tensor:
+    if _BUFFER_ALLOCATOR is not None:
+        return _BUFFER_ALLOCATOR(numel, dtype, device)
+    return torch.zeros(numel, dtype=dtype, device=device)
+
+
 def flatten_parameters(named_params: List[Tuple[str, torch.nn.Parameter]], layout: FlatLayout) -> Dict[torch.dtype, torch.Tensor]:
     """Move every parameter into one flat buffer per dtype following ``layout`` (``param.data`` becomes a view).
     Returns the buffers by dtype."""
@@ -86,7 +102,7 @@ def flatten_parameters(named_params: List[Tuple[str, torch.nn.Parameter]], layou
         ):
             buffers[dtype] = existing  # already flattened with this layout
             continue
-        buf = torch.zeros(layout.total, dtype=dtype, device=device)
+        buf = alloc_flat(layout.total, dtype, device)
         with torch.no_grad():
             for name, p in items:
                 v = layout.view(buf, name, p.shape)

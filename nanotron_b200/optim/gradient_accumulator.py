@@ -22,7 +22,7 @@ from typing import Callable, Dict, Iterator, Optional, Tuple
 import torch
 
 import nanotron_b200.distributed as dist
-from nanotron_b200.optim.flat_layout import ALIGN, FlatLayout, _round_up, flatten_parameters
+from nanotron_b200.optim.flat_layout import ALIGN, FlatLayout, _round_up, alloc_flat, flatten_parameters
 from nanotron_b200.parallel.parameters import NanotronParameter
 
 
@@ -115,7 +115,7 @@ class FP32GradientAccumulator(GradientAccumulator):
         if layout is None:
             layout = FlatLayout.build([(n, p.numel()) for n, p in named_parameters])
         offsets = layout.offsets
-        buf = torch.zeros(layout.total, dtype=torch.float32, device=device)
+        buf = alloc_flat(layout.total, torch.float32, device)
         out = OrderedDict()
         for name, p in named_parameters:
             view = buf[offsets[name] : offsets[name] + p.numel()].view(p.shape)

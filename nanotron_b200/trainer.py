@@ -122,7 +122,21 @@ class DistributedTrainer:
         self.model = self.init_model()
         self.unwrapped_model: NanotronModel = self.model
         parametrization_method = ParametrizationMethod.SPECTRAL_MUP if hasattr(self.config.model.init_method, "use_mup") else ParametrizationMethod.STANDARD
-        self.optimizer, self.grad_accumulator = init_optimizer_and_grad_accumulator(parametrization_method=parametrization_method, model=self.model, optimizer_args=self.config.optimizer, parallel_context=self.parallel_context)
+        symm_alloc = self._maybe_enable_symmetric_buffers()
+        try:
+            self.optimizer, self.grad_accumulator = init_optimizer_and_grad_accumulator(parametrization_method=parametrization_method, model=self.model, optimizer_args=self.config.optimizer, parallel_context=self.parallel_context)
+        finally:
+            from nanotron_b200.optim.flat_layout import set_buffer_allocator
+
+            set_buffer_allocator(None)
+        self.fused_dp = None
+        if symm_alloc is not None:
+            from nanotron_b200.optim.fused_adamw import FusedAdamW
+            from nanotron_b200.optim.fused_zero import FusedDataParallelStep
+
+            if isinstance(self.optimizer.get_base_optimizer(), FusedAdamW) and self.grad_accumulator is not None:
+                self.fused_dp = FusedDataParallelStep(symm_alloc, self.grad_accumulator, self.optimizer, self.parallel_context.dp_pg, self.parallel_context.mp_pg, self.config.optimizer.clip_grad)
+                log_rank("Data-parallel step: in-kernel NVLink reduce-scatter + AdamW + all-gather", logger=logger, level=logging.INFO, rank=0)
         if self.init_checkpoint_path is not None and self.config.checkpoints.load_optimizer:
             load_optimizer(optimizer=self.optimizer, parallel_context=self.parallel_context, root_folder=self.init_checkpoint_path, param_shard_metadata=self.param_shard_metadata, model=self.unwrapped_model, map_location="cpu")
         self.lr_scheduler = lr_scheduler_builder(optimizer=self.optimizer, lr_scheduler_args=self.config.optimizer.learning_rate_scheduler, total_training_steps=self.config.tokens.train_steps)
@@ -147,6 +161,27 @@ class DistributedTrainer:
         self._stop_requested = False
         self._kill_switch_path = Path(os.environ["NANOTRON_KILL_SWITCH"]) if os.environ.get("NANOTRON_KILL_SWITCH") else None
         self.post_init()
+
+    def _maybe_enable_symmetric_buffers(self):
+        """Put the flat gradient / parameter buffers in peer-mapped memory when the fused data-parallel step applies."""
+        ctx, opt = self.parallel_context, self.config.optimizer
+        if opt.fused_zero_comm is False or ctx.device.type != "cuda" or ctx.dp_pg.size() == 1:
+            return None
+        if not opt.accumulate_grad_in_fp32 or opt.optimizer_factory.name != "adamW" or ctx.cp_pg.size() > 1 or ctx.expert_parallel_size > 1:
+            return None
+        if ctx.world_size > ctx.local_world_size:
+            dp_ranks = dist.get_global_ranks(ctx.dp_pg)
+            if len({r // ctx.local_world_size for r in dp_ranks}) > 1:
+                return None  # the dp group spans nodes: NVLink peer access does not reach
+        from nanotron_b200 import ops
+        from nanotron_b200.optim.flat_layout import set_buffer_allocator
+        from nanotron_b200.parallel import symm
+
+        if ops.get_mode() == "torch" or not symm.is_available(ctx.dp_pg):
+            return None
+        alloc = symm.SymmetricAllocator(ctx.dp_pg)
+        set_buffer_allocator(lambda numel, dtype, device: alloc.zeros(numel, dtype).tensor)
+        return alloc
 
     # ------------------------------------------------------------------ hooks
     def pre_init(self):
@@ -316,12 +351,14 @@ class DistributedTrainer:
                 nb_microbatches=self.n_micro_batches_per_batch, grad_accumulator=self.grad_accumulator,
             )
         after_tbi_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator)
-        with nanotron_timer("sync_gradients"), torch.profiler.record_function("sync_gradients"):
-            self._sync_gradients()
+        fused = self.fused_dp is not None
+        if not fused:
+            with nanotron_timer("sync_gradients"), torch.profiler.record_function("sync_gradients"):
+                self._sync_gradients()
         # tied / replicated-by-design parameters (norm weights under sequence parallelism, tied embeddings)
         sync_tied_weights_gradients(module=self.unwrapped_model, parallel_context=self.parallel_context, grad_accumulator=self.grad_accumulator)
         self.grad_norm_unclipped = None
-        if self.config.optimizer.clip_grad is not None:
+        if self.config.optimizer.clip_grad is not None and not fused:
             with nanotron_timer("clip_gradients"), torch.profiler.record_function("clip_gradients"):
                 self.grad_norm_unclipped = self._clip_gradients()
         # loss average over data (and context) parallel replicas, for logging
@@ -341,7 +378,10 @@ class DistributedTrainer:
             self._move_optimizer_state_to_device()
         before_optim_step_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator, self.optimizer)
         with nanotron_timer("optimizer_step"), torch.profiler.record_function("optimizer_step"):
-            self.optimizer.step()
+            if fused:
+                self.grad_norm_unclipped = self.fused_dp.step()
+            else:
+                self.optimizer.step()
             self.optimizer.zero_grad()
         self.lr_scheduler.step()
         after_optim_step_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator)
