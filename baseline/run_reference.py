@@ -117,6 +117,9 @@ def run_reference(args):
     except torch.cuda.OutOfMemoryError as e:
         return _unavailable(f"reference ran out of GPU memory on this config: {str(e)[:160]}")
     except Exception as e:
+        import traceback
+
+        traceback.print_exc(file=sys.stderr)
         return _unavailable(f"reference failed on its stock path: {type(e).__name__}: {str(e)[:300]}")
     ms = torch.tensor([state["start"].elapsed_time(state["end"])], dtype=torch.float64, device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)

@@ -1,0 +1,130 @@
+#!/usr/bin/env python
+"""Training entry point (parity: reference run_train.py).
+
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 run_train.py --config-file examples/config_tiny_llama.yaml
+
+Builds one dataloader per data stage: the dummy generator when ``data.dataset`` is null, a HuggingFace text dataset
+(tokenised and packed) for ``PretrainDatasetsArgs`` / ``SFTDatasetsArgs``, or pre-tokenised token files
+(``NanosetDatasetsArgs``).  Stages are created lazily so only the active one holds memory.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+from typing import Dict, Optional
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from nanotron_b200 import logging  # noqa: E402
+from nanotron_b200.config import DataArgs, DatasetStageArgs, LlamaConfig, NanosetDatasetsArgs, PretrainDatasetsArgs, SFTDatasetsArgs, Starcoder2Config  # noqa: E402
+from nanotron_b200.data.dataloader import dummy_infinite_data_generator, get_train_dataloader  # noqa: E402
+from nanotron_b200.helpers import compute_remain_train_steps_of_a_data_stage_from_ckp, get_consumed_train_samples_of_a_data_stage_from_ckp  # noqa: E402
+from nanotron_b200.logging import log_rank  # noqa: E402
+from nanotron_b200.parallel.pipeline_parallel.utils import get_input_output_pp_ranks  # noqa: E402
+from nanotron_b200.trainer import DistributedTrainer  # noqa: E402
+
+logger = logging.get_logger("nanotron_b200.run_train")
+
+
+def get_dataloader_from_data_stage(trainer: DistributedTrainer, data: DataArgs, consumed_train_samples_stage: int, consumed_tokens_per_dataset_folder: Dict[str, int], num_remaining_train_steps: int, sequence_length: Optional[int] = None):
+    assert consumed_train_samples_stage >= 0 and num_remaining_train_steps >= 0
+    input_pp_rank, output_pp_rank = get_input_output_pp_ranks(model=trainer.model)
+    seq = sequence_length or trainer.sequence_length
+    uses_mask = isinstance(trainer.model_config, (LlamaConfig, Starcoder2Config))
+    if data.dataset is None:
+        log_rank("Using dummy data generator", logger=logger, level=logging.INFO, rank=0)
+        return dummy_infinite_data_generator(
+            micro_batch_size=trainer.micro_batch_size, sequence_length=seq, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank,
+            vocab_size=trainer.model_config.vocab_size, seed=data.seed, parallel_context=trainer.parallel_context, use_position_ids=not uses_mask,
+        )()
+    if isinstance(data.dataset, (PretrainDatasetsArgs, SFTDatasetsArgs)):
+        from transformers import AutoTokenizer
+
+        from nanotron_b200.data.processing import clm_process, get_datasets
+        from nanotron_b200.utils import main_rank_first
+
+        tokenizer_path = trainer.config.tokenizer.tokenizer_name_or_path
+        log_rank(f"Loading tokenizer from {tokenizer_path}", logger=logger, level=logging.INFO, rank=0)
+        with main_rank_first(trainer.parallel_context.world_pg):
+            raw = get_datasets(hf_dataset_or_datasets=data.dataset.hf_dataset_or_datasets, hf_dataset_config_name=data.dataset.hf_dataset_config_name, splits=data.dataset.hf_dataset_splits)["train"]
+            tokenizer = AutoTokenizer.from_pretrained(tokenizer_path)
+            tokenizer.pad_token = tokenizer.pad_token or tokenizer.eos_token
+            tokenizer.padding_side = "left"
+            assert tokenizer.vocab_size <= trainer.model_config.vocab_size, f"tokenizer vocab ({tokenizer.vocab_size}) larger than the model's ({trainer.model_config.vocab_size})"
+            if isinstance(data.dataset, SFTDatasetsArgs):
+                from nanotron_b200.data.sft_processing import prepare_sft_dataset
+
+                train_dataset = prepare_sft_dataset(raw, tokenizer, seq, debug_max_samples=data.dataset.debug_max_samples, num_proc=data.dataset.dataset_processing_num_proc_per_process)
+            else:
+                train_dataset = clm_process(raw_dataset=raw, tokenizer=tokenizer, text_column_name=data.dataset.text_column_name, dataset_processing_num_proc_per_process=data.dataset.dataset_processing_num_proc_per_process, dataset_overwrite_cache=data.dataset.dataset_overwrite_cache, sequence_length=seq)
+        if isinstance(data.dataset, SFTDatasetsArgs):
+            from torch.utils.data import DataLoader
+
+            from nanotron_b200.data.clm_collator import DataCollatorForSFT
+            from nanotron_b200.data.samplers import get_sampler
+            import nanotron_b200.distributed as dist
+
+            ctx = trainer.parallel_context
+            sampler = get_sampler(dl_ranks_size=ctx.dp_pg.size(), dl_rank=dist.get_rank(ctx.dp_pg), train_dataset=train_dataset, consumed_train_samples=consumed_train_samples_stage, seed=data.seed)
+            return DataLoader(train_dataset.with_format("numpy"), batch_size=trainer.micro_batch_size, sampler=sampler, collate_fn=DataCollatorForSFT(seq, input_pp_rank, output_pp_rank, ctx), num_workers=data.num_loading_workers, drop_last=True)
+        dataloader = get_train_dataloader(
+            train_dataset=train_dataset, sequence_length=seq, parallel_context=trainer.parallel_context, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank,
+            micro_batch_size=trainer.micro_batch_size, consumed_train_samples=consumed_train_samples_stage, dataloader_num_workers=data.num_loading_workers,
+            seed_worker=data.seed, dataloader_drop_last=True, use_position_ids=not uses_mask,
+        )
+        total_tokens_dataset = len(dataloader.dataset) * seq
+        needed = num_remaining_train_steps * trainer.global_batch_size * seq
+        assert needed < total_tokens_dataset, f"Dataset is too small for steps ({total_tokens_dataset} < {needed}), try train_steps<={len(dataloader.dataset) // trainer.global_batch_size + trainer.iteration_step}"
+        return dataloader
+    if isinstance(data.dataset, NanosetDatasetsArgs):
+        from nanotron_b200.data.nanoset import Nanoset
+        from nanotron_b200.utils import main_rank_first
+
+        with main_rank_first(trainer.parallel_context.world_pg):
+            train_dataset = Nanoset(
+                dataset_folders=data.dataset.dataset_folder, dataset_weights=data.dataset.dataset_weights, sequence_length=seq,
+                token_size=data.dataset.token_size_in_bytes or (4 if trainer.model_config.vocab_size > 65535 else 2),
+                train_split_num_samples=trainer.config.tokens.train_steps * trainer.global_batch_size, random_seed=data.seed,
+                return_positions=bool(data.dataset.return_positions), eos_token_id=getattr(trainer.model_config, "eos_token_id", None),
+            )
+        return get_train_dataloader(
+            train_dataset=train_dataset, sequence_length=seq, parallel_context=trainer.parallel_context, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank,
+            micro_batch_size=trainer.micro_batch_size, consumed_train_samples=consumed_train_samples_stage, dataloader_num_workers=data.num_loading_workers,
+            seed_worker=data.seed, dataloader_drop_last=True, use_position_ids=not uses_mask, use_doc_masking=getattr(trainer.model_config, "_use_doc_masking", False),
+        )
+    raise ValueError(f"Unhandled case of `self.config.data.dataset`. Got: {data.dataset}")
+
+
+def get_dataloader(trainer: DistributedTrainer):
+    """{stage name: dataloader or zero-argument factory}.  The stage to resume is built now, later stages lazily."""
+    dataloaders = {}
+    stages = sorted(trainer.config.data_stages, key=lambda s: s.start_training_step)
+    for stage_idx, stage in enumerate(stages):
+        stage: DatasetStageArgs
+        consumed = get_consumed_train_samples_of_a_data_stage_from_ckp(stage, trainer.metadata)
+        assert consumed is not None, f"Cannot find consumed_train_samples for stage {stage.start_training_step} in the checkpoint"
+        remaining = compute_remain_train_steps_of_a_data_stage_from_ckp(stage, trainer.config, trainer.metadata)
+        meta_stage = next(s for s in trainer.metadata.data_stages if s.start_training_step == stage.start_training_step)
+        log_rank(f"[Training Plan] Stage {stage.name} has {remaining} remaining training steps and has consumed {consumed} samples", logger=logger, level=logging.INFO, rank=0)
+
+        def build(stage=stage, consumed=consumed, remaining=remaining, meta_stage=meta_stage):
+            return get_dataloader_from_data_stage(trainer, stage.data, consumed_train_samples_stage=consumed, consumed_tokens_per_dataset_folder=meta_stage.consumed_tokens_per_dataset_folder, num_remaining_train_steps=remaining, sequence_length=stage.sequence_length)
+
+        is_current = stage_idx == (trainer.metadata.last_stage_idx or 0)
+        dataloaders[stage.name] = build() if is_current else build
+    return dataloaders
+
+
+def get_args():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--config-file", type=str, required=True, help="Path to the YAML or python config file")
+    parser.add_argument("--sanity-check-dataloader-interval", type=int, default=None, help="Log a decoded batch every N steps (debug)")
+    return parser.parse_args()
+
+
+if __name__ == "__main__":
+    args = get_args()
+    trainer = DistributedTrainer(args.config_file)
+    dataloader = get_dataloader(trainer)
+    trainer.train(dataloader)
