@@ -43,7 +43,7 @@ def run_reference(args):
         import nanotron  # noqa: F401
         from nanotron import distributed as dist
         from nanotron.config import (
-            AdamWOptimizerArgs, CheckpointsArgs, Config, DataArgs, DatasetStageArgs, GeneralArgs, LlamaConfig, LoggingArgs,
+            AdamWOptimizerArgs, CheckpointsArgs, Config, DataArgs, DatasetStageArgs, GeneralArgs, LoggingArgs, Qwen2Config,
             LRSchedulerArgs, ModelArgs, OptimizerArgs, ParallelismArgs, RandomInit, TokenizerArgs, TokensArgs,
         )
         from nanotron.data.dataloader import dummy_infinite_data_generator
@@ -57,7 +57,11 @@ def run_reference(args):
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
     m = dict(MODELS[args.model])
-    model_config = LlamaConfig(bos_token_id=1, eos_token_id=2, hidden_act="silu", initializer_range=0.02, pretraining_tp=1, rope_scaling=None, use_cache=True, rope_interleaved=False, **m)
+    # The reference's `LlamaForTraining.init_model_randomly` fails on its stock path (models/llama.py:1095 hands
+    # `config.model` to a parametrizator that reads `config.model.init_method`: AttributeError), so the Llama-3-8B shape
+    # is run through its maintained decoder implementation, `Qwen2ForTraining`, which without attention bias is the same
+    # architecture (RMSNorm, RoPE, GQA, SwiGLU) with the same parameter count and FLOPs.
+    model_config = Qwen2Config(bos_token_id=1, eos_token_id=2, hidden_act="silu", initializer_range=0.02, pretraining_tp=1, rope_scaling=None, use_cache=True, rope_interleaved=False, attention_bias=False, log_attn_probs=False, **m)
     total_steps = args.warmup + args.steps
     ckpt_dir = tempfile.mkdtemp(prefix="ref_ckpt_")
     config = Config(
@@ -111,7 +115,7 @@ def run_reference(args):
         dataloader = dummy_infinite_data_generator(
             micro_batch_size=trainer.micro_batch_size, sequence_length=trainer.sequence_length, input_pp_rank=input_pp_rank,
             output_pp_rank=output_pp_rank, vocab_size=trainer.model_config.vocab_size, seed=42, parallel_context=trainer.parallel_context,
-            use_position_ids=False, cp_pg=trainer.parallel_context.cp_pg,
+            use_position_ids=True, cp_pg=trainer.parallel_context.cp_pg,
         )()
         trainer.train({"bench": dataloader})
     except torch.cuda.OutOfMemoryError as e:

@@ -146,8 +146,9 @@ class FP32GradientAccumulator(GradientAccumulator):
                     # masters carry the same sharding / tying metadata as the parameter they shadow
                     setattr(master, NanotronParameter.NANOTRON_PARAMETER_METADATA_ATTRIBUTE_NAME, dict(half._meta))
                 g = self.fp32_grad_buffers[n]["fp32_grad"].view(-1)[s:e]
-                master.grad = g.view(half.shape) if (s, e) == (0, half.numel()) else g
-                self.parameters[n] = {"fp32": master, "half": half, "master_offset": offs[n]}
+                grad_view = g.view(half.shape) if (s, e) == (0, half.numel()) else g
+                master.grad = grad_view
+                self.parameters[n] = {"fp32": master, "half": half, "master_offset": offs[n], "grad_view": grad_view}
 
     def assign_param_offsets(self, param_name_to_offsets: Dict[str, Dict[int, Tuple[int, int]]], dp_rank: int):
         """ZeRO-1: keep masters only for the slice ``param_name_to_offsets[name][dp_rank]`` of every parameter."""
@@ -194,6 +195,9 @@ class FP32GradientAccumulator(GradientAccumulator):
         self._contiguous_fp32_grad_buffer.zero_()
         for d in self.fp32_grad_buffers.values():
             d["half"].grad = None
+        # optimizers drop ``.grad`` in their own zero_grad: re-attach the views of the flat buffer to the masters
+        for d in self.parameters.values():
+            d["fp32"].grad = d["grad_view"]
 
     def get_parameter_for_optimizer(self, name: str) -> NanotronParameter:
         return self.parameters[name]["fp32"]

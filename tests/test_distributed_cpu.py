@@ -143,6 +143,11 @@ def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123):
             else:
                 b["label_ids"] = TensorPointer(trainer.unwrapped_model.output_pp_rank)
                 b["label_mask"] = TensorPointer(trainer.unwrapped_model.output_pp_rank)
+            cp, cp_rank = ctx.cp_pg.size(), dist.get_rank(ctx.cp_pg)
+            if cp > 1:
+                from nanotron_b200.parallel.context_parallel.zigzag import zigzag_slice
+
+                b = {k: (zigzag_slice(v, cp_rank, cp, dim=1).contiguous() if isinstance(v, torch.Tensor) else v) for k, v in b.items()}
             out.append(b)
     return out
 
@@ -177,6 +182,8 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
 
     dp = topology.get("dp", 1)
     mbs = topology.pop("mbs", 1)
+    if topology.get("cp", 1) > 1:
+        topology["fp32_accum"] = True
     accum = total_mbs // (dp * mbs)
     mc = tiny_llama_config() if model == "llama" else tiny_qwen_config()
     cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
@@ -229,3 +236,25 @@ def test_3d_and_qwen_topologies(tmp_path):
     got = _losses_for(tmp_path, 4, "qpp", model="qwen", pp=2, tp=2, pp_engine="1f1b")
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4, (got, base)
+    got = _losses_for(tmp_path, 2, "qcp", model="qwen", cp=2)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-4, (got, base)
+
+
+def test_single_process_overfits_fixed_batch():
+    """Guards the optimizer wiring: the fp32 masters must keep receiving gradients after ``zero_grad``."""
+    from helpers import single_process_env
+    from nanotron_b200.trainer import DistributedTrainer
+
+    single_process_env()
+    t = DistributedTrainer(make_config(tiny_llama_config(), seq=32, steps=8, lr=1e-2))
+    t.prepare_training()
+    batch = next(dummy_dataloader(t))
+    losses = []
+    for _ in range(8):
+        _, loss, _ = t.training_step(iter([batch]))
+        t.iteration_step += 1
+        losses.append(float(loss))
+    t.parallel_context.destroy()
+    assert all(b < a for a, b in zip(losses, losses[1:])), losses
+    assert losses[-1] < losses[0] - 0.5, losses
