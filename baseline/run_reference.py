@@ -40,6 +40,9 @@ def run_reference(args):
 
         if not torch.cuda.is_available():
             return _unavailable("no CUDA device")
+        import flash_attn_compat
+
+        flash_attn_compat.apply()
         import nanotron  # noqa: F401
         from nanotron import distributed as dist
         from nanotron.config import (

@@ -1,0 +1,426 @@
+// Flash attention backward on tcgen05 / TMEM (sm_100a): head dim 128, bf16, causal or full, GQA, packed sequences.
+//
+// One CTA owns a tile of 128 keys of one KV head and walks every query head of its group and every 64-query tile that can
+// see those keys.  All five products are issued "transposed" so that M = 128 everywhere and the key index is the TMEM
+// lane:
+//     S^T  = K Q^T        (128 keys x 64 queries)          dP^T = V dO^T
+//     P^T  = exp2(S^T c - lse)     dS^T = P^T (dP^T - delta) * scale        (thread = key row, registers -> bf16 smem)
+//     dV  += P^T dO       dK += dS^T Q       (fp32 accumulators in TMEM for the whole CTA lifetime)
+//     dQ^T = K^T dS^T     (128 head-dim lanes x 64 queries) -> red.global.add.f32 into an fp32 dQ buffer; a warp's 32
+//                          lanes hit 32 consecutive floats, so the reductions are coalesced.
+// Warp roles: warp 0 TMA producer (K, V once; Q / dO double buffered), warp 1 MMA issuer, warps 2-5 softmax + dQ read-out
+// + final dK / dV write-out.  A small pre-pass computes delta = rowsum(dO * O); a post-pass casts dQ to bf16.
+// All waits are bounded (see sm100_ptx.cuh).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int BK = 128;  // keys per CTA
+constexpr int BQ = 64;   // queries per step
+constexpr int KV_TILE_BYTES = BK * HD * 2;   // 32 KiB (two [128][64] panels)
+constexpr int KV_PANEL = BK * 64 * 2;        // 16 KiB
+constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KiB (two [64][64] panels)
+constexpr int Q_PANEL = BQ * 64 * 2;         // 8 KiB
+constexpr int PT_BYTES = BK * BQ * 2;        // 16 KiB: [128 key rows][64 queries]
+constexpr int BWD_THREADS = 192;
+constexpr int BWD_SMEM = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 2 * PT_BYTES + 4096 /*lse, delta per warp*/ + 1024 + 256;
+
+struct BwdParams {
+  int num_heads, num_kv_heads, causal, window;
+  float scale, scale_log2;
+  const int* cu_q;
+  const int* cu_k;
+  const float* lse;    // [Hq, total_q]
+  const float* delta;  // [Hq, total_q]
+  float* dq_acc;       // [total_q, Hq, 128] fp32, zero-initialised
+  __nv_bfloat16* dk;   // strided [total_k, Hkv, 128]
+  __nv_bfloat16* dv;
+  int64_t dk_stride_t;
+  int total_q;
+  int* status;
+};
+
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta, int total_q, int heads) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= total_q * heads) return;
+  const int t = warp / heads, h = warp % heads;
+  const __nv_bfloat16* o = out + (static_cast<int64_t>(t) * heads + h) * HD + lane * 4;
+  const __nv_bfloat16* d = dout + (static_cast<int64_t>(t) * heads + h) * HD + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(o), b = *reinterpret_cast<const uint2*>(d);
+  const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(bh[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<int64_t>(h) * total_q + t] = s;
+}
+
+__global__ void cast_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int64_t rows, int heads, int64_t dq_stride_t) {
+  const int64_t idx = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (idx >= rows * heads * HD) return;
+  const int64_t t = idx / (heads * HD);
+  const int64_t rem = idx % (heads * HD);
+  float f[8];
+  *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(acc + idx);
+  *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(acc + idx + 4);
+  Vec8<__nv_bfloat16> v;
+  v.from_float(f);
+  v.store(dq + t * dq_stride_t + rem);
+}
+
+__device__ __forceinline__ void red_add_f32(float* p, float v) { asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory"); }
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KV_TILE_BYTES;
+  uint8_t* sQ = sV + KV_TILE_BYTES;           // 2 stages
+  uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;       // 2 stages
+  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;
+  uint8_t* sdST = sPT + PT_BYTES;
+  float* s_stats = reinterpret_cast<float*>(sdST + PT_BYTES);  // [4 warps][2 buffers][64 lse*log2e | 64 delta]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_stats) + 4096);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* qdo_full = bars + 1;     // [2]
+  uint64_t* qdo_empty = bars + 3;    // [2]
+  uint64_t* sdp_full = bars + 5;     // 1
+  uint64_t* pds_full = bars + 6;     // 1
+  uint64_t* mma_done = bars + 7;     // 1  (dV, dK, dQ^T products of a step finished)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, hk = blockIdx.y;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const int k0 = blockIdx.x * BK;
+  if (k0 >= k_len) return;
+  const int shift = k_len - q_len;
+  const int group = p.num_heads / p.num_kv_heads;
+  // query tiles that can see at least one key of this tile
+  int qt_begin = 0;
+  if (p.causal) qt_begin = max(0, k0 - shift) / BQ;
+  int qt_end = (q_len + BQ - 1) / BQ;
+  if (p.window > 0) qt_end = min(qt_end, (k0 + BK - 1 - shift + p.window - 1) / BQ + 1);
+  const int tiles_per_head = max(0, qt_end - qt_begin);
+  const int n_steps = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; s++) {
+      ptx::mbar_init(&qdo_full[s], 1);
+      ptx::mbar_init(&qdo_empty[s], 1);
+    }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(pds_full, 4);
+    ptx::mbar_init(mma_done, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tmap(&tmap_q);
+    ptx::prefetch_tmap(&tmap_do);
+    ptx::prefetch_tmap(&tmap_k);
+    ptx::prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_ST = tmem_base;         // 64 columns
+  const uint32_t tm_dPT = tmem_base + 64;   // 64
+  const uint32_t tm_dQT = tmem_base + 128;  // 64
+  const uint32_t tm_dV = tmem_base + 256;   // 128
+  const uint32_t tm_dK = tmem_base + 384;   // 128
+
+  if (warp == 0) {
+    if (ptx::elect_one() && n_steps > 0) {
+      ptx::mbar_expect_tx(kv_full, 2 * KV_TILE_BYTES);
+      ptx::tma_load_3d(sK, &tmap_k, kv_full, 0, hk, k_begin + k0);
+      ptx::tma_load_3d(sK + KV_PANEL, &tmap_k, kv_full, 64, hk, k_begin + k0);
+      ptx::tma_load_3d(sV, &tmap_v, kv_full, 0, hk, k_begin + k0);
+      ptx::tma_load_3d(sV + KV_PANEL, &tmap_v, kv_full, 64, hk, k_begin + k0);
+      for (int n = 0; n < n_steps; n++) {
+        const int s = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        const int h = hk * group + n / tiles_per_head;
+        const int row = q_begin + (qt_begin + n % tiles_per_head) * BQ;
+        if (!ptx::mbar_wait(&qdo_empty[s], ph ^ 1, abort_flag)) break;
+        ptx::mbar_expect_tx(&qdo_full[s], 2 * Q_TILE_BYTES);
+        ptx::tma_load_3d(sQ + s * Q_TILE_BYTES, &tmap_q, &qdo_full[s], 0, h, row);
+        ptx::tma_load_3d(sQ + s * Q_TILE_BYTES + Q_PANEL, &tmap_q, &qdo_full[s], 64, h, row);
+        ptx::tma_load_3d(sdO + s * Q_TILE_BYTES, &tmap_do, &qdo_full[s], 0, h, row);
+        ptx::tma_load_3d(sdO + s * Q_TILE_BYTES + Q_PANEL, &tmap_do, &qdo_full[s], 64, h, row);
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one() && n_steps > 0) {
+      constexpr uint32_t idesc_s = ptx::make_idesc_bf16(BK, BQ, false, false);   // K Q^T, V dO^T
+      constexpr uint32_t idesc_dv = ptx::make_idesc_bf16(BK, HD, false, true);   // P^T dO, dS^T Q
+      constexpr uint32_t idesc_dq = ptx::make_idesc_bf16(HD, BQ, true, true);    // K^T dS^T
+      const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV), aPT = ptx::smem_u32(sPT), adST = ptx::smem_u32(sdST);
+      bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
+      auto issue_s = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!ptx::mbar_wait(&qdo_full[s], (n >> 1) & 1, abort_flag)) return false;
+        ptx::tc_fence_after();
+        const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t offA = (k >> 2) * KV_PANEL + (k & 3) * 32;
+          const uint32_t offB = (k >> 2) * Q_PANEL + (k & 3) * 32;
+          ptx::umma_f16(tm_ST, ptx::make_smem_desc(aK + offA, 16, 1024), ptx::make_smem_desc(aQ + offB, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t offA = (k >> 2) * KV_PANEL + (k & 3) * 32;
+          const uint32_t offB = (k >> 2) * Q_PANEL + (k & 3) * 32;
+          ptx::umma_f16(tm_dPT, ptx::make_smem_desc(aV + offA, 16, 1024), ptx::make_smem_desc(adO + offB, 16, 1024), idesc_s, k != 0);
+        }
+        ptx::umma_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int n = 0; n < n_steps && ok; n++) {
+        const int s = n & 1;
+        if (!ptx::mbar_wait(pds_full, n & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
+        // dV += P^T dO ; dK += dS^T Q   (K dimension = 64 queries: 4 steps of 16 rows)
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++) {
+          ptx::umma_f16(tm_dV, ptx::make_smem_desc(aPT + k * 32, 16, 1024), ptx::make_smem_desc(adO + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++) {
+          ptx::umma_f16(tm_dK, ptx::make_smem_desc(adST + k * 32, 16, 1024), ptx::make_smem_desc(aQ + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
+        }
+        // dQ^T = K^T dS^T   (K dimension = 128 keys: 8 steps of 16 rows)
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++) {
+          ptx::umma_f16(tm_dQT, ptx::make_smem_desc(aK + k * 16 * 128, KV_PANEL, 1024), ptx::make_smem_desc(adST + k * 16 * 128, PT_BYTES, 1024), idesc_dq, k != 0);
+        }
+        ptx::umma_commit(&qdo_empty[s]);
+        ptx::umma_commit(mma_done);
+        if (n + 1 < n_steps) {
+          if (!issue_s(n + 1)) { ok = false; break; }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / dQ read-out / final write-out
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // key row (S^T, dV, dK) and head-dim row (dQ^T)
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int kpos = k0 + r;
+    const bool key_valid = kpos < k_len;
+    bool ok = true;
+    int prev_h = 0, prev_q0 = 0;
+    auto flush_dq = [&](int h, int q0) {
+      // dQ^T[r = head-dim index][64 queries] -> dq_acc[(q_begin + q0 + c), h, r]
+#pragma unroll 1
+      for (int c = 0; c < 2; c++) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(tm_dQT + lane_addr + c * 32, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const int qpos = q0 + c * 32 + i;
+          if (qpos < q_len) red_add_f32(p.dq_acc + (static_cast<int64_t>(q_begin + qpos) * p.num_heads + h) * HD + r, __uint_as_float(v[i]));
+        }
+      }
+    };
+    for (int n = 0; n < n_steps && ok; n++) {
+      const int h = hk * group + n / tiles_per_head;
+      const int q0 = (qt_begin + n % tiles_per_head) * BQ;
+      // per-warp copy of the 64 row statistics of this query tile (no cross-warp synchronisation needed)
+      float* lse_s = s_stats + ((warp - 2) * 2 + (n & 1)) * 128;
+      float* delta_s = lse_s + BQ;
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        const int qpos = q0 + c * 32 + lane;
+        const bool in = qpos < q_len;
+        const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
+        lse_s[c * 32 + lane] = in ? p.lse[idx] * 1.4426950408889634f : INFINITY;
+        delta_s[c * 32 + lane] = in ? p.delta[idx] : 0.f;
+      }
+      __syncwarp();
+      if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after();
+      uint32_t pk_p[32], pk_ds[32];  // 64 bf16 each
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t sv[32], dv[32];
+        ptx::tmem_ld_32x32(tm_ST + lane_addr + c * 32, sv);
+        ptx::tmem_ld_32x32(tm_dPT + lane_addr + c * 32, dv);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pp[2], dd[2];
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            const int col = c * 32 + i + u;
+            const int qpos = q0 + col;
+            bool vis = key_valid && qpos < q_len;
+            if (p.causal) vis = vis && (kpos <= qpos + shift);
+            if (p.window > 0) vis = vis && (kpos > qpos + shift - p.window);
+            const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i + u]), p.scale_log2, -lse_s[col])) : 0.f;
+            pp[u] = pr;
+            dd[u] = vis ? pr * (__uint_as_float(dv[i + u]) - delta_s[col]) * p.scale : 0.f;
+          }
+          __nv_bfloat162 hp = __floats2bfloat162_rn(pp[0], pp[1]), hd = __floats2bfloat162_rn(dd[0], dd[1]);
+          pk_p[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hp);
+          pk_ds[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hd);
+        }
+      }
+      // the previous step's products still read P^T / dS^T from shared memory and own dQ^T
+      if (n > 0) {
+        if (!ptx::mbar_wait(mma_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        flush_dq(prev_h, prev_q0);
+      }
+      uint8_t* prow = sPT + r * 128;
+      uint8_t* drow = sdST + r * 128;
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int sw = (u ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk_p[u * 4], pk_p[u * 4 + 1], pk_p[u * 4 + 2], pk_p[u * 4 + 3]);
+        *reinterpret_cast<uint4*>(drow + sw) = make_uint4(pk_ds[u * 4], pk_ds[u * 4 + 1], pk_ds[u * 4 + 2], pk_ds[u * 4 + 3]);
+      }
+      ptx::tc_fence_before();
+      ptx::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(pds_full);
+      prev_h = h;
+      prev_q0 = q0;
+    }
+    if (ok && n_steps > 0 && ptx::mbar_wait(mma_done, (n_steps - 1) & 1, abort_flag)) {
+      ptx::tc_fence_after();
+      flush_dq(prev_h, prev_q0);
+      // dK, dV rows of this key
+      if (key_valid) {
+        const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
+#pragma unroll 1
+        for (int which = 0; which < 2; which++) {
+          __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
+          const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
+#pragma unroll 1
+          for (int c = 0; c < 4; c++) {
+            uint32_t v[32];
+            ptx::tmem_ld_32x32(src + c * 32, v);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              uint4 pk;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+              pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+              pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + c * 32 + u * 8) = pk;
+            }
+          }
+        }
+      }
+    } else if (n_steps == 0 && key_valid) {
+      // no query sees these keys: their gradients are zero
+      const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
+      for (int c = 0; c < HD; c += 8) {
+        *reinterpret_cast<uint4*>(p.dk + off + c) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(p.dv + off + c) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, NTB_ERR_TIMEOUT);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn bwd_get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap* m, const void* ptr, int64_t tokens, int heads, int64_t stride_t, int64_t stride_h, int box_rows) {
+  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_t * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+  cuuint32_t es[3] = {1, 1, 1};
+  return bwd_get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// dout / out: [total_q, Hq, 128] contiguous.  q, k, v: strided like the forward (v shares k's strides).  delta: fp32 [Hq, total_q]
+// scratch; dq_acc: fp32 [total_q, Hq, 128] zero-filled scratch.  dq / dk / dv: bf16 outputs with token strides dq_stride_t /
+// dk_stride_t (head stride 128), e.g. views of one fused [T, Hq + 2 Hkv, 128] buffer.
+NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, float* dq_acc,
+                                  void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int max_seqlen_k, int total_q,
+                                  int total_k, int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
+                                  int64_t dq_stride_t, int64_t dk_stride_t, float softmax_scale, int causal, int window, int* status, cudaStream_t stream) {
+  if (!bwd_get_encode() || batch <= 0 || total_q <= 0 || total_k <= 0 || num_heads % num_kv_heads) return NTB_ERR_ARG;
+  if ((q_stride_t | q_stride_h | k_stride_t | k_stride_h | dq_stride_t | dk_stride_t) % 8) return NTB_ERR_ARG;
+  CUtensorMap tq, tdo, tk, tv;
+  if (!make_map(&tq, q, total_q, num_heads, q_stride_t, q_stride_h, BQ) || !make_map(&tdo, dout, total_q, num_heads, (int64_t)num_heads * HD, HD, BQ) ||
+      !make_map(&tk, k, total_k, num_kv_heads, k_stride_t, k_stride_h, BK) || !make_map(&tv, v, total_k, num_kv_heads, k_stride_t, k_stride_h, BK))
+    return NTB_ERR_ARG;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
+  }
+  {
+    const int64_t warps = static_cast<int64_t>(total_q) * num_heads;
+    delta_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, total_q, num_heads);
+  }
+  BwdParams p;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.causal = causal;
+  p.window = window;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.cu_q = cu_q;
+  p.cu_k = cu_k;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq_acc = dq_acc;
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.dk_stride_t = dk_stride_t;
+  p.total_q = total_q;
+  p.status = status;
+  dim3 grid((max_seqlen_k + BK - 1) / BK, num_kv_heads, batch);
+  flash_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tdo, tk, tv, p);
+  int rc = ntb_check_launch();
+  if (rc) return rc;
+  const int64_t n8 = static_cast<int64_t>(total_q) * num_heads * HD / 8;
+  cast_dq_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), total_q, num_heads, dq_stride_t);
+  return ntb_check_launch();
+}

@@ -45,3 +45,31 @@ def test_flash_fwd_sliding_window():
     out, _ = native_attn.flash_attn_fwd(q, k, v, cu, cu, 400, 400, True, 0.088, 160)
     exp = ref.attention_varlen(q, k, v, cu, cu, causal=True, softmax_scale=0.088, window=160)
     torch.testing.assert_close(out.float(), exp.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv,causal", [([128], 1, 1, True), ([256], 2, 1, True), ([200, 56, 333], 4, 2, True), ([384, 100], 2, 2, False), ([1024], 8, 2, True)])
+def test_flash_bwd_matches_oracle(lens, Hq, Hkv, causal):
+    from nanotron_b200 import ops
+    from nanotron_b200.ops import native, native_gemm
+
+    native.lib()
+    T = sum(lens)
+    q, k, v = _qkv(T, Hq, Hkv, seed=5)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(128)
+    qg, kg, vg = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    ops.set_attention("native")
+    try:
+        out = ops.flash_attn_varlen(qg, kg, vg, cu, cu, max(lens), max(lens), causal=causal, softmax_scale=scale)
+        g = torch.randn_like(out)
+        out.backward(g)
+    finally:
+        ops.set_attention("auto")
+    native_gemm.check_status(DEV)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    exp = ref.attention_varlen(qf, kf, vf, cu, cu, causal=causal, softmax_scale=scale)
+    exp.backward(g.float())
+    for name, a, b in (("dq", qg.grad, qf.grad), ("dk", kg.grad, kf.grad), ("dv", vg.grad, vf.grad)):
+        err = (a.float() - b).abs().max().item()
+        ref_mag = b.abs().max().item()
+        assert err < 3e-2 * max(ref_mag, 1.0), f"{name}: max err {err} vs magnitude {ref_mag}"
