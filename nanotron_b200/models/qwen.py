@@ -114,6 +114,18 @@ class Qwen2Attention(nn.Module, LogMixin):
         """hidden_states: [T_local, h] (T_local = b*s/tp under sequence parallelism); position_ids: [b, s_local]."""
         qkv = self.qkv_proj(hidden_states)  # [T, local_q + 2*local_kv]
         T = qkv.shape[0]
+        if self.cp_size == 1 and self.attn_impl == "flash_attention_2" and ops._ATTN == "native" and ops.fused_qkv_attention_supported(qkv, self.local_heads, self.local_kv_heads, self.head_dim, self.sliding_window_size):
+            b, s = position_ids.shape
+            cu = cu_seqlens if cu_seqlens is not None else regular_cu_seqlens(b, s, hidden_states.device)
+            if self.use_rope:
+                self.rotary_emb._ensure_tables(self.rotary_emb.max_seq_len, qkv.device)
+                cos, sin, interleaved = self.rotary_emb.cos_table, self.rotary_emb.sin_table, self.rotary_emb.interleaved
+            else:
+                cos = sin = None
+                interleaved = False
+            out = ops.fused_qkv_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, cu, s, causal=True, window=self.sliding_window_size, interleaved=interleaved, use_rope=self.use_rope)
+            out = self.o_proj(out.reshape(T, self.local_q_size))
+            return {"hidden_states": out, "position_ids": position_ids}
         q = qkv[:, : self.local_q_size].view(T, self.local_heads, self.head_dim)
         k = qkv[:, self.local_q_size : self.local_q_size + self.local_kv_size].view(T, self.local_kv_heads, self.head_dim)
         v = qkv[:, self.local_q_size + self.local_kv_size :].view(T, self.local_kv_heads, self.head_dim)

@@ -320,10 +320,66 @@ def flash_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, ma
     if q.is_cuda and _MODE != "torch":
         from nanotron_b200.ops import native
 
-        if _ATTN != "sdpa" and native.flash_attn_supported(q, k, v, window):
+        if _ATTN == "native" and native.flash_attn_supported(q, k, v, window):
             return _FlashAttnVarlen.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
         return _sdpa_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
     return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=scale, window=window)
+
+
+class _FusedQKVAttention(torch.autograd.Function):
+    """RoPE (in place on the q / k parts of the fused projection output) + flash attention, with ONE gradient tensor for the
+    whole qkv buffer: the attention backward writes dq / dk / dv into a single [T, (Hq + 2 Hkv) * D] buffer and the inverse
+    rotation is applied in place, so autograd never materialises per-slice gradients or concatenates them."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, positions, n_heads, n_kv, head_dim, cu, max_len, causal, scale, window, interleaved, use_rope):
+        from nanotron_b200.ops import native
+
+        T = qkv.shape[0]
+        q = qkv[:, : n_heads * head_dim].view(T, n_heads, head_dim)
+        k = qkv[:, n_heads * head_dim : (n_heads + n_kv) * head_dim].view(T, n_kv, head_dim)
+        v = qkv[:, (n_heads + n_kv) * head_dim :].view(T, n_kv, head_dim)
+        if use_rope:
+            native.rope(q, cos, sin, interleaved, inverse=False, inplace=True, positions=positions)
+            native.rope(k, cos, sin, interleaved, inverse=False, inplace=True, positions=positions)
+        out, lse = native.flash_attn_fwd(q, k, v, cu, cu, max_len, max_len, causal, scale, window)
+        ctx.save_for_backward(qkv, out, lse, cu, cos, sin, positions)
+        ctx.cfg = (n_heads, n_kv, head_dim, max_len, causal, scale, window, interleaved, use_rope)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from nanotron_b200.ops import native
+
+        qkv, out, lse, cu, cos, sin, positions = ctx.saved_tensors
+        n_heads, n_kv, head_dim, max_len, causal, scale, window, interleaved, use_rope = ctx.cfg
+        T = qkv.shape[0]
+        q = qkv[:, : n_heads * head_dim].view(T, n_heads, head_dim)
+        k = qkv[:, n_heads * head_dim : (n_heads + n_kv) * head_dim].view(T, n_kv, head_dim)
+        v = qkv[:, (n_heads + n_kv) * head_dim :].view(T, n_kv, head_dim)
+        dq, dk, dv = native.flash_attn_bwd(dout.contiguous(), q, k, v, out, lse, cu, cu, max_len, max_len, causal, scale, window)
+        if use_rope:
+            native.rope(dq, cos, sin, interleaved, inverse=True, inplace=True, positions=positions)
+            native.rope(dk, cos, sin, interleaved, inverse=True, inplace=True, positions=positions)
+        # dq is a view at offset 0 of the fused [T, Hq + 2 Hkv, D] gradient buffer
+        dqkv = torch.as_strided(dq, (T, (n_heads + 2 * n_kv) * head_dim), ((n_heads + 2 * n_kv) * head_dim, 1), storage_offset=dq.storage_offset())
+        return (dqkv,) + (None,) * 13
+
+
+def fused_qkv_attention_supported(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window) -> bool:
+    if not (qkv.is_cuda and _MODE != "torch" and _ATTN != "sdpa" and qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.is_contiguous()):
+        return False
+    from nanotron_b200.ops import native, native_attn
+
+    native.lib()
+    return native_attn._HAS["fwd"] and native_attn._HAS["bwd"] and n_heads % n_kv == 0
+
+
+def fused_qkv_attention(qkv, cos_table, sin_table, positions, n_heads, n_kv, head_dim, cu_seqlens, max_seqlen, causal=True, softmax_scale=None, window=None, interleaved=False, use_rope=True):
+    """qkv: [T, (Hq + 2 Hkv) * D] fresh output of the fused projection (it is rotated in place).  Returns [T, Hq, D]."""
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+    pos = positions.to(torch.int64).contiguous() if positions is not None else None
+    return _FusedQKVAttention.apply(qkv, cos_table, sin_table, pos, n_heads, n_kv, head_dim, cu_seqlens.to(torch.int32), max_seqlen, causal, scale, window, interleaved, use_rope)
 
 
 from nanotron_b200.ops import tp_fused  # noqa: E402,F401

@@ -170,6 +170,30 @@ NTB_EXPORT int ntb_symm_barrier(const uint64_t* flag_ptrs, int me, int world, ui
   return ntb_check_launch();
 }
 
+namespace {
+// Spins (bounded) until the first `world` local flag words reached `epoch`.
+__global__ void symm_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, unsigned long long limit_ns, int* status) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  const uint64_t t0 = ptx::globaltimer();
+  while (true) {
+    if (static_cast<int32_t>(ld_acquire_sys_u32(flags + t) - epoch) >= 0) break;
+    if (ptx::globaltimer() - t0 > limit_ns) {
+      if (status) atomicExch(status, NTB_ERR_TIMEOUT);
+      break;
+    }
+    __nanosleep(200);
+  }
+  __threadfence_system();
+}
+}  // namespace
+
+NTB_EXPORT int ntb_symm_wait(const uint32_t* flags, int world, uint32_t epoch, unsigned long long limit_ns, int* status, cudaStream_t stream) {
+  if (world < 1 || world > 32) return NTB_ERR_ARG;
+  symm_wait_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, limit_ns, status);
+  return ntb_check_launch();
+}
+
 NTB_EXPORT int ntb_dp_num_partials() { return 148 * 4; }
 
 // sumsq_partial: fp32 [ntb_dp_num_partials()]; sumsq_out: fp32 [1] receives the sum of squares of the reduced shard.

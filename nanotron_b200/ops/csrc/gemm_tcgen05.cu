@@ -37,7 +37,29 @@ constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACCUM = 2 };
+enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACCUM = 2, OUT_PEER_BF16 = 3 };
+
+// Tensor-parallel fusion hooks (all disabled when world == 0):
+//  * all-gather -> GEMM: the A operand is a gathered buffer of `world` row blocks of `ag_rows` rows that peers fill with
+//    plain stores; block r is valid once `ag_flags[r] >= epoch`.  The TMA producer polls that word (bounded) before its
+//    first load from a block, and row blocks are visited starting with this rank's own, so the GEMM on blocks that
+//    already arrived overlaps the NVLink transfer of the others.
+//  * GEMM -> reduce-scatter (OUT_PEER_BF16): the epilogue stores each bf16 tile straight into the staging buffer of the
+//    rank that owns those rows (`rs_dst[owner] + me * rs_slot_elems`), visiting row blocks starting with the next rank's.
+//    The last CTA to finish publishes `epoch` in every owner's `rs_flags[me]`; owners then sum the `world` slots.
+constexpr int TP_MAX = 8;
+struct TpFuse {
+  int world = 0, me = 0;
+  uint32_t epoch = 0;
+  int m_rot = 0;                      // tile-row rotation (in 128-row tiles)
+  const uint32_t* ag_flags = nullptr; // local flag words [world]
+  int ag_rows = 0;                    // rows per gathered block
+  void* rs_dst[TP_MAX] = {};          // per-owner staging base (bf16), slot-major [world][rs_rows][N]
+  uint32_t* rs_flags[TP_MAX] = {};    // per-owner flag words [world]
+  int rs_rows = 0;                    // rows per owner
+  long long rs_slot_elems = 0;
+  unsigned int* done_counter = nullptr;  // local counter, zero before launch
+};
 
 struct TileCoord {
   int m_blk, n_blk;
@@ -58,7 +80,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                    int M, int N, int K, int* __restrict__ status) {
+                    int M, int N, int K, int* __restrict__ status, const __grid_constant__ TpFuse fuse) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
@@ -106,8 +128,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (ptx::elect_one()) {
       int it = 0;
       bool ok = true;
+      uint32_t ag_ready = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
+        if (fuse.ag_flags != nullptr) {
+          // rows [m_blk*128, +128) may span two gathered blocks when ag_rows is not a multiple of 128
+          const int first = (tc.m_blk * BLOCK_M) / fuse.ag_rows;
+          const int last = min(fuse.world - 1, (min(M, (tc.m_blk + 1) * BLOCK_M) - 1) / fuse.ag_rows);
+          for (int src = first; src <= last && ok; src++) {
+            if (ag_ready & (1u << src)) continue;
+            const uint64_t t0 = ptx::globaltimer();
+            while (true) {
+              uint32_t v;
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(fuse.ag_flags + src) : "memory");
+              if (static_cast<int32_t>(v - fuse.epoch) >= 0) { ag_ready |= 1u << src; break; }
+              if (*abort_flag || ptx::globaltimer() - t0 > NTB_WAIT_LIMIT_NS) { *abort_flag = 1; ok = false; break; }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) break;
+          // data written by peers with generic stores must be visible to the async (TMA) proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -166,20 +209,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* my_epi = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
-    constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;  // 128 bytes of output per row
+    constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;  // 128 bytes of output per row (peer mode: 32 columns from registers)
     constexpr int CHUNKS = BLOCK_N / CHUNK_COLS;
     int tile_it = 0, buf = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_it++) {
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
       const int row0 = tc.m_blk * BLOCK_M + q * 32;
+      if (OUT == OUT_PEER_BF16) {
+        // one thread = one output row: 32 fp32 accumulators -> 32 bf16 -> four 16-byte stores into the owner's staging slot.
+        // Every lane issues the (warp-aligned) TMEM loads; only the stores are predicated.
+        const int row = row0 + lane;
+        const bool row_ok = row < M;
+        const int owner = row_ok ? row / fuse.rs_rows : 0;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(fuse.rs_dst[owner]) + static_cast<long long>(fuse.me) * fuse.rs_slot_elems +
+                             static_cast<long long>(row - owner * fuse.rs_rows) * N + tc.n_blk * BLOCK_N;
 #pragma unroll 1
-      for (int c = 0; c < CHUNKS; c++) {
+        for (int c = 0; c < BLOCK_N / 32; c++) {
+          uint32_t r0[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r0);
+          ptx::tmem_ld_wait();
+          if (row_ok && tc.n_blk * BLOCK_N + c * 32 < N) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              uint4 pk;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 0]), __uint_as_float(r0[j * 8 + 1]));
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2]), __uint_as_float(r0[j * 8 + 3]));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 4]), __uint_as_float(r0[j * 8 + 5]));
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 6]), __uint_as_float(r0[j * 8 + 7]));
+              pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+              pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = pk;
+            }
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < (OUT == OUT_PEER_BF16 ? 0 : CHUNKS); c++) {
         uint8_t* stage_buf = my_epi + buf * EPI_BUF_BYTES;
         // the TMA store that last read this staging buffer must be done reading it
         if (lane == 0) ptx::tma_wait_group_read<1>();
@@ -241,6 +313,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (OUT == OUT_PEER_BF16 && fuse.done_counter != nullptr && threadIdx.x == 0) {
+    // all stores of this CTA (made by the epilogue warps before the barrier above) become visible system-wide, then the
+    // last CTA to get here tells every owner that this rank's partial sums are complete
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(fuse.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < fuse.world; r++)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(fuse.rs_flags[r] + fuse.me), "r"(fuse.epoch) : "memory");
+      *fuse.done_counter = 0;
+    }
+  }
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, NTB_ERR_TIMEOUT);
 }
 
@@ -289,7 +373,8 @@ bool make_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t
 }
 
 template <bool A_MN, bool B_MN, int OUT>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
+           const TpFuse& fuse = TpFuse()) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT>;
   static bool configured = false;
   if (!configured) {
@@ -298,7 +383,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, 
   }
   const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status);
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status, fuse);
   return ntb_check_launch();
 }
 
@@ -328,4 +413,158 @@ NTB_EXPORT int ntb_gemm_bf16(const void* a, const void* b, void* d, int M, int N
   NTB_GEMM_CASE(1, 0, 0) NTB_GEMM_CASE(1, 0, 1) NTB_GEMM_CASE(1, 0, 2)
 #undef NTB_GEMM_CASE
   return NTB_ERR_ARG;
+}
+
+
+// ---------------------------------------------------------------------------------------------- tensor-parallel fused entry points
+namespace {
+
+struct PushPeers {
+  void* dst[TP_MAX];
+  uint32_t* flags[TP_MAX];
+};
+
+// Copies this rank's block into slot `me` of every rank's gather buffer (16-byte peer stores), then the last CTA publishes
+// `epoch` in every rank's flag word `me`.
+__global__ void ag_push_kernel(const uint4* __restrict__ src, PushPeers peers, int me, int world, long long n16, long long slot16, uint32_t epoch,
+                               unsigned int* done_counter) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const uint4 v = src[i];
+    for (int k = 0; k < world; k++) {
+      const int r = (me + k) % world;
+      reinterpret_cast<uint4*>(peers.dst[r])[me * slot16 + i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < world; r++) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[r] + me), "r"(epoch) : "memory");
+      *done_counter = 0;
+    }
+  }
+}
+
+// out[i] = sum over slots (fixed order) of staging[slot][i], after every slot's flag reached `epoch`.
+__global__ void rs_reduce_kernel(const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __restrict__ out, const uint32_t* __restrict__ flags, int world,
+                                 long long n, long long slot_elems, uint32_t epoch, unsigned long long limit_ns, int* status) {
+  __shared__ int bad;
+  if (threadIdx.x == 0) {
+    bad = 0;
+    const uint64_t t0 = ptx::globaltimer();
+    for (int r = 0; r < world; r++) {
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+        if (static_cast<int32_t>(v - epoch) >= 0) break;
+        if (ptx::globaltimer() - t0 > limit_ns) { bad = 1; break; }
+        __nanosleep(100);
+      }
+      if (bad) break;
+    }
+  }
+  __syncthreads();
+  if (bad) {
+    if (threadIdx.x == 0 && status) atomicExch(status, NTB_ERR_TIMEOUT);
+    return;
+  }
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; r++) {
+      uint4 raw;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "l"(staging + r * slot_elems + i) : "memory");
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    Vec8<__nv_bfloat16> o;
+    o.from_float(acc);
+    o.store(out + i);
+  }
+}
+
+}  // namespace
+
+// Push this rank's [rows, K] bf16 block into slot `me` of every rank's gather buffer and raise flag `me` everywhere.
+NTB_EXPORT int ntb_tp_allgather_push(const void* src, const uint64_t* gather_ptrs, const uint64_t* flag_ptrs, int me, int world, long long elems,
+                                     uint32_t epoch, unsigned int* done_counter, cudaStream_t stream) {
+  if (world < 1 || world > TP_MAX || elems <= 0 || elems % 8 || (reinterpret_cast<uintptr_t>(src) & 15)) return NTB_ERR_ARG;
+  PushPeers peers;
+  for (int r = 0; r < TP_MAX; r++) {
+    peers.dst[r] = r < world ? reinterpret_cast<void*>(gather_ptrs[r]) : nullptr;
+    peers.flags[r] = r < world ? reinterpret_cast<uint32_t*>(flag_ptrs[r]) : nullptr;
+  }
+  const long long n16 = elems / 8;
+  int blocks = static_cast<int>((n16 + 255) / 256);
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  ag_push_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(src), peers, me, world, n16, n16, epoch, done_counter);
+  return ntb_check_launch();
+}
+
+// D = gathered_A @ B^T where gathered_A = [world * ag_rows, K] is filled by ntb_tp_allgather_push on every rank.
+NTB_EXPORT int ntb_gemm_bf16_ag(const void* a_gathered, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int b_mn,
+                                const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !get_encode() || world < 1 || world > TP_MAX || ag_rows % BLOCK_M) return NTB_ERR_ARG;
+  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) || ldd % 8) return NTB_ERR_ARG;
+  CUtensorMap ta, tb, td;
+  bool ok = make_map_kmajor(&ta, a_gathered, M, K, lda, BLOCK_M);
+  ok = ok && (b_mn ? make_map_mnmajor(&tb, b, N, K, ldb, BLOCK_N) : make_map_kmajor(&tb, b, N, K, ldb, BLOCK_N));
+  ok = ok && make_map_out(&td, d, M, N, ldd, false);
+  if (!ok) return NTB_ERR_ARG;
+  TpFuse f;
+  f.world = world;
+  f.me = me;
+  f.epoch = epoch;
+  f.ag_flags = ag_flags;
+  f.ag_rows = ag_rows;
+  f.m_rot = (me * ag_rows) / BLOCK_M;  // start with the rows this rank contributed itself
+  if (num_sms <= 0) num_sms = 148;
+  return b_mn ? launch<false, true, OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f) : launch<false, false, OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f);
+}
+
+// Partial product A @ B^T whose rows [r*rs_rows, (r+1)*rs_rows) are stored (bf16) into rank r's staging slot `me`.
+NTB_EXPORT int ntb_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const uint64_t* staging_ptrs,
+                                const uint64_t* flag_ptrs, int rs_rows, int me, int world, uint32_t epoch, unsigned int* done_counter, int* status, int num_sms,
+                                cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !get_encode() || world < 1 || world > TP_MAX || rs_rows * world != M || N % 32) return NTB_ERR_ARG;
+  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8))) return NTB_ERR_ARG;
+  CUtensorMap ta, tb, td;
+  bool ok = make_map_kmajor(&ta, a, M, K, lda, BLOCK_M);
+  ok = ok && (b_mn ? make_map_mnmajor(&tb, b, N, K, ldb, BLOCK_N) : make_map_kmajor(&tb, b, N, K, ldb, BLOCK_N));
+  if (!ok) return NTB_ERR_ARG;
+  td = ta;  // unused in this mode
+  TpFuse f;
+  f.world = world;
+  f.me = me;
+  f.epoch = epoch;
+  f.rs_rows = rs_rows;
+  f.rs_slot_elems = static_cast<long long>(rs_rows) * N;
+  for (int r = 0; r < world; r++) {
+    f.rs_dst[r] = reinterpret_cast<void*>(staging_ptrs[r]);
+    f.rs_flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  f.done_counter = done_counter;
+  const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
+  f.m_rot = ((((me + 1) % world) * rs_rows) / BLOCK_M) % tiles_m;  // the next rank's rows first, our own last
+  if (num_sms <= 0) num_sms = 148;
+  return b_mn ? launch<false, true, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f) : launch<false, false, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f);
+}
+
+// out[rs_rows, N] = sum of the `world` staging slots once every peer published `epoch`.
+NTB_EXPORT int ntb_tp_reduce_slots(const void* staging, void* out, const uint32_t* flags, int world, long long elems, uint32_t epoch,
+                                   unsigned long long limit_ns, int* status, cudaStream_t stream) {
+  if (world < 1 || world > TP_MAX || elems <= 0 || elems % 8) return NTB_ERR_ARG;
+  long long blocks = (elems / 8 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  rs_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(staging), reinterpret_cast<__nv_bfloat16*>(out), flags, world,
+                                                                       elems, elems, epoch, limit_ns, status);
+  return ntb_check_launch();
 }

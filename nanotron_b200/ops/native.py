@@ -59,6 +59,17 @@ def _declare(L):
         L.ntb_symm_barrier.argtypes = [c_void_p, c_int, c_int, c_uint32, c_ull, c_void_p, c_void_p]
         L.ntb_dp_reduce_scatter.restype = c_int
         L.ntb_dp_reduce_scatter.argtypes = [c_void_p, c_int, c_int, c_int64, c_int64, c_float, c_int, c_void_p, c_void_p, c_void_p]
+        L.ntb_symm_wait.restype = c_int
+        L.ntb_symm_wait.argtypes = [c_void_p, c_int, c_uint32, c_ull, c_void_p, c_void_p]
+        if hasattr(L, "ntb_gemm_bf16_ag"):
+            L.ntb_tp_allgather_push.restype = c_int
+            L.ntb_tp_allgather_push.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_uint32, c_void_p, c_void_p]
+            L.ntb_gemm_bf16_ag.restype = c_int
+            L.ntb_gemm_bf16_ag.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_int, c_void_p]
+            L.ntb_gemm_bf16_rs.restype = c_int
+            L.ntb_gemm_bf16_rs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p, c_int, c_void_p]
+            L.ntb_tp_reduce_slots.restype = c_int
+            L.ntb_tp_reduce_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.c_longlong, c_uint32, c_ull, c_void_p, c_void_p]
         L.ntb_dp_adamw_allgather.restype = c_int
         L.ntb_dp_adamw_allgather.argtypes = [c_void_p] * 5 + [c_int, c_int, c_int64, c_int64] + [c_void_p] * 3 + [c_int] + [c_float] * 5 + [c_void_p, c_void_p]
     for fn in ("ntb_norm_fwd", "ntb_norm_bwd", "ntb_rope", "ntb_swiglu_fwd", "ntb_swiglu_bwd", "ntb_ce_partials", "ntb_ce_backward", "ntb_adamw_flat", "ntb_sumsq"):

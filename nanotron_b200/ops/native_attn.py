@@ -18,7 +18,7 @@ def declare(L):
         L.ntb_flash_attn_fwd.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
     if _HAS["bwd"]:
         L.ntb_flash_attn_bwd.restype = c_int
-        L.ntb_flash_attn_bwd.argtypes = [c_void_p] * 13 + [c_int] * 6 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
+        L.ntb_flash_attn_bwd.argtypes = [c_void_p] * 13 + [c_int] * 7 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
 
 
 def _ok(t: torch.Tensor) -> bool:

@@ -110,36 +110,50 @@ class _TPLinear(torch.autograd.Function):
             grad_output = _all_gather_dim0(grad_output, group, buffer_name="allgather2")
         # (all_reduce forward -> identity backward)
         # ---- recover the full input if it was gathered in forward
+        fused_ok = ctx.async_comm and grad_output.is_cuda and tp > 1
         if pre == "all_gather" and tp > 1 and ctx.recompute_allgather:
             xs = saved_in.contiguous()
-            total = MemoryBuffer().get("allgather", (xs.shape[0] * tp, *xs.shape[1:]), dtype=xs.dtype, device=xs.device)
-            if ctx.async_comm:
-                handle = dist.all_gather_into_tensor(total, xs, group=group, async_op=True)
-            else:
-                dist.all_gather_into_tensor(total, xs, group=group)
+            total = None
+            if fused_ok:
+                g = ops.tp_fused.fused_all_gather(xs.reshape(-1, xs.shape[-1]), group)
+                if g is not None:
+                    total = g.view(xs.shape[0] * tp, *xs.shape[1:])
+            if total is None:
+                total = MemoryBuffer().get("allgather", (xs.shape[0] * tp, *xs.shape[1:]), dtype=xs.dtype, device=xs.device)
+                if ctx.async_comm:
+                    handle = dist.all_gather_into_tensor(total, xs, group=group, async_op=True)
+                else:
+                    dist.all_gather_into_tensor(total, xs, group=group)
         else:
             total = saved_in
         go2, _ = _flatten2d(grad_output)
         grad_input = grad_weight = grad_bias = None
         sub_handle = None
         if ctx.needs_input_grad[0]:
-            gi2 = ops.linear_dgrad(go2, weight)
-            gi = gi2.view(*grad_output.shape[:-1], weight.shape[1])
-            if tp > 1 and pre == "all_gather":
-                out_gi = torch.empty((gi.shape[0] // tp, *gi.shape[1:]), dtype=gi.dtype, device=gi.device)
-                if ctx.async_comm:
-                    sub_handle = dist.reduce_scatter_tensor(out_gi, gi, group=group, async_op=True)
-                else:
-                    dist.reduce_scatter_tensor(out_gi, gi, group=group)
-                grad_input = out_gi
-            elif tp > 1 and ctx.input_grad_reduce:
-                if ctx.async_comm:
-                    sub_handle = dist.all_reduce(gi, group=group, async_op=True)
-                else:
-                    dist.all_reduce(gi, group=group)
-                grad_input = gi
+            gi_fused = None
+            if fused_ok and pre == "all_gather":
+                # dgrad GEMM whose epilogue scatters the partial sums to their owners (GEMM -> reduce-scatter)
+                gi_fused = ops.tp_fused.fused_matmul_reduce_scatter(go2, weight, group, b_mn=True)
+            if gi_fused is not None:
+                grad_input = gi_fused.view(grad_output.shape[0] // tp, *grad_output.shape[1:-1], weight.shape[1])
             else:
-                grad_input = gi
+                gi2 = ops.linear_dgrad(go2, weight)
+                gi = gi2.view(*grad_output.shape[:-1], weight.shape[1])
+                if tp > 1 and pre == "all_gather":
+                    out_gi = torch.empty((gi.shape[0] // tp, *gi.shape[1:]), dtype=gi.dtype, device=gi.device)
+                    if ctx.async_comm:
+                        sub_handle = dist.reduce_scatter_tensor(out_gi, gi, group=group, async_op=True)
+                    else:
+                        dist.reduce_scatter_tensor(out_gi, gi, group=group)
+                    grad_input = out_gi
+                elif tp > 1 and ctx.input_grad_reduce:
+                    if ctx.async_comm:
+                        sub_handle = dist.all_reduce(gi, group=group, async_op=True)
+                    else:
+                        dist.all_reduce(gi, group=group)
+                    grad_input = gi
+                else:
+                    grad_input = gi
         if handle is not None:
             handle.wait()
         if weight.requires_grad or ctx.needs_input_grad[1]:

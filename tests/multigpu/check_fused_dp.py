@@ -1,0 +1,69 @@
+"""Run with torchrun on N >= 2 GPUs: the in-kernel NVLink data-parallel step (reduce-scatter + AdamW + all-gather over peer
+memory) must give the same loss curve and the same parameters as the NCCL path, with ZeRO-1 and with a replicated optimizer.
+
+    torchrun --nproc-per-node 2 --master-addr 127.0.0.1 tests/multigpu/check_fused_dp.py
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from helpers import dummy_dataloader, make_config, tiny_llama_config  # noqa: E402
+
+
+def run(fused: bool, zero: int, steps: int = 5):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.trainer import DistributedTrainer
+
+    world = int(os.environ["WORLD_SIZE"])
+    mc = tiny_llama_config(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=2, vocab_size=1024)
+    cfg = make_config(mc, dp=world, seq=128, mbs=2, steps=steps, dtype="bfloat16", zero=zero, lr=1e-3)
+    cfg.optimizer.fused_zero_comm = None if fused else False
+    torch.manual_seed(0)
+    t = DistributedTrainer(cfg)
+    assert (t.fused_dp is not None) == fused, f"fused path active={t.fused_dp is not None}, expected {fused}"
+    t.prepare_training()
+    dl = dummy_dataloader(t)
+    losses = []
+    for _ in range(steps):
+        _, loss, _ = t.training_step(dl)
+        t.iteration_step += 1
+        losses.append(float(loss))
+    if t.fused_dp is not None:
+        t.fused_dp.alloc.check()
+    params = torch.cat([p.detach().float().reshape(-1) for _, p in sorted(t.unwrapped_model.named_parameters())])
+    # replicas agree bit for bit
+    ref = params.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(ref, params), "data-parallel replicas diverged"
+    norm = float(t.grad_norm_unclipped) if t.grad_norm_unclipped is not None else None
+    return losses, params, norm
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    for zero in (1, 0):
+        base_losses, base_params, base_norm = run(fused=False, zero=zero)
+        fused_losses, fused_params, fused_norm = run(fused=True, zero=zero)
+        diff = (base_params - fused_params).abs().max().item()
+        if rank == 0:
+            print(f"zero={zero} nccl   losses {['%.4f' % l for l in base_losses]} grad_norm {base_norm}")
+            print(f"zero={zero} fused  losses {['%.4f' % l for l in fused_losses]} grad_norm {fused_norm}")
+            print(f"zero={zero} max |param diff| = {diff:.3e}")
+        assert all(abs(a - b) < 2e-2 for a, b in zip(base_losses, fused_losses)), (base_losses, fused_losses)
+        assert diff < 2e-2, diff
+        assert abs(base_norm - fused_norm) < 1e-2 * max(1.0, base_norm), (base_norm, fused_norm)
+    if rank == 0:
+        print("FUSED_DP_OK")
+    import torch.distributed as tdist
+
+    if tdist.is_initialized():
+        tdist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

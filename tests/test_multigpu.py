@@ -1,0 +1,28 @@
+"""Multi-GPU checks: each spawns ``torchrun`` on the GPUs of this machine and is skipped when there are fewer than two."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(script, nproc, port, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1", "--master-port", str(port), script]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_data_parallel_step_matches_nccl():
+    r = _torchrun("tests/multigpu/check_fused_dp.py", 2, 29731)
+    assert r.returncode == 0 and "FUSED_DP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tensor_parallel_linears_match_nccl():
+    r = _torchrun("tests/multigpu/check_fused_tp.py", 2, 29732)
+    assert r.returncode == 0 and "FUSED_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
