@@ -248,6 +248,26 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool 
     return out
 
 
+# ---------------------------------------------------------------------------- fp8
+def has_fp8_quantize() -> bool:
+    return hasattr(lib(), "ntb_fp8_quantize_1x128")
+
+
+def fp8_quantize_1x128(x: torch.Tensor, dtype: torch.dtype):
+    from nanotron_b200.fp8.quantize import FP8BlockTensor
+
+    rows, cols = x.shape
+    L = lib()
+    L.ntb_fp8_quantize_1x128.restype = c_int
+    L.ntb_fp8_quantize_1x128.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+    q = torch.empty((rows, cols), dtype=dtype, device=x.device)
+    scale = torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = L.ntb_fp8_quantize_1x128(x.data_ptr(), q.data_ptr(), scale.data_ptr(), rows, cols, int(dtype == torch.float8_e5m2), _stream(x))
+    _check(rc, "fp8_quantize_1x128")
+    return FP8BlockTensor(q, scale, (1, 128))
+
+
 # ---------------------------------------------------------------------------- GEMM / attention: see native_gemm / native_attn
 from nanotron_b200.ops.native_attn import flash_attn_bwd, flash_attn_fwd, flash_attn_supported  # noqa: E402,F401
 from nanotron_b200.ops.native_gemm import gemm_nn, gemm_nt, gemm_supported, gemm_tn, gemm_tn_accum_fp32  # noqa: E402,F401
