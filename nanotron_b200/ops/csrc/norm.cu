@@ -256,3 +256,53 @@ NTB_EXPORT int ntb_norm_bwd(int is_rms, int dtype, const void* dy, const void* p
   if (!is_rms && db_out) reduce_partials_kernel<<<(cols + 31) / 32, rb, 0, stream>>>(db_partial, db_out, nparts, cols);
   return ntb_check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate (declared in ntb_noalloc.h).
+//
+// The regular entry point above needs a caller-provided fp32 scratch of [partials, cols] for the per-CTA partial sums of
+// dW.  Some callers cannot provide one: library hooks invoked from inside another framework's allocator callbacks, and
+// runtimes that pre-plan every byte of device memory and forbid cudaMalloc (and torch's caching allocator) after start-up.  For them this variant keeps the
+// scratch in a fixed array that is part of the loaded library image: every GPU that loads the library holds
+// NTB_NOALLOC_PARTIALS * NTB_NOALLOC_MAX_COLS * 4 bytes (4.6 MiB) from load until exit.
+//
+// The array's name is only a host-side handle; the device address is looked up with cudaGetSymbolAddress the first time
+// the entry point is called on each device (with that device current).  That first call should therefore come before
+// any stream capture.  All calls share the one array: two calls whose kernels overlap on the GPU (different streams
+// without ordering) would mix their partial sums.  Nothing in the array has to start at zero: every launch rewrites
+// the rows it reads back.
+constexpr int NTB_NOALLOC_PARTIALS = 148;
+constexpr int NTB_NOALLOC_MAX_COLS = 8192;
+static __device__ __align__(256) float g_noalloc_dw_partials[NTB_NOALLOC_PARTIALS * NTB_NOALLOC_MAX_COLS];
+static float* g_noalloc_dw_ptr[64] = {};
+
+NTB_EXPORT int ntb_rmsnorm_bwd_noalloc_max_cols() { return NTB_NOALLOC_MAX_COLS; }
+
+NTB_EXPORT int ntb_rmsnorm_bwd_noalloc(int dtype, const void* dy, const void* pre, const void* w, const float* rstd, const void* dres, void* dx, float* dw_out,
+                                       int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0) return NTB_ERR_ARG;
+  if (cols > NTB_NOALLOC_MAX_COLS) return NTB_ERR_ARG;  // larger rows do not fit the built-in scratch: use ntb_norm_bwd
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NTB_ERR_LAUNCH;
+  if (g_noalloc_dw_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partials) != cudaSuccess || p == nullptr) return NTB_ERR_LAUNCH;
+    g_noalloc_dw_ptr[dev] = p;
+  }
+  float* partial = g_noalloc_dw_ptr[dev];
+  const int nparts = rows < NTB_NOALLOC_PARTIALS ? rows : NTB_NOALLOC_PARTIALS;
+  const int iters = (cols + NORM_THREADS * 8 - 1) / (NORM_THREADS * 8);
+#define NTB_NORM_BWD_NA(IT) \
+  norm_bwd_kernel<T, true, IT><<<nparts, NORM_THREADS, 0, stream>>>((const T*)dy, (const T*)pre, (const T*)w, nullptr, rstd, (const T*)dres, (T*)dx, partial, nullptr, rows, cols);
+  NTB_DISPATCH_DTYPE(dtype, {
+    if (iters <= 1) { NTB_NORM_BWD_NA(1) }
+    else if (iters <= 2) { NTB_NORM_BWD_NA(2) }
+    else { NTB_NORM_BWD_NA(4) }
+  });
+#undef NTB_NORM_BWD_NA
+  int rc = ntb_check_launch();
+  if (rc) return rc;
+  dim3 rb(32, 8);
+  reduce_partials_kernel<<<(cols + 31) / 32, rb, 0, stream>>>(partial, dw_out, nparts, cols);
+  return ntb_check_launch();
+}
