@@ -44,7 +44,38 @@ class Router(nn.Module):
         return top_p, top_i.to(torch.int32), probs
 
     def forward(self, x: torch.Tensor):
+        if x.is_cuda:
+            from nanotron_b200 import ops
+            from nanotron_b200.ops import native
+
+            if ops.get_mode() != "torch" and native.moe_router_supported(x, self.weight, self.num_experts_per_token):
+                return _FusedRouter.apply(x, self.weight, self.num_experts_per_token)
         return self.routing(self.gating(x))
+
+
+class _FusedRouter(torch.autograd.Function):
+    """Router forward as one kernel (fp32 logits, softmax, top-k, histogram); backward is the softmax Jacobian applied to
+    the gradients that reach the selected probabilities and the full distribution (auxiliary loss)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, k):
+        from nanotron_b200.ops import native
+
+        top_p, top_i, probs, counts = native.moe_router_fwd(x, weight, k)
+        ctx.save_for_backward(x, weight, probs, top_i)
+        ctx.mark_non_differentiable(top_i)
+        return top_p, top_i, probs
+
+    @staticmethod
+    def backward(ctx, d_top_p, _d_top_i, d_probs):
+        x, weight, probs, top_i = ctx.saved_tensors
+        d = d_probs.clone() if d_probs is not None else torch.zeros_like(probs)
+        if d_top_p is not None:
+            d.scatter_add_(1, top_i.long(), d_top_p.float())
+        dlogits = probs * (d - (d * probs).sum(-1, keepdim=True))
+        dw = dlogits.t() @ x.float()
+        dx = (dlogits @ weight).to(x.dtype)
+        return dx, dw, None
 
 
 def grouped_mlp_reference(x_sorted, counts, w_gate_up, w_down):

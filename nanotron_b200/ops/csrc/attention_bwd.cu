@@ -308,18 +308,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (ok && n_steps > 0 && ptx::mbar_wait(mma_done, (n_steps - 1) & 1, abort_flag)) {
       ptx::tc_fence_after();
       flush_dq(prev_h, prev_q0);
-      // dK, dV rows of this key
-      if (key_valid) {
-        const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
+      // dK, dV rows of this key.  Every lane issues the warp-aligned TMEM loads; only the stores depend on key_valid.
+      const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
 #pragma unroll 1
-        for (int which = 0; which < 2; which++) {
-          __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
-          const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
+      for (int which = 0; which < 2; which++) {
+        __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
+        const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
 #pragma unroll 1
-          for (int c = 0; c < 4; c++) {
-            uint32_t v[32];
-            ptx::tmem_ld_32x32(src + c * 32, v);
-            ptx::tmem_ld_wait();
+        for (int c = 0; c < 4; c++) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(src + c * 32, v);
+          ptx::tmem_ld_wait();
+          if (key_valid) {
 #pragma unroll
             for (int u = 0; u < 4; u++) {
               uint4 pk;

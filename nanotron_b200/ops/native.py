@@ -248,6 +248,29 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool 
     return out
 
 
+# ---------------------------------------------------------------------------- MoE router
+def moe_router_supported(x: torch.Tensor, weight: torch.Tensor, k: int) -> bool:
+    E = weight.shape[0]
+    return x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and x.is_contiguous() and weight.is_contiguous() and E % 16 == 0 and E <= 128 and (16 * E) % 256 == 0 and hasattr(lib(), "ntb_moe_router_fwd")
+
+
+def moe_router_fwd(x: torch.Tensor, weight: torch.Tensor, k: int):
+    """Returns (top_p [T,k] fp32, top_i [T,k] int32, probs [T,E] fp32, counts [E] int32)."""
+    T, h = x.shape
+    E = weight.shape[0]
+    L = lib()
+    L.ntb_moe_router_fwd.restype = c_int
+    L.ntb_moe_router_fwd.argtypes = [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
+    probs = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    top_p = torch.empty((T, k), dtype=torch.float32, device=x.device)
+    top_i = torch.empty((T, k), dtype=torch.int32, device=x.device)
+    counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = L.ntb_moe_router_fwd(x.data_ptr(), weight.data_ptr(), probs.data_ptr(), top_p.data_ptr(), top_i.data_ptr(), counts.data_ptr(), T, h, E, k, _stream(x))
+    _check(rc, "moe_router_fwd")
+    return top_p, top_i, probs, counts
+
+
 # ---------------------------------------------------------------------------- fp8
 def has_fp8_quantize() -> bool:
     return hasattr(lib(), "ntb_fp8_quantize_1x128")

@@ -182,3 +182,21 @@ def test_sumsq():
     xa = torch.empty(1_000_004, device=DEV)[:1_000_003].copy_(x)
     got = native.sumsq(xa)
     _close(got.squeeze(), x.double().pow(2).sum().float(), atol=0, rtol=1e-4, what="sumsq")
+
+
+@pytest.mark.parametrize("T,h,E,k", [(50, 256, 16, 2), (1000, 2048, 64, 4), (33, 512, 128, 8)])
+def test_moe_router_kernel(T, h, E, k):
+    from nanotron_b200.ops import native
+
+    torch.manual_seed(7)
+    x = torch.randn(T, h, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(E, h, device=DEV) * 0.05
+    top_p, top_i, probs, counts = native.moe_router_fwd(x, w, k)
+    exp_probs = torch.softmax(x.float() @ w.t(), dim=-1)
+    _close(probs, exp_probs, atol=1e-5, rtol=1e-4, what="probs")
+    exp_p, exp_i = torch.topk(exp_probs, k, dim=-1)
+    _close(top_p, exp_p, atol=1e-5, rtol=1e-4, what="top probs")
+    # ties aside, the same experts are chosen
+    assert (top_i.long() == exp_i).float().mean() > 0.999
+    assert int(counts.sum()) == T * k
+    assert torch.equal(counts.long(), torch.bincount(top_i.reshape(-1).long(), minlength=E))
