@@ -120,7 +120,10 @@ def get_context(group) -> Optional[TPFusedContext]:
 
             if ENABLED and ops.get_mode() != "torch" and group.size() <= 8 and symm.is_available(group):
                 ctx = TPFusedContext(group)
-        except Exception:  # symmetric memory not usable for this group (e.g. spans nodes)
+        except Exception as e:  # symmetric memory not usable for this group (e.g. spans nodes)
+            import warnings
+
+            warnings.warn(f"fused tensor-parallel kernels disabled for this group, using NCCL: {type(e).__name__}: {e}")
             ctx = None
         _CONTEXTS[key] = ctx
     return _CONTEXTS[key]

@@ -27,7 +27,9 @@ def is_available(group) -> bool:
     if not torch.cuda.is_available() or dist.get_backend(group) != "nccl":
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+
+        importlib.import_module("torch.distributed._symmetric_memory")
     except ImportError:
         return False
     from nanotron_b200.ops import native

@@ -45,6 +45,9 @@ def check_ops(ctx):
             c = tp_fused.get_context(ctx.tp_pg)
             assert c is not None, "fused context was not created"
             c.alloc.check()
+            assert c.ag_calls >= 2 and c.rs_calls >= 2, (c.ag_calls, c.rs_calls)  # forward + backward of each linear went through the fused kernels
+            if rank == 0:
+                print(f"  fused kernel calls: all-gather(+GEMM) {c.ag_calls}, GEMM+reduce-scatter {c.rs_calls}")
     names = ["column out", "row out", "dx", "dW column", "dW row"]
     for n, a, b in zip(names, results[True], results[False]):
         e = rel(a, b)
@@ -71,6 +74,9 @@ def train(fused: bool, steps=4):
         _, loss, _ = t.training_step(dl)
         t.iteration_step += 1
         losses.append(float(loss))
+    if fused:
+        c = tp_fused.get_context(t.parallel_context.tp_pg)
+        assert c is not None and c.ag_calls > 0 and c.rs_calls > 0, "training did not go through the fused tensor-parallel kernels"
     return losses, t.parallel_context
 
 
