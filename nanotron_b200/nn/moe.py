@@ -24,6 +24,9 @@ from nanotron_b200.parallel.parameters import NanotronParameter
 from nanotron_b200.parallel.sharded_parameters import SplitConfig, create_sharded_parameter_from_config
 
 
+FUSED_EXPERTS = True  # tests switch this off to compare the kernels with the PyTorch dispatch / grouped-GEMM path
+
+
 class Router(nn.Module):
     """fp32 linear scorer h -> E; returns (top-k probs [T,k], top-k expert ids int32 [T,k], full probs [T,E])."""
 
@@ -43,14 +46,20 @@ class Router(nn.Module):
         top_p, top_i = torch.topk(probs, k=self.num_experts_per_token, dim=-1)
         return top_p, top_i.to(torch.int32), probs
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor, return_counts: bool = False):
+        """With ``return_counts`` a fourth value is returned: int32 [E] assignments per expert (computed by the fused
+        kernel on CUDA, by ``bincount`` otherwise)."""
         if x.is_cuda:
             from nanotron_b200 import ops
             from nanotron_b200.ops import native
 
             if ops.get_mode() != "torch" and native.moe_router_supported(x, self.weight, self.num_experts_per_token):
-                return _FusedRouter.apply(x, self.weight, self.num_experts_per_token)
-        return self.routing(self.gating(x))
+                top_p, top_i, probs, counts = _FusedRouter.apply(x, self.weight, self.num_experts_per_token)
+                return (top_p, top_i, probs, counts) if return_counts else (top_p, top_i, probs)
+        top_p, top_i, probs = self.routing(self.gating(x))
+        if return_counts:
+            return top_p, top_i, probs, torch.bincount(top_i.reshape(-1).long(), minlength=self.num_experts).to(torch.int32)
+        return top_p, top_i, probs
 
 
 class _FusedRouter(torch.autograd.Function):
@@ -63,11 +72,11 @@ class _FusedRouter(torch.autograd.Function):
 
         top_p, top_i, probs, counts = native.moe_router_fwd(x, weight, k)
         ctx.save_for_backward(x, weight, probs, top_i)
-        ctx.mark_non_differentiable(top_i)
-        return top_p, top_i, probs
+        ctx.mark_non_differentiable(top_i, counts)
+        return top_p, top_i, probs, counts
 
     @staticmethod
-    def backward(ctx, d_top_p, _d_top_i, d_probs):
+    def backward(ctx, d_top_p, _d_top_i, d_probs, _d_counts):
         x, weight, probs, top_i = ctx.saved_tensors
         d = d_probs.clone() if d_probs is not None else torch.zeros_like(probs)
         if d_top_p is not None:
@@ -192,10 +201,25 @@ class Qwen2MoELayer(nn.Module):
         out.index_add_(0, token_of, y_sorted * w.unsqueeze(-1))
         return out, counts
 
+    def _fused_path(self, x: torch.Tensor) -> bool:
+        if not x.is_cuda:
+            return False
+        from nanotron_b200 import ops
+        from nanotron_b200.ops import moe_fused
+
+        if ops.get_mode() == "torch" or not FUSED_EXPERTS:
+            return False
+        return moe_fused.supported(x, self.experts.merged_gate_up_proj, self.experts.merged_down_proj, self.num_experts, self.top_k, self.ep_pg)
+
     def _core_forward(self, hidden_states: torch.Tensor):
         x = hidden_states
-        top_p, top_i, probs = self.router(x)
-        out, counts = self._dispatch_compute_combine(x, top_p, top_i)
+        top_p, top_i, probs, counts = self.router(x, return_counts=True)
+        if self._fused_path(x):
+            from nanotron_b200.ops import moe_fused
+
+            out = moe_fused.fused_moe_experts(x, top_p, top_i, counts, self.experts.merged_gate_up_proj, self.experts.merged_down_proj, self.ep_pg)
+        else:
+            out, counts = self._dispatch_compute_combine(x, top_p, top_i)
         # load-balance auxiliary loss: E * sum_e f_e * P_e
         f = counts.to(torch.float32) / max(1, top_i.numel())
         P = probs.mean(dim=0)

@@ -126,12 +126,69 @@ def bench_elementwise():
         print(f"{name:46s} {ms:8.3f} ms  {gbs:8.1f} GB/s  {gbs / bw:5.2f} of measured copy bandwidth", flush=True)
 
 
+def bench_moe():
+    """Grouped expert GEMMs (tcgen05, device-side offsets) against the library grouped GEMM, and the dispatch / combine
+    kernels against the copy-bandwidth roofline; 8192 tokens, top-4 of 64 experts, h = 2048, expert width 1408."""
+    from nanotron_b200.ops import moe_fused, native
+
+    native.lib()
+    pk = _peaks()
+    T, E, k, h, inter = 8192, 64, 4, 2048, 1408
+    torch.manual_seed(0)
+    probs = torch.softmax(torch.randn(T, E, device="cuda"), -1)
+    top_p, top_i = torch.topk(probs, k, dim=-1)
+    top_p, top_i = top_p.float().contiguous(), top_i.to(torch.int32).contiguous()
+    counts = torch.bincount(top_i.reshape(-1), minlength=E).to(torch.int32)
+    ctx = moe_fused.get_context(None, h, T, k, E)
+    plan = ctx.make_plan(counts, top_i)
+    x = torch.randn(T, h, device="cuda", dtype=torch.bfloat16)
+    w1 = (torch.randn(E, h, 2 * inter, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(E, inter, h, device="cuda") * 0.02).to(torch.bfloat16)
+    cap = ctx.cap_rows
+    rows = T * k
+    ms = time_fn(lambda: ctx.make_plan(counts, top_i))
+    print(f"plan + rank (T*k = {rows})                       {ms:8.3f} ms", flush=True)
+    ms = time_fn(lambda: ctx.dispatch(x, top_i, plan, None, zero_pad=True))
+    gbs = (T * h * 2 + rows * h * 2) / ms / 1e6
+    print(f"dispatch (read T rows, write T*k rows)           {ms:8.3f} ms  {gbs:8.1f} GB/s  {gbs / pk['hbm_gbs']:5.2f} of measured copy bandwidth", flush=True)
+    xp = ctx.recv.tensor.view(cap, h).clone()
+    ctx.ybuf.tensor.copy_(ctx.recv.tensor)
+    ms = time_fn(lambda: ctx.combine(top_i, plan, top_p, T, False))
+    gbs = (T * h * 2 + rows * h * 2) / ms / 1e6
+    print(f"combine (read T*k rows, write T rows)            {ms:8.3f} ms  {gbs:8.1f} GB/s  {gbs / pk['hbm_gbs']:5.2f} of measured copy bandwidth", flush=True)
+    f1 = 2.0 * rows * h * 2 * inter
+    ms = time_fn(lambda: ctx.grouped(xp, w1, True, plan))
+    print(f"gate_up grouped tcgen05 [{rows}x{h}]x[{h}x{2 * inter}]  {ms:8.3f} ms  {f1 / ms / 1e9:7.1f} TFLOP/s  {f1 / ms / 1e9 / pk['bf16_tflops']:5.2f} of measured peak (useful rows)", flush=True)
+    # library path: rows grouped without padding
+    order = torch.argsort(top_i.reshape(-1).long(), stable=True)
+    xs = x.index_select(0, order // k)
+    offs = torch.cumsum(counts, 0).to(torch.int32)
+    if hasattr(torch, "_grouped_mm"):
+        ms = time_fn(lambda: torch._grouped_mm(xs, w1, offs=offs))
+        print(f"gate_up grouped library                          {ms:8.3f} ms  {f1 / ms / 1e9:7.1f} TFLOP/s", flush=True)
+    gu = ctx.grouped(xp, w1, True, plan)
+    a = native.swiglu_fwd(gu)
+    f2 = 2.0 * rows * inter * h
+    ms = time_fn(lambda: ctx.grouped(a, w2, True, plan))
+    print(f"down grouped tcgen05                             {ms:8.3f} ms  {f2 / ms / 1e9:7.1f} TFLOP/s  {f2 / ms / 1e9 / pk['bf16_tflops']:5.2f} of measured peak", flush=True)
+    dy = torch.randn(cap, h, device="cuda", dtype=torch.bfloat16)
+    ms = time_fn(lambda: ctx.grouped(dy, w2, False, plan))
+    print(f"down dgrad grouped tcgen05                       {ms:8.3f} ms  {f2 / ms / 1e9:7.1f} TFLOP/s  {f2 / ms / 1e9 / pk['bf16_tflops']:5.2f} of measured peak", flush=True)
+    w2.main_grad = torch.zeros(E, inter, h, device="cuda", dtype=torch.float32)
+    ms = time_fn(lambda: ctx.grouped_wgrad(a, dy, w2, plan))
+    print(f"down wgrad grouped tcgen05 (+= fp32)             {ms:8.3f} ms  {f2 / ms / 1e9:7.1f} TFLOP/s  {f2 / ms / 1e9 / pk['bf16_tflops']:5.2f} of measured peak", flush=True)
+    torch.cuda.synchronize()
+    ctx.check()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm(small="--small" in sys.argv)
     elif what == "elementwise":
         bench_elementwise()
+    elif what == "moe":
+        bench_moe()
     elif what == "attention":
         from nanotron_b200.ops.bench_attention import main
 

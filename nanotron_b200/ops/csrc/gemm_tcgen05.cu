@@ -65,6 +65,24 @@ struct TileCoord {
   int m_blk, n_blk;
 };
 
+// Grouped (mixture-of-experts) products.  Token rows live in a padded layout: expert e owns rows [seg_off[e], seg_off[e+1]),
+// every offset a multiple of 128, so a 128-row block never mixes experts and the reduction range of a weight gradient is a
+// whole number of 64-row k-blocks.  Offsets, the block -> expert table and the number of used blocks are DEVICE data
+// (written by the dispatch kernels), so no launch parameter depends on the routing.
+//   GROUP 1 (forward / dgrad): D[rows, N] = A[rows, K] x B[e(row block)]; blocks at or beyond *num_m_tiles are skipped.
+//   GROUP 2 (wgrad):           D[e][M, N] = sum over the rows r of expert e of A[r, m] * B[r, n]  (both operands MN-major).
+struct GroupArgs {
+  const int* tile_expert = nullptr;  // GROUP 1: expert of each 128-row block
+  const int* num_m_tiles = nullptr;  // GROUP 1: number of used 128-row blocks
+  const int* seg_off = nullptr;      // GROUP 2: [E + 1] padded row offsets
+  int E = 0;
+};
+
+struct Tile {
+  int m_blk, n_blk, e, kb0, kbs;
+  bool skip;
+};
+
 // Tiles are visited in column-major order inside bands of 8 tile-rows so that CTAs running at the same time share B
 // tiles (and a few A tiles) through L2.
 __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n) {
@@ -77,10 +95,39 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
   return {first_m + r % rows, r / rows};
 }
 
-template <bool A_MN, bool B_MN, int OUT>
+template <int GROUP>
+__device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int k_blocks, const TpFuse& fuse, const GroupArgs& grp) {
+  Tile r;
+  if (GROUP == 2) {
+    const int per = tiles_m * tiles_n;
+    r.e = t / per;
+    const TileCoord tc = tile_coord(t - r.e * per, tiles_m, tiles_n);
+    r.m_blk = tc.m_blk;
+    r.n_blk = tc.n_blk;
+    const int lo = __ldg(grp.seg_off + r.e), hi = __ldg(grp.seg_off + r.e + 1);
+    r.kb0 = lo / BLOCK_K;
+    r.kbs = (hi - lo) / BLOCK_K;
+    r.skip = r.kbs <= 0;
+  } else {
+    const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+    r.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
+    r.n_blk = tc.n_blk;
+    r.kb0 = 0;
+    r.kbs = k_blocks;
+    r.e = 0;
+    r.skip = false;
+    if (GROUP == 1) {
+      r.skip = r.m_blk >= __ldg(grp.num_m_tiles);
+      if (!r.skip) r.e = __ldg(grp.tile_expert + r.m_blk);
+    }
+  }
+  return r;
+}
+
+template <bool A_MN, bool B_MN, int OUT, int GROUP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                    int M, int N, int K, int* __restrict__ status, const __grid_constant__ TpFuse fuse) {
+                    int M, int N, int K, int* __restrict__ status, const __grid_constant__ TpFuse fuse, const __grid_constant__ GroupArgs grp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
@@ -96,7 +143,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int lane = threadIdx.x & 31;
   const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
   const int tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * (GROUP == 2 ? grp.E : 1);
   const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
 
   if (threadIdx.x == 0) {
@@ -130,8 +177,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       uint32_t ag_ready = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-        tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
+        const Tile tc = decode_tile<GROUP>(t, tiles_m, tiles_n, k_blocks, fuse, grp);
+        if (tc.skip) continue;
         if (fuse.ag_flags != nullptr) {
           // rows [m_blk*128, +128) may span two gathered blocks when ag_rows is not a multiple of 128
           const int first = (tc.m_blk * BLOCK_M) / fuse.ag_rows;
@@ -151,17 +198,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // data written by peers with generic stores must be visible to the async (TMA) proxy
           asm volatile("fence.proxy.async.global;" ::: "memory");
         }
-        for (int kb = 0; kb < k_blocks; kb++, it++) {
+        for (int kb = 0; kb < tc.kbs; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
+          const int kx = (tc.kb0 + kb) * BLOCK_K;
           ptx::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          if (A_MN) ptx::tma_load_3d(sa, &tmap_a, &full_bar[s], 0, kb * BLOCK_K, tc.m_blk * (BLOCK_M / 64));
-          else      ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BLOCK_K, tc.m_blk * BLOCK_M);
-          if (B_MN) ptx::tma_load_3d(sb, &tmap_b, &full_bar[s], 0, kb * BLOCK_K, tc.n_blk * (BLOCK_N / 64));
-          else      ptx::tma_load_2d(sb, &tmap_b, &full_bar[s], kb * BLOCK_K, tc.n_blk * BLOCK_N);
+          if (A_MN) ptx::tma_load_3d(sa, &tmap_a, &full_bar[s], 0, kx, tc.m_blk * (BLOCK_M / 64));
+          else      ptx::tma_load_2d(sa, &tmap_a, &full_bar[s], kx, tc.m_blk * BLOCK_M);
+          if (GROUP == 1) {  // the B operand of this row block is the weight of its expert (outermost map dimension)
+            if (B_MN) ptx::tma_load_4d(sb, &tmap_b, &full_bar[s], 0, kx, tc.n_blk * (BLOCK_N / 64), tc.e);
+            else      ptx::tma_load_3d(sb, &tmap_b, &full_bar[s], kx, tc.n_blk * BLOCK_N, tc.e);
+          } else {
+            if (B_MN) ptx::tma_load_3d(sb, &tmap_b, &full_bar[s], 0, kx, tc.n_blk * (BLOCK_N / 64));
+            else      ptx::tma_load_2d(sb, &tmap_b, &full_bar[s], kx, tc.n_blk * BLOCK_N);
+          }
         }
       }
       if (!ok) {
@@ -181,13 +234,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       constexpr uint32_t idesc = ptx::make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
       int it = 0, tile_it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_it++) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Tile tc = decode_tile<GROUP>(t, tiles_m, tiles_n, k_blocks, fuse, grp);
+        if (tc.skip) continue;
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
+        tile_it++;
         if (!ptx::mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < k_blocks; kb++, it++) {
+        for (int kb = 0; kb < tc.kbs; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
@@ -213,11 +269,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int CHUNKS = BLOCK_N / CHUNK_COLS;
     int tile_it = 0, buf = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_it++) {
-      TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-      tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const Tile tc = decode_tile<GROUP>(t, tiles_m, tiles_n, k_blocks, fuse, grp);
+      if (tc.skip) continue;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
+      tile_it++;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
@@ -291,8 +348,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0) {
           const int x = tc.n_blk * BLOCK_N + c * CHUNK_COLS;
           if (x < N && row0 < M) {
-            if (OUT == OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
-            else ptx::tma_store_2d(&tmap_d, stage_buf, x, row0);
+            if (GROUP == 2) {  // one weight-gradient matrix per expert: outermost map dimension
+              if (OUT == OUT_F32_ACCUM) ptx::tma_reduce_add_3d(&tmap_d, stage_buf, x, row0, tc.e);
+              else ptx::tma_store_3d(&tmap_d, stage_buf, x, row0, tc.e);
+            } else {
+              if (OUT == OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
+              else ptx::tma_store_2d(&tmap_d, stage_buf, x, row0);
+            }
           }
           ptx::tma_commit_group();
         }
@@ -372,18 +434,18 @@ bool make_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int OUT>
+template <bool A_MN, bool B_MN, int OUT, int GROUP = 0>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
-           const TpFuse& fuse = TpFuse()) {
-  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT>;
+           const TpFuse& fuse = TpFuse(), const GroupArgs& grp = GroupArgs()) {
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT, GROUP>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return NTB_ERR_LAUNCH;
     configured = true;
   }
-  const int tiles = ((M + BLOCK_M - 1) / BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N);
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status, fuse);
+  const long long tiles = static_cast<long long>((M + BLOCK_M - 1) / BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N) * (GROUP == 2 ? grp.E : 1);
+  const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status, fuse, grp);
   return ntb_check_launch();
 }
 
@@ -413,6 +475,88 @@ NTB_EXPORT int ntb_gemm_bf16(const void* a, const void* b, void* d, int M, int N
   NTB_GEMM_CASE(1, 0, 0) NTB_GEMM_CASE(1, 0, 1) NTB_GEMM_CASE(1, 0, 2)
 #undef NTB_GEMM_CASE
   return NTB_ERR_ARG;
+}
+
+
+// ---------------------------------------------------------------------------------------------- grouped (mixture-of-experts) entry points
+namespace {
+
+// Expert weights, K-major: [E, rows, k] contiguous -> 3-D map {k, rows, E}, box {64, 256, 1}.
+bool make_map_kmajor_batched(CUtensorMap* m, const void* ptr, int64_t rows, int64_t k, int64_t ld, int64_t E, int box_rows) {
+  cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)E};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)ld * 2 * (cuuint64_t)rows};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  return get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Expert weights, MN-major: [E, k, mn] contiguous -> 4-D map {64, k, mn/64, E}.
+bool make_map_mnmajor_batched(CUtensorMap* m, const void* ptr, int64_t mn, int64_t k, int64_t ld, int64_t E, int box_mn) {
+  cuuint64_t dims[4] = {64, (cuuint64_t)k, (cuuint64_t)((mn + 63) / 64), (cuuint64_t)E};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, 128, (cuuint64_t)ld * 2 * (cuuint64_t)k};
+  cuuint32_t box[4] = {64, (cuuint32_t)BLOCK_K, (cuuint32_t)(box_mn / 64), 1};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  return get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Per-expert output [E, rows, cols] contiguous -> 3-D map {cols, rows, E}.
+bool make_map_out_batched(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t E, bool f32) {
+  const cuuint64_t esz = f32 ? 4 : 2;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)E};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * esz, (cuuint64_t)cols * esz * (cuuint64_t)rows};
+  cuuint32_t box[3] = {(cuuint32_t)(f32 ? 32 : 64), 32, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  return get_encode()(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ptr, dims, strides, box, es,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Rows of `a` [rows_cap, K] (bf16, padded expert layout) times the weight of each row block's expert:
+//   b_mn = 0: b is [E, N, K] (d = a @ b[e]^T, e.g. dgrad against [E, K_in, N_out] weights seen as [E, N, K]);
+//   b_mn = 1: b is [E, K, N] (d = a @ b[e], the forward of [E, in, out] weights).
+// d is [rows_cap, N] bf16.  tile_expert[rows_cap / 128] and num_m_tiles[1] are device data.
+NTB_EXPORT int ntb_gemm_bf16_grouped(const void* a, const void* b, void* d, int rows_cap, int N, int K, int b_mn, int E, const int* tile_expert,
+                                     const int* num_m_tiles, int* status, int num_sms, cudaStream_t stream) {
+  if (rows_cap <= 0 || rows_cap % BLOCK_M || N <= 0 || K <= 0 || E <= 0 || !get_encode() || !tile_expert || !num_m_tiles) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
+  if (K % 8 || N % 8 || (b_mn && N % 64)) return NTB_ERR_ARG;
+  CUtensorMap ta, tb, td;
+  bool ok = make_map_kmajor(&ta, a, rows_cap, K, K, BLOCK_M);
+  ok = ok && (b_mn ? make_map_mnmajor_batched(&tb, b, N, K, N, E, BLOCK_N) : make_map_kmajor_batched(&tb, b, N, K, K, E, BLOCK_N));
+  ok = ok && make_map_out(&td, d, rows_cap, N, N, false);
+  if (!ok) return NTB_ERR_ARG;
+  GroupArgs g;
+  g.tile_expert = tile_expert;
+  g.num_m_tiles = num_m_tiles;
+  g.E = E;
+  if (num_sms <= 0) num_sms = 148;
+  return b_mn ? launch<false, true, OUT_BF16, 1>(ta, tb, td, rows_cap, N, K, status, num_sms, stream, TpFuse(), g)
+              : launch<false, false, OUT_BF16, 1>(ta, tb, td, rows_cap, N, K, status, num_sms, stream, TpFuse(), g);
+}
+
+// Weight gradients of every expert in one launch: dw[e][m, n] (=|+=) sum over rows r in [seg_off[e], seg_off[e+1]) of x[r, m] * dy[r, n].
+// x is [rows_cap, M], dy is [rows_cap, N] (bf16; rows in padding must be zero), dw is [E, M, N] (out_mode 0 bf16, 1 fp32, 2 fp32 +=).
+// Experts without rows are skipped: in the store modes the caller provides a zeroed `dw`.
+NTB_EXPORT int ntb_gemm_bf16_grouped_wgrad(const void* x, const void* dy, void* dw, int rows_cap, int M, int N, int E, const int* seg_off, int out_mode,
+                                           int* status, int num_sms, cudaStream_t stream) {
+  if (rows_cap <= 0 || rows_cap % BLOCK_M || M <= 0 || N <= 0 || E <= 0 || !get_encode() || !seg_off || out_mode < 0 || out_mode > 2) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dw)) & 15) return NTB_ERR_ARG;
+  if (M % 64 || N % 64) return NTB_ERR_ARG;
+  CUtensorMap ta, tb, td;
+  bool ok = make_map_mnmajor(&ta, x, M, rows_cap, M, BLOCK_M);
+  ok = ok && make_map_mnmajor(&tb, dy, N, rows_cap, N, BLOCK_N);
+  ok = ok && make_map_out_batched(&td, dw, M, N, E, out_mode != OUT_BF16);
+  if (!ok) return NTB_ERR_ARG;
+  GroupArgs g;
+  g.seg_off = seg_off;
+  g.E = E;
+  if (num_sms <= 0) num_sms = 148;
+  if (out_mode == OUT_BF16) return launch<true, true, OUT_BF16, 2>(ta, tb, td, M, N, rows_cap, status, num_sms, stream, TpFuse(), g);
+  if (out_mode == OUT_F32) return launch<true, true, OUT_F32, 2>(ta, tb, td, M, N, rows_cap, status, num_sms, stream, TpFuse(), g);
+  return launch<true, true, OUT_F32_ACCUM, 2>(ta, tb, td, M, N, rows_cap, status, num_sms, stream, TpFuse(), g);
 }
 
 

@@ -26,3 +26,9 @@ def test_fused_data_parallel_step_matches_nccl():
 def test_fused_tensor_parallel_linears_match_nccl():
     r = _torchrun("tests/multigpu/check_fused_tp.py", 2, 29732)
     assert r.returncode == 0 and "FUSED_TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_expert_parallel_moe_matches_nccl():
+    r = _torchrun("tests/multigpu/check_fused_ep.py", 2, 29733)
+    assert r.returncode == 0 and "FUSED_EP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
