@@ -106,23 +106,35 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restr
     }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  // Software pipeline over rows: the loads of row r + gridDim.x are issued before the block reduction of row r, so two
+  // rows are in flight per CTA and the reduction latency is hidden behind memory latency.
+  Vec8<T> n_dy[ITERS], n_x[ITERS], n_dr[ITERS];
+  int row = blockIdx.x;
+  if (row < rows) {
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
+      const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+      if (c < cols) {
+        n_dy[it].load(dy + (size_t)row * cols + c);
+        n_x[it].load(pre + (size_t)row * cols + c);
+        if (dres) n_dr[it].load(dres + (size_t)row * cols + c);
+      }
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
     const float rstd = rstd_in[row];
     const float mean = RMS ? 0.f : mean_in[row];
-    const T* dyr = dy + (size_t)row * cols;
-    const T* xr = pre + (size_t)row * cols;
     float wdy[ITERS][8], xhat[ITERS][8];
+    Vec8<T> c_dr[ITERS];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
       const int c = (it * NORM_THREADS + threadIdx.x) * 8;
       if (c < cols) {
-        Vec8<T> a, bv;
         float fdy[8], fx[8];
-        a.load(dyr + c);
-        bv.load(xr + c);
-        a.to_float(fdy);
-        bv.to_float(fx);
+        n_dy[it].to_float(fdy);
+        n_x[it].to_float(fx);
+        c_dr[it] = n_dr[it];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           xhat[it][i] = (fx[i] - mean) * rstd;
@@ -134,7 +146,19 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restr
         }
       }
     }
-    // one block reduction for both sums (parity-indexed scratch: no barrier needed before the next row's write)
+    const int nrow = row + gridDim.x;
+    if (nrow < rows) {
+#pragma unroll
+      for (int it = 0; it < ITERS; it++) {
+        const int c = (it * NORM_THREADS + threadIdx.x) * 8;
+        if (c < cols) {
+          n_dy[it].load(dy + (size_t)nrow * cols + c);
+          n_x[it].load(pre + (size_t)nrow * cols + c);
+          if (dres) n_dr[it].load(dres + (size_t)nrow * cols + c);
+        }
+      }
+    }
+    // one block reduction for both sums
     s1 = warp_sum(s1);
     if (!RMS) s2 = warp_sum(s2);
     float* sc = scratch[0];
@@ -146,7 +170,6 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restr
     const float c1 = warp_sum(r1) / cols;
     const float c2 = RMS ? 0.f : warp_sum(r2) / cols;
     T* dxr = dx + (size_t)row * cols;
-    const T* drr = dres ? dres + (size_t)row * cols : nullptr;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
       const int c = (it * NORM_THREADS + threadIdx.x) * 8;
@@ -154,11 +177,9 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_bwd_kernel(const T* __restr
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) f[i] = (wdy[it][i] - xhat[it][i] * c1 - c2) * rstd;
-        if (drr) {
-          Vec8<T> r;
+        if (dres) {
           float g[8];
-          r.load(drr + c);
-          r.to_float(g);
+          c_dr[it].to_float(g);
 #pragma unroll
           for (int i = 0; i < 8; i++) f[i] += g[i];
         }

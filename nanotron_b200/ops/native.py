@@ -251,7 +251,7 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool 
 # ---------------------------------------------------------------------------- MoE router
 def moe_router_supported(x: torch.Tensor, weight: torch.Tensor, k: int) -> bool:
     E = weight.shape[0]
-    return x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and x.is_contiguous() and weight.is_contiguous() and E % 16 == 0 and E <= 128 and (16 * E) % 256 == 0 and hasattr(lib(), "ntb_moe_router_fwd")
+    return x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.float32 and x.is_contiguous() and weight.is_contiguous() and E % 16 == 0 and E <= 128 and x.shape[1] % 8 == 0 and hasattr(lib(), "ntb_moe_router_fwd")
 
 
 def moe_router_fwd(x: torch.Tensor, weight: torch.Tensor, k: int):
