@@ -124,6 +124,43 @@ def linear_wgrad(go2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> O
     return go2.t().matmul(x2)
 
 
+# ============================================================================ embedding
+class _MaskedEmbedding(torch.autograd.Function):
+    """Vocabulary-range-masked lookup; the weight gradient goes straight into the fp32 ``main_grad`` buffer when there is one
+    (parity: reference tensor_parallel/nn.py:275-301 masks the ids, looks up, then masks the output again)."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, min_id, max_id):
+        from nanotron_b200.ops import native
+
+        ctx.save_for_backward(ids, weight)
+        ctx.range = (min_id, max_id)
+        return native.embedding_fwd(ids, weight, min_id, max_id)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from nanotron_b200.ops import native
+
+        ids, weight = ctx.saved_tensors
+        min_id, max_id = ctx.range
+        main_grad = getattr(weight, "main_grad", None)
+        if main_grad is not None:
+            native.embedding_bwd_accum(ids, dout, main_grad, min_id, max_id)
+            return None, None, None, None
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        native.embedding_bwd_accum(ids, dout, dw, min_id, max_id)
+        return None, dw.to(weight.dtype), None, None
+
+
+def masked_embedding(ids: torch.Tensor, weight: torch.Tensor, min_id: int, max_id: int) -> torch.Tensor:
+    """Rows of ``weight`` ([max_id - min_id, h]) for ids inside [min_id, max_id), zeros for the others."""
+    if _use_native(weight) and ids.dtype == torch.int64 and weight.is_contiguous() and (weight.shape[1] * weight.element_size()) % 16 == 0 and weight.shape[1] % 8 == 0:
+        return _MaskedEmbedding.apply(ids, weight, min_id, max_id)
+    mask = (ids < min_id) | (ids >= max_id)
+    out = torch.nn.functional.embedding((ids - min_id).masked_fill(mask, 0), weight)
+    return out.masked_fill(mask.unsqueeze(-1), 0.0)
+
+
 # ============================================================================ norms
 class _RMSNorm(torch.autograd.Function):
     @staticmethod

@@ -248,6 +248,33 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool 
     return out
 
 
+# ---------------------------------------------------------------------------- embedding
+def embedding_fwd(ids: torch.Tensor, weight: torch.Tensor, min_id: int, max_id: int) -> torch.Tensor:
+    """out[..., h] = weight[ids - min_id] for ids in [min_id, max_id), zeros elsewhere."""
+    L = lib()
+    L.ntb_embedding_fwd.restype = c_int
+    L.ntb_embedding_fwd.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p]
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty((*ids.shape, weight.shape[1]), dtype=weight.dtype, device=weight.device)
+    with torch.cuda.device(weight.device):
+        rc = L.ntb_embedding_fwd(_DT[weight.dtype], flat.data_ptr(), weight.data_ptr(), out.data_ptr(), flat.numel(), weight.shape[1], min_id, max_id, _stream(weight))
+    _check(rc, "embedding_fwd")
+    return out
+
+
+def embedding_bwd_accum(ids: torch.Tensor, dout: torch.Tensor, dweight_fp32: torch.Tensor, min_id: int, max_id: int) -> None:
+    """dweight_fp32[ids - min_id] += dout (fp32 vector atomics)."""
+    L = lib()
+    L.ntb_embedding_bwd.restype = c_int
+    L.ntb_embedding_bwd.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p]
+    flat = ids.reshape(-1).contiguous()
+    d2 = dout.reshape(-1, dout.shape[-1]).contiguous()
+    assert dweight_fp32.dtype == torch.float32 and dweight_fp32.is_contiguous()
+    with torch.cuda.device(dout.device):
+        rc = L.ntb_embedding_bwd(_DT[d2.dtype], flat.data_ptr(), d2.data_ptr(), dweight_fp32.data_ptr(), flat.numel(), d2.shape[1], min_id, max_id, _stream(dout))
+    _check(rc, "embedding_bwd")
+
+
 # ---------------------------------------------------------------------------- MoE router
 def moe_router_supported(x: torch.Tensor, weight: torch.Tensor, k: int) -> bool:
     E = weight.shape[0]

@@ -175,14 +175,19 @@ class TensorParallelEmbedding(nn.Embedding):
         mark_all_parameters_in_module_as_sharded(self, pg=self.pg, split_config=SplitConfig(split_dim=0, contiguous_chunks=contiguous_chunks))
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
-        if self.world_size > 1:
-            mask = (input_ids < self.min_id) | (input_ids >= self.max_id)
-            local_ids = (input_ids - self.min_id).masked_fill(mask, 0)
+        if self.padding_idx is None and self.max_norm is None and not self.scale_grad_by_freq and not self.sparse:
+            from nanotron_b200 import ops
+
+            out = ops.masked_embedding(input_ids, self.weight, self.min_id, self.max_id)  # gather + range mask in one pass
         else:
-            mask, local_ids = None, input_ids
-        out = super().forward(local_ids)
-        if mask is not None:
-            out = out.masked_fill(mask.unsqueeze(-1), 0.0)
+            if self.world_size > 1:
+                mask = (input_ids < self.min_id) | (input_ids >= self.max_id)
+                local_ids = (input_ids - self.min_id).masked_fill(mask, 0)
+            else:
+                mask, local_ids = None, input_ids
+            out = super().forward(local_ids)
+            if mask is not None:
+                out = out.masked_fill(mask.unsqueeze(-1), 0.0)
         if self.mode is TensorParallelLinearMode.ALL_REDUCE:
             out = differentiable_all_reduce_sum(out, group=self.pg)
         elif self.mode is TensorParallelLinearMode.REDUCE_SCATTER:

@@ -200,3 +200,30 @@ def test_moe_router_kernel(T, h, E, k):
     assert (top_i.long() == exp_i).float().mean() > 0.999
     assert int(counts.sum()) == T * k
     assert torch.equal(counts.long(), torch.bincount(top_i.reshape(-1).long(), minlength=E))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_masked_embedding_forward_and_fp32_accumulating_backward(dtype):
+    from nanotron_b200 import ops
+
+    V, h, n = 1000, 256, 777
+    min_id, max_id = 250, 500
+    torch.manual_seed(0)
+    w = torch.randn(max_id - min_id, h, device="cuda", dtype=dtype, requires_grad=True)
+    ids = torch.randint(0, V, (7, 111), device="cuda")
+    out = ops.masked_embedding(ids, w, min_id, max_id)
+    mask = (ids < min_id) | (ids >= max_id)
+    exp = torch.nn.functional.embedding((ids - min_id).masked_fill(mask, 0), w.detach()).masked_fill(mask.unsqueeze(-1), 0.0)
+    assert torch.equal(out, exp)
+    g = torch.randn_like(out)
+    # plain gradient
+    out.backward(g)
+    exp_dw = torch.zeros(max_id - min_id, h, device="cuda", dtype=torch.float32)
+    exp_dw.index_add_(0, (ids - min_id).masked_fill(mask, 0).reshape(-1), (g.float() * (~mask).unsqueeze(-1)).reshape(-1, h))
+    torch.testing.assert_close(w.grad.float(), exp_dw, atol=3e-2 if dtype == torch.bfloat16 else 1e-4, rtol=2e-2)
+    # accumulation into an fp32 main-gradient buffer
+    w.grad = None
+    w.main_grad = torch.full((max_id - min_id, h), 0.25, device="cuda", dtype=torch.float32)
+    ops.masked_embedding(ids, w, min_id, max_id).backward(g)
+    assert w.grad is None
+    torch.testing.assert_close(w.main_grad, exp_dw + 0.25, atol=1e-4, rtol=1e-4)
