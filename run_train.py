@@ -77,6 +77,25 @@ def get_dataloader_from_data_stage(trainer: DistributedTrainer, data: DataArgs, 
         needed = num_remaining_train_steps * trainer.global_batch_size * seq
         assert needed < total_tokens_dataset, f"Dataset is too small for steps ({total_tokens_dataset} < {needed}), try train_steps<={len(dataloader.dataset) // trainer.global_batch_size + trainer.iteration_step}"
         return dataloader
+    if isinstance(data.dataset, NanosetDatasetsArgs) and (data.dataset.use_old_brrr_dataloader or data.dataset.dataset_read_path):
+        # streamed token files / folders mirrored under another root: blended folders + the Megatron batch sampler
+        from nanotron_b200.data.tokenized_bytes import get_tb_dataloader, get_tb_datasets
+
+        if data.dataset.token_size_in_bytes is None:
+            data.dataset.token_size_in_bytes = 4 if trainer.model_config.vocab_size > 65535 else 2
+        train_dataset, data_log = get_tb_datasets(
+            data.dataset, sequence_length=seq, global_batch_size=trainer.global_batch_size, train_steps=trainer.config.tokens.train_steps,
+            current_iteration=trainer.iteration_step, parallel_context=trainer.parallel_context, eos_token_id=getattr(trainer.model_config, "eos_token_id", None),
+            shuffle=bool(data.dataset.shuffle_files), seed=data.seed, consumed_samples=consumed_train_samples_stage,
+            consumed_tokens_per_dataset_folder=consumed_tokens_per_dataset_folder,
+        )
+        log_rank(f"[tokenized bytes] {data_log.human_total_train_tokens} training tokens in {data_log.train_num_samples} samples", logger=logger, level=logging.INFO, rank=0)
+        return get_tb_dataloader(
+            train_dataset, sequence_length=seq, micro_batch_size=trainer.micro_batch_size, global_batch_size=trainer.global_batch_size, cfg=data.dataset,
+            num_workers=data.num_loading_workers, consumed_samples=consumed_train_samples_stage, num_samples=len(train_dataset), parallel_context=trainer.parallel_context,
+            input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank, use_position_ids=not uses_mask and bool(data.dataset.return_positions),
+            use_doc_masking=getattr(trainer.model_config, "_use_doc_masking", False),
+        )
     if isinstance(data.dataset, NanosetDatasetsArgs):
         from nanotron_b200.data.nanoset import Nanoset
         from nanotron_b200.utils import main_rank_first

@@ -1,0 +1,70 @@
+"""Token-file datasets: streamed single files (sequential, skipping, random access, wrap-around, token budgets), streamed and
+memory-mapped folders, weighted blending of folders through ``get_tb_datasets``."""
+import numpy as np
+import pytest
+
+from nanotron_b200.data.tokenized_bytes import OldTokenizedBytesFolderDataset, TokenizedBytesFileDataset, TokenizedBytesFolderDataset, build_dataset, get_tb_datasets
+
+
+def _write(path, n, start=0, dtype=np.uint16):
+    np.arange(start, start + n, dtype=dtype).tofile(path)
+
+
+def test_file_dataset_streams_skips_and_wraps(tmp_path):
+    p = str(tmp_path / "a.ds")
+    _write(p, 1000)
+    seq = 9
+    ds = TokenizedBytesFileDataset(p, seq)
+    assert len(ds) == 100
+    assert ds[0]["input_ids"].tolist() == list(range(10))
+    assert ds[1]["input_ids"].tolist() == list(range(10, 20))  # consecutive: same stream
+    assert ds[5]["input_ids"].tolist() == list(range(50, 60))  # skip ahead inside the stream
+    assert ds[2]["input_ids"].tolist() == list(range(20, 30))  # going back reopens
+    assert ds[103]["input_ids"].tolist() == list(range(30, 40))  # wraps around
+    assert ds[0]["input_ids"].dtype.is_floating_point is False
+    budget = TokenizedBytesFileDataset(p, seq, max_tokens=55, skip_tokens=7)
+    assert len(budget) == 5 and budget[0]["input_ids"].tolist() == list(range(7, 17)) and budget[4]["input_ids"].tolist() == list(range(47, 57))
+    no_skip = TokenizedBytesFileDataset(p, seq, skip_in_stream=False)
+    assert no_skip[3]["input_ids"].tolist() == list(range(30, 40)) and no_skip[7]["input_ids"].tolist() == list(range(70, 80))
+
+
+def test_folder_datasets(tmp_path):
+    for i in range(3):
+        _write(str(tmp_path / f"f{i}.ds"), 205, start=1000 * i)
+    (tmp_path / "notes.txt").write_text("x")
+    seq = 9
+    old = OldTokenizedBytesFolderDataset(str(tmp_path), seq, filename_pattern=".*\\.ds$")
+    assert len(old) == 60 and old.subset_log.num_samples == 60
+    assert old[0]["input_ids"].tolist() == list(range(10)) and old[20]["input_ids"].tolist() == list(range(1000, 1010)) and old[59]["input_ids"][0] == 2190
+    assert old[61]["input_ids"].tolist() == list(range(10, 20))
+    capped = OldTokenizedBytesFolderDataset(str(tmp_path), seq, filename_pattern=".*\\.ds$", max_tokens=250)
+    assert len(capped) == 20 + 5
+    mm = TokenizedBytesFolderDataset(str(tmp_path), seq, filename_pattern="*.ds", recursive=False, token_size=2)
+    # memory-mapped files share the boundary token between consecutive samples: (205 - 1) // 9 = 22 samples per file
+    assert len(mm) == 66 and mm[0]["input_ids"].tolist() == list(range(10)) and mm[1]["input_ids"].tolist() == list(range(9, 19))
+    assert mm[22]["input_ids"].tolist() == list(range(1000, 1010))
+    shuffled = TokenizedBytesFolderDataset(str(tmp_path), seq, shuffle=True, seed=3)
+    assert sorted(shuffled.subset_log.files_order) == sorted(mm.subset_log.files_order)
+    pos = TokenizedBytesFolderDataset(str(tmp_path), seq, return_positions=True, eos_token_id=13)
+    item = pos[1]
+    assert item["input_ids"].tolist() == list(range(9, 19)) and item["positions"].tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3, 4]
+    assert isinstance(build_dataset(str(tmp_path), seq, 2), TokenizedBytesFolderDataset)
+    assert isinstance(build_dataset(str(tmp_path), seq, 2, use_old_brrr_dataloader=True), OldTokenizedBytesFolderDataset)
+
+
+def test_get_tb_datasets_blends_folders(tmp_path):
+    from nanotron_b200.config import NanosetDatasetsArgs
+
+    a, b = tmp_path / "a", tmp_path / "b"
+    a.mkdir()
+    b.mkdir()
+    _write(str(a / "x.ds"), 5000, start=0)
+    _write(str(b / "y.ds"), 5000, start=30000)
+    cfg = NanosetDatasetsArgs(dataset_folder=[str(a), str(b)], dataset_weights=[3, 1], token_size_in_bytes=2, return_positions=False)
+    blend, log = get_tb_datasets(cfg, sequence_length=9, global_batch_size=8, train_steps=10, current_iteration=0, parallel_context=None)
+    assert len(blend) == 80 and log.train_num_samples == 80 and log.total_training_tokens == 720
+    firsts = [int(blend[i]["input_ids"][0]) for i in range(80)]
+    assert sum(1 for f in firsts if f < 30000) == 60 and sum(1 for f in firsts if f >= 30000) == 20
+    # resuming a later stage shifts the folder that was already consumed
+    later, _ = get_tb_datasets(cfg, 9, 8, 10, 0, None, last_stages_consumed_tokens_per_dataset_folder={str(a): 90})
+    assert int(later[0]["input_ids"][0]) == 90
