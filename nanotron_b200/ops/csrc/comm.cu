@@ -62,31 +62,43 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int me, int world, uint32_t 
 }
 
 // grads.p[r]: base of rank r's flat fp32 gradient buffer.  Range [start, start+n) is this rank's shard (n % 4 == 0).
+// Each thread keeps U x world 16-byte loads in flight (U chosen by the host so that U * world ~ 8): peer loads cross NVLink
+// with a few microseconds of latency, so the bytes in flight per SM, not the instruction rate, set the bandwidth.
+template <int U, int WMAX>
 __global__ void __launch_bounds__(COMM_THREADS) dp_reduce_scatter_kernel(PeerPtrs grads, int me, int world, int64_t start, int64_t n, float scale,
                                                                          int broadcast, float* __restrict__ sumsq_partial) {
   __shared__ float scratch[32];
   float* own = reinterpret_cast<float*>(grads.p[me]) + start;
   float sq = 0.f;
   const int64_t stride = (int64_t)gridDim.x * COMM_THREADS * 4;
-  for (int64_t i = ((int64_t)blockIdx.x * COMM_THREADS + threadIdx.x) * 4; i < n; i += stride) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    // fixed order 0..world-1 keeps the sum deterministic; loads of different peers are independent and overlap
-    float4 vals[MAX_RANKS];
+  for (int64_t i0 = ((int64_t)blockIdx.x * COMM_THREADS + threadIdx.x) * 4; i0 < n; i0 += stride * U) {
+    float4 vals[U][WMAX];
 #pragma unroll
-    for (int r = 0; r < MAX_RANKS; r++)
-      if (r < world) vals[r] = (r == me) ? *reinterpret_cast<const float4*>(own + i) : ld_sys_f4(reinterpret_cast<const float*>(grads.p[r]) + start + i);
+    for (int u = 0; u < U; u++) {
+      const int64_t i = i0 + u * stride;
 #pragma unroll
-    for (int r = 0; r < MAX_RANKS; r++)
-      if (r < world) { acc.x += vals[r].x; acc.y += vals[r].y; acc.z += vals[r].z; acc.w += vals[r].w; }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    *reinterpret_cast<float4*>(own + i) = acc;
-    if (broadcast) {
-      for (int k = 1; k < world; k++) {
-        const int r = (me + k) % world;  // staggered so ranks do not all hit the same peer at once
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + start + i) = acc;
-      }
+      for (int r = 0; r < WMAX; r++)
+        if (r < world && i < n) vals[u][r] = (r == me) ? *reinterpret_cast<const float4*>(own + i) : ld_sys_f4(reinterpret_cast<const float*>(grads.p[r]) + start + i);
     }
-    sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int64_t i = i0 + u * stride;
+      if (i >= n) break;
+      // fixed order 0..world-1 keeps the sum deterministic
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < WMAX; r++)
+        if (r < world) { acc.x += vals[u][r].x; acc.y += vals[u][r].y; acc.z += vals[u][r].z; acc.w += vals[u][r].w; }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      *reinterpret_cast<float4*>(own + i) = acc;
+      if (broadcast) {
+        for (int k = 1; k < world; k++) {
+          const int r = (me + k) % world;  // staggered so ranks do not all hit the same peer at once
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[r]) + start + i) = acc;
+        }
+      }
+      sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
   }
   sq = block_sum(sq, scratch);
   if (threadIdx.x == 0) sumsq_partial[blockIdx.x] = sq;
@@ -202,7 +214,10 @@ NTB_EXPORT int ntb_dp_reduce_scatter(const uint64_t* grad_ptrs, int me, int worl
   PeerPtrs g;
   if (!fill_peers(g, grad_ptrs, world) || n <= 0 || n % 4 || start % 4) return NTB_ERR_ARG;
   const int blocks = ntb_dp_num_partials();
-  dp_reduce_scatter_kernel<<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  if (world <= 2) dp_reduce_scatter_kernel<4, 2><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else if (world <= 4) dp_reduce_scatter_kernel<2, 4><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else if (world <= 8) dp_reduce_scatter_kernel<2, 8><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else dp_reduce_scatter_kernel<1, MAX_RANKS><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
   sum_partials_kernel<<<1, 256, 0, stream>>>(sumsq_partial, blocks, sumsq_out);
   return ntb_check_launch();
 }

@@ -44,9 +44,10 @@ enum OutMode { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ACCUM = 2, OUT_PEER_BF16 = 3 }
 //    plain stores; block r is valid once `ag_flags[r] >= epoch`.  The TMA producer polls that word (bounded) before its
 //    first load from a block, and row blocks are visited starting with this rank's own, so the GEMM on blocks that
 //    already arrived overlaps the NVLink transfer of the others.
-//  * GEMM -> reduce-scatter (OUT_PEER_BF16): the epilogue stores each bf16 tile straight into the staging buffer of the
-//    rank that owns those rows (`rs_dst[owner] + me * rs_slot_elems`), visiting row blocks starting with the next rank's.
-//    The last CTA to finish publishes `epoch` in every owner's `rs_flags[me]`; owners then sum the `world` slots.
+//  * GEMM -> reduce-scatter (OUT_PEER_BF16): the epilogue TMA-stores each bf16 tile straight into the staging buffer of the
+//    rank that owns those rows (one tensor map per owner over its [world * rs_rows, N] staging area, slot `me`), visiting
+//    row blocks starting with the next rank's.  The last CTA to finish publishes `epoch` in every owner's `rs_flags[me]`;
+//    owners then sum the `world` slots.
 constexpr int TP_MAX = 8;
 struct TpFuse {
   int world = 0, me = 0;
@@ -54,11 +55,15 @@ struct TpFuse {
   int m_rot = 0;                      // tile-row rotation (in 128-row tiles)
   const uint32_t* ag_flags = nullptr; // local flag words [world]
   int ag_rows = 0;                    // rows per gathered block
-  void* rs_dst[TP_MAX] = {};          // per-owner staging base (bf16), slot-major [world][rs_rows][N]
   uint32_t* rs_flags[TP_MAX] = {};    // per-owner flag words [world]
   int rs_rows = 0;                    // rows per owner
   long long rs_slot_elems = 0;
   unsigned int* done_counter = nullptr;  // local counter, zero before launch
+};
+
+// Per-owner output maps of the GEMM -> reduce-scatter epilogue (unused otherwise).
+struct PeerMaps {
+  CUtensorMap m[TP_MAX];
 };
 
 struct TileCoord {
@@ -127,7 +132,8 @@ __device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int
 template <bool A_MN, bool B_MN, int OUT, int GROUP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                    int M, int N, int K, int* __restrict__ status, const __grid_constant__ TpFuse fuse, const __grid_constant__ GroupArgs grp) {
+                    int M, int N, int K, int* __restrict__ status, const __grid_constant__ TpFuse fuse, const __grid_constant__ GroupArgs grp,
+                    const __grid_constant__ PeerMaps pmaps) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
@@ -265,7 +271,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint8_t* my_epi = epi_smem + (warp - 2) * 2 * EPI_BUF_BYTES;
-    constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;  // 128 bytes of output per row (peer mode: 32 columns from registers)
+    constexpr bool BF16_OUT = (OUT == OUT_BF16 || OUT == OUT_PEER_BF16);
+    constexpr int CHUNK_COLS = BF16_OUT ? 64 : 32;  // 128 bytes of output per row
     constexpr int CHUNKS = BLOCK_N / CHUNK_COLS;
     int tile_it = 0, buf = 0;
     bool ok = true;
@@ -279,42 +286,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
       const int row0 = tc.m_blk * BLOCK_M + q * 32;
-      if (OUT == OUT_PEER_BF16) {
-        // one thread = one output row: 32 fp32 accumulators -> 32 bf16 -> four 16-byte stores into the owner's staging slot.
-        // Every lane issues the (warp-aligned) TMEM loads; only the stores are predicated.
-        const int row = row0 + lane;
-        const bool row_ok = row < M;
-        const int owner = row_ok ? row / fuse.rs_rows : 0;
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(fuse.rs_dst[owner]) + static_cast<long long>(fuse.me) * fuse.rs_slot_elems +
-                             static_cast<long long>(row - owner * fuse.rs_rows) * N + tc.n_blk * BLOCK_N;
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; c++) {
-          uint32_t r0[32];
-          ptx::tmem_ld_32x32(taddr + c * 32, r0);
-          ptx::tmem_ld_wait();
-          if (row_ok && tc.n_blk * BLOCK_N + c * 32 < N) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              uint4 pk;
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 0]), __uint_as_float(r0[j * 8 + 1]));
-              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 2]), __uint_as_float(r0[j * 8 + 3]));
-              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 4]), __uint_as_float(r0[j * 8 + 5]));
-              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r0[j * 8 + 6]), __uint_as_float(r0[j * 8 + 7]));
-              pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-              pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-              *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = pk;
-            }
-          }
-        }
-      }
-#pragma unroll 1
-      for (int c = 0; c < (OUT == OUT_PEER_BF16 ? 0 : CHUNKS); c++) {
+      for (int c = 0; c < CHUNKS; c++) {
         uint8_t* stage_buf = my_epi + buf * EPI_BUF_BYTES;
         // the TMA store that last read this staging buffer must be done reading it
         if (lane == 0) ptx::tma_wait_group_read<1>();
         __syncwarp();
         uint8_t* my_row = stage_buf + lane * 128;
-        if (OUT == OUT_BF16) {
+        if (BF16_OUT) {
           uint32_t r0[32], r1[32];
           ptx::tmem_ld_32x32(taddr + c * 64, r0);
           ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
@@ -347,7 +326,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         __syncwarp();
         if (lane == 0) {
           const int x = tc.n_blk * BLOCK_N + c * CHUNK_COLS;
-          if (x < N && row0 < M) {
+          if (OUT == OUT_PEER_BF16) {
+            if (x < N && row0 < M) {
+              const int owner = row0 / fuse.rs_rows;  // rs_rows is a multiple of 32: the 32 rows of this warp share an owner
+              ptx::tma_store_2d(&pmaps.m[owner], stage_buf, x, fuse.me * fuse.rs_rows + (row0 - owner * fuse.rs_rows));
+            }
+          } else if (x < N && row0 < M) {
             if (GROUP == 2) {  // one weight-gradient matrix per expert: outermost map dimension
               if (OUT == OUT_F32_ACCUM) ptx::tma_reduce_add_3d(&tmap_d, stage_buf, x, row0, tc.e);
               else ptx::tma_store_3d(&tmap_d, stage_buf, x, row0, tc.e);
@@ -365,7 +349,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
     }
-    if (lane == 0) ptx::tma_wait_group<0>();  // all stores complete before the CTA exits
+    if (lane == 0) {
+      ptx::tma_wait_group<0>();  // all stores complete before the CTA exits
+      if (OUT == OUT_PEER_BF16) {
+        // the peer stores were made by the async proxy: order them before the generic-proxy flag store that follows the CTA barrier
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence_system();
+      }
+    }
     __syncwarp();
   }
 
@@ -436,7 +427,7 @@ bool make_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t
 
 template <bool A_MN, bool B_MN, int OUT, int GROUP = 0>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
-           const TpFuse& fuse = TpFuse(), const GroupArgs& grp = GroupArgs()) {
+           const TpFuse& fuse = TpFuse(), const GroupArgs& grp = GroupArgs(), const PeerMaps* pmaps = nullptr) {
   auto kern = gemm_tcgen05_kernel<A_MN, B_MN, OUT, GROUP>;
   static bool configured = false;
   if (!configured) {
@@ -445,7 +436,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, 
   }
   const long long tiles = static_cast<long long>((M + BLOCK_M - 1) / BLOCK_M) * ((N + BLOCK_N - 1) / BLOCK_N) * (GROUP == 2 ? grp.E : 1);
   const int grid = tiles < num_sms ? static_cast<int>(tiles) : num_sms;
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status, fuse, grp);
+  static const PeerMaps no_maps = {};
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, td, M, N, K, status, fuse, grp, pmaps ? *pmaps : no_maps);
   return ntb_check_launch();
 }
 
@@ -678,7 +670,7 @@ NTB_EXPORT int ntb_gemm_bf16_ag(const void* a_gathered, const void* b, void* d, 
 NTB_EXPORT int ntb_gemm_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const uint64_t* staging_ptrs,
                                 const uint64_t* flag_ptrs, int rs_rows, int me, int world, uint32_t epoch, unsigned int* done_counter, int* status, int num_sms,
                                 cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || !get_encode() || world < 1 || world > TP_MAX || rs_rows * world != M || N % 32) return NTB_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || !get_encode() || world < 1 || world > TP_MAX || rs_rows * world != M || rs_rows % 32 || N % 8) return NTB_ERR_ARG;
   if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8))) return NTB_ERR_ARG;
   CUtensorMap ta, tb, td;
   bool ok = make_map_kmajor(&ta, a, M, K, lda, BLOCK_M);
@@ -691,15 +683,18 @@ NTB_EXPORT int ntb_gemm_bf16_rs(const void* a, const void* b, int M, int N, int 
   f.epoch = epoch;
   f.rs_rows = rs_rows;
   f.rs_slot_elems = static_cast<long long>(rs_rows) * N;
+  PeerMaps pm = {};
   for (int r = 0; r < world; r++) {
-    f.rs_dst[r] = reinterpret_cast<void*>(staging_ptrs[r]);
+    if (staging_ptrs[r] & 15) return NTB_ERR_ARG;
+    if (!make_map_out(&pm.m[r], reinterpret_cast<void*>(staging_ptrs[r]), static_cast<int64_t>(world) * rs_rows, N, N, false)) return NTB_ERR_ARG;
     f.rs_flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
   }
   f.done_counter = done_counter;
   const int tiles_m = (M + BLOCK_M - 1) / BLOCK_M;
   f.m_rot = ((((me + 1) % world) * rs_rows) / BLOCK_M) % tiles_m;  // the next rank's rows first, our own last
   if (num_sms <= 0) num_sms = 148;
-  return b_mn ? launch<false, true, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f) : launch<false, false, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f);
+  return b_mn ? launch<false, true, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, GroupArgs(), &pm)
+              : launch<false, false, OUT_PEER_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, GroupArgs(), &pm);
 }
 
 // out[rs_rows, N] = sum of the `world` staging slots once every peer published `epoch`.
