@@ -83,7 +83,48 @@ __global__ void __launch_bounds__(CE_THREADS) ce_backward_kernel(const T* logits
   }
 }
 
+constexpr int CE_MAX_RANKS = 8;
+struct CePeers {
+  const float* p[CE_MAX_RANKS];
+};
+
+// Tensor-parallel reduction of the per-rank (max, sum exp, target logit) triples by peer loads: every rank reads the [3, rows]
+// partial arrays of all ranks (after a cross-rank barrier made them visible) and finishes logZ and the loss locally, in the
+// same fixed rank order everywhere, so all ranks get bit-identical results without a collective.
+__global__ void ce_combine_peers_kernel(CePeers parts, int world, int64_t rows, int64_t pitch, float* __restrict__ logz, float* __restrict__ loss) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  float m[CE_MAX_RANKS], s[CE_MAX_RANKS], t = 0.f, gmax = -INFINITY;
+#pragma unroll
+  for (int r = 0; r < CE_MAX_RANKS; r++) {
+    if (r < world) {
+      float tv;
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(m[r]) : "l"(parts.p[r] + i) : "memory");
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(s[r]) : "l"(parts.p[r] + pitch + i) : "memory");
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(tv) : "l"(parts.p[r] + 2 * pitch + i) : "memory");
+      t += tv;
+      gmax = fmaxf(gmax, m[r]);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int r = 0; r < CE_MAX_RANKS; r++)
+    if (r < world) sum += s[r] * __expf(m[r] - gmax);
+  const float lz = gmax + __logf(sum);
+  logz[i] = lz;
+  loss[i] = lz - t;
+}
+
 }  // namespace
+
+// part_ptrs[r]: rank r's partial array, laid out [3][pitch] fp32 (max, sum exp, target logit), `rows` valid entries per plane.
+NTB_EXPORT int ntb_ce_combine_peers(const uint64_t* part_ptrs, int world, int64_t rows, int64_t pitch, float* logz, float* loss, cudaStream_t stream) {
+  if (world < 1 || world > CE_MAX_RANKS || rows <= 0 || pitch < rows) return NTB_ERR_ARG;
+  CePeers pp;
+  for (int r = 0; r < CE_MAX_RANKS; r++) pp.p[r] = r < world ? reinterpret_cast<const float*>(part_ptrs[r]) : nullptr;
+  ce_combine_peers_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, stream>>>(pp, world, rows, pitch, logz, loss);
+  return ntb_check_launch();
+}
 
 NTB_EXPORT int ntb_ce_partials(int dtype, const void* logits, const int64_t* target, float* out_max, float* out_sum, float* out_tgt, int64_t rows,
                                int vocab, int64_t vocab_start, cudaStream_t stream) {

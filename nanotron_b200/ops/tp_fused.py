@@ -45,9 +45,37 @@ class TPFusedContext:
         self.rs_flags = [self.alloc.zeros(32, torch.int32) for _ in range(2)]
         self.ag_calls = 0
         self.rs_calls = 0
+        self.ce_calls = 0
+        self.ce_parts = [None, None]
         self.counter = torch.zeros(4, dtype=torch.int32, device=dev)
         self.status = self.alloc.status
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+
+    # ---- vocabulary-parallel cross entropy: (max, sum exp, target logit) combined by peer loads
+    def ce_combine(self, local_max: torch.Tensor, local_sumexp: torch.Tensor, local_tgt: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Returns (logZ, loss) per row from every rank's partial statistics; no NCCL collective."""
+        from nanotron_b200.ops import native
+
+        rows = local_max.numel()
+        i = self.ce_calls & 1
+        self.ce_calls += 1
+        cur = self.ce_parts[i]
+        if cur is None or cur.tensor.numel() < 3 * rows:
+            cur = self.ce_parts[i] = self.alloc.zeros(3 * rows, torch.float32)  # collective: same size on every rank
+        pitch = cur.tensor.numel() // 3
+        view = cur.tensor.view(3, pitch)
+        view[0, :rows].copy_(local_max)
+        view[1, :rows].copy_(local_sumexp)
+        view[2, :rows].copy_(local_tgt)
+        self.alloc.barrier()  # every rank's triple is in place (the other parity buffer may still be read by a slow peer)
+        logz = torch.empty(rows, dtype=torch.float32, device=local_max.device)
+        loss = torch.empty_like(logz)
+        L = native.lib()
+        L.ntb_ce_combine_peers.restype = ctypes.c_int
+        L.ntb_ce_combine_peers.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        rc = L.ntb_ce_combine_peers(cur.ptrs, self.world, rows, pitch, logz.data_ptr(), loss.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "ce_combine_peers")
+        return logz, loss
 
     def _buf(self, pool, i: int, numel: int):
         cur = pool[i]

@@ -230,6 +230,16 @@ class _ShardedCrossEntropy(torch.autograd.Function):
         tgt = target.reshape(-1)
         vocab_start = rank * vshard
         local_max, local_sumexp, local_tgt = ops.ce_partials(logits2, tgt, vocab_start)
+        fused = None
+        if tp > 1 and logits2.is_cuda and ops.tp_fused.ENABLED:
+            fused = ops.tp_fused.get_context(group)
+        if fused is not None:
+            logz, loss = fused.ce_combine(local_max, local_sumexp, local_tgt)  # tp reduction by peer loads inside the kernel
+            ctx.save_for_backward(logits2, tgt, logz)
+            ctx.vocab_start, ctx.lead, ctx.z = vocab_start, lead, z_loss_coef
+            if z_loss_coef > 0:
+                return loss.view(lead), (z_loss_coef * logz.square()).view(lead)
+            return loss.view(lead), None
         if tp > 1:
             gmax = local_max.clone()
             dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
