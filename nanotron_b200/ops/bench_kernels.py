@@ -181,12 +181,39 @@ def bench_moe():
     ctx.check()
 
 
+def bench_fp8():
+    """Block-scaled fp8 GEMM (tcgen05 kind::f8f6f4, 1x128 / 128x128 scales promoted in fp32) on Llama-3-8B shapes, against the
+    in-tree and library bf16 GEMMs of the same shape."""
+    from nanotron_b200.fp8.quantize import quantize_1x128, quantize_128x128_reference
+    from nanotron_b200.ops import native, native_gemm as g
+
+    native.lib()
+    peak = _peaks()["bf16_tflops"]
+    for name, M, N, K in [("qkv", 8192, 6144, 4096), ("gate_up", 8192, 28672, 4096), ("down", 8192, 4096, 14336)]:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        xq = quantize_1x128(x)
+        wq = quantize_128x128_reference(w)
+        flops = 2.0 * M * N * K
+        ms8 = time_fn(lambda: native.gemm_fp8_blockscaled(xq, wq, epi_warps=8))
+        ms8b = time_fn(lambda: native.gemm_fp8_blockscaled(xq, wq, epi_warps=16))
+        g.check_status("cuda")
+        ms16 = time_fn(lambda: torch.nn.functional.linear(x, w))
+        msq = time_fn(lambda: quantize_1x128(x))
+        print(f"{name:8s} M={M} N={N} K={K}  fp8 tcgen05 {ms8:7.3f} ms {flops / ms8 / 1e9:7.1f} TFLOP/s ({flops / ms8 / 1e9 / peak:4.2f} of measured bf16 peak; 16 promotion warps: {ms8b:7.3f} ms) | "
+              f"library bf16 {ms16:7.3f} ms {flops / ms16 / 1e9:7.1f} TFLOP/s | 1x128 quantise of x {msq:6.3f} ms", flush=True)
+        del x, w, xq, wq
+        torch.cuda.empty_cache()
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm(small="--small" in sys.argv)
     elif what == "elementwise":
         bench_elementwise()
+    elif what == "fp8":
+        bench_fp8()
     elif what == "moe":
         bench_moe()
     elif what == "attention":

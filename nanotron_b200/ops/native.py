@@ -318,6 +318,37 @@ def fp8_quantize_1x128(x: torch.Tensor, dtype: torch.dtype):
     return FP8BlockTensor(q, scale, (1, 128))
 
 
+def has_fp8_gemm() -> bool:
+    return hasattr(lib(), "ntb_gemm_fp8_blockscaled")
+
+
+def gemm_fp8_blockscaled(a, b, out: Optional[torch.Tensor] = None, accumulate_fp32: bool = False, epi_warps: int = 0) -> torch.Tensor:
+    """``a`` [M, K] (1 x 128 scales) times ``b`` [N, K]^T (128 x 128 or 1 x 128 scales) on the fp8 tensor cores, with the per-block
+    scales applied in fp32 between k-blocks.  Returns bf16 [M, N], or accumulates into the fp32 ``out`` when ``accumulate_fp32``."""
+    from nanotron_b200.ops import native_gemm
+
+    M, K = a.data.shape
+    N, Kb = b.data.shape
+    assert K == Kb and a.block == (1, 128) and b.block in ((1, 128), (128, 128)) and a.data.is_contiguous() and b.data.is_contiguous()
+    assert a.scale.is_contiguous() and b.scale.is_contiguous() and a.scale.shape[1] == (K + 127) // 128 == b.scale.shape[1]
+    L = lib()
+    L.ntb_gemm_fp8_blockscaled.restype = c_int
+    L.ntb_gemm_fp8_blockscaled.argtypes = [c_void_p] * 5 + [c_int] * 3 + [c_int64] * 3 + [c_int] * 5 + [c_void_p, c_int, c_void_p]
+    if accumulate_fp32:
+        assert out is not None and out.dtype == torch.float32 and out.shape == (M, N) and out.is_contiguous()
+        mode = 2
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.data.device) if out is None else out
+        mode = 0
+    status = native_gemm.status_word(a.data.device)
+    with torch.cuda.device(a.data.device):
+        rc = L.ntb_gemm_fp8_blockscaled(a.data.data_ptr(), a.scale.data_ptr(), b.data.data_ptr(), b.scale.data_ptr(), out.data_ptr(), M, N, K, K, K, N,
+                                        int(a.data.dtype == torch.float8_e5m2), int(b.data.dtype == torch.float8_e5m2), int(b.block == (1, 128)), mode, epi_warps,
+                                        status.data_ptr(), 0, _stream(a.data))
+    _check(rc, "gemm_fp8_blockscaled")
+    return out
+
+
 # ---------------------------------------------------------------------------- GEMM / attention: see native_gemm / native_attn
 from nanotron_b200.ops.native_attn import flash_attn_bwd, flash_attn_fwd, flash_attn_supported  # noqa: E402,F401
 from nanotron_b200.ops.native_gemm import gemm_nn, gemm_nt, gemm_supported, gemm_tn, gemm_tn_accum_fp32  # noqa: E402,F401

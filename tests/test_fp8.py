@@ -44,3 +44,53 @@ def test_fp8_quantize_kernel_matches_reference():
         exp = quantize_1x128_reference(x, q)
         torch.testing.assert_close(got.scale, exp.scale, rtol=1e-6, atol=0)
         torch.testing.assert_close(dequantize(got, torch.float32), dequantize(exp, torch.float32), rtol=0.13, atol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (384, 256, 1024), (130, 264, 208)])
+def test_fp8_tensor_core_gemm_matches_dequantised_product(M, N, K):
+    from nanotron_b200.fp8.quantize import dequantize, quantize_1x128_reference, quantize_128x128_reference
+    from nanotron_b200.ops import native, native_gemm
+
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    for a_dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        xq = quantize_1x128_reference(x, a_dtype)
+        wq = quantize_128x128_reference(w, torch.float8_e4m3fn)
+        exp = dequantize(xq, torch.float32) @ dequantize(wq, torch.float32).t()
+        got = native.gemm_fp8_blockscaled(xq, wq)
+        native_gemm.check_status("cuda")
+        torch.testing.assert_close(got.float(), exp, atol=2e-2 * float(exp.abs().max()), rtol=2e-2)
+        # both operands with per-row scales (the weight-gradient form), accumulated into fp32
+        wq_row = quantize_1x128_reference(w, torch.float8_e4m3fn)
+        exp_row = dequantize(xq, torch.float32) @ dequantize(wq_row, torch.float32).t()
+        acc = torch.full((M, N), 0.5, device="cuda", dtype=torch.float32)
+        native.gemm_fp8_blockscaled(xq, wq_row, out=acc, accumulate_fp32=True)
+        native_gemm.check_status("cuda")
+        torch.testing.assert_close(acc, exp_row + 0.5, atol=1e-3 * float(exp_row.abs().max()) + 1e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_fp8_linear_native_path_matches_dequantised_path():
+    from nanotron_b200 import ops
+    from nanotron_b200.fp8.linear import FP8Linear
+
+    torch.manual_seed(0)
+    lin = FP8Linear(512, 384, bias=False).cuda().to(torch.bfloat16)
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+    res = {}
+    for mode in ("auto", "torch"):
+        ops.set_mode(mode)
+        try:
+            lin.weight.grad = None
+            xi = x.clone().requires_grad_(True)
+            y = lin(xi)
+            y.backward(g)
+            res[mode] = (y.detach().float(), xi.grad.float(), lin.weight.grad.float().clone())
+        finally:
+            ops.set_mode("auto")
+    for a, b, name in zip(res["auto"], res["torch"], ("y", "dx", "dW")):
+        err = (a - b).abs().max() / b.abs().max()
+        assert err < 2e-2, (name, float(err))
