@@ -98,7 +98,8 @@ def lr_scheduler_builder(optimizer, lr_scheduler_args: LRSchedulerArgs, total_tr
         return lmbda / initial_lr if initial_lr != 0 else 0.0
 
     base = optimizer.get_base_optimizer() if hasattr(optimizer, "get_base_optimizer") else optimizer
-    lambdas = [partial(lr_lambda, initial_lr=g["lr"]) for g in base.param_groups]
+    # a resumed optimizer carries the current lr in "lr" and the base value in "initial_lr"
+    lambdas = [partial(lr_lambda, initial_lr=g.get("initial_lr", g["lr"])) for g in base.param_groups]
     return LambdaLR(base, lr_lambda=lambdas)
 
 

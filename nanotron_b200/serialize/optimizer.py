@@ -181,15 +181,22 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
 
 
 def _local_shape(meta: TensorMetadata):
+    """Shape of the shard described by a slice map: per dimension the largest explicit local stop, or, when the local slice
+    is the whole dimension (``slice(None)``), the extent of the matching global slice."""
     shape = []
-    first = meta.local_global_slices_pairs
+    pairs = meta.local_global_slices_pairs
     ndim = len(meta.unsharded_shape)
     for d in range(ndim):
-        stops = [sp.local_slices[d].stop for sp in first]
-        if any(s is None for s in stops):
-            shape.append(meta.unsharded_shape[d])
-        else:
-            shape.append(max(stops))
+        extent = 0
+        for sp in pairs:
+            ls, gs = sp.local_slices[d], sp.global_slices[d]
+            if ls.stop is not None:
+                extent = max(extent, ls.stop)
+            else:
+                g0 = gs.start or 0
+                g1 = gs.stop if gs.stop is not None else meta.unsharded_shape[d]
+                extent = max(extent, (ls.start or 0) + (g1 - g0))
+        shape.append(extent)
     return tuple(shape)
 
 
@@ -202,4 +209,7 @@ def load_lr_scheduler(lr_scheduler, is_zero, parallel_context: ParallelContext, 
         path = candidates[0]
     state_dict = torch.load(path, weights_only=False)
     lr_scheduler.load_state_dict(state_dict)
-    lr_scheduler._initial_step()
+    # Put the learning rates the scheduler had computed for the next step back into the optimizer.  (The reference calls
+    # ``_initial_step()`` here, serialize/optimizer.py:369-370, which advances the schedule by one extra step on every resume.)
+    for group, lr in zip(lr_scheduler.optimizer.param_groups, lr_scheduler.get_last_lr()):
+        group["lr"] = lr

@@ -1,0 +1,97 @@
+"""Checkpoints: the on-disk layout (file names the reference uses), exact resume of a run (weights, fp32 masters, optimizer
+moments, lr schedule, step / sample counters), and resuming under a different topology (tp 2 -> 1, dp 2 + ZeRO-1 -> 1)."""
+import json
+import os
+
+import torch
+
+from helpers import make_config, run_distributed, tiny_llama_config
+from test_distributed_cpu import _deterministic_init, _fixed_batches
+
+
+def _run(out_file, ckpt_dir, steps, first_step=0, save=False, resume=None, total_mbs=4, **topology):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.trainer import DistributedTrainer as _Base
+
+    class DistributedTrainer(_Base):
+        def _load_model_checkpoint(self, model):
+            if self.init_checkpoint_path is not None:
+                return super()._load_model_checkpoint(model)
+            _deterministic_init(model)
+            return model
+
+    dp = topology.get("dp", 1)
+    accum = total_mbs // dp
+    mc = tiny_llama_config()
+    cfg = make_config(mc, seq=16, mbs=1, accum=accum, steps=8, lr=1e-2, ckpt_path=ckpt_dir, **topology)
+    if resume is not None:
+        cfg.checkpoints.resume_checkpoint_path = resume
+    t = DistributedTrainer(cfg)
+    t.prepare_training()
+    assert t.iteration_step == first_step + 1, (t.iteration_step, first_step)  # the step about to run
+    all_batches = _fixed_batches(t, first_step + steps, total_mbs, 16, mc.vocab_size, uses_mask=True)
+    per_step = len(all_batches) // (first_step + steps)
+    batches = iter(all_batches[first_step * per_step :])
+    losses = []
+    for i in range(steps):
+        _, loss, _ = t.training_step(batches)
+        t.metadata.last_train_step = t.iteration_step
+        t.metadata.consumed_train_samples += t.global_batch_size
+        t.metadata.data_stages[0].consumed_train_samples += t.global_batch_size
+        if loss is not None:
+            losses.append(float(loss))
+        if save and i == steps - 1:
+            t.save_checkpoint()
+        t.iteration_step += 1
+    if dist.get_rank(t.parallel_context.world_pg) == t.logger_ranks[0]:
+        torch.save(losses, out_file)
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def _losses(tmp_path, name, world, **kw):
+    f = str(tmp_path / f"{name}.pt")
+    run_distributed(_run, world, out_file=f, **kw)
+    return torch.load(f)
+
+
+def test_resume_continues_the_same_run_and_layout_matches(tmp_path):
+    ckpt = str(tmp_path / "ckpt")
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4)
+    first = _losses(tmp_path, "first", 1, ckpt_dir=ckpt, steps=2, save=True)
+    assert first == full[:2]
+    step_dir = os.path.join(ckpt, "2")
+    # layout
+    assert open(os.path.join(ckpt, "latest.txt")).read().strip() == "2"
+    meta = json.load(open(os.path.join(step_dir, "checkpoint_metadata.json")))
+    assert meta["metas"]["last_train_step"] == 2 and meta["tp"] == 1 and meta["dp"] == 1
+    assert os.path.isfile(os.path.join(step_dir, "config.yaml"))
+    assert os.path.isfile(os.path.join(step_dir, "model", "model", "token_position_embeddings", "pp_block", "token_embedding", "model_weight_pp-rank-0-of-1_tp-rank-0-of-1.safetensors"))
+    assert os.path.isfile(os.path.join(step_dir, "model", "model", "decoder", "0", "pp_block", "attn", "qkv_proj", "model_weight_pp-rank-0-of-1_tp-rank-0-of-1.safetensors"))
+    assert os.path.isfile(os.path.join(step_dir, "model", "model", "final_layer_norm", "pp_block", "model_weight.safetensors"))  # replicated: no suffix
+    assert os.path.isfile(os.path.join(step_dir, "optimizer", "optimizer_config.json"))
+    assert any(f.startswith("optimizer_pp-0-of-1") and f.endswith(".pt") for f in os.listdir(os.path.join(step_dir, "optimizer")))
+    assert os.listdir(os.path.join(step_dir, "lr_scheduler")) == ["lr_scheduler_pp-0-of-1_tp-0-of-1_exp-0-of-1.pt"]
+    assert os.listdir(os.path.join(step_dir, "random")) == ["tp-0-of-1_dp-0-of-1_pp-0-of-1.pt"]
+    # exact continuation
+    resumed = _losses(tmp_path, "resumed", 1, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 1e-6, (resumed, full)
+
+
+def test_resume_under_another_topology(tmp_path):
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4)
+    # tensor parallel 2 -> 1: sharded weights and optimizer moments are merged on load
+    ckpt_tp = str(tmp_path / "ckpt_tp")
+    _losses(tmp_path, "tp_first", 2, ckpt_dir=ckpt_tp, steps=2, save=True, tp=2, tp_mode="reduce_scatter")
+    names = os.listdir(os.path.join(ckpt_tp, "2", "model", "model", "decoder", "0", "pp_block", "attn", "qkv_proj"))
+    assert sorted(names) == ["model_weight_pp-rank-0-of-1_tp-rank-0-of-2.safetensors", "model_weight_pp-rank-0-of-1_tp-rank-1-of-2.safetensors"]
+    resumed = _losses(tmp_path, "tp_resumed", 1, ckpt_dir=ckpt_tp, steps=2, first_step=2, resume=ckpt_tp)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
+    # data parallel 2 with ZeRO-1 -> single process: optimizer shards are concatenated on load
+    ckpt_dp = str(tmp_path / "ckpt_dp")
+    _losses(tmp_path, "dp_first", 2, ckpt_dir=ckpt_dp, steps=2, save=True, dp=2, zero=1)
+    resumed = _losses(tmp_path, "dp_resumed", 1, ckpt_dir=ckpt_dp, steps=2, first_step=2, resume=ckpt_dp)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
