@@ -300,14 +300,41 @@ class DistributedTrainer:
         self.initial_iter_step = self.metadata.last_train_step + 1
         self.last_iter_step = self.config.tokens.train_steps
         prof = get_profiler(config=self.config)
+        from nanotron_b200 import fault_tolerance
+
+        world_rank = dist.get_rank(self.parallel_context.world_pg)
+        self.heartbeat, self.watchdog = fault_tolerance.from_env(world_rank, self.parallel_context.world_pg.size())
+        step_deadline = float(os.environ["NANOTRON_STEP_DEADLINE"]) if os.environ.get("NANOTRON_STEP_DEADLINE") else None
+        try:
+            self._train_loop(prof, dataloader_or_dls, step_deadline)
+        except BaseException:
+            if self.heartbeat is not None:
+                self.heartbeat.stop("failed")  # peers learn of the failure from the heartbeat before their next launch
+            raise
+        if self.heartbeat is not None:
+            self.heartbeat.stop("done")
+        dist.barrier(self.parallel_context.world_pg)
+        if self.config.checkpoints is not None and self.config.checkpoints.save_final_state and not self._stop_requested:
+            if self.iteration_step % self.config.checkpoints.checkpoint_interval != 0:
+                self.save_checkpoint()
+        self.post_training()
+
+    def _train_loop(self, prof, dataloader_or_dls, step_deadline):
+        from nanotron_b200 import fault_tolerance
+
         with prof:
             for self.iteration_step in range(self.initial_iter_step, self.last_iter_step + 1):
                 if hasattr(prof, "step"):
                     prof.step()
+                if self.watchdog is not None:
+                    self.watchdog.raise_if_failed()  # between steps: nothing of ours is in flight towards a dead peer
+                if self.heartbeat is not None:
+                    self.heartbeat.beat(self.iteration_step)
                 self.iteration_timer = nanotron_timer("iteration_time", "cuda" if self.parallel_context.device.type == "cuda" else "cpu", cuda_sync=False, enabled=True)
                 self.iteration_timer.start()
                 self._update_dataloader_based_on_training_stages(dataloader_or_dls)
-                outputs, loss_avg, z_loss_avg = self.training_step(dataloader=self.current_dataloader)
+                with fault_tolerance.StepDeadline(step_deadline):
+                    outputs, loss_avg, z_loss_avg = self.training_step(dataloader=self.current_dataloader)
                 # bookkeeping
                 self.metadata.consumed_train_samples += self.global_batch_size
                 self.metadata.consumed_tokens_total = (self.metadata.consumed_tokens_total or 0) + self.global_batch_size * self.sequence_length
@@ -328,11 +355,6 @@ class DistributedTrainer:
                 if stop:
                     log_rank("Stop requested (signal or kill-switch file): checkpoint saved, leaving the training loop", logger=logger, level=logging.WARNING, rank=0)
                     break
-        dist.barrier(self.parallel_context.world_pg)
-        if self.config.checkpoints is not None and self.config.checkpoints.save_final_state and not self._stop_requested:
-            if self.iteration_step % self.config.checkpoints.checkpoint_interval != 0:
-                self.save_checkpoint()
-        self.post_training()
 
     def prepare_training(self):
         """Set up what ``train`` sets up before its loop, for callers that drive ``training_step`` themselves."""

@@ -227,3 +227,31 @@ def test_masked_embedding_forward_and_fp32_accumulating_backward(dtype):
     ops.masked_embedding(ids, w, min_id, max_id).backward(g)
     assert w.grad is None
     torch.testing.assert_close(w.main_grad, exp_dw + 0.25, atol=1e-4, rtol=1e-4)
+
+
+def test_device_side_wait_gives_up_and_reports():
+    """A wait on a flag that nothing sets must run out after its limit, set the status word and leave the context usable."""
+    import ctypes
+    import time
+
+    from nanotron_b200.ops import native
+
+    L = native.lib()
+    flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L.ntb_symm_wait.restype = ctypes.c_int
+    L.ntb_symm_wait.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p]
+    torch.cuda.synchronize()
+    t0 = time.time()
+    rc = L.ntb_symm_wait(flags.data_ptr(), 2, 1, 50_000_000, status.data_ptr(), torch.cuda.current_stream().cuda_stream)  # 50 ms
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    assert int(status.item()) == 3  # NTB_ERR_TIMEOUT
+    # the same wait succeeds at once when the flags carry the epoch, and ordinary kernels still run
+    flags.fill_(1)
+    status.zero_()
+    assert L.ntb_symm_wait(flags.data_ptr(), 2, 1, 50_000_000, status.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
