@@ -93,10 +93,13 @@ def build_config(args, world: int):
     import nanotron_b200.config as c
 
     mc = c.LlamaConfig(**MODELS[args.model])
-    zero = 1 if world > 1 else 0
+    tp, pp = args.tp, args.pp
+    assert world % (tp * pp) == 0, f"world size {world} is not a multiple of tp * pp = {tp * pp}"
+    dp = world // (tp * pp)
+    zero = 1 if dp > 1 else 0
     return c.Config(
         general=c.GeneralArgs(project="bench", run="bench", seed=42, ignore_sanity_checks=True),
-        parallelism=c.ParallelismArgs(dp=world, pp=1, tp=1, pp_engine="1f1b", tp_mode="reduce_scatter", tp_linear_async_communication=False, recompute_layer=args.recompute),
+        parallelism=c.ParallelismArgs(dp=dp, pp=pp, tp=tp, pp_engine="1f1b", tp_mode="reduce_scatter", tp_linear_async_communication=tp > 1, recompute_layer=args.recompute),
         model=c.ModelArgs(model_config=mc, init_method=c.RandomInit(std=0.02), dtype="bfloat16"),
         tokenizer=c.TokenizerArgs(),
         checkpoints=c.CheckpointsArgs(checkpoints_path="/tmp/ntb_bench_ckpt", checkpoint_interval=10**9, save_final_state=False),
@@ -138,7 +141,8 @@ def run_native(args):
 
     def gen(host_pinned: bool):
         return dummy_infinite_data_generator(
-            micro_batch_size=args.mbs, sequence_length=args.seq, input_pp_rank=0, output_pp_rank=0, vocab_size=mc.vocab_size,
+            micro_batch_size=args.mbs, sequence_length=args.seq, input_pp_rank=trainer.unwrapped_model.input_pp_rank,
+            output_pp_rank=trainer.unwrapped_model.output_pp_rank, vocab_size=mc.vocab_size,
             seed=42, parallel_context=ctx, use_position_ids=False, host_pinned=host_pinned,
         )()
 
@@ -152,8 +156,8 @@ def run_native(args):
         for _ in range(steps):
             _, loss, _ = trainer.training_step(loader)
             trainer.iteration_step += 1
-            if read_loss:
-                last = float(loss.item())  # device -> host read of the step result
+            if read_loss and isinstance(loss, torch.Tensor):
+                last = float(loss.item())  # device -> host read of the step result (pipeline ranks without the loss have none)
             else:
                 last = loss
         end.record()
@@ -169,11 +173,15 @@ def run_native(args):
     sampler.start()
     ms, launches, loss = timed(dev_loader, args.steps, read_loss=False)
     clocks = sampler.stop()
-    loss_val = float(loss.item())
+    loss_t = loss if isinstance(loss, torch.Tensor) else torch.zeros((), device="cuda")
+    loss_t = loss_t.detach().float().reshape(1).clone()
+    dist.all_reduce(loss_t, op=dist.ReduceOp.MAX, group=ctx.world_pg)  # ranks that do not hold the loss contribute 0
+    loss_val = float(loss_t.item())
     timed(host_loader, 1, read_loss=True)
     e2e_ms, _, _ = timed(host_loader, args.steps, read_loss=True)
 
-    tokens_per_step = args.mbs * args.seq * args.accum * world
+    dp = ctx.dp_pg.size()
+    tokens_per_step = args.mbs * args.seq * args.accum * dp
     value = tokens_per_step / (ms / args.steps / 1000.0)
     e2e_value = tokens_per_step / (e2e_ms / args.steps / 1000.0)
     flops, _ = get_flops(num_layers=mc.num_hidden_layers, hidden_size=mc.hidden_size, num_heads=mc.num_attention_heads, num_key_value_heads=mc.num_key_value_heads, vocab_size=mc.vocab_size, seq_len=args.seq, ffn_hidden_size=mc.intermediate_size, batch_size=1)
@@ -194,8 +202,9 @@ def run_native(args):
             "tokens_per_sec_per_gpu": value / world, "model_tflops_per_gpu": tflops_per_gpu, "mfu_of_measured_sustained_peak": tflops_per_gpu / peak,
             "loss": loss_val, "impl": "nanotron_b200",
             "config": {
-                "model": args.model, "global_batch": args.mbs * args.accum * world, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
-                "parallelism": f"dp{world}" + ("+zero1" if world > 1 else ""), "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
+                "model": args.model, "global_batch": args.mbs * args.accum * dp, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
+                "parallelism": f"dp{dp}" + ("+zero1" if dp > 1 else "") + (f"+tp{args.tp}(sequence-parallel, fused AG/RS kernels)" if args.tp > 1 else "") + (f"+pp{args.pp}(1f1b)" if args.pp > 1 else ""),
+                "dp_step": "in-tree NVLink kernels (reduce-scatter + AdamW + all-gather)" if getattr(trainer, "fused_dp", None) is not None else "NCCL", "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
                 "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush",
                 "gemm": ops._GEMM, "attention": ops._ATTN,
             },
@@ -220,6 +229,8 @@ def main():
     ap.add_argument("--mbs", type=int, default=1)
     ap.add_argument("--accum", type=int, default=8)
     ap.add_argument("--recompute", action="store_true")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence-parallel mode); dp = gpus / (tp * pp)")
+    ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (1F1B)")
     args = ap.parse_args()
     if args.impl == "reference":
         from baseline.run_reference import run_reference
