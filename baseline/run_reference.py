@@ -74,7 +74,11 @@ def run_reference(args):
         model=ModelArgs(init_method=RandomInit(std=0.02), model_config=model_config),
         tokenizer=TokenizerArgs(tokenizer_name_or_path=None),
         optimizer=OptimizerArgs(
-            zero_stage=1 if world > 1 else 0, weight_decay=0.01, clip_grad=1.0, accumulate_grad_in_fp32=True,
+            # ZeRO-1 together with fp32 gradient accumulation and dp > 1 is not runnable in the reference: its DDP hook raises
+            # NotImplementedError("Not implemented") on the reduce-scatter branch (optim/gradient_accumulator.py:354-355, selected by
+            # helpers.py:460 whenever the optimizer is a ZeroDistributedOptimizer).  Its working data-parallel path is the fp32
+            # all-reduce with a replicated optimizer, so that is what runs here at every N.
+            zero_stage=0, weight_decay=0.01, clip_grad=1.0, accumulate_grad_in_fp32=True,
             learning_rate_scheduler=LRSchedulerArgs(learning_rate=3e-4, lr_warmup_steps=2, lr_warmup_style="linear", lr_decay_style="cosine", min_decay_lr=3e-5),
             optimizer_factory=AdamWOptimizerArgs(adam_eps=1e-8, adam_beta1=0.9, adam_beta2=0.95, torch_adam_is_fused=True),
         ),
