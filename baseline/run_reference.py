@@ -86,9 +86,9 @@ def run_reference(args):
         tokens=TokensArgs(sequence_length=args.seq, train_steps=total_steps, micro_batch_size=args.mbs, batch_accumulation_per_replica=args.accum),
         data_stages=[DatasetStageArgs(name="bench", start_training_step=1, data=DataArgs(dataset=None, seed=42, num_loading_workers=0))],
     )
+    # the reference trainer wants a file path; every rank writes its own (identical) copy into its own scratch directory
     cfg_path = os.path.join(ckpt_dir, "config.yaml")
-    if rank == 0:
-        config.save_as_yaml(cfg_path)
+    config.save_as_yaml(cfg_path)
     state = {"start": None, "end": None, "sampler": None, "clocks": None}
 
     class TimedTrainer(DistributedTrainer):
@@ -110,14 +110,7 @@ def run_reference(args):
                     state["clocks"] = state["sampler"].stop()
 
     try:
-        # every rank parses the same file; wait for rank 0 to have written it
-        import time
-
-        for _ in range(600):
-            if os.path.exists(cfg_path):
-                break
-            time.sleep(0.1)
-        trainer = TimedTrainer(cfg_path if os.path.exists(cfg_path) else config)
+        trainer = TimedTrainer(cfg_path)
         input_pp_rank, output_pp_rank = get_input_output_pp_ranks(model=trainer.model)
         dataloader = dummy_infinite_data_generator(
             micro_batch_size=trainer.micro_batch_size, sequence_length=trainer.sequence_length, input_pp_rank=input_pp_rank,

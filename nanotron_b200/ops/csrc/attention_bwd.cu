@@ -40,6 +40,15 @@ struct BwdParams {
   int64_t dk_stride_t;
   int total_q;
   int* status;
+  int cp, cp_me, cp_chunk;  // context parallel: group size (0 = off), this rank, tokens per chunk
+};
+
+constexpr int CP_MAX = 8;
+struct CpBwd {
+  CUtensorMap k[CP_MAX];
+  CUtensorMap v[CP_MAX];
+  float* dk_acc[CP_MAX];  // per owner: fp32 [batch * 2 * chunk, Hkv, 128]
+  float* dv_acc[CP_MAX];
 };
 
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta, int total_q, int heads) {
@@ -78,7 +87,7 @@ __device__ __forceinline__ void red_add_f32(float* p, float v) { asm volatile("r
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const BwdParams p) {
+                 const __grid_constant__ CUtensorMap tmap_v, const BwdParams p, const __grid_constant__ CpBwd cpb) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -100,19 +109,50 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, hk = blockIdx.y;
-  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
-  const int k0 = blockIdx.x * BK;
+  const bool cpm_on = p.cp > 0;
+  const int q_begin = cpm_on ? b * 2 * p.cp_chunk : p.cu_q[b];
+  const int q_len = cpm_on ? 2 * p.cp_chunk : p.cu_q[b + 1] - q_begin;
+  const int k_begin = cpm_on ? 0 : p.cu_k[b];
+  const int k_len = cpm_on ? 2 * p.cp * p.cp_chunk : p.cu_k[b + 1] - k_begin;
+  const int k0 = blockIdx.x * BK;  // first key of the tile: local position, or the global one under context parallelism
   if (k0 >= k_len) return;
-  const int shift = k_len - q_len;
+  const int shift = cpm_on ? 0 : k_len - q_len;
   const int group = p.num_heads / p.num_kv_heads;
-  // query tiles that can see at least one key of this tile
-  int qt_begin = 0;
-  if (p.causal) qt_begin = max(0, k0 - shift) / BQ;
-  int qt_end = (q_len + BQ - 1) / BQ;
-  if (p.window > 0) qt_end = min(qt_end, (k0 + BK - 1 - shift + p.window - 1) / BQ + 1);
-  const int tiles_per_head = max(0, qt_end - qt_begin);
+  // Runs of 64-query steps that can see at least one key of this tile: one run normally, up to two (one per local chunk) under
+  // context parallelism.  seg_q0 = local position of the run's first query, seg_m0 = its position for the masks.
+  int seg_q0[2] = {0, 0}, seg_m0[2] = {0, 0}, seg_n[2] = {0, 0};
+  int kv_owner = 0, kv_row = k_begin + k0;
+  if (!cpm_on) {
+    int qt_begin = 0;
+    if (p.causal) qt_begin = max(0, k0 - shift) / BQ;
+    int qt_end = (q_len + BQ - 1) / BQ;
+    if (p.window > 0) qt_end = min(qt_end, (k0 + BK - 1 - shift + p.window - 1) / BQ + 1);
+    seg_q0[0] = seg_m0[0] = qt_begin * BQ;
+    seg_n[0] = max(0, qt_end - qt_begin);
+  } else {
+    const int c = p.cp_chunk;
+    for (int half = 0; half < 2; half++) {
+      const int chunk = half == 0 ? p.cp_me : 2 * p.cp - 1 - p.cp_me;
+      const int first = max(0, k0 - chunk * c) / BQ * BQ;  // first query of the chunk (relative) that sees key k0
+      if (first < c) {
+        seg_q0[half] = half * c + first;
+        seg_m0[half] = chunk * c + first;
+        seg_n[half] = (c - first) / BQ;
+      }
+    }
+    const int kchunk = k0 / c;
+    kv_owner = kchunk < p.cp ? kchunk : 2 * p.cp - 1 - kchunk;
+    kv_row = b * 2 * c + (kchunk < p.cp ? 0 : c) + (k0 - kchunk * c);
+  }
+  const int tiles_per_head = seg_n[0] + seg_n[1];
   const int n_steps = tiles_per_head * group;
+  // step index inside a head -> (local query position, mask position)
+  auto step_pos = [&](int i, int& q0, int& m0) {
+    if (i < seg_n[0]) { q0 = seg_q0[0] + i * BQ; m0 = seg_m0[0] + i * BQ; }
+    else { q0 = seg_q0[1] + (i - seg_n[0]) * BQ; m0 = seg_m0[1] + (i - seg_n[0]) * BQ; }
+  };
+  const CUtensorMap* map_k = cpm_on ? &cpb.k[kv_owner] : &tmap_k;
+  const CUtensorMap* map_v = cpm_on ? &cpb.v[kv_owner] : &tmap_v;
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(kv_full, 1);
@@ -147,15 +187,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (warp == 0) {
     if (ptx::elect_one() && n_steps > 0) {
       ptx::mbar_expect_tx(kv_full, 2 * KV_TILE_BYTES);
-      ptx::tma_load_3d(sK, &tmap_k, kv_full, 0, hk, k_begin + k0);
-      ptx::tma_load_3d(sK + KV_PANEL, &tmap_k, kv_full, 64, hk, k_begin + k0);
-      ptx::tma_load_3d(sV, &tmap_v, kv_full, 0, hk, k_begin + k0);
-      ptx::tma_load_3d(sV + KV_PANEL, &tmap_v, kv_full, 64, hk, k_begin + k0);
+      ptx::tma_load_3d(sK, map_k, kv_full, 0, hk, kv_row);
+      ptx::tma_load_3d(sK + KV_PANEL, map_k, kv_full, 64, hk, kv_row);
+      ptx::tma_load_3d(sV, map_v, kv_full, 0, hk, kv_row);
+      ptx::tma_load_3d(sV + KV_PANEL, map_v, kv_full, 64, hk, kv_row);
       for (int n = 0; n < n_steps; n++) {
         const int s = n & 1;
         const uint32_t ph = (n >> 1) & 1;
         const int h = hk * group + n / tiles_per_head;
-        const int row = q_begin + (qt_begin + n % tiles_per_head) * BQ;
+        int sq0, sm0;
+        step_pos(n % tiles_per_head, sq0, sm0);
+        const int row = q_begin + sq0;
         if (!ptx::mbar_wait(&qdo_empty[s], ph ^ 1, abort_flag)) break;
         ptx::mbar_expect_tx(&qdo_full[s], 2 * Q_TILE_BYTES);
         ptx::tma_load_3d(sQ + s * Q_TILE_BYTES, &tmap_q, &qdo_full[s], 0, h, row);
@@ -243,7 +285,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     };
     for (int n = 0; n < n_steps && ok; n++) {
       const int h = hk * group + n / tiles_per_head;
-      const int q0 = (qt_begin + n % tiles_per_head) * BQ;
+      int q0, m0;
+      step_pos(n % tiles_per_head, q0, m0);
       // per-warp copy of the 64 row statistics of this query tile (no cross-warp synchronisation needed)
       float* lse_s = s_stats + ((warp - 2) * 2 + (n & 1)) * 128;
       float* delta_s = lse_s + BQ;
@@ -272,9 +315,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           for (int u = 0; u < 2; u++) {
             const int col = c * 32 + i + u;
             const int qpos = q0 + col;
+            const int mpos = m0 + col;  // query position for the masks (kpos is already global under context parallelism)
             bool vis = key_valid && qpos < q_len;
-            if (p.causal) vis = vis && (kpos <= qpos + shift);
-            if (p.window > 0) vis = vis && (kpos > qpos + shift - p.window);
+            if (p.causal) vis = vis && (kpos <= mpos + shift);
+            if (p.window > 0) vis = vis && (kpos > mpos + shift - p.window);
             const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i + u]), p.scale_log2, -lse_s[col])) : 0.f;
             pp[u] = pr;
             dd[u] = vis ? pr * (__uint_as_float(dv[i + u]) - delta_s[col]) * p.scale : 0.f;
@@ -310,16 +354,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       flush_dq(prev_h, prev_q0);
       // dK, dV rows of this key.  Every lane issues the warp-aligned TMEM loads; only the stores depend on key_valid.
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
+      const int64_t acc_off = (static_cast<int64_t>(kv_row + r) * p.num_kv_heads + hk) * HD;  // context parallel: row in the owner's accumulators
 #pragma unroll 1
       for (int which = 0; which < 2; which++) {
         __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
+        float* acc = cpm_on ? (which == 0 ? cpb.dk_acc[kv_owner] : cpb.dv_acc[kv_owner]) + acc_off : nullptr;
         const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
 #pragma unroll 1
         for (int c = 0; c < 4; c++) {
           uint32_t v[32];
           ptx::tmem_ld_32x32(src + c * 32, v);
           ptx::tmem_ld_wait();
-          if (key_valid) {
+          if (cpm_on) {
+            // partial sums of the queries of THIS rank: reduce into the key owner's fp32 rows (16-byte reductions, local or over NVLink)
+            if (key_valid) {
+#pragma unroll
+              for (int u = 0; u < 8; u++)
+                atomicAdd(reinterpret_cast<float4*>(acc + c * 32 + u * 4),
+                          make_float4(__uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]), __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3])));
+            }
+          } else if (key_valid) {
 #pragma unroll
             for (int u = 0; u < 4; u++) {
               uint4 pk;
@@ -334,7 +388,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
       }
-    } else if (n_steps == 0 && key_valid) {
+    } else if (n_steps == 0 && key_valid && !cpm_on) {
       // no query sees these keys: their gradients are zero
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
       for (int c = 0; c < HD; c += 8) {
@@ -417,10 +471,83 @@ NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k
   p.total_q = total_q;
   p.status = status;
   dim3 grid((max_seqlen_k + BK - 1) / BK, num_kv_heads, batch);
-  flash_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tdo, tk, tv, p);
+  p.cp = 0;
+  p.cp_me = 0;
+  p.cp_chunk = 0;
+  static const CpBwd no_cp = {};
+  flash_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tdo, tk, tv, p, no_cp);
   int rc = ntb_check_launch();
   if (rc) return rc;
   const int64_t n8 = static_cast<int64_t>(total_q) * num_heads * HD / 8;
   cast_dq_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), total_q, num_heads, dq_stride_t);
   return ntb_check_launch();
 }
+
+// Context-parallel backward (zig-zag layout, causal).  k_ptrs / v_ptrs: every rank's K / V as in ntb_flash_attn_fwd_cp; dk_acc_ptrs /
+// dv_acc_ptrs: every rank's fp32 [batch * 2 * chunk, Hkv, 128] accumulators, zeroed and made visible by a barrier before this launch.
+// dq (bf16, token stride dq_stride_t) is complete when the stream reaches the end of this call; dK / dV of this rank are complete in
+// its accumulators only after the NEXT cross-rank barrier (peers add into them); ntb_cast_f32_to_bf16_rows then converts them.
+NTB_EXPORT int ntb_flash_attn_bwd_cp(const void* dout, const void* q, const uint64_t* k_ptrs, const uint64_t* v_ptrs, const void* out, const float* lse, float* delta,
+                                     float* dq_acc, void* dq, const uint64_t* dk_acc_ptrs, const uint64_t* dv_acc_ptrs, int batch, int chunk, int cp, int me,
+                                     int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t kv_stride_t, int64_t kv_stride_h,
+                                     int64_t dq_stride_t, float softmax_scale, int* status, cudaStream_t stream) {
+  if (!bwd_get_encode() || batch <= 0 || chunk <= 0 || chunk % BK || cp < 1 || cp > CP_MAX || me < 0 || me >= cp || num_heads % num_kv_heads) return NTB_ERR_ARG;
+  if ((q_stride_t | q_stride_h | kv_stride_t | kv_stride_h | dq_stride_t) % 8) return NTB_ERR_ARG;
+  const int total = batch * 2 * chunk;
+  CUtensorMap tq, tdo;
+  CpBwd cpb = {};
+  if (!make_map(&tq, q, total, num_heads, q_stride_t, q_stride_h, BQ) || !make_map(&tdo, dout, total, num_heads, (int64_t)num_heads * HD, HD, BQ)) return NTB_ERR_ARG;
+  for (int r = 0; r < cp; r++) {
+    if ((k_ptrs[r] | v_ptrs[r] | dk_acc_ptrs[r] | dv_acc_ptrs[r]) & 15) return NTB_ERR_ARG;
+    if (!make_map(&cpb.k[r], reinterpret_cast<const void*>(k_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h, BK) ||
+        !make_map(&cpb.v[r], reinterpret_cast<const void*>(v_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h, BK))
+      return NTB_ERR_ARG;
+    cpb.dk_acc[r] = reinterpret_cast<float*>(dk_acc_ptrs[r]);
+    cpb.dv_acc[r] = reinterpret_cast<float*>(dv_acc_ptrs[r]);
+  }
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
+  }
+  {
+    const int64_t warps = static_cast<int64_t>(total) * num_heads;
+    delta_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, total, num_heads);
+  }
+  BwdParams p;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.causal = 1;
+  p.window = 0;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
+  p.lse = lse;
+  p.delta = delta;
+  p.dq_acc = dq_acc;
+  p.dk = nullptr;
+  p.dv = nullptr;
+  p.dk_stride_t = 0;
+  p.total_q = total;
+  p.status = status;
+  p.cp = cp;
+  p.cp_me = me;
+  p.cp_chunk = chunk;
+  dim3 grid(2 * cp * chunk / BK, num_kv_heads, batch);
+  flash_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tdo, cpb.k[me], cpb.v[me], p, cpb);
+  int rc = ntb_check_launch();
+  if (rc) return rc;
+  const int64_t n8 = static_cast<int64_t>(total) * num_heads * HD / 8;
+  cast_dq_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), total, num_heads, dq_stride_t);
+  return ntb_check_launch();
+}
+
+// fp32 [rows, heads, 128] -> bf16 with token stride dst_stride_t (head stride 128).
+NTB_EXPORT int ntb_cast_f32_to_bf16_rows(const float* src, void* dst, int64_t rows, int heads, int64_t dst_stride_t, cudaStream_t stream) {
+  if (rows <= 0 || heads <= 0 || dst_stride_t % 8) return NTB_ERR_ARG;
+  const int64_t n8 = rows * heads * HD / 8;
+  cast_dq_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), rows, heads, dst_stride_t);
+  return ntb_check_launch();
+}
+

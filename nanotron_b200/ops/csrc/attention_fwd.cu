@@ -10,6 +10,12 @@
 // Epilogue: O / l from TMEM straight to global memory (rows past the end of the sequence are not written), LSE to global.
 // Tiles hanging over the end of a packed sequence read the next sequence's keys: those columns are masked to -inf.
 // All barrier waits are bounded; a timeout raises `status` and the CTA unwinds.
+//
+// Context-parallel mode (p.cp > 0): the sequence is split in 2 * cp chunks of `cp_chunk` tokens and rank r holds chunks r and
+// 2 cp - 1 - r (zig-zag) of every batch row, one after the other.  Keys / values stay where they are: every rank's K and V live in
+// peer-mapped buffers and the TMA producer of this kernel reads the tiles it needs straight from their owner (one tensor map per
+// peer, per-CTA loads over NVLink), so the "ring exchange" happens tile by tile inside the attention kernel and overlaps its MMAs.
+// Masking uses global positions: key tile j covers global keys [128 j, 128 j + 128) wherever it is stored.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -36,6 +42,13 @@ struct FwdParams {
   float* lse;          // [Hq, T]
   int total_q;
   int* status;
+  int cp, cp_me, cp_chunk;  // context parallel: group size (0 = off), this rank, tokens per chunk (multiple of 128)
+};
+
+constexpr int CP_MAX = 8;
+struct CpMaps {
+  CUtensorMap k[CP_MAX];
+  CUtensorMap v[CP_MAX];
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -51,7 +64,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                 const FwdParams p) {
+                 const FwdParams p, const __grid_constant__ CpMaps cpm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -73,17 +86,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y;
-  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  const int k_begin = p.cu_k[b], k_len = p.cu_k[b + 1] - k_begin;
+  const bool cpm_on = p.cp > 0;
+  const int q_begin = cpm_on ? b * 2 * p.cp_chunk : p.cu_q[b];
+  const int q_len = cpm_on ? 2 * p.cp_chunk : p.cu_q[b + 1] - q_begin;
+  const int k_begin = cpm_on ? 0 : p.cu_k[b];
+  const int k_len = cpm_on ? 2 * p.cp * p.cp_chunk : p.cu_k[b + 1] - k_begin;
   // heavy (late) query tiles first: with a causal mask they have the most key tiles
   const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
   const int q0 = q_tile * BM;
   if (q0 >= q_len) return;  // uniform for the CTA
-  const int shift = k_len - q_len;  // bottom-right aligned causal mask
+  // position of the tile's first query for masking: local position, or the global one under context parallelism
+  int mq0 = q0;
+  if (cpm_on) {
+    const int half = q0 / p.cp_chunk;
+    const int chunk = half == 0 ? p.cp_me : 2 * p.cp - 1 - p.cp_me;
+    mq0 = chunk * p.cp_chunk + (q0 - half * p.cp_chunk);
+  }
+  const int shift = cpm_on ? 0 : k_len - q_len;  // bottom-right aligned causal mask
   int kv_end = k_len;
-  if (p.causal) kv_end = min(k_len, q0 + BM + shift);
+  if (p.causal) kv_end = min(k_len, mq0 + BM + shift);
   int kv_start = 0;
-  if (p.window > 0) kv_start = max(0, (q0 + shift - p.window + 1) / BN * BN);
+  if (p.window > 0) kv_start = max(0, (mq0 + shift - p.window + 1) / BN * BN);
   const int n_tiles = kv_end > kv_start ? (kv_end - kv_start + BN - 1) / BN : 0;
   const int hk = h / (p.num_heads / p.num_kv_heads);
 
@@ -124,15 +147,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       for (int j = 0; j < n_tiles; j++) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int krow = k_begin + kv_start + j * BN;
+        int krow = k_begin + kv_start + j * BN;
+        const CUtensorMap* mk = &tmap_k;
+        const CUtensorMap* mv = &tmap_v;
+        if (cpm_on) {
+          // global key tile -> the rank that stores it and the row inside that rank's [batch, 2 chunks] buffer
+          const int gk = kv_start + j * BN;
+          const int chunk = gk / p.cp_chunk;
+          const int owner = chunk < p.cp ? chunk : 2 * p.cp - 1 - chunk;
+          krow = b * 2 * p.cp_chunk + (chunk < p.cp ? 0 : p.cp_chunk) + (gk - chunk * p.cp_chunk);
+          mk = &cpm.k[owner];
+          mv = &cpm.v[owner];
+        }
         if (!ptx::mbar_wait(&k_empty[s], ph ^ 1, abort_flag)) break;
         ptx::mbar_expect_tx(&k_full[s], TILE_BYTES);
-        ptx::tma_load_3d(sK + s * TILE_BYTES, &tmap_k, &k_full[s], 0, hk, krow);
-        ptx::tma_load_3d(sK + s * TILE_BYTES + PANEL_BYTES, &tmap_k, &k_full[s], 64, hk, krow);
+        ptx::tma_load_3d(sK + s * TILE_BYTES, mk, &k_full[s], 0, hk, krow);
+        ptx::tma_load_3d(sK + s * TILE_BYTES + PANEL_BYTES, mk, &k_full[s], 64, hk, krow);
         if (!ptx::mbar_wait(&v_empty[s], ph ^ 1, abort_flag)) break;
         ptx::mbar_expect_tx(&v_full[s], TILE_BYTES);
-        ptx::tma_load_3d(sV + s * TILE_BYTES, &tmap_v, &v_full[s], 0, hk, krow);
-        ptx::tma_load_3d(sV + s * TILE_BYTES + PANEL_BYTES, &tmap_v, &v_full[s], 64, hk, krow);
+        ptx::tma_load_3d(sV + s * TILE_BYTES, mv, &v_full[s], 0, hk, krow);
+        ptx::tma_load_3d(sV + s * TILE_BYTES + PANEL_BYTES, mv, &v_full[s], 64, hk, krow);
       }
     }
   } else if (warp == 1) {
@@ -182,7 +216,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // ------------------------------------------------------------------ softmax / correction / epilogue
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;       // query row inside the tile
-    const int qpos = q0 + r;                  // position inside the sequence
+    const int qpos = q0 + r;                  // position inside the (local) sequence: validity and output row
+    const int mpos = mq0 + r;                 // position used by the masks
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -195,9 +230,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t tS = tmem_S + lane_addr + s * BN;
       // columns this row may look at: [lo, hi)
       int hi = k_len - k0;
-      if (p.causal) hi = min(hi, qpos + shift - k0 + 1);
+      if (p.causal) hi = min(hi, mpos + shift - k0 + 1);
       int lo = 0;
-      if (p.window > 0) lo = max(0, qpos + shift - p.window + 1 - k0);
+      if (p.window > 0) lo = max(0, mpos + shift - p.window + 1 - k0);
       const bool need_mask = (hi < BN) || (lo > 0);
       // pass 1: row max
       float mx = -INFINITY;
@@ -375,7 +410,56 @@ NTB_EXPORT int ntb_flash_attn_fwd(const void* q, const void* k, const void* v, v
   p.lse = lse;
   p.total_q = total_q;
   p.status = status;
+  p.cp = 0;
+  p.cp_me = 0;
+  p.cp_chunk = 0;
+  static const CpMaps no_cp = {};
   dim3 grid((max_seqlen_q + BM - 1) / BM, num_heads, batch);
-  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(tq, tk, tv, p);
+  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(tq, tk, tv, p, no_cp);
+  return ntb_check_launch();
+}
+
+// Context-parallel forward.  q: this rank's [batch * 2 * chunk, Hq, 128] (chunk r then chunk 2 cp - 1 - r of every batch row);
+// k_ptrs / v_ptrs: device addresses of every rank's [batch * 2 * chunk, Hkv, 128] K and V (peer-mapped, same strides everywhere,
+// filled and made visible by a cross-rank barrier before this launch).  Causal only.  out / lse as in ntb_flash_attn_fwd.
+NTB_EXPORT int ntb_flash_attn_fwd_cp(const void* q, const uint64_t* k_ptrs, const uint64_t* v_ptrs, void* out, float* lse, int batch, int chunk, int cp, int me,
+                                     int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t kv_stride_t, int64_t kv_stride_h,
+                                     float softmax_scale, int* status, cudaStream_t stream) {
+  if (!fa_get_encode() || batch <= 0 || chunk <= 0 || chunk % BM || cp < 1 || cp > CP_MAX || me < 0 || me >= cp || num_heads % num_kv_heads) return NTB_ERR_ARG;
+  if ((q_stride_t | q_stride_h | kv_stride_t | kv_stride_h) % 8) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15) return NTB_ERR_ARG;
+  const int total = batch * 2 * chunk;
+  CUtensorMap tq;
+  CpMaps maps = {};
+  if (!make_qkv_map(&tq, q, total, num_heads, q_stride_t, q_stride_h)) return NTB_ERR_ARG;
+  for (int r = 0; r < cp; r++) {
+    if ((k_ptrs[r] | v_ptrs[r]) & 15) return NTB_ERR_ARG;
+    if (!make_qkv_map(&maps.k[r], reinterpret_cast<const void*>(k_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h) ||
+        !make_qkv_map(&maps.v[r], reinterpret_cast<const void*>(v_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h))
+      return NTB_ERR_ARG;
+  }
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
+  }
+  FwdParams p;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.causal = 1;
+  p.window = 0;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.total_q = total;
+  p.status = status;
+  p.cp = cp;
+  p.cp_me = me;
+  p.cp_chunk = chunk;
+  dim3 grid(2 * chunk / BM, num_heads, batch);
+  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(tq, maps.k[me], maps.v[me], p, maps);
   return ntb_check_launch();
 }
