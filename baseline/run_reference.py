@@ -32,6 +32,9 @@ def run_reference(args):
     sys.path.insert(0, REF)
     os.environ.setdefault("WANDB_MODE", "disabled")
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "1")
+    # the reference's data-parallel path (replicated fp32 optimizer + DDP buckets) sits within a few GB of the 180 GB of a B200 for
+    # an 8B model: let the caching allocator grow segments instead of fragmenting, so that it gets every byte it can use
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29534")
     os.environ.setdefault("RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1"), os.environ.setdefault("LOCAL_RANK", "0")

@@ -104,7 +104,7 @@ class Qwen2Attention(nn.Module, LogMixin):
                 interleaved=config.rope_interleaved, seq_len_scaling_factor=getattr(config, "rope_seq_len_interpolation_factor", None),
             )
         self.attn_impl = config._attn_implementation or "flash_attention_2"
-        if self.cp_size > 1 and self.attn_impl not in ("ring", "llama3_ring_attention", "ring_flash_triton"):
+        if self.cp_size > 1 and self.attn_impl not in ("ring", "llama3_ring_attention", "ring_flash_triton", "ring_fused"):
             self.attn_impl = "ring"
         self.attention = ALL_ATTENTION_FUNCTIONS[self.attn_impl]
         self.sliding_window_size = getattr(config, "sliding_window_size", None)

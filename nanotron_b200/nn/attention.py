@@ -65,5 +65,6 @@ ALL_ATTENTION_FUNCTIONS: Dict[str, Callable] = {
     "ring_flash_triton": _ring("ring"),
     "ring": _ring("ring"),
     "llama3_ring_attention": _ring("allgather"),
+    "ring_fused": _ring("fused"),
 }
 AttentionImplementation = str

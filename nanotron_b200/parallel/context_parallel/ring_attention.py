@@ -62,6 +62,13 @@ def ring_attention(q, k, v, cp_pg, causal: bool = True, softmax_scale: Optional[
         cu = torch.arange(0, (b + 1) * s_local, s_local, dtype=torch.int32, device=q.device)
         return ops.flash_attn_varlen(q, k, v, cu, cu, s_local, s_local, causal=causal, softmax_scale=softmax_scale)
     assert causal, "zig-zag sharding is only meaningful for causal attention"
+    if variant == "fused" or ops._ATTN == "native":
+        from nanotron_b200.parallel.context_parallel import fused_ring
+
+        if fused_ring.supported(q, k, cp_pg, s_local // 2):
+            # K / V stay on their owners: the attention kernels read / reduce them over NVLink tile by tile
+            return fused_ring.fused_ring_attention(q, k, v, cp_pg, batch=b, softmax_scale=softmax_scale)
+        assert variant != "fused", "fused context-parallel attention needs CUDA, bf16, head_dim 128, chunks of a multiple of 128 tokens and cp <= 8 inside one node"
     rank = dist.get_rank(cp_pg)
     c = s_local // 2
     Hq, D = q.shape[1], q.shape[2]
