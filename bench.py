@@ -133,6 +133,10 @@ def run_native(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
     torch.cuda.set_device(local_rank)
+    ops.set_gemm(args.gemm)
+    from nanotron_b200.ops import native_gemm
+
+    native_gemm.set_variant(args.gemm_variant)
     cfg = build_config(args, world)
     trainer = DistributedTrainer(cfg)
     trainer.prepare_training()
@@ -206,7 +210,7 @@ def run_native(args):
                 "parallelism": f"dp{dp}" + ("+zero1" if dp > 1 else "") + (f"+tp{args.tp}(sequence-parallel, fused AG/RS kernels)" if args.tp > 1 else "") + (f"+pp{args.pp}(1f1b)" if args.pp > 1 else ""),
                 "dp_step": "in-tree NVLink kernels (reduce-scatter + AdamW + all-gather)" if getattr(trainer, "fused_dp", None) is not None else "NCCL", "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
                 "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush",
-                "gemm": ops._GEMM, "attention": ops._ATTN,
+                "gemm": ops._GEMM, "gemm_kernel": args.gemm_variant, "attention": ops._ATTN,
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * args.mbs * args.seq * 8 * args.accum, "d2h_bytes_per_step": 4},
@@ -229,6 +233,8 @@ def main():
     ap.add_argument("--mbs", type=int, default=1)
     ap.add_argument("--accum", type=int, default=8)
     ap.add_argument("--recompute", action="store_true")
+    ap.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "cublas"], help="auto: in-tree fused wgrad+accumulate, library forward/dgrad; tcgen05: every linear-layer product in-tree")
+    ap.add_argument("--gemm-variant", default="pair", choices=["single", "pair"], help="in-tree GEMM kernel: one CTA per 128x256 tile, or CTA pairs (cta_group::2) per 256x256 tile")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence-parallel mode); dp = gpus / (tp * pp)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (1F1B)")
     args = ap.parse_args()

@@ -1,6 +1,6 @@
 """Throughput of the fused compute + collective kernels against their rooflines and against the NCCL + library path.
 
-    torchrun --nproc-per-node N --master-addr 127.0.0.1 -m nanotron_b200.ops.bench_fused [tp] [dp] [ep]
+    torchrun --nproc-per-node N --master-addr 127.0.0.1 -m nanotron_b200.ops.bench_fused [tp] [dp] [ep] [cp]
 
 Every number is CUDA-event time on the launching stream, 3 warm-up + 10 timed iterations, maximum over ranks.
 Roofline of a fused kernel = the slower of (FLOPs / measured GEMM peak) and (bytes that must cross NVLink per GPU / 770 GB/s,
@@ -166,14 +166,50 @@ def bench_ep(group, rank, world, pk):
     ctx.check()
 
 
+def bench_cp(group, rank, world, pk):
+    from nanotron_b200 import ops
+    from nanotron_b200.parallel.context_parallel import fused_ring
+    from nanotron_b200.parallel.context_parallel.ring_attention import ring_attention
+
+    B, Hq, Hkv, D = 1, 32, 8, 128
+    S = 8192 * world  # 8192 local tokens per GPU (Llama-3-8B heads)
+    chunk = S // (2 * world)
+    T = 2 * chunk
+    torch.manual_seed(rank)
+    q, k, v = (torch.randn(T, h, D, device="cuda").to(torch.bfloat16).requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    g = torch.randn(T, Hq, D, device="cuda").to(torch.bfloat16)
+    pos = torch.zeros(B, T, dtype=torch.long, device="cuda")
+
+    def fused():
+        out = fused_ring.fused_ring_attention(q, k, v, group, batch=B)
+        out.backward(g)
+
+    def nccl():
+        ops.set_attention("auto")
+        out = ring_attention(q, k, v, cp_pg=group, causal=True, variant="allgather", position_ids=pos)
+        out.backward(g)
+
+    ms_f = timed(fused, n_iter=5)
+    ms_n = timed(nccl, n_iter=5)
+    # causal attention of this rank's 2 chunks against everything before them: forward 4 * q * keys * D per head, backward 2.5x
+    keys = sum((c + 1) * chunk for c in (rank, 2 * world - 1 - rank))
+    flops = 3.5 * 4.0 * chunk * (keys - chunk / 2.0) * Hq * D / 1.0
+    t = torch.tensor([flops], device="cuda")
+    tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+    link = (world - 1) / world * S * Hkv * D * 2 * 2 * 3  # K and V read in forward and backward, fp32-sized dK / dV traffic about the same again
+    roof = max(float(t) / (pk["bf16_tflops"] * 1e9), link / (NVLINK_GBS * 1e6))
+    say(rank, f"cp{world} causal attention fwd+bwd, seq {S} ({T} tokens per GPU)  in-kernel KV exchange {ms_f:7.3f} ms | NCCL all-gather + library attention {ms_n:7.3f} ms | roofline {roof:6.3f} ms -> {roof / ms_f:4.2f} of roofline")
+    fused_ring.get_context(group, T, Hkv).alloc.check()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     tdist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
     group = tdist.group.WORLD
     pk = _peaks()
-    what = sys.argv[1:] or ["tp", "dp", "ep"]
-    for name, fn in (("tp", bench_tp), ("dp", bench_dp), ("ep", bench_ep)):
+    what = sys.argv[1:] or ["tp", "dp", "ep", "cp"]
+    for name, fn in (("tp", bench_tp), ("dp", bench_dp), ("ep", bench_ep), ("cp", bench_cp)):
         if name in what:
             fn(group, rank, world, pk)
             torch.cuda.empty_cache()

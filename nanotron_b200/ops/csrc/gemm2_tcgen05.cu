@@ -1,0 +1,419 @@
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2 + TMEM + TMA), persistent and warp-specialised (sm_100a).
+//
+//   D[M,N] (=|+=) sum_k A(m,k) * B(n,k)          same operand-storage and output conventions as gemm_tcgen05.cu
+//
+// Two CTAs of a cluster (one per SM of a pair) work on one 256 x 256 output tile.  Each CTA keeps in its own shared memory the
+// 128 rows of A that it owns and HALF of the B tile (128 of the 256 output columns); one thread of the leader CTA issues
+// tcgen05.mma.cta_group::2 (256 x 256 x 16), the hardware reads both halves of B for both SMs, and each CTA's TMEM receives its
+// 128 rows x 256 columns of accumulators.  Per MMA each SM reads 8 KB of operands instead of the 12 KB of the one-CTA 128 x 256
+// tile, and its shared memory holds 32 KB per stage instead of 48, so six stages fit.
+//
+// Warp roles per CTA: warp 0 TMA producer (own A rows + own half of B into the CTA's own shared memory; the loads are the
+// cta_group::2 form of cp.async.bulk.tensor, whose completion bytes are counted on the LEADER's stage barrier, so the leader's MMA
+// thread waits on one barrier for both halves); warp 1: the MMA issuer in the leader, idle in the peer; warps 2..5 epilogue
+// (tcgen05.ld -> swizzled staging -> TMA store / reduce-add of the CTA's own rows).
+// Cross-CTA signals besides the loads are plain remote mbarrier arrives: the leader's producer forwards every "stage free" to the
+// peer's producer, one leader epilogue warp forwards "accumulator ready" to the peer's epilogue, and the peer's epilogue warps hand
+// accumulators back to the leader's MMA thread.  All waits are bounded; the two CTAs meet in a cluster barrier before TMEM is freed.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace {
+
+constexpr int P_BLOCK_M = 128;   // rows per CTA (256 per pair)
+constexpr int P_BLOCK_N = 256;   // columns per pair; each CTA stages 128 of them
+constexpr int P_HALF_N = 128;
+constexpr int P_BLOCK_K = 64;
+constexpr int P_UMMA_K = 16;
+constexpr int P_MAX_STAGES = 6;
+constexpr int P_A_BYTES = P_BLOCK_M * P_BLOCK_K * 2;  // 16 KiB
+constexpr int P_B_BYTES = P_HALF_N * P_BLOCK_K * 2;   // 16 KiB
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_EPI_WARPS = 4;
+constexpr int P_EPI_BUF = 32 * 128;
+constexpr int P_EPI_BYTES = P_EPI_WARPS * 2 * P_EPI_BUF;
+constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
+constexpr int P_SMEM = P_MAX_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 + 512;
+
+enum POut { P_OUT_BF16 = 0, P_OUT_F32 = 1, P_OUT_F32_ACCUM = 2 };
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cta address of this CTA -> shared::cluster address of the same location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Forwarding a hardware completion (nothing this thread wrote has to become visible): no release fence on the hot path.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at shared::cluster address `addr` once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma2_commit(uint32_t addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(addr) : "memory");
+}
+
+// Tiled loads whose mbarrier may live in the other CTA of the pair (`bar_cluster_addr` is a shared::cluster address).
+__device__ __forceinline__ void tma2_load_2d(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(ptx::smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(ptx::smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
+struct PTile {
+  int m_blk, n_blk;  // in units of 256 x 256 pair tiles
+};
+__device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n) {
+  constexpr int BAND = 4;
+  const int band_size = BAND * tiles_n;
+  const int band = t / band_size;
+  const int first_m = band * BAND;
+  const int rows = min(BAND, tiles_m - first_m);
+  const int r = t - band * band_size;
+  return {first_m + r % rows, r / rows};
+}
+
+template <bool A_MN, bool B_MN, int OUT, int P_STAGES>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
+                     int M, int N, int K, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_smem = smem + P_MAX_STAGES * P_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + P_EPI_BYTES);
+  uint64_t* full_bar = bars;                       // [STAGES]  (leader) both CTAs' loads of the stage have landed
+  uint64_t* empty_bar = bars + 2 * P_MAX_STAGES;       // [STAGES]  the MMAs that read this stage are done
+  uint64_t* tmem_full = bars + 3 * P_MAX_STAGES;       // [2]
+  uint64_t* tmem_empty = tmem_full + 2;            // [2]  (leader) both CTAs' epilogues have drained the accumulator
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
+  const int tiles_n = (N + P_BLOCK_N - 1) / P_BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + P_BLOCK_K - 1) / P_BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; s++) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      ptx::mbar_init(&tmem_full[b], 1);  // leader: the MMA commit; peer: the remote arrive that forwards it
+      ptx::mbar_init(&tmem_empty[b], 2 * P_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+    ptx::prefetch_tmap(&tmap_d);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_base_slot, 512);
+    tmem_relinquish2();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive or commit can reach them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (ptx::elect_one()) {
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const PTile tc = pair_tile(t, tiles_m, tiles_n);
+        const int m0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M;           // this CTA's rows of A
+        const int n0 = tc.n_blk * P_BLOCK_N + static_cast<int>(cta) * P_HALF_N;      // this CTA's half of B
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + s * P_STAGE_BYTES;
+          uint8_t* sb = sa + P_A_BYTES;
+          if (cta == 0) {
+            // the stage is free in both CTAs (the MMAs that read it are complete): tell the peer's producer, then expect both halves
+            if (it >= P_STAGES) mbar_arrive_cluster_relaxed(map_to_cta(ptx::smem_u32(&empty_bar[s]), 1));
+            ptx::mbar_expect_tx(&full_bar[s], 2 * P_STAGE_BYTES);
+          }
+          const uint32_t fb = map_to_cta(ptx::smem_u32(&full_bar[s]), 0);  // bytes of both CTAs are counted on the leader's barrier
+          if (A_MN) tma2_load_3d(sa, &tmap_a, fb, 0, kb * P_BLOCK_K, m0 / 64);
+          else      tma2_load_2d(sa, &tmap_a, fb, kb * P_BLOCK_K, m0);
+          if (B_MN) tma2_load_3d(sb, &tmap_b, fb, 0, kb * P_BLOCK_K, n0 / 64);
+          else      tma2_load_2d(sb, &tmap_b, fb, kb * P_BLOCK_K, n0);
+        }
+      }
+      if (!ok && cta == 1) {
+        // this CTA's loads in flight are counted on the leader's barrier: give them time to land before the shared memory goes away
+        const uint64_t t0 = ptx::globaltimer();
+        while (ptx::globaltimer() - t0 < 100000ull) {}
+      }
+      if (!ok && cta == 0) {
+        const uint64_t t0 = ptx::globaltimer();
+        for (int s = 0; s < P_STAGES; s++) {
+          const int last = it - 1 - ((it - 1 - s) % P_STAGES + P_STAGES) % P_STAGES;
+          if (it == 0 || last < 0) continue;
+          const uint32_t ph = (last / P_STAGES) & 1;
+          while (!ptx::mbar_try_wait(&full_bar[s], ph) && ptx::globaltimer() - t0 < NTB_WAIT_LIMIT_NS) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      if (cta == 0) {
+        // ---------------------------------------------------------------- MMA issuer (leader)
+        constexpr uint32_t idesc = ptx::make_idesc_bf16(2 * P_BLOCK_M, P_BLOCK_N, A_MN, B_MN);
+        int it = 0, tile_it = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
+          const int acc = tile_it & 1;
+          const uint32_t acc_ph = (tile_it >> 1) & 1;
+          if (!ptx::mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t tmem_d = tmem_base + acc * P_BLOCK_N;
+          for (int kb = 0; kb < k_blocks; kb++, it++) {
+            const int s = it % P_STAGES;
+            const uint32_t ph = (it / P_STAGES) & 1;
+            if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t sa = ptx::smem_u32(smem + s * P_STAGE_BYTES);
+            const uint32_t sb = sa + P_A_BYTES;
+#pragma unroll
+            for (int k = 0; k < P_BLOCK_K / P_UMMA_K; k++) {
+              const uint64_t adesc = A_MN ? ptx::make_smem_desc(sa + k * P_UMMA_K * 128, P_BLOCK_K * 128, 1024) : ptx::make_smem_desc(sa + k * P_UMMA_K * 2, 16, 1024);
+              const uint64_t bdesc = B_MN ? ptx::make_smem_desc(sb + k * P_UMMA_K * 128, P_BLOCK_K * 128, 1024) : ptx::make_smem_desc(sb + k * P_UMMA_K * 2, 16, 1024);
+              umma2_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma2_commit(ptx::smem_u32(&empty_bar[s]));  // the stage is free once these MMAs (in both SMs) have read it
+          }
+          if (ok) umma2_commit(ptx::smem_u32(&tmem_full[acc]));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    uint8_t* my_epi = epi_smem + (warp - 2) * 2 * P_EPI_BUF;
+    constexpr bool BF16_OUT = (OUT == P_OUT_BF16);
+    constexpr int CHUNK_COLS = BF16_OUT ? 64 : 32;
+    constexpr int CHUNKS = P_BLOCK_N / CHUNK_COLS;
+    int tile_it = 0, buf = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
+      const PTile tc = pair_tile(t, tiles_m, tiles_n);
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1;
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
+      if (cta == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_full[acc]), 1));  // forward to the peer's epilogue
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * P_BLOCK_N;
+      const int row0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; c++) {
+        uint8_t* stage_buf = my_epi + buf * P_EPI_BUF;
+        if (lane == 0) ptx::tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* my_row = stage_buf + lane * 128;
+        if (BF16_OUT) {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32(taddr + c * 64, r0);
+          ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint32_t* src = (j < 4) ? &r0[j * 8] : &r1[(j - 4) * 8];
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = pk;
+          }
+        } else {
+          uint32_t r0[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r0);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            uint4 pk = make_uint4(r0[j * 4], r0[j * 4 + 1], r0[j * 4 + 2], r0[j * 4 + 3]);
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = pk;
+          }
+        }
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          const int x = tc.n_blk * P_BLOCK_N + c * CHUNK_COLS;
+          if (x < N && row0 < M) {
+            if (OUT == P_OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
+            else ptx::tma_store_2d(&tmap_d, stage_buf, x, row0);
+          }
+          ptx::tma_commit_group();
+        }
+        buf ^= 1;
+      }
+      // accumulator fully read: hand it back to the leader's MMA thread (a remote arrive from the peer CTA)
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (cta == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+        else mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_empty[acc]), 0));
+      }
+    }
+    if (lane == 0) ptx::tma_wait_group<0>();
+    __syncwarp();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the leader's MMAs write the peer's TMEM and read its shared memory: nobody leaves or frees before both are done
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, NTB_ERR_TIMEOUT);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn p_get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+bool p_map_kmajor(CUtensorMap* m, const void* ptr, int64_t rows, int64_t k, int64_t ld) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t es[2] = {1, 1};
+  return p_get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+bool p_map_mnmajor(CUtensorMap* m, const void* ptr, int64_t mn, int64_t k, int64_t ld) {
+  cuuint64_t dims[3] = {64, (cuuint64_t)k, (cuuint64_t)((mn + 63) / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)P_BLOCK_K, 2};
+  cuuint32_t es[3] = {1, 1, 1};
+  return p_get_encode()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+bool p_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld, bool f32) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (f32 ? 4 : 2)};
+  cuuint32_t box[2] = {(cuuint32_t)(f32 ? 32 : 64), 32};
+  cuuint32_t es[2] = {1, 1};
+  return p_get_encode()(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, int OUT, int ST = P_MAX_STAGES>
+int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream) {
+  if (ST == P_MAX_STAGES) {
+    // experiment knob: NTB_PAIR_STAGES=3 runs the forward layout with a 3-stage ring (same shared-memory footprint)
+    const char* e = getenv("NTB_PAIR_STAGES");
+    if (e && atoi(e) == 3 && !A_MN && !B_MN && OUT == P_OUT_BF16) return p_launch<false, false, P_OUT_BF16, 3>(ta, tb, td, M, N, K, status, num_sms, stream);
+  }
+  auto kern = gemm2_tcgen05_kernel<A_MN, B_MN, OUT, ST>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
+  }
+  const long long tiles = static_cast<long long>((M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M)) * ((N + P_BLOCK_N - 1) / P_BLOCK_N);
+  long long pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(P_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, status) != cudaSuccess) {
+    cudaGetLastError();
+    return NTB_ERR_LAUNCH;
+  }
+  return ntb_check_launch();
+}
+
+}  // namespace
+
+// Same contract as ntb_gemm_bf16 (gemm_tcgen05.cu); additionally M-major / N-major operands need M % 128 == 0 / N % 128 == 0 is NOT
+// required: edges are clipped by TMA.  a_mn / b_mn: 0 = K-major, 1 = MN-major.  out_mode: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate.
+NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_mode,
+                              int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !p_get_encode()) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
+  if (a_mn ? (lda % 64 || M % 64) : (lda % 8)) return NTB_ERR_ARG;
+  if (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) return NTB_ERR_ARG;
+  if (out_mode == P_OUT_BF16 ? (ldd % 8) : (ldd % 4)) return NTB_ERR_ARG;
+  if (num_sms <= 1) num_sms = 148;
+  CUtensorMap ta, tb, td;
+  bool ok = a_mn ? p_map_mnmajor(&ta, a, M, K, lda) : p_map_kmajor(&ta, a, M, K, lda);
+  ok = ok && (b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb));
+  ok = ok && p_map_out(&td, d, M, N, ldd, out_mode != P_OUT_BF16);
+  if (!ok) return NTB_ERR_ARG;
+#define NTB_P_CASE(AM, BM, OM) \
+  if (a_mn == AM && b_mn == BM && out_mode == OM) return p_launch<AM != 0, BM != 0, OM>(ta, tb, td, M, N, K, status, num_sms, stream);
+  NTB_P_CASE(0, 0, 0) NTB_P_CASE(0, 0, 1) NTB_P_CASE(0, 0, 2)
+  NTB_P_CASE(0, 1, 0) NTB_P_CASE(0, 1, 1) NTB_P_CASE(0, 1, 2)
+  NTB_P_CASE(1, 1, 0) NTB_P_CASE(1, 1, 1) NTB_P_CASE(1, 1, 2)
+  NTB_P_CASE(1, 0, 0) NTB_P_CASE(1, 0, 1) NTB_P_CASE(1, 0, 2)
+#undef NTB_P_CASE
+  return NTB_ERR_ARG;
+}

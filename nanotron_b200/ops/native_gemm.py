@@ -13,7 +13,14 @@ from typing import Optional
 
 import torch
 
-_HAS = {"gemm": False}
+_HAS = {"gemm": False, "pair": False}
+# "single": one CTA per 128 x 256 tile (gemm_tcgen05.cu); "pair": two CTAs per 256 x 256 tile with cta_group::2 (gemm2_tcgen05.cu)
+VARIANT = {"kernel": "pair"}
+
+
+def set_variant(name: str):
+    assert name in ("single", "pair")
+    VARIANT["kernel"] = name
 _STATUS = {}
 _SMS = {}
 
@@ -23,6 +30,10 @@ def declare(L):
     if _HAS["gemm"]:
         L.ntb_gemm_bf16.restype = c_int
         L.ntb_gemm_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+    _HAS["pair"] = hasattr(L, "ntb_gemm2_bf16")
+    if _HAS["pair"]:
+        L.ntb_gemm2_bf16.restype = c_int
+        L.ntb_gemm2_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
 
 
 def status_word(device) -> torch.Tensor:
@@ -76,8 +87,10 @@ def _launch(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode):
     from nanotron_b200.ops import native
 
     dev = a.device
+    L = native.lib()
+    fn = L.ntb_gemm2_bf16 if (VARIANT["kernel"] == "pair" and _HAS["pair"]) else L.ntb_gemm_bf16
     with torch.cuda.device(dev):
-        rc = native.lib().ntb_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(dev).data_ptr(), _sms(dev), torch.cuda.current_stream(dev).cuda_stream)
+        rc = fn(a.data_ptr(), b.data_ptr(), d.data_ptr(), M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(dev).data_ptr(), _sms(dev), torch.cuda.current_stream(dev).cuda_stream)
     native._check(rc, "gemm_tcgen05")
     return d
 

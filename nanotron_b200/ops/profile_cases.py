@@ -25,9 +25,11 @@ def case_gemm():
     w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
     dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
     acc = torch.zeros(N, K, device="cuda", dtype=torch.float32)
-    _twice(lambda: g.gemm_nt(x, w))
-    _twice(lambda: g.gemm_nn(dy, w))
-    _twice(lambda: g.gemm_tn_accum_fp32(dy, x, acc))
+    for variant in ("single", "pair"):
+        g.set_variant(variant)
+        _twice(lambda: g.gemm_nt(x, w))
+        _twice(lambda: g.gemm_nn(dy, w))
+        _twice(lambda: g.gemm_tn_accum_fp32(dy, x, acc))
     g.check_status("cuda")
 
 

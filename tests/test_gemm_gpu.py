@@ -6,6 +6,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=["single", "pair"], autouse=True)
+def gemm_variant(request):
+    """Every test runs on both in-tree kernels: one CTA per tile, and CTA pairs (cta_group::2)."""
+    from nanotron_b200.ops import native_gemm
+
+    old = native_gemm.VARIANT["kernel"]
+    native_gemm.set_variant(request.param)
+    yield request.param
+    native_gemm.set_variant(old)
+
+
 def _rel_err(got, exp):
     return ((got.float() - exp).abs().max() / exp.abs().max().clamp(min=1e-6)).item()
 
