@@ -168,7 +168,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1;
-          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 64)) { ok = false; break; }
           uint8_t* sa = smem + s * P_STAGE_BYTES;
           uint8_t* sb = sa + P_A_BYTES;
           if (cta == 0) {
@@ -243,7 +243,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const PTile tc = pair_tile(t, tiles_m, tiles_n);
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
-      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 256)) { ok = false; break; }
       if (cta == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_full[acc]), 1));  // forward to the peer's epilogue
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * P_BLOCK_N;

@@ -207,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int kb = 0; kb < tc.kbs; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 64)) { ok = false; break; }
           uint8_t* sa = smem + s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
           const int kx = (tc.kb0 + kb) * BLOCK_K;
@@ -282,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       tile_it++;
-      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) { ok = false; break; }
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 256)) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
       const int row0 = tc.m_blk * BLOCK_M + q * 32;

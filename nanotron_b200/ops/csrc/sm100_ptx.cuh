@@ -61,13 +61,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. `abort_flag` (shared memory) lets one role tell the others to stop waiting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 2048; i++)
+// `sleep_ns` > 0 makes a waiter that is expected to wait long (an epilogue warp during a main loop, a producer on a full ring)
+// back off between polls instead of spinning: polling warps cost issue slots and power, and on a power-capped GPU that power is
+// taken from the tensor cores' clock.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns = 0) {
+  for (int i = 0; i < (sleep_ns ? 8 : 2048); i++)
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer();
   while (true) {
-    for (int i = 0; i < 64; i++)
+    for (int i = 0; i < 64; i++) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (sleep_ns) __nanosleep(sleep_ns);
+    }
     if (*abort_flag) return false;
     if (globaltimer() - t0 > NTB_WAIT_LIMIT_NS) {
       *abort_flag = 1;
