@@ -1,7 +1,10 @@
 """Writes ``examples/config_tiny_llama.yaml``: a tiny Llama on dummy data, dp2 x tp2 x pp2 (8 processes)."""
 import os
+import sys
 
-from nanotron_b200.config import (
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nanotron_b200.config import (  # noqa: E402
     AdamWOptimizerArgs, CheckpointsArgs, Config, DataArgs, DatasetStageArgs, GeneralArgs, LlamaConfig, LoggingArgs, LRSchedulerArgs,
     ModelArgs, OptimizerArgs, ParallelismArgs, RandomInit, TokenizerArgs, TokensArgs,
 )

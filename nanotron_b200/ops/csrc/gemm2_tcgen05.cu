@@ -96,8 +96,9 @@ __device__ __forceinline__ void tma2_load_3d(void* smem_dst, const CUtensorMap* 
 struct PTile {
   int m_blk, n_blk;  // in units of 256 x 256 pair tiles
 };
-__device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n) {
-  constexpr int BAND = 4;
+// Tiles are visited column by column inside bands of `BAND` tile rows: the band's rows of A stay in L2 while B streams through
+// once per band.  The host picks the band so that its A rows take about a third of L2, i.e. B is re-read as rarely as possible.
+__device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n, int BAND) {
   const int band_size = BAND * tiles_n;
   const int band = t / band_size;
   const int first_m = band * BAND;
@@ -109,7 +110,7 @@ __device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n) {
 template <bool A_MN, bool B_MN, int OUT, int P_STAGES>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                     int M, int N, int K, int* __restrict__ status) {
+                     int M, int N, int K, int band, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + P_MAX_STAGES * P_STAGE_BYTES;
@@ -162,13 +163,13 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int it = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const PTile tc = pair_tile(t, tiles_m, tiles_n);
+        const PTile tc = pair_tile(t, tiles_m, tiles_n, band);
         const int m0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M;           // this CTA's rows of A
         const int n0 = tc.n_blk * P_BLOCK_N + static_cast<int>(cta) * P_HALF_N;      // this CTA's half of B
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1;
-          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 64)) { ok = false; break; }
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 200)) { ok = false; break; }
           uint8_t* sa = smem + s * P_STAGE_BYTES;
           uint8_t* sb = sa + P_A_BYTES;
           if (cta == 0) {
@@ -240,10 +241,10 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     int tile_it = 0, buf = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
-      const PTile tc = pair_tile(t, tiles_m, tiles_n);
+      const PTile tc = pair_tile(t, tiles_m, tiles_n, band);
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
-      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 256)) { ok = false; break; }
+      if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 1000)) { ok = false; break; }
       if (cta == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_full[acc]), 1));  // forward to the peer's epilogue
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * P_BLOCK_N;
@@ -384,7 +385,12 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, status) != cudaSuccess) {
+  // rows of A (256 per tile row, K deep, bf16) that should stay resident in the 126 MB L2 while B streams: about 40 MB
+  int band = static_cast<int>(40000000ll / (512ll * (K > 0 ? K : 1)));
+  const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
+  if (band < 2) band = 2;
+  if (band > tiles_m) band = tiles_m;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status) != cudaSuccess) {
     cudaGetLastError();
     return NTB_ERR_LAUNCH;
   }
