@@ -71,14 +71,12 @@ def _use_native(t: torch.Tensor) -> bool:
 
 # ============================================================================ GEMM
 def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor, kind: str) -> bool:
-    """Which GEMMs run on the in-tree tcgen05 kernel.  "auto": the weight-gradient product with fp32 accumulation
-    (a fused op the library does not offer: it would need a bf16 product plus a separate fp32 add) always does;
-    plain forward / dgrad products go to the library.  "tcgen05": everything the kernel supports.  "cublas": nothing."""
+    """Which GEMMs run on the in-tree tcgen05 kernels.  "auto": every linear-layer product (forward, dgrad, wgrad with or without
+    fp32 accumulation) whose operands the kernels accept and that is large enough to fill the GPU; small or oddly shaped
+    products go to the library.  "tcgen05": the same without the size threshold.  "cublas": nothing (comparison runs)."""
     if _GEMM == "cublas" or not a.is_cuda or _MODE == "torch":
         return False
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
-        return False
-    if _GEMM == "auto" and kind != "wgrad_accum":
         return False
     from nanotron_b200.ops import native
 
