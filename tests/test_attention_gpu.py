@@ -73,3 +73,39 @@ def test_flash_bwd_matches_oracle(lens, Hq, Hkv, causal):
         err = (a.float() - b).abs().max().item()
         ref_mag = b.abs().max().item()
         assert err < 3e-2 * max(ref_mag, 1.0), f"{name}: max err {err} vs magnitude {ref_mag}"
+
+
+def test_fused_qkv_rope_attention_matches_composition():
+    """RoPE + attention on the fused projection output with one gradient buffer == rotate q / k, attend, differentiate (fp32)."""
+    from nanotron_b200 import ops
+
+    lens, Hq, Hkv, D = [200, 312], 4, 2, 128
+    T = sum(lens)
+    cu = torch.tensor([0, 200, 512], dtype=torch.int32, device=DEV)
+    positions = torch.cat([torch.arange(n, device=DEV) for n in lens])
+    cos, sin = ref.rope_cos_sin(torch.arange(512, device=DEV), D, 10000.0)
+    torch.manual_seed(3)
+    qkv0 = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16)
+    g = torch.randn(T, Hq, D, device=DEV, dtype=torch.bfloat16)
+    # oracle in fp32
+    x = qkv0.float().requires_grad_(True)
+    q = x[:, : Hq * D].view(T, Hq, D)
+    k = x[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    v = x[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    c, s_ = cos[positions], sin[positions]
+    qr, kr = ref.rope_apply(q, c, s_, False), ref.rope_apply(k, c, s_, False)
+    exp = ref.attention_varlen(qr, kr, v, cu, cu, causal=True, softmax_scale=1 / math.sqrt(D))
+    exp.backward(g.float())
+    # fused op (it rotates its input in place: give it a copy)
+    ops.set_attention("native")
+    try:
+        y = qkv0.clone().requires_grad_(True)
+        buf = y * 1  # non-leaf, as the projection output is
+        assert ops.fused_qkv_attention_supported(buf, Hq, Hkv, D, None)
+        out = ops.fused_qkv_attention(buf, cos, sin, positions, Hq, Hkv, D, cu, max(lens))
+        out.backward(g)
+    finally:
+        ops.set_attention("auto")
+    torch.testing.assert_close(out.float(), exp.detach(), atol=3e-2, rtol=3e-2)
+    err = (y.grad.float() - x.grad).abs().max() / x.grad.abs().max()
+    assert err < 3e-2, float(err)
