@@ -167,3 +167,22 @@ def test_dataloader_worker_failure_propagates():
         for _ in dl:
             pass
     assert "disk went away" in str(ei.value)
+
+
+def test_trainer_writes_heartbeats(tmp_path):
+    import json
+
+    from nanotron_b200.trainer import DistributedTrainer
+
+    single_process_env()
+    os.environ["NANOTRON_HEARTBEAT_DIR"] = str(tmp_path / "hb")
+    os.environ["NANOTRON_HEARTBEAT_INTERVAL"] = "0.05"
+    try:
+        cfg = make_config(tiny_llama_config(), seq=16, mbs=1, steps=3, ckpt_path=str(tmp_path / "ckpt"), ckpt_interval=1000)
+        t = DistributedTrainer(cfg)
+        t.train({"stable": dummy_dataloader(t)})
+        beat = json.load(open(tmp_path / "hb" / "rank_0.json"))
+        assert beat["state"] == "done" and beat["step"] == 3 and beat["rank"] == 0
+        t.parallel_context.destroy()
+    finally:
+        del os.environ["NANOTRON_HEARTBEAT_DIR"], os.environ["NANOTRON_HEARTBEAT_INTERVAL"]
