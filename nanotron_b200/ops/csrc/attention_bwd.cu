@@ -104,8 +104,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* sdp_full = bars + 5;     // 1
   uint64_t* pds_full = bars + 6;     // 1
   uint64_t* mma_done = bars + 7;     // 1  (dV, dK, dQ^T products of a step finished)
-  uint64_t* sdp_read = bars + 8;     // 1  (S^T and dP^T of a step are in registers: their TMEM columns may be overwritten)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -164,7 +163,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     ptx::mbar_init(sdp_full, 1);
     ptx::mbar_init(pds_full, 4);
     ptx::mbar_init(mma_done, 1);
-    ptx::mbar_init(sdp_read, 4);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -238,13 +236,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (ok) ok = issue_s(0);
       for (int n = 0; n < n_steps && ok; n++) {
         const int s = n & 1;
-        // S^T / dP^T of the next step are issued as soon as the softmax warps hold this step's in registers, so they are computed
-        // while the exponentials of this step run
-        if (n + 1 < n_steps) {
-          if (!ptx::mbar_wait(sdp_read, n & 1, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after();
-          if (!issue_s(n + 1)) { ok = false; break; }
-        }
         if (!ptx::mbar_wait(pds_full, n & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
@@ -264,6 +255,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         ptx::umma_commit(&qdo_empty[s]);
         ptx::umma_commit(mma_done);
+        if (n + 1 < n_steps) {
+          if (!issue_s(n + 1)) { ok = false; break; }
+        }
       }
     }
   } else {
@@ -308,20 +302,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t pk_p[32], pk_ds[32];  // 64 bf16 each
-      // S^T and dP^T (64 columns each) come into registers with four loads and one wait; their TMEM columns then go back to the
-      // MMA warp, which issues the next step's S^T / dP^T while this step's exponentials run
-      uint32_t sv[2][32], dv[2][32];
 #pragma unroll
       for (int c = 0; c < 2; c++) {
-        ptx::tmem_ld_32x32(tm_ST + lane_addr + c * 32, sv[c]);
-        ptx::tmem_ld_32x32(tm_dPT + lane_addr + c * 32, dv[c]);
-      }
-      ptx::tmem_ld_wait();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(sdp_read);
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+        uint32_t sv[32], dv[32];
+        ptx::tmem_ld_32x32(tm_ST + lane_addr + c * 32, sv);
+        ptx::tmem_ld_32x32(tm_dPT + lane_addr + c * 32, dv);
+        ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float pp[2], dd[2];
@@ -333,9 +319,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             bool vis = key_valid && qpos < q_len;
             if (p.causal) vis = vis && (kpos <= mpos + shift);
             if (p.window > 0) vis = vis && (kpos > mpos + shift - p.window);
-            const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[c][i + u]), p.scale_log2, -lse_s[col])) : 0.f;
+            const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i + u]), p.scale_log2, -lse_s[col])) : 0.f;
             pp[u] = pr;
-            dd[u] = vis ? pr * (__uint_as_float(dv[c][i + u]) - delta_s[col]) * p.scale : 0.f;
+            dd[u] = vis ? pr * (__uint_as_float(dv[i + u]) - delta_s[col]) * p.scale : 0.f;
           }
           __nv_bfloat162 hp = __floats2bfloat162_rn(pp[0], pp[1]), hd = __floats2bfloat162_rn(dd[0], dd[1]);
           pk_p[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hp);

@@ -60,20 +60,6 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
-// 2^x for x <= 0 on the FMA / ALU pipes: round to the nearest integer n with the 1.5 * 2^23 trick, a degree-4 polynomial for
-// 2^f on f in [-0.5, 0.5] (relative error ~4e-5, far below the bf16 rounding of P), then n added into the exponent field.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float xr = x + 12582912.f;
-  const int n = __float_as_int(xr) - 0x4B400000;
-  const float f = x - (xr - 12582912.f);
-  float p = fmaf(f, 0.0096181291f, 0.0555041087f);
-  p = fmaf(p, f, 0.2402265070f);
-  p = fmaf(p, f, 0.6931471806f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (n << 23));
-}
-
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
@@ -248,29 +234,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int lo = 0;
       if (p.window > 0) lo = max(0, mpos + shift - p.window + 1 - k0);
       const bool need_mask = (hi < BN) || (lo > 0);
-      // the whole score row (128 fp32) comes into registers with four loads and ONE wait; the TMEM buffer is then free for the
-      // QK^T of tile j + 2 while this warp is still busy with the exponentials
-      uint32_t sv[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; c++) ptx::tmem_ld_32x32(tS + c * 32, sv[c]);
-      ptx::tmem_ld_wait();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&s_empty[s]);
+      // pass 1: row max
       float mx = -INFINITY;
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < 4; c++)
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(tS + c * 32, v);
+        ptx::tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; i++) {
             const int col = c * 32 + i;
-            if (col >= lo && col < hi) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+            if (col >= lo && col < hi) mx = fmaxf(mx, __uint_as_float(v[i]));
           }
-      } else {
+        } else {
 #pragma unroll
-        for (int c = 0; c < 4; c++)
-#pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
       }
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // fully masked row so far: keep exp2 finite
@@ -293,19 +273,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_st_wait();
         }
       }
-      // probabilities -> bf16 -> shared memory (A operand of P*V), row sum.  One exponential in four is evaluated as a polynomial
-      // on the FMA pipe: the special-function unit (16 exp2 per clock per SM) is the scarcest resource of this loop.
+      // pass 2: probabilities -> bf16 -> shared memory (A operand of P*V), row sum
       float sum = 0.f;
       const float neg_m = -m_use * p.scale_log2;
       uint8_t* prow0 = sP + r * 128;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 4; c++) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(tS + c * 32, v);
+        ptx::tmem_ld_wait();
         float e[32];
 #pragma unroll
         for (int i = 0; i < 32; i++) {
           const int col = c * 32 + i;
-          const float t = fmaf(__uint_as_float(sv[c][i]), p.scale_log2, neg_m);
-          float x = (i & 3) == 3 ? exp2_poly(t) : exp2f(t);
+          float x = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, neg_m));
           if (need_mask && (col < lo || col >= hi)) x = 0.f;
           e[i] = x;
           sum += x;
@@ -324,10 +305,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
-      // P written: tell the MMA warp (the S buffer was handed back right after it was read)
+      // S buffer read, P written: tell the MMA warp
+      ptx::tc_fence_before();
       ptx::fence_proxy_async();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(p_full);
+      if (lane == 0) {
+        ptx::mbar_arrive(&s_empty[s]);
+        ptx::mbar_arrive(p_full);
+      }
     }
     // ------------------------------------------------------------------ epilogue
     if (ok && ptx::mbar_wait(pv_done, (n_tiles - 1) & 1, abort_flag)) {
