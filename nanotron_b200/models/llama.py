@@ -94,8 +94,7 @@ class LlamaDecoderLayer(nn.Module):
         self.recompute_layer = parallel_config.recompute_layer if parallel_config is not None else False
 
     def _core_forward(self, hidden_states, sequence_mask):
-        residual = hidden_states
-        normed = self.input_layernorm(hidden_states)
+        normed, residual = self.input_layernorm(hidden_states, prenorm=True)
         attn_out = self.attn(hidden_states=normed, sequence_mask=sequence_mask)["hidden_states"]
         normed, residual = self.post_attention_layernorm(attn_out, residual=residual)
         hidden_states = self.mlp(hidden_states=normed)["hidden_states"] + residual

@@ -126,6 +126,17 @@ class Qwen2Attention(nn.Module, LogMixin):
             out = ops.fused_qkv_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, cu, s, causal=True, window=self.sliding_window_size, interleaved=interleaved, use_rope=self.use_rope)
             out = self.o_proj(out.reshape(T, self.local_q_size))
             return {"hidden_states": out, "position_ids": position_ids}
+        if self.cp_size == 1 and self.attn_impl == "flash_attention_2" and ops.fused_qkv_library_attention_supported(qkv, self.head_dim, self.sliding_window_size, cu_seqlens):
+            b, s = position_ids.shape
+            if self.use_rope:
+                self.rotary_emb._ensure_tables(self.rotary_emb.max_seq_len, qkv.device)
+                cos, sin, interleaved = self.rotary_emb.cos_table, self.rotary_emb.sin_table, self.rotary_emb.interleaved
+            else:
+                cos = sin = None
+                interleaved = False
+            out = ops.fused_qkv_library_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, b, s, interleaved=interleaved, use_rope=self.use_rope)
+            out = self.o_proj(out.reshape(T, self.local_q_size))
+            return {"hidden_states": out, "position_ids": position_ids}
         q = qkv[:, : self.local_q_size].view(T, self.local_heads, self.head_dim)
         k = qkv[:, self.local_q_size : self.local_q_size + self.local_kv_size].view(T, self.local_kv_heads, self.head_dim)
         v = qkv[:, self.local_q_size + self.local_kv_size :].view(T, self.local_kv_heads, self.head_dim)
@@ -165,8 +176,7 @@ class Qwen2DecoderLayer(nn.Module):
         self.use_doc_masking = getattr(config, "_use_doc_masking", False)
 
     def _core_forward(self, hidden_states, position_ids, cu_seqlens=None):
-        residual = hidden_states
-        normed = self.input_layernorm(hidden_states)
+        normed, residual = self.input_layernorm(hidden_states, prenorm=True)
         attn_out = self.attn(hidden_states=normed, position_ids=position_ids, cu_seqlens=cu_seqlens)["hidden_states"]
         normed, residual = self.post_attention_layernorm(attn_out, residual=residual)
         mlp_out = self.mlp(hidden_states=normed)

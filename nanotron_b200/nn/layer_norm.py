@@ -21,9 +21,11 @@ class RMSNorm(nn.Module):
         nn.init.ones_(self.weight)
 
     def forward(self, input, residual=None, dropout_p=0.0, prenorm=False, residual_in_fp32=False, return_dropout_mask=False):
-        """With ``residual``: returns (norm(input + residual), input + residual)."""
+        """With ``residual``: returns (norm(input + residual), input + residual).  With ``prenorm`` and no residual: returns
+        (norm(input), input); taking the skip connection from that second output lets the backward kernel sum the two
+        gradient paths of ``input`` itself."""
         assert dropout_p == 0.0 and not return_dropout_mask, "dropout inside the norm is not supported"
-        return ops.rms_norm(input, self.weight, self.eps, residual=residual)
+        return ops.rms_norm(input, self.weight, self.eps, residual=residual, return_input=prenorm and residual is None)
 
 
 class LayerNorm(nn.Module):

@@ -162,7 +162,7 @@ def masked_embedding(ids: torch.Tensor, weight: torch.Tensor, min_id: int, max_i
 # ============================================================================ norms
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, eps, residual):
+    def forward(ctx, x, weight, eps, residual, passthrough=False):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         r2 = residual.reshape(-1, shape[-1]) if residual is not None else None
@@ -177,6 +177,10 @@ class _RMSNorm(torch.autograd.Function):
         ctx.shape = shape
         if residual is not None:
             return y.view(shape), pre.view(shape)
+        if passthrough:
+            # the input comes back as a second output, so the gradient of its other consumers arrives here as ``dpre`` and the
+            # backward kernel adds it while it writes dx (no separate accumulation kernel in autograd)
+            return y.view(shape), x
         return y.view(shape), None
 
     @staticmethod
@@ -191,13 +195,15 @@ class _RMSNorm(torch.autograd.Function):
         else:
             dx, dw = ref.rms_norm_bwd(dy2, pre, weight, rstd, dres)
         dx = dx.view(ctx.shape)
-        return dx, dw.to(weight.dtype), None, (dx if ctx.has_residual else None)
+        return dx, dw.to(weight.dtype), None, (dx if ctx.has_residual else None), None
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
-    """Returns ``y`` (no residual) or ``(y, x + residual)``: the fused residual-add + norm used between blocks."""
-    y, pre = _RMSNorm.apply(x, weight, eps, residual)
-    return y if residual is None else (y, pre)
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None, return_input: bool = False):
+    """Returns ``y`` (no residual) or ``(y, x + residual)``: the fused residual-add + norm used between blocks.
+    ``return_input`` (without a residual) returns ``(y, x)`` where the second output stands for ``x`` in the rest of the graph: use
+    it for the skip connection and the sum of the two gradient paths is fused into the norm's backward kernel."""
+    y, pre = _RMSNorm.apply(x, weight, eps, residual, return_input and residual is None)
+    return y if (residual is None and not return_input) else (y, pre)
 
 
 class _LayerNorm(torch.autograd.Function):
@@ -401,6 +407,62 @@ class _FusedQKVAttention(torch.autograd.Function):
         return (dqkv,) + (None,) * 13
 
 
+class _FusedQKVAttentionLib(torch.autograd.Function):
+    """The same fusion around the LIBRARY attention kernel (equal-length causal sequences): RoPE in place on the q / k parts of
+    the projection output, attention on the strided views, and a backward that rotates dq / dk straight into their slices of one
+    [T, (Hq + 2 Hkv) * D] gradient buffer.  Without it autograd builds that buffer per layer from three zero fills, three
+    strided copies and two full-size adds (the backward of slicing q, k and v out of qkv)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, positions, n_heads, n_kv, head_dim, batch, seqlen, scale, interleaved, use_rope):
+        from nanotron_b200.ops import native
+
+        T = qkv.shape[0]
+        q = qkv[:, : n_heads * head_dim].view(T, n_heads, head_dim)
+        k = qkv[:, n_heads * head_dim : (n_heads + n_kv) * head_dim].view(T, n_kv, head_dim)
+        v = qkv[:, (n_heads + n_kv) * head_dim :].view(T, n_kv, head_dim)
+        if use_rope:
+            native.rope(q, cos, sin, interleaved, inverse=False, inplace=True, positions=positions)
+            native.rope(k, cos, sin, interleaved, inverse=False, inplace=True, positions=positions)
+        needs_grad = ctx.needs_input_grad[0]
+        with torch.set_grad_enabled(needs_grad):
+            ql, kl, vl = (t.detach().requires_grad_(needs_grad) for t in (q, k, v))
+            qb = ql.view(batch, seqlen, n_heads, head_dim).transpose(1, 2)
+            kb = kl.view(batch, seqlen, n_kv, head_dim).transpose(1, 2)
+            vb = vl.view(batch, seqlen, n_kv, head_dim).transpose(1, 2)
+            o = torch.nn.functional.scaled_dot_product_attention(qb, kb, vb, is_causal=True, scale=scale, enable_gqa=n_heads != n_kv)
+            out = o.transpose(1, 2).reshape(T, n_heads, head_dim)
+        ctx.inner = (ql, kl, vl, out) if needs_grad else None  # the library op's own graph: its backward is replayed below
+        ctx.save_for_backward(cos, sin, positions)
+        ctx.cfg = (n_heads, n_kv, head_dim, interleaved, use_rope, qkv.dtype)
+        return out.detach()
+
+    @staticmethod
+    def backward(ctx, dout):
+        from nanotron_b200.ops import native
+
+        cos, sin, positions = ctx.saved_tensors
+        n_heads, n_kv, head_dim, interleaved, use_rope, dtype = ctx.cfg
+        ql, kl, vl, out = ctx.inner
+        ctx.inner = None
+        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), dout)
+        T = dq.shape[0]
+        dqkv = torch.empty((T, (n_heads + 2 * n_kv) * head_dim), dtype=dtype, device=dq.device)
+        gq = dqkv[:, : n_heads * head_dim].view(T, n_heads, head_dim)
+        gk = dqkv[:, n_heads * head_dim : (n_heads + n_kv) * head_dim].view(T, n_kv, head_dim)
+        gv = dqkv[:, (n_heads + n_kv) * head_dim :].view(T, n_kv, head_dim)
+        if use_rope:
+            dq = dq if dq.stride(-1) == 1 and dq.stride(0) % 8 == 0 and dq.stride(1) % 8 == 0 else dq.contiguous()
+            dk = dk if dk.stride(-1) == 1 and dk.stride(0) % 8 == 0 and dk.stride(1) % 8 == 0 else dk.contiguous()
+            native.rope(dq, cos, sin, interleaved, inverse=True, inplace=False, positions=positions, out=gq)
+            native.rope(dk, cos, sin, interleaved, inverse=True, inplace=False, positions=positions, out=gk)
+        else:
+            gq.copy_(dq)
+            gk.copy_(dk)
+        gv.copy_(dv)
+        return (dqkv,) + (None,) * 11
+
+
 def fused_qkv_attention_supported(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window) -> bool:
     if not (qkv.is_cuda and _MODE != "torch" and _ATTN != "sdpa" and qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.is_contiguous()):
         return False
@@ -415,6 +477,19 @@ def fused_qkv_attention(qkv, cos_table, sin_table, positions, n_heads, n_kv, hea
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
     pos = positions.to(torch.int64).contiguous() if positions is not None else None
     return _FusedQKVAttention.apply(qkv, cos_table, sin_table, pos, n_heads, n_kv, head_dim, cu_seqlens.to(torch.int32), max_seqlen, causal, scale, window, interleaved, use_rope)
+
+
+def fused_qkv_library_attention_supported(qkv: torch.Tensor, head_dim: int, window, cu_seqlens) -> bool:
+    """Equal-length causal sequences (no packed documents, no window) on CUDA in bf16 / fp16 with the native element-wise kernels."""
+    return (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.is_contiguous() and head_dim % 8 == 0
+            and window is None and cu_seqlens is None)
+
+
+def fused_qkv_library_attention(qkv, cos_table, sin_table, positions, n_heads, n_kv, head_dim, batch, seqlen, softmax_scale=None, interleaved=False, use_rope=True):
+    """qkv: [batch * seqlen, (Hq + 2 Hkv) * D] fresh output of the fused projection (it is rotated in place).  Returns [T, Hq, D]."""
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+    pos = positions.to(torch.int64).contiguous() if positions is not None else None
+    return _FusedQKVAttentionLib.apply(qkv, cos_table, sin_table, pos, n_heads, n_kv, head_dim, batch, seqlen, scale, interleaved, use_rope)
 
 
 from nanotron_b200.ops import tp_fused  # noqa: E402,F401

@@ -150,11 +150,15 @@ def layernorm_bwd(dy2, pre, weight, mean, rstd, dres, has_bias):
 
 
 # ---------------------------------------------------------------------------- rope / swiglu
-def rope(x, cos, sin, interleaved: bool, inverse: bool, inplace: bool, positions: Optional[torch.Tensor] = None):
-    """x: [T, H, D] with contiguous last dim (any token / head strides that are multiples of 8 elements)."""
+def rope(x, cos, sin, interleaved: bool, inverse: bool, inplace: bool, positions: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """x: [T, H, D] with contiguous last dim (any token / head strides that are multiples of 8 elements).  ``out`` may be a
+    strided [T, H, D] view (e.g. a slice of a fused qkv gradient buffer)."""
     T, H, D = x.shape
     assert x.stride(-1) == 1 and cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
-    out = x if inplace else torch.empty((T, H, D), dtype=x.dtype, device=x.device)
+    if out is None:
+        out = x if inplace else torch.empty((T, H, D), dtype=x.dtype, device=x.device)
+    else:
+        assert out.shape == x.shape and out.dtype == x.dtype and out.stride(-1) == 1
     if positions is not None:
         positions = positions.to(torch.int64).contiguous()
     with torch.cuda.device(x.device):

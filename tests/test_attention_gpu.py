@@ -109,3 +109,36 @@ def test_fused_qkv_rope_attention_matches_composition():
     torch.testing.assert_close(out.float(), exp.detach(), atol=3e-2, rtol=3e-2)
     err = (y.grad.float() - x.grad).abs().max() / x.grad.abs().max()
     assert err < 3e-2, float(err)
+
+
+def test_fused_qkv_library_attention_matches_composition():
+    """The fusion around the library attention (in-place RoPE, one qkv gradient buffer) == rotate, attend, differentiate in fp32."""
+    from nanotron_b200 import ops
+
+    B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+    T = B * S
+    cu = torch.tensor([0, S, 2 * S], dtype=torch.int32, device=DEV)
+    positions = torch.arange(S, device=DEV).repeat(B)
+    cos, sin = ref.rope_cos_sin(torch.arange(S, device=DEV), D, 10000.0)
+    torch.manual_seed(5)
+    qkv0 = torch.randn(T, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16)
+    g = torch.randn(T, Hq, D, device=DEV, dtype=torch.bfloat16)
+    x = qkv0.float().requires_grad_(True)
+    q = x[:, : Hq * D].view(T, Hq, D)
+    k = x[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    v = x[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    c, s_ = cos[positions], sin[positions]
+    exp = ref.attention_varlen(ref.rope_apply(q, c, s_, False), ref.rope_apply(k, c, s_, False), v, cu, cu, causal=True, softmax_scale=1 / math.sqrt(D))
+    exp.backward(g.float())
+    y = qkv0.clone().requires_grad_(True)
+    buf = y * 1
+    assert ops.fused_qkv_library_attention_supported(buf, D, None, None)
+    out = ops.fused_qkv_library_attention(buf, cos, sin, positions, Hq, Hkv, D, B, S)
+    out.backward(g)
+    torch.testing.assert_close(out.float(), exp.detach(), atol=3e-2, rtol=3e-2)
+    err = (y.grad.float() - x.grad).abs().max() / x.grad.abs().max()
+    assert err < 3e-2, float(err)
+    # no-grad call (generation / evaluation)
+    with torch.no_grad():
+        out2 = ops.fused_qkv_library_attention(qkv0.clone(), cos, sin, positions, Hq, Hkv, D, B, S)
+    torch.testing.assert_close(out2, out.detach())

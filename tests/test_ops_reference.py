@@ -102,3 +102,24 @@ def test_adamw_reference_matches_torch():
         opt.step()
         ref.adamw_step(p, g, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
     torch.testing.assert_close(p, ref_p.detach(), atol=1e-6, rtol=1e-5)
+
+
+def test_rms_norm_return_input_fuses_the_skip_gradient():
+    """``rms_norm(x, return_input=True)`` hands ``x`` back as a second output; gradients that reach it are summed into dx by the
+    norm's own backward.  Compare with plain autograd where ``x`` feeds both the norm and the skip connection."""
+    torch.manual_seed(0)
+    x0 = torch.randn(6, 32, dtype=torch.float64)
+    w0 = torch.randn(32, dtype=torch.float64)
+    x, w = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    y, skip = ops.rms_norm(x, w, 1e-5, return_input=True)
+    ((y * y).sum() + (skip * 3).sum() + (y.sum(-1, keepdim=True) * skip).sum()).backward()
+    xr, wr = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    ((yr * yr).sum() + (xr * 3).sum() + (yr.sum(-1, keepdim=True) * xr).sum()).backward()
+    torch.testing.assert_close(x.grad, xr.grad, atol=1e-4, rtol=1e-4)  # the oracle keeps fp32 statistics
+    torch.testing.assert_close(w.grad, wr.grad, atol=1e-4, rtol=1e-4)
+    # the skip output alone
+    x2 = x0.clone().requires_grad_(True)
+    _, skip2 = ops.rms_norm(x2, w0, 1e-5, return_input=True)
+    skip2.sum().backward()
+    torch.testing.assert_close(x2.grad, torch.ones_like(x2))
