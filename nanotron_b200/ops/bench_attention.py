@@ -26,6 +26,9 @@ def main():
         cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device="cuda")
         scale = 1 / math.sqrt(128)
         flops = 4.0 * B * Hq * S * S * 128 / 2
+        native_attn.set_forward_variant("one_tile")
+        ms1 = time_fn(lambda: native_attn.flash_attn_fwd(q, k, v, cu, cu, S, S, True, scale, None))
+        native_attn.set_forward_variant("two_tile")
         ms = time_fn(lambda: native_attn.flash_attn_fwd(q, k, v, cu, cu, S, S, True, scale, None))
         native_gemm.check_status("cuda")
         qb = q.reshape(B, S, Hq, 128).transpose(1, 2)
@@ -42,6 +45,7 @@ def main():
         go = torch.randn_like(o)
         ms_lb = time_fn(lambda: torch.autograd.grad(o, (qg, kg, vg), go, retain_graph=True))
         print(f"B={B} S={S} bwd: tcgen05 {ms_b:7.3f} ms {2.5 * flops / ms_b / 1e9:7.1f} TFLOP/s | library {ms_lb:7.3f} ms {2.5 * flops / ms_lb / 1e9:7.1f} TFLOP/s", flush=True)
+        print(f"B={B} S={S} Hq={Hq} Hkv={Hkv}  tcgen05 fwd, one query tile per CTA {ms1:7.3f} ms {flops / ms1 / 1e9:7.1f} TFLOP/s", flush=True)
         print(f"B={B} S={S} Hq={Hq} Hkv={Hkv}  tcgen05 fwd {ms:7.3f} ms {flops / ms / 1e9:7.1f} TFLOP/s ({flops / ms / 1e9 / peak:4.2f} of measured GEMM peak) | library fwd {ms_lib:7.3f} ms {flops / ms_lib / 1e9:7.1f} TFLOP/s", flush=True)
 
 

@@ -1,4 +1,5 @@
-"""Bindings of the flash-attention kernels (``csrc/attention_fwd.cu``, ``csrc/attention_bwd.cu``)."""
+"""Bindings of the flash-attention kernels (``csrc/attention_fwd2.cu``: two query tiles per CTA, the default forward;
+``csrc/attention_fwd.cu``: one query tile per CTA, also the context-parallel forward; ``csrc/attention_bwd.cu``)."""
 from __future__ import annotations
 
 import ctypes
@@ -7,7 +8,13 @@ from typing import Optional
 
 import torch
 
-_HAS = {"fwd": False, "bwd": False}
+_HAS = {"fwd": False, "fwd2": False, "bwd": False}
+FWD_VARIANT = {"kernel": "two_tile"}  # "two_tile" | "one_tile"
+
+
+def set_forward_variant(name: str):
+    assert name in ("two_tile", "one_tile")
+    FWD_VARIANT["kernel"] = name
 
 
 def declare(L):
@@ -16,6 +23,10 @@ def declare(L):
     if _HAS["fwd"]:
         L.ntb_flash_attn_fwd.restype = c_int
         L.ntb_flash_attn_fwd.argtypes = [c_void_p] * 7 + [c_int] * 6 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
+    _HAS["fwd2"] = hasattr(L, "ntb_flash_attn_fwd2")
+    if _HAS["fwd2"]:
+        L.ntb_flash_attn_fwd2.restype = c_int
+        L.ntb_flash_attn_fwd2.argtypes = L.ntb_flash_attn_fwd.argtypes
     if _HAS["bwd"]:
         L.ntb_flash_attn_bwd.restype = c_int
         L.ntb_flash_attn_bwd.argtypes = [c_void_p] * 13 + [c_int] * 7 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
@@ -44,8 +55,10 @@ def flash_attn_fwd(q, k, v, cu_q, cu_k, max_q: int, max_k: int, causal: bool, sc
     lse = torch.empty((Hq, Tq), dtype=torch.float32, device=q.device)
     cu_q = cu_q.to(torch.int32)
     cu_k = cu_k.to(torch.int32)
+    L = native.lib()
+    fn = L.ntb_flash_attn_fwd2 if (_HAS["fwd2"] and FWD_VARIANT["kernel"] == "two_tile") else L.ntb_flash_attn_fwd
     with torch.cuda.device(q.device):
-        rc = native.lib().ntb_flash_attn_fwd(
+        rc = fn(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(), cu_q.numel() - 1, int(max_q), Tq, k.shape[0],
             Hq, k.shape[1], q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), float(scale), int(bool(causal)), int(window or 0),
             status_word(q.device).data_ptr(), torch.cuda.current_stream(q.device).cuda_stream,

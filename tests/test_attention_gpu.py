@@ -20,8 +20,18 @@ def _qkv(T, Hq, Hkv, seed=0):
     return q, k, v
 
 
-@pytest.mark.parametrize("lens,Hq,Hkv,causal", [([128], 1, 1, True), ([256], 2, 1, True), ([200, 56, 333], 4, 2, True), ([512, 100], 2, 2, False), ([1024], 8, 2, True)])
-def test_flash_fwd_matches_oracle(lens, Hq, Hkv, causal):
+@pytest.fixture(params=["two_tile", "one_tile"])
+def fwd_variant(request):
+    """Both forward kernels: two query tiles per CTA with P in tensor memory (default), one query tile per CTA."""
+    from nanotron_b200.ops import native_attn
+
+    native_attn.set_forward_variant(request.param)
+    yield request.param
+    native_attn.set_forward_variant("two_tile")
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv,causal", [([128], 1, 1, True), ([256], 2, 1, True), ([200, 56, 333], 4, 2, True), ([512, 100], 2, 2, False), ([1024], 8, 2, True), ([1300, 257, 640], 2, 1, True)])
+def test_flash_fwd_matches_oracle(lens, Hq, Hkv, causal, fwd_variant):
     from nanotron_b200.ops import native, native_attn, native_gemm
 
     native.lib()
@@ -36,7 +46,26 @@ def test_flash_fwd_matches_oracle(lens, Hq, Hkv, causal):
     torch.testing.assert_close(lse, exp_lse, atol=2e-2, rtol=1e-3)
 
 
-def test_flash_fwd_sliding_window():
+def test_flash_fwd_large_logits_move_the_running_maximum(fwd_variant):
+    """Scores whose row maximum keeps growing along the keys (by far more than the lazy-rescale threshold of the two-tile kernel)."""
+    from nanotron_b200.ops import native, native_attn, native_gemm
+
+    native.lib()
+    T, Hq, Hkv = 1024, 2, 1
+    q, k, v = _qkv(T, Hq, Hkv, seed=11)
+    ramp = torch.linspace(0.2, 3.0, T, device=DEV).view(T, 1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)  # later keys give larger scores
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    scale = 0.5
+    for causal in (True, False):
+        out, lse = native_attn.flash_attn_fwd(q, k, v, cu, cu, T, T, causal, scale, None)
+        native_gemm.check_status(DEV)
+        exp, exp_lse = ref.attention_varlen(q, k, v, cu, cu, causal=causal, softmax_scale=scale, return_lse=True)
+        torch.testing.assert_close(out.float(), exp.float(), atol=3e-2, rtol=3e-2)
+        torch.testing.assert_close(lse, exp_lse, atol=2e-2, rtol=1e-3)
+
+
+def test_flash_fwd_sliding_window(fwd_variant):
     from nanotron_b200.ops import native, native_attn
 
     native.lib()
