@@ -11,13 +11,17 @@
 //               MMAs of one thread execute in issue order, which is what makes the reuse of S_t safe without a barrier:
 //               S_t(j+1) is issued after the P_t(j) V(j) product that reads the same columns.
 //   warps 2-5   softmax of query tile 0, warps 6-9 of tile 1: thread r owns query row r of its tile and reads the whole
-//               128-column score row into registers with one wait (row max, exp2, row sum, bf16 P back to TMEM).  The running maximum is only moved (and O rescaled, by this same
-//               warp) when some row of the warp exceeds it by more than 2^8: probabilities stay below 256, the final O / l is
-//               exact, and most tiles need no pass over O.  `s_full[t]` firing also means P_t(j-1) V(j-1) has completed (a commit
-//               covers every earlier MMA of the thread), so O_t may be rescaled as soon as S_t(j) can be read.
+//               128-column score row into registers with one wait.  In steady state there is NO row maximum: the exponentials
+//               are taken relative to the reference maximum of the earlier tiles and the row sum (needed anyway) shows whether
+//               that was good enough; if not (a row sums to more than 1024, or is not finite) the warp computes the exact
+//               maximum from its registers, rescales O and l, and recomputes the tile.  The final O / l is exact either way.
+//               `s_full[t]` firing also means P_t(j-1) V(j-1) has completed (a commit covers every earlier MMA of the thread),
+//               so O_t may be rescaled as soon as S_t(j) can be read.
 // Epilogue: O_t / l from TMEM straight to global memory (rows past the end of the sequence are not written), LSE to global.
 // Tiles hanging over the end of a packed sequence read the next sequence's keys: those columns are masked.
 // All barrier waits are bounded; a timeout raises `status` and the CTA unwinds.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -32,7 +36,7 @@ constexpr int TILE_BYTES = 128 * HD * 2;
 constexpr int PANEL_BYTES = 128 * 64 * 2;
 constexpr int F2_THREADS = 320;
 constexpr int F2_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 1024 + 256;
-constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+constexpr float SUM_LIMIT = 1024.f;  // a tile's row sum above this moves the reference maximum
 
 struct Fwd2Params {
   int num_heads, num_kv_heads;
@@ -84,6 +88,51 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// packed fp32 pairs (one issue slot for two elements) and the three-input maximum
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for a pair of arguments on the FMA / integer pipes (the special-function unit is the scarce resource of this kernel):
+// n = round(x) by the magic-number addition, f = x - n in [-0.5, 0.5], degree-3 polynomial for 2^f (relative error 1e-4, well
+// under the bf16 rounding of the probabilities), n added into the exponent field.
+__device__ __forceinline__ void exp2_poly_pair(float y0, float y1, float& x0, float& x1) {
+  y0 = fmaxf(y0, -126.f);
+  y1 = fmaxf(y1, -126.f);
+  const uint64_t y2 = pack2(y0, y1);
+  const uint64_t t2 = add2(y2, pack2(12582912.f, 12582912.f));
+  const uint64_t n2 = add2(t2, pack2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), y2);
+  uint64_t p2 = fma2(pack2(0.05592203512787819f, 0.05592203512787819f), f2, pack2(0.24264007806777954f, 0.24264007806777954f));
+  p2 = fma2(p2, f2, pack2(0.6931210160255432f, 0.6931210160255432f));
+  p2 = fma2(p2, f2, pack2(0.9999244809150696f, 0.9999244809150696f));
+  float t0, t1, p0, p1;
+  unpack2(t2, t0, t1);
+  unpack2(p2, p0, p1);
+  x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
+// POLY_PAIRS: of every four element pairs, how many take exp2_poly_pair instead of the special-function unit.
+template <int POLY_PAIRS>
 __global__ void __launch_bounds__(F2_THREADS, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                   const Fwd2Params p) {
@@ -105,13 +154,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y;
+  // grid: x = (sequence, head), y = query-tile pair.  Blocks are handed out x-fastest, so all (sequence, head) instances of the
+  // heaviest pair start first and the light ones fill the tail
+  const int b = blockIdx.x / p.num_heads, h = blockIdx.x % p.num_heads;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
   const int k_begin = p.cu_k[b];
   const int k_len = p.cu_k[b + 1] - k_begin;
   // heavy (late) query tiles first: with a causal mask they have the most key tiles
-  const int pair = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+  const int pair = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
   const int q0 = pair * 2 * BM;
   if (q0 >= q_len) return;  // uniform for the CTA
   const int shift = k_len - q_len;  // bottom-right aligned causal mask
@@ -265,56 +316,74 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
               if (col < lo || col >= hi) v[c][i] = 0xff800000u;  // -inf: exp2 gives 0
             }
         }
-        // row max: four independent chains
-        float mxc[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-          mxc[c] = fmaxf(__uint_as_float(v[c][0]), __uint_as_float(v[c][1]));
-#pragma unroll
-          for (int i = 2; i < 32; i += 2) mxc[c] = fmaxf(mxc[c], fmaxf(__uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1])));
-        }
-        const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
-        // move the reference maximum only when some row of the warp outgrew it by more than the threshold
-        const bool grow = (mx - m_ref) * p.scale_log2 > RESCALE_THRESHOLD;  // true for the first finite maximum (m_ref = -inf)
-        float alpha = 1.f;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float m_new = fmaxf(m_ref, mx);
-          const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
-          alpha = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_fin) * p.scale_log2);
-          if (j > 0) {  // O_t holds the sum over earlier tiles relative to the old reference
+        // Fast path: exponentials relative to the reference maximum m_ref of the earlier tiles, no row maximum at all.  The row
+        // sum (needed anyway) tells whether that was good enough: if some row of the warp sums to more than SUM_LIMIT (or is
+        // not finite), the warp takes the slow path once for this tile: exact row maximum from the registers, new reference,
+        // O and l rescaled, exponentials recomputed.  Probabilities therefore stay below SUM_LIMIT and the result is exact.
+        float alpha = 1.f, sum = 0.f;
+        bool slow = (j == 0) || __any_sync(0xffffffffu, m_ref == -INFINITY);
 #pragma unroll 1
+        for (int attempt = 0; attempt < 2; attempt++) {
+          if (slow) {
+            float mxc[4];
+#pragma unroll
             for (int c = 0; c < 4; c++) {
-              uint32_t o[32];
-              ptx::tmem_ld_32x32(tO + c * 32, o);
-              ptx::tmem_ld_wait();
+              mxc[c] = fmaxf(__uint_as_float(v[c][0]), __uint_as_float(v[c][1]));
 #pragma unroll
-              for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st_32x32b(tO + c * 32, o);
+              for (int i = 2; i < 32; i += 2) mxc[c] = max3(mxc[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
             }
-          }
-          m_ref = m_new;
-        }
-        // probabilities relative to m_ref -> bf16 pairs -> the first 64 columns of S_t; row sum in eight independent chains
-        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const float neg_m = -m_use * p.scale_log2;
-        float sa[4], sb[4];
+            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])));
+            const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_fin) * p.scale_log2);
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+              // O_t holds the sum over earlier tiles relative to the old reference (its last P*V completed before S_t(j))
+#pragma unroll 1
+              for (int c = 0; c < 4; c++) {
+                uint32_t o[32];
+                ptx::tmem_ld_32x32(tO + c * 32, o);
+                ptx::tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          uint32_t pk[16];
-          sa[c] = 0.f;
-          sb[c] = 0.f;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float x0 = ex2(fmaf(__uint_as_float(v[c][i]), p.scale_log2, neg_m));
-            const float x1 = ex2(fmaf(__uint_as_float(v[c][i + 1]), p.scale_log2, neg_m));
-            sa[c] += x0;
-            sb[c] += x1;
-            __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
-            pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st_32x32b(tO + c * 32, o);
+              }
+            }
+            m_ref = m_new;
           }
-          tmem_st_32x16(tS + c * 16, pk);
+          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const float neg_m = -m_use * p.scale_log2;
+          const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(neg_m, neg_m);
+          uint64_t acc2[4];
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            uint32_t pk[16];
+            acc2[c] = 0ull;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float y0, y1;
+              unpack2(fma2(pack2(__uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1])), sl2, nm2), y0, y1);
+              float x0, x1;
+              if (((i >> 1) & 3) < POLY_PAIRS) {
+                exp2_poly_pair(y0, y1, x0, x1);
+              } else {
+                x0 = ex2(y0);
+                x1 = ex2(y1);
+              }
+              acc2[c] = add2(acc2[c], pack2(x0, x1));
+              __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+              pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            // P may go to tensor memory right away (the score row is in registers); a retry simply overwrites it
+            tmem_st_32x16(tS + c * 16, pk);
+          }
+          float s0, s1, s2, s3, s4, s5, s6, s7;
+          unpack2(acc2[0], s0, s1);
+          unpack2(acc2[1], s2, s3);
+          unpack2(acc2[2], s4, s5);
+          unpack2(acc2[3], s6, s7);
+          sum = ((s0 + s1) + (s2 + s3)) + ((s4 + s5) + (s6 + s7));
+          if (slow || !__any_sync(0xffffffffu, !(sum <= SUM_LIMIT))) break;
+          slow = true;
         }
-        const float sum = ((sa[0] + sb[0]) + (sa[1] + sb[1])) + ((sa[2] + sb[2]) + (sa[3] + sb[3]));
         tmem_st_wait2();
         l_run = l_run * alpha + sum;
         // P written (and O rescaled): tell the MMA warp
@@ -400,10 +469,16 @@ NTB_EXPORT int ntb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   if (!f2_make_map(&tq, q, total_q, num_heads, q_stride_t, q_stride_h) || !f2_make_map(&tk, k, total_k, num_kv_heads, k_stride_t, k_stride_h) ||
       !f2_make_map(&tv, v, total_k, num_kv_heads, v_stride_t, v_stride_h))
     return NTB_ERR_ARG;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
-    configured = true;
+  static int poly = -1;
+  if (poly < 0) {
+    const char* e = getenv("NTB_FA_POLY_PAIRS");  // 0..2 of every four pairs on the FMA pipe (tuning knob)
+    int v = e ? atoi(e) : 0;
+    v = v < 0 ? 0 : (v > 2 ? 2 : v);
+    if (cudaFuncSetAttribute(flash_fwd2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess)
+      return NTB_ERR_LAUNCH;
+    poly = v;
   }
   Fwd2Params p;
   p.num_heads = num_heads;
@@ -418,7 +493,10 @@ NTB_EXPORT int ntb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   p.lse = lse;
   p.total_q = total_q;
   p.status = status;
-  dim3 grid((max_seqlen_q + 2 * BM - 1) / (2 * BM), num_heads, batch);
-  flash_fwd2_kernel<<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
+  dim3 grid(num_heads * batch, (max_seqlen_q + 2 * BM - 1) / (2 * BM), 1);
+  if (grid.y > 65535) return NTB_ERR_ARG;
+  if (poly == 0) flash_fwd2_kernel<0><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
+  else if (poly == 1) flash_fwd2_kernel<1><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
+  else flash_fwd2_kernel<2><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
   return ntb_check_launch();
 }
