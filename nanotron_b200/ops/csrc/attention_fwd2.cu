@@ -34,8 +34,9 @@ constexpr int K_STAGES = 2;
 constexpr int V_STAGES = 2;
 constexpr int TILE_BYTES = 128 * HD * 2;
 constexpr int PANEL_BYTES = 128 * 64 * 2;
-constexpr int F2_THREADS = 320;
-constexpr int F2_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 1024 + 256;
+constexpr int F2_THREADS = 576;  // TMA warp, MMA warp, 16 softmax warps (two per 32 query rows of each tile)
+constexpr int XCH_BYTES = 2 * 2 * 4 * 2 * 32 * 4 + 256;  // [slot][tile][quarter][half][lane] floats + flags
+constexpr int F2_SMEM = TILE_BYTES * (2 + K_STAGES + V_STAGES) + 1024 + 256 + XCH_BYTES;
 constexpr float SUM_LIMIT = 1024.f;  // a tile's row sum above this moves the reference maximum
 
 struct Fwd2Params {
@@ -133,7 +134,7 @@ __device__ __forceinline__ void exp2_poly_pair(float y0, float y1, float& x0, fl
 
 // POLY_PAIRS: of every four element pairs, how many take exp2_poly_pair instead of the special-function unit.
 template <int POLY_PAIRS>
-__global__ void __launch_bounds__(F2_THREADS, 1)
+__global__ void __maxnreg__(96)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                   const Fwd2Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -152,6 +153,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* o_done = p_full + 2;                // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);            // [2 slots][2][4][2][32]
+  volatile int* xflag = reinterpret_cast<volatile int*>(xch + 2 * 2 * 4 * 2 * 32);          // [2 slots][2][4][2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // grid: x = (sequence, head), y = query-tile pair.  Blocks are handed out x-fastest, so all (sequence, head) instances of the
@@ -191,7 +194,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     for (int t = 0; t < 2; t++) {
       ptx::mbar_init(&s_full[t], 1);
-      ptx::mbar_init(&p_full[t], 4);
+      ptx::mbar_init(&p_full[t], 8);
       ptx::mbar_init(&o_done[t], 1);
     }
     *abort_flag = 0;
@@ -261,7 +264,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
         for (int k = 0; k < BN / 16; k++) {
           const uint64_t bdesc = ptx::make_smem_desc(aV + k * 16 * 128, PANEL_BYTES, 1024);
-          umma_f16_ts(tO, tP + k * 8, bdesc, idesc_pv, (j | k) != 0);
+          umma_f16_ts(tO, tP + (k < 4 ? k * 8 : 64 + (k - 4) * 8), bdesc, idesc_pv, (j | k) != 0);
         }
         if (j == (t ? n_t1 : n_t0) - 1) ptx::umma_commit(&o_done[t]);
         return true;
@@ -281,64 +284,77 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax / correction / epilogue of query tile t
-    const int t = (warp - 2) >> 2;
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    // warp -> (query tile t, half h of the key columns and of the head dim, TMEM lane quarter): two warps share 32 query rows
+    const int t = (warp - 2) >> 3;
+    const int hh = ((warp - 2) >> 2) & 1;
     const int n_tiles = t ? n_t1 : n_t0;
     if (n_tiles > 0) {
       const int quarter = warp & 3;            // TMEM lane quarter this warp may access
       const int r = quarter * 32 + lane;       // query row inside the tile
       const int qpos = q0 + t * BM + r;        // position inside the sequence
       const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-      const uint32_t tS = tmem_base + lane_addr + t * BN;
-      const uint32_t tO = tmem_base + lane_addr + 256 + t * HD;
-      float m_ref = -INFINITY, l_run = 0.f;  // m_ref: the maximum the stored probabilities and O are relative to
+      const uint32_t tS = tmem_base + lane_addr + t * BN + hh * 64;       // my 64 score columns; my P goes to their first 32
+      const uint32_t tO = tmem_base + lane_addr + 256 + t * HD + hh * 64; // my 64 columns of O
+      const int pair_bar = 1 + t * 4 + quarter;                          // named barrier of the two warps of these rows
+      auto xslot = [&](int slot, int half) -> float* { return xch + ((((slot * 2 + t) * 4 + quarter) * 2 + half) * 32) + lane; };
+      auto fslot = [&](int slot, int half) -> volatile int* { return xflag + (((slot * 2 + t) * 4 + quarter) * 2 + half); };
+      float m_ref = -INFINITY, l_run = 0.f;  // m_ref: the maximum the stored probabilities and O are relative to (same in both warps)
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; j++) {
-        const int k0 = kv_start + j * BN;
+        const int k0 = kv_start + j * BN + hh * 64;
         if (!ptx::mbar_wait(&s_full[t], j & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         int hi = k_len - k0;
         if (p.causal) hi = min(hi, qpos + shift - k0 + 1);
         int lo = 0;
         if (p.window > 0) lo = max(0, qpos + shift - p.window + 1 - k0);
-        const bool need_mask = (hi < BN) || (lo > 0);
-        // the whole score row (128 columns) goes to registers with one wait: the TMEM read latency is paid once per tile
-        uint32_t v[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; c++) ptx::tmem_ld_32x32(tS + c * 32, v[c]);
-        ptx::tmem_ld_wait();
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < 4; c++)
+        const bool need_mask = (hi < 64) || (lo > 0);
+        // one 32-column chunk of my half of the score row at a time (register budget: 18 warps share the register file)
+        auto load_chunk = [&](int c, uint32_t (&v)[32]) {
+          ptx::tmem_ld_32x32(tS + c * 32, v);
+          ptx::tmem_ld_wait();
+          if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 32; i++) {
               const int col = c * 32 + i;
-              if (col < lo || col >= hi) v[c][i] = 0xff800000u;  // -inf: exp2 gives 0
+              if (col < lo || col >= hi) v[i] = 0xff800000u;  // -inf: exp2 gives 0
             }
-        }
+          }
+        };
         // Fast path: exponentials relative to the reference maximum m_ref of the earlier tiles, no row maximum at all.  The row
-        // sum (needed anyway) tells whether that was good enough: if some row of the warp sums to more than SUM_LIMIT (or is
-        // not finite), the warp takes the slow path once for this tile: exact row maximum from the registers, new reference,
-        // O and l rescaled, exponentials recomputed.  Probabilities therefore stay below SUM_LIMIT and the result is exact.
+        // sum (needed anyway) tells whether that was good enough: if some row of either warp sums to more than SUM_LIMIT (or is
+        // not finite), both warps take the slow path once for this tile: exact row maximum (scores read again: P is only
+        // stored after the decision; the two halves exchanged through shared memory), new reference, O and l rescaled,
+        // exponentials recomputed.  The result is exact either way.
         float alpha = 1.f, sum = 0.f;
+        uint32_t pk[2][16];
         bool slow = (j == 0) || __any_sync(0xffffffffu, m_ref == -INFINITY);
 #pragma unroll 1
         for (int attempt = 0; attempt < 2; attempt++) {
           if (slow) {
-            float mxc[4];
+            float mine = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 2; c++) {
+              uint32_t v[32];
+              load_chunk(c, v);
+              float m0 = fmaxf(__uint_as_float(v[0]), __uint_as_float(v[1])), m1 = fmaxf(__uint_as_float(v[2]), __uint_as_float(v[3]));
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-              mxc[c] = fmaxf(__uint_as_float(v[c][0]), __uint_as_float(v[c][1]));
-#pragma unroll
-              for (int i = 2; i < 32; i += 2) mxc[c] = max3(mxc[c], __uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1]));
+              for (int i = 4; i < 32; i += 4) {
+                m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              }
+              mine = max3(mine, m0, m1);
             }
-            const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])));
+            *xslot(j & 1, hh) = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const float m_new = fmaxf(m_ref, fmaxf(mine, *xslot(j & 1, hh ^ 1)));
             const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
             alpha = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_fin) * p.scale_log2);
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-              // O_t holds the sum over earlier tiles relative to the old reference (its last P*V completed before S_t(j))
+              // my half of O_t holds the sum over earlier tiles relative to the old reference (its last P*V completed before S_t(j))
 #pragma unroll 1
-              for (int c = 0; c < 4; c++) {
+              for (int c = 0; c < 2; c++) {
                 uint32_t o[32];
                 ptx::tmem_ld_32x32(tO + c * 32, o);
                 ptx::tmem_ld_wait();
@@ -352,15 +368,16 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
           const float neg_m = -m_use * p.scale_log2;
           const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(neg_m, neg_m);
-          uint64_t acc2[4];
+          uint64_t acc2[2];
 #pragma unroll
-          for (int c = 0; c < 4; c++) {
-            uint32_t pk[16];
+          for (int c = 0; c < 2; c++) {
+            uint32_t v[32];
+            load_chunk(c, v);
             acc2[c] = 0ull;
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               float y0, y1;
-              unpack2(fma2(pack2(__uint_as_float(v[c][i]), __uint_as_float(v[c][i + 1])), sl2, nm2), y0, y1);
+              unpack2(fma2(pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sl2, nm2), y0, y1);
               float x0, x1;
               if (((i >> 1) & 3) < POLY_PAIRS) {
                 exp2_poly_pair(y0, y1, x0, x1);
@@ -369,37 +386,44 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
                 x1 = ex2(y1);
               }
               acc2[c] = add2(acc2[c], pack2(x0, x1));
-              __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
-              pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+              __nv_bfloat162 hb = __floats2bfloat162_rn(x0, x1);
+              pk[c][i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
             }
-            // P may go to tensor memory right away (the score row is in registers); a retry simply overwrites it
-            tmem_st_32x16(tS + c * 16, pk);
           }
-          float s0, s1, s2, s3, s4, s5, s6, s7;
+          float s0, s1, s2, s3;
           unpack2(acc2[0], s0, s1);
           unpack2(acc2[1], s2, s3);
-          unpack2(acc2[2], s4, s5);
-          unpack2(acc2[3], s6, s7);
-          sum = ((s0 + s1) + (s2 + s3)) + ((s4 + s5) + (s6 + s7));
-          if (slow || !__any_sync(0xffffffffu, !(sum <= SUM_LIMIT))) break;
+          sum = (s0 + s1) + (s2 + s3);
+          if (slow) break;
+          // both warps of these rows must take the same decision
+          const bool bad = __any_sync(0xffffffffu, !(sum <= SUM_LIMIT));
+          if (lane == 0) *fslot(j & 1, hh) = bad ? 1 : 0;
+          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+          if (!(bad || *fslot(j & 1, hh ^ 1) != 0)) break;
           slow = true;
         }
+        // the scores are not needed any more: P over the first 32 columns of my half
+        tmem_st_32x16(tS, pk[0]);
+        tmem_st_32x16(tS + 16, pk[1]);
         tmem_st_wait2();
         l_run = l_run * alpha + sum;
-        // P written (and O rescaled): tell the MMA warp
+        // my half of P written (and of O rescaled): tell the MMA warp
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&p_full[t]);
       }
-      // ---------------------------------------------------------------- epilogue
+      // ---------------------------------------------------------------- epilogue: my 64 columns of O
       if (ok && ptx::mbar_wait(&o_done[t], 0, abort_flag)) {
         ptx::tc_fence_after();
-        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        *xslot(n_tiles & 1, hh) = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        const float l_tot = l_run + *xslot(n_tiles & 1, hh ^ 1);
+        const float inv_l = l_tot > 0.f ? 1.f / l_tot : 0.f;
         const bool valid = qpos < q_len;
         const int64_t tok = static_cast<int64_t>(q_begin) + qpos;
-        __nv_bfloat16* orow = p.out + (tok * p.num_heads + h) * HD;
+        __nv_bfloat16* orow = p.out + (tok * p.num_heads + h) * HD + hh * 64;
 #pragma unroll 1
-        for (int c = 0; c < 4; c++) {
+        for (int c = 0; c < 2; c++) {
           uint32_t v[32];
           ptx::tmem_ld_32x32(tO + c * 32, v);
           ptx::tmem_ld_wait();
@@ -417,7 +441,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
         }
-        if (valid) p.lse[static_cast<int64_t>(h) * p.total_q + tok] = (l_run > 0.f) ? m_ref * p.scale + logf(l_run) : -INFINITY;
+        if (valid && hh == 0) p.lse[static_cast<int64_t>(h) * p.total_q + tok] = (l_tot > 0.f) ? m_ref * p.scale + logf(l_tot) : -INFINITY;
       }
     }
   }
