@@ -84,6 +84,23 @@ __global__ void cast_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __r
 }
 
 __device__ __forceinline__ void red_add_f32(float* p, float v) { asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// packed fp32 pairs: one issue slot for two elements
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_k,
@@ -270,16 +287,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     bool ok = true;
     int prev_h = 0, prev_q0 = 0;
     auto flush_dq = [&](int h, int q0) {
-      // dQ^T[r = head-dim index][64 queries] -> dq_acc[(q_begin + q0 + c), h, r]
+      // dQ^T[r = head-dim index][64 queries] -> dq_acc[(q_begin + q0 + c), h, r]: a warp's 32 lanes add 32 consecutive floats
+      const int64_t stride = static_cast<int64_t>(p.num_heads) * HD;
+      float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0) * p.num_heads + h) * HD + r;
+      const int nq = min(BQ, q_len - q0);
 #pragma unroll 1
       for (int c = 0; c < 2; c++) {
         uint32_t v[32];
         ptx::tmem_ld_32x32(tm_dQT + lane_addr + c * 32, v);
         ptx::tmem_ld_wait();
+        if (nq == BQ) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const int qpos = q0 + c * 32 + i;
-          if (qpos < q_len) red_add_f32(p.dq_acc + (static_cast<int64_t>(q_begin + qpos) * p.num_heads + h) * HD + r, __uint_as_float(v[i]));
+          for (int i = 0; i < 32; i++) red_add_f32(ptr + (c * 32 + i) * stride, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++)
+            if (c * 32 + i < nq) red_add_f32(ptr + (c * 32 + i) * stride, __uint_as_float(v[i]));
         }
       }
     };
@@ -295,13 +318,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int qpos = q0 + c * 32 + lane;
         const bool in = qpos < q_len;
         const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
-        lse_s[c * 32 + lane] = in ? p.lse[idx] * 1.4426950408889634f : INFINITY;
-        delta_s[c * 32 + lane] = in ? p.delta[idx] : 0.f;
+        lse_s[c * 32 + lane] = in ? -p.lse[idx] * 1.4426950408889634f : -INFINITY;  // exp2(s c - lse) = 0 for rows past the end
+        delta_s[c * 32 + lane] = in ? p.delta[idx] * p.scale : 0.f;
       }
       __syncwarp();
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t pk_p[32], pk_ds[32];  // 64 bf16 each
+      // query columns this key row may look at: [clo, chi).  Queries past the end of the sequence are handled by lse = +inf.
+      int clo = 0, chi = key_valid ? BQ : 0;
+      if (p.causal) clo = max(0, kpos - shift - m0);
+      if (p.window > 0) chi = min(chi, kpos - shift + p.window - m0);
+      const bool full = __all_sync(0xffffffffu, clo == 0 && chi == BQ);
+      const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), sc2 = pack2(p.scale, p.scale);
 #pragma unroll
       for (int c = 0; c < 2; c++) {
         uint32_t sv[32], dv[32];
@@ -309,23 +338,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         ptx::tmem_ld_32x32(tm_dPT + lane_addr + c * 32, dv);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pp[2], dd[2];
-#pragma unroll
-          for (int u = 0; u < 2; u++) {
-            const int col = c * 32 + i + u;
-            const int qpos = q0 + col;
-            const int mpos = m0 + col;  // query position for the masks (kpos is already global under context parallelism)
-            bool vis = key_valid && qpos < q_len;
-            if (p.causal) vis = vis && (kpos <= mpos + shift);
-            if (p.window > 0) vis = vis && (kpos > mpos + shift - p.window);
-            const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[i + u]), p.scale_log2, -lse_s[col])) : 0.f;
-            pp[u] = pr;
-            dd[u] = vis ? pr * (__uint_as_float(dv[i + u]) - delta_s[col]) * p.scale : 0.f;
+        for (int i = 0; i < 32; i += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(lse_s + c * 32 + i);    // -lse * log2(e)
+          const float4 ds = *reinterpret_cast<const float4*>(delta_s + c * 32 + i);  // delta * scale
+          float e0, e1, e2, e3, t0, t1, t2, t3;
+          unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sl2, pack2(nl.x, nl.y)), e0, e1);
+          unpack2(fma2(pack2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])), sl2, pack2(nl.z, nl.w)), e2, e3);
+          float p0 = ex2_approx(e0), p1 = ex2_approx(e1), p2 = ex2_approx(e2), p3 = ex2_approx(e3);
+          if (!full) {
+            const int col = c * 32 + i;
+            if (col < clo || col >= chi) p0 = 0.f;
+            if (col + 1 < clo || col + 1 >= chi) p1 = 0.f;
+            if (col + 2 < clo || col + 2 >= chi) p2 = 0.f;
+            if (col + 3 < clo || col + 3 >= chi) p3 = 0.f;
           }
-          __nv_bfloat162 hp = __floats2bfloat162_rn(pp[0], pp[1]), hd = __floats2bfloat162_rn(dd[0], dd[1]);
-          pk_p[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hp);
-          pk_ds[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hd);
+          // dS = P (dP - delta) scale
+          const uint64_t u01 = fma2(pack2(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), sc2, pack2(-ds.x, -ds.y));
+          const uint64_t u23 = fma2(pack2(__uint_as_float(dv[i + 2]), __uint_as_float(dv[i + 3])), sc2, pack2(-ds.z, -ds.w));
+          unpack2(fma2(pack2(p0, p1), u01, 0ull), t0, t1);
+          unpack2(fma2(pack2(p2, p3), u23, 0ull), t2, t3);
+          __nv_bfloat162 hp0 = __floats2bfloat162_rn(p0, p1), hp1 = __floats2bfloat162_rn(p2, p3);
+          __nv_bfloat162 hd0 = __floats2bfloat162_rn(t0, t1), hd1 = __floats2bfloat162_rn(t2, t3);
+          pk_p[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hp0);
+          pk_p[c * 16 + i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hp1);
+          pk_ds[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hd0);
+          pk_ds[c * 16 + i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hd1);
         }
       }
       // the previous step's products still read P^T / dS^T from shared memory and own dQ^T
