@@ -24,7 +24,7 @@ constexpr int KV_PANEL = BK * 64 * 2;        // 16 KiB
 constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KiB (two [64][64] panels)
 constexpr int Q_PANEL = BQ * 64 * 2;         // 8 KiB
 constexpr int PT_BYTES = BK * BQ * 2;        // 16 KiB: [128 key rows][64 queries]
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, two softmax warpgroups
 constexpr int BWD_SMEM = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 2 * PT_BYTES + 4096 /*lse, delta per warp*/ + 1024 + 256;
 
 struct BwdParams {
@@ -113,7 +113,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;       // 2 stages
   uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;
   uint8_t* sdST = sPT + PT_BYTES;
-  float* s_stats = reinterpret_cast<float*>(sdST + PT_BYTES);  // [4 warps][2 buffers][64 lse*log2e | 64 delta]
+  float* s_stats = reinterpret_cast<float*>(sdST + PT_BYTES);  // [8 warps][2 buffers][32 (-lse log2 e) | 32 (delta scale)]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_stats) + 4096);
   uint64_t* kv_full = bars;          // 1
   uint64_t* qdo_full = bars + 1;     // [2]
@@ -178,7 +178,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ptx::mbar_init(&qdo_empty[s], 1);
     }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_full, 4);
+    ptx::mbar_init(pds_full, 8);
     ptx::mbar_init(mma_done, 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -286,67 +286,81 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const bool key_valid = kpos < k_len;
     bool ok = true;
     int prev_h = 0, prev_q0 = 0;
+    // Two warpgroups split the 64 query columns of a step: warpgroup `wg` owns columns [32 wg, 32 wg + 32) of S^T / dP^T / P^T /
+    // dS^T / dQ^T for all 128 key (or head-dim) rows, and after the last step writes out dK (wg 0) or dV (wg 1).
+    const int wg = (warp - 2) >> 2;
     auto flush_dq = [&](int h, int q0) {
-      // dQ^T[r = head-dim index][64 queries] -> dq_acc[(q_begin + q0 + c), h, r]: a warp's 32 lanes add 32 consecutive floats
+      // dQ^T[r = head-dim index][my 32 queries] -> dq_acc[(q_begin + q0 + col), h, r]: a warp's 32 lanes add 32 consecutive floats
       const int64_t stride = static_cast<int64_t>(p.num_heads) * HD;
-      float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0) * p.num_heads + h) * HD + r;
-      const int nq = min(BQ, q_len - q0);
-#pragma unroll 1
-      for (int c = 0; c < 2; c++) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(tm_dQT + lane_addr + c * 32, v);
-        ptx::tmem_ld_wait();
-        if (nq == BQ) {
+      float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0 + wg * 32) * p.num_heads + h) * HD + r;
+      const int nq = min(32, q_len - q0 - wg * 32);
+      uint32_t v[32];
+      ptx::tmem_ld_32x32(tm_dQT + lane_addr + wg * 32, v);
+      ptx::tmem_ld_wait();
+      if (nq == 32) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) red_add_f32(ptr + (c * 32 + i) * stride, __uint_as_float(v[i]));
-        } else {
+        for (int i = 0; i < 32; i++) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++)
-            if (c * 32 + i < nq) red_add_f32(ptr + (c * 32 + i) * stride, __uint_as_float(v[i]));
-        }
+        for (int i = 0; i < 32; i++)
+          if (i < nq) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
       }
     };
+    // row statistics of my 32 query columns of a step: (-lse log2 e, delta * scale), fetched one step ahead
+    auto fetch_stats = [&](int n, float& nl, float& ds) {
+      const int h = hk * group + n / tiles_per_head;
+      int q0, m0;
+      step_pos(n % tiles_per_head, q0, m0);
+      const int qpos = q0 + wg * 32 + lane;
+      const bool in = qpos < q_len;
+      const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
+      nl = in ? -p.lse[idx] * 1.4426950408889634f : -INFINITY;  // exp2(s c - lse) = 0 for rows past the end
+      ds = in ? p.delta[idx] * p.scale : 0.f;
+    };
+    float nl_next = 0.f, ds_next = 0.f;
+    if (n_steps > 0) fetch_stats(0, nl_next, ds_next);
     for (int n = 0; n < n_steps && ok; n++) {
       const int h = hk * group + n / tiles_per_head;
       int q0, m0;
       step_pos(n % tiles_per_head, q0, m0);
-      // per-warp copy of the 64 row statistics of this query tile (no cross-warp synchronisation needed)
-      float* lse_s = s_stats + ((warp - 2) * 2 + (n & 1)) * 128;
-      float* delta_s = lse_s + BQ;
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
-        const int qpos = q0 + c * 32 + lane;
-        const bool in = qpos < q_len;
-        const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
-        lse_s[c * 32 + lane] = in ? -p.lse[idx] * 1.4426950408889634f : -INFINITY;  // exp2(s c - lse) = 0 for rows past the end
-        delta_s[c * 32 + lane] = in ? p.delta[idx] * p.scale : 0.f;
-      }
+      // per-warp copy of the 32 row statistics of this step (no cross-warp synchronisation needed)
+      float* lse_s = s_stats + ((warp - 2) * 2 + (n & 1)) * 64;
+      float* delta_s = lse_s + 32;
+      lse_s[lane] = nl_next;
+      delta_s[lane] = ds_next;
       __syncwarp();
+      if (n + 1 < n_steps) fetch_stats(n + 1, nl_next, ds_next);  // in flight during this step
+      // the previous step's products still read P^T / dS^T from shared memory and own dQ^T: read dQ^T out while S^T / dP^T of
+      // this step are being computed
+      if (n > 0) {
+        if (!ptx::mbar_wait(mma_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        flush_dq(prev_h, prev_q0);
+      }
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
-      uint32_t pk_p[32], pk_ds[32];  // 64 bf16 each
+      uint32_t pk_p[16], pk_ds[16];  // 32 bf16 each
       // query columns this key row may look at: [clo, chi).  Queries past the end of the sequence are handled by lse = +inf.
       int clo = 0, chi = key_valid ? BQ : 0;
       if (p.causal) clo = max(0, kpos - shift - m0);
       if (p.window > 0) chi = min(chi, kpos - shift + p.window - m0);
       const bool full = __all_sync(0xffffffffu, clo == 0 && chi == BQ);
       const uint64_t sl2 = pack2(p.scale_log2, p.scale_log2), sc2 = pack2(p.scale, p.scale);
-#pragma unroll
-      for (int c = 0; c < 2; c++) {
+      {
         uint32_t sv[32], dv[32];
-        ptx::tmem_ld_32x32(tm_ST + lane_addr + c * 32, sv);
-        ptx::tmem_ld_32x32(tm_dPT + lane_addr + c * 32, dv);
+        ptx::tmem_ld_32x32(tm_ST + lane_addr + wg * 32, sv);
+        ptx::tmem_ld_32x32(tm_dPT + lane_addr + wg * 32, dv);
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 nl = *reinterpret_cast<const float4*>(lse_s + c * 32 + i);    // -lse * log2(e)
-          const float4 ds = *reinterpret_cast<const float4*>(delta_s + c * 32 + i);  // delta * scale
+          const float4 nl = *reinterpret_cast<const float4*>(lse_s + i);    // -lse * log2(e)
+          const float4 ds = *reinterpret_cast<const float4*>(delta_s + i);  // delta * scale
           float e0, e1, e2, e3, t0, t1, t2, t3;
           unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sl2, pack2(nl.x, nl.y)), e0, e1);
           unpack2(fma2(pack2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])), sl2, pack2(nl.z, nl.w)), e2, e3);
           float p0 = ex2_approx(e0), p1 = ex2_approx(e1), p2 = ex2_approx(e2), p3 = ex2_approx(e3);
           if (!full) {
-            const int col = c * 32 + i;
+            const int col = wg * 32 + i;
             if (col < clo || col >= chi) p0 = 0.f;
             if (col + 1 < clo || col + 1 >= chi) p1 = 0.f;
             if (col + 2 < clo || col + 2 >= chi) p2 = 0.f;
@@ -359,23 +373,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           unpack2(fma2(pack2(p2, p3), u23, 0ull), t2, t3);
           __nv_bfloat162 hp0 = __floats2bfloat162_rn(p0, p1), hp1 = __floats2bfloat162_rn(p2, p3);
           __nv_bfloat162 hd0 = __floats2bfloat162_rn(t0, t1), hd1 = __floats2bfloat162_rn(t2, t3);
-          pk_p[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hp0);
-          pk_p[c * 16 + i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hp1);
-          pk_ds[c * 16 + i / 2] = *reinterpret_cast<uint32_t*>(&hd0);
-          pk_ds[c * 16 + i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hd1);
+          pk_p[i / 2] = *reinterpret_cast<uint32_t*>(&hp0);
+          pk_p[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hp1);
+          pk_ds[i / 2] = *reinterpret_cast<uint32_t*>(&hd0);
+          pk_ds[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hd1);
         }
-      }
-      // the previous step's products still read P^T / dS^T from shared memory and own dQ^T
-      if (n > 0) {
-        if (!ptx::mbar_wait(mma_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after();
-        flush_dq(prev_h, prev_q0);
       }
       uint8_t* prow = sPT + r * 128;
       uint8_t* drow = sdST + r * 128;
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int sw = (u ^ (r & 7)) << 4;
+      for (int u = 0; u < 4; u++) {
+        const int sw = ((wg * 4 + u) ^ (r & 7)) << 4;
         *reinterpret_cast<uint4*>(prow + sw) = make_uint4(pk_p[u * 4], pk_p[u * 4 + 1], pk_p[u * 4 + 2], pk_p[u * 4 + 3]);
         *reinterpret_cast<uint4*>(drow + sw) = make_uint4(pk_ds[u * 4], pk_ds[u * 4 + 1], pk_ds[u * 4 + 2], pk_ds[u * 4 + 3]);
       }
@@ -392,8 +400,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // dK, dV rows of this key.  Every lane issues the warp-aligned TMEM loads; only the stores depend on key_valid.
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
       const int64_t acc_off = (static_cast<int64_t>(kv_row + r) * p.num_kv_heads + hk) * HD;  // context parallel: row in the owner's accumulators
-#pragma unroll 1
-      for (int which = 0; which < 2; which++) {
+      {
+        const int which = wg;  // warpgroup 0 writes dK, warpgroup 1 dV
         __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
         float* acc = cpm_on ? (which == 0 ? cpb.dk_acc[kv_owner] : cpb.dv_acc[kv_owner]) + acc_off : nullptr;
         const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
