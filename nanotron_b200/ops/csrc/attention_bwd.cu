@@ -25,7 +25,7 @@ constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KiB (two [64][64] panels)
 constexpr int Q_PANEL = BQ * 64 * 2;         // 8 KiB
 constexpr int PT_BYTES = BK * BQ * 2;        // 16 KiB: [128 key rows][64 queries]
 constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, two softmax warpgroups
-constexpr int BWD_SMEM = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 2 * PT_BYTES + 4096 /*lse, delta per warp*/ + 1024 + 256;
+constexpr int BWD_SMEM = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 4 * PT_BYTES + 4096 /*lse, delta per warp*/ + 1024 + 256;
 
 struct BwdParams {
   int num_heads, num_kv_heads, causal, window;
@@ -111,17 +111,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sV = sK + KV_TILE_BYTES;
   uint8_t* sQ = sV + KV_TILE_BYTES;           // 2 stages
   uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;       // 2 stages
-  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;
-  uint8_t* sdST = sPT + PT_BYTES;
-  float* s_stats = reinterpret_cast<float*>(sdST + PT_BYTES);  // [8 warps][2 buffers][32 (-lse log2 e) | 32 (delta scale)]
+  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;      // 2 buffers
+  uint8_t* sdST = sPT + 2 * PT_BYTES;         // 2 buffers
+  float* s_stats = reinterpret_cast<float*>(sdST + 2 * PT_BYTES);  // [8 warps][2 buffers][32 (-lse log2 e) | 32 (delta scale)]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_stats) + 4096);
   uint64_t* kv_full = bars;          // 1
   uint64_t* qdo_full = bars + 1;     // [2]
   uint64_t* qdo_empty = bars + 3;    // [2]
   uint64_t* sdp_full = bars + 5;     // 1
   uint64_t* pds_full = bars + 6;     // 1
-  uint64_t* mma_done = bars + 7;     // 1  (dV, dK, dQ^T products of a step finished)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* mma_done = bars + 7;     // [2] (dV, dK, dQ^T products of a step finished; steps alternate between the two)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,7 +179,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     ptx::mbar_init(sdp_full, 1);
     ptx::mbar_init(pds_full, 8);
-    ptx::mbar_init(mma_done, 1);
+    ptx::mbar_init(&mma_done[0], 1);
+    ptx::mbar_init(&mma_done[1], 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -197,7 +198,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_ST = tmem_base;         // 64 columns
   const uint32_t tm_dPT = tmem_base + 64;   // 64
-  const uint32_t tm_dQT = tmem_base + 128;  // 64
+  const uint32_t tm_dQT = tmem_base + 128;  // 2 x 64 (steps alternate)
   const uint32_t tm_dV = tmem_base + 256;   // 128
   const uint32_t tm_dK = tmem_base + 384;   // 128
 
@@ -255,26 +256,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int s = n & 1;
         if (!ptx::mbar_wait(pds_full, n & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
-        const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
-        // dV += P^T dO ; dK += dS^T Q   (K dimension = 64 queries: 4 steps of 16 rows)
-#pragma unroll
-        for (int k = 0; k < BQ / 16; k++) {
-          ptx::umma_f16(tm_dV, ptx::make_smem_desc(aPT + k * 32, 16, 1024), ptx::make_smem_desc(adO + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < BQ / 16; k++) {
-          ptx::umma_f16(tm_dK, ptx::make_smem_desc(adST + k * 32, 16, 1024), ptx::make_smem_desc(aQ + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
-        }
-        // dQ^T = K^T dS^T   (K dimension = 128 keys: 8 steps of 16 rows)
-#pragma unroll
-        for (int k = 0; k < BK / 16; k++) {
-          ptx::umma_f16(tm_dQT, ptx::make_smem_desc(aK + k * 16 * 128, KV_PANEL, 1024), ptx::make_smem_desc(adST + k * 16 * 128, PT_BYTES, 1024), idesc_dq, k != 0);
-        }
-        ptx::umma_commit(&qdo_empty[s]);
-        ptx::umma_commit(mma_done);
+        // the softmax warps hold S^T / dP^T of this step in registers: the next step's scores go first, so that its softmax
+        // overlaps the three products of this step
         if (n + 1 < n_steps) {
           if (!issue_s(n + 1)) { ok = false; break; }
         }
+        const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
+        const uint32_t aPTs = aPT + s * PT_BYTES, adSTs = adST + s * PT_BYTES;
+        // dV += P^T dO ; dK += dS^T Q   (K dimension = 64 queries: 4 steps of 16 rows)
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++) {
+          ptx::umma_f16(tm_dV, ptx::make_smem_desc(aPTs + k * 32, 16, 1024), ptx::make_smem_desc(adO + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++) {
+          ptx::umma_f16(tm_dK, ptx::make_smem_desc(adSTs + k * 32, 16, 1024), ptx::make_smem_desc(aQ + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
+        }
+        // dQ^T = K^T dS^T   (K dimension = 128 keys: 8 steps of 16 rows), into the dQ^T buffer of this step's parity
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++) {
+          ptx::umma_f16(tm_dQT + s * BQ, ptx::make_smem_desc(aK + k * 16 * 128, KV_PANEL, 1024), ptx::make_smem_desc(adSTs + k * 16 * 128, PT_BYTES, 1024), idesc_dq, k != 0);
+        }
+        ptx::umma_commit(&qdo_empty[s]);
+        ptx::umma_commit(&mma_done[s]);
       }
     }
   } else {
@@ -289,13 +293,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // Two warpgroups split the 64 query columns of a step: warpgroup `wg` owns columns [32 wg, 32 wg + 32) of S^T / dP^T / P^T /
     // dS^T / dQ^T for all 128 key (or head-dim) rows, and after the last step writes out dK (wg 0) or dV (wg 1).
     const int wg = (warp - 2) >> 2;
-    auto flush_dq = [&](int h, int q0) {
+    auto flush_dq = [&](int h, int q0, int par) {
       // dQ^T[r = head-dim index][my 32 queries] -> dq_acc[(q_begin + q0 + col), h, r]: a warp's 32 lanes add 32 consecutive floats
       const int64_t stride = static_cast<int64_t>(p.num_heads) * HD;
       float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0 + wg * 32) * p.num_heads + h) * HD + r;
       const int nq = min(32, q_len - q0 - wg * 32);
       uint32_t v[32];
-      ptx::tmem_ld_32x32(tm_dQT + lane_addr + wg * 32, v);
+      ptx::tmem_ld_32x32(tm_dQT + lane_addr + par * BQ + wg * 32, v);
       ptx::tmem_ld_wait();
       if (nq == 32) {
 #pragma unroll
@@ -330,13 +334,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       delta_s[lane] = ds_next;
       __syncwarp();
       if (n + 1 < n_steps) fetch_stats(n + 1, nl_next, ds_next);  // in flight during this step
-      // the previous step's products still read P^T / dS^T from shared memory and own dQ^T: read dQ^T out while S^T / dP^T of
-      // this step are being computed
-      if (n > 0) {
-        if (!ptx::mbar_wait(mma_done, (n - 1) & 1, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after();
-        flush_dq(prev_h, prev_q0);
-      }
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t pk_p[16], pk_ds[16];  // 32 bf16 each
@@ -379,8 +376,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           pk_ds[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hd1);
         }
       }
-      uint8_t* prow = sPT + r * 128;
-      uint8_t* drow = sdST + r * 128;
+      // P^T / dS^T buffer of this step's parity: its last readers were the products of step n - 2, awaited during step n - 1
+      uint8_t* prow = sPT + (n & 1) * PT_BYTES + r * 128;
+      uint8_t* drow = sdST + (n & 1) * PT_BYTES + r * 128;
 #pragma unroll
       for (int u = 0; u < 4; u++) {
         const int sw = ((wg * 4 + u) ^ (r & 7)) << 4;
@@ -391,12 +389,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ptx::fence_proxy_async();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(pds_full);
+      // off the critical path: dQ^T of the previous step (the tensor core is busy with this step's scores / products meanwhile).
+      // mma_done[b] completes one phase per two steps and the products of step n + 1 cannot start before this warp's next
+      // arrival, so the barrier is never more than one phase ahead of this wait.
+      if (n > 0) {
+        if (!ptx::mbar_wait(&mma_done[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        flush_dq(prev_h, prev_q0, (n - 1) & 1);
+      }
       prev_h = h;
       prev_q0 = q0;
     }
-    if (ok && n_steps > 0 && ptx::mbar_wait(mma_done, (n_steps - 1) & 1, abort_flag)) {
+    if (ok && n_steps > 0 && ptx::mbar_wait(&mma_done[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_flag)) {
       ptx::tc_fence_after();
-      flush_dq(prev_h, prev_q0);
+      flush_dq(prev_h, prev_q0, (n_steps - 1) & 1);
       // dK, dV rows of this key.  Every lane issues the warp-aligned TMEM loads; only the stores depend on key_valid.
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
       const int64_t acc_off = (static_cast<int64_t>(kv_row + r) * p.num_kv_heads + hk) * HD;  // context parallel: row in the owner's accumulators
