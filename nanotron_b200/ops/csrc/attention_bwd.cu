@@ -8,8 +8,10 @@
 //     dV  += P^T dO       dK += dS^T Q       (fp32 accumulators in TMEM for the whole CTA lifetime)
 //     dQ^T = K^T dS^T     (128 head-dim lanes x 64 queries) -> red.global.add.f32 into an fp32 dQ buffer; a warp's 32
 //                          lanes hit 32 consecutive floats, so the reductions are coalesced.
-// Warp roles: warp 0 TMA producer (K, V once; Q / dO double buffered), warp 1 MMA issuer, warps 2-5 softmax + dQ read-out
-// + final dK / dV write-out.  A small pre-pass computes delta = rowsum(dO * O); a post-pass casts dQ to bf16.
+// Warp roles: warp 0 TMA producer (K, V once; Q / dO double buffered), warp 1 MMA issuer (the scores of step n + 1 are issued
+// before the three products of step n, so the softmax of the next step overlaps them; dQ^T in tensor memory and P^T / dS^T in
+// shared memory are double buffered), warps 2-9 softmax (two warpgroups, 32 query columns each) + final dK / dV write-out,
+// warps 10-13 dQ^T read-out.  A small pre-pass computes delta = rowsum(dO * O); a post-pass casts dQ to bf16.
 // All waits are bounded (see sm100_ptx.cuh).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -24,8 +26,13 @@ constexpr int KV_PANEL = BK * 64 * 2;        // 16 KiB
 constexpr int Q_TILE_BYTES = BQ * HD * 2;    // 16 KiB (two [64][64] panels)
 constexpr int Q_PANEL = BQ * 64 * 2;         // 8 KiB
 constexpr int PT_BYTES = BK * BQ * 2;        // 16 KiB: [128 key rows][64 queries]
-constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, two softmax warpgroups
-constexpr int BWD_SMEM = 2 * KV_TILE_BYTES + 4 * Q_TILE_BYTES + 4 * PT_BYTES + 4096 /*lse, delta per warp*/ + 1024 + 256;
+constexpr int BWD_THREADS = 448;  // TMA warp, MMA warp, two softmax warpgroups, one dQ read-out warpgroup
+constexpr int QDO_STAGES = 3;                // Q / dO tiles in flight: products of step n, scores of step n + 1, prefetch
+constexpr int BWD_HEAD_BYTES = 256 + 2048;   // barriers, then per-warp row statistics, in front of the 1024-byte aligned tiles
+constexpr int BWD_TILE_BYTES = 2 * KV_TILE_BYTES + 2 * QDO_STAGES * Q_TILE_BYTES + 4 * PT_BYTES;  // 224 KiB
+// With a 1024-byte aligned dynamic shared memory base this is exactly the 227 KiB a CTA may have; the kernel checks that the
+// tiles fit behind the aligned offset and gives up with an error status otherwise.
+constexpr int BWD_SMEM = 3072 + BWD_TILE_BYTES;
 
 struct BwdParams {
   int num_heads, num_kv_heads, causal, window;
@@ -102,26 +109,31 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   return d;
 }
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __maxnreg__(128)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const BwdParams p, const __grid_constant__ CpBwd cpb) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  float* s_stats = reinterpret_cast<float*>(smem_raw + 256);  // [8 warps][32 (-lse log2 e) | 32 (delta scale)]
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + BWD_HEAD_BYTES + 1023) & ~uintptr_t(1023));
+  if (smem + BWD_TILE_BYTES > smem_raw + BWD_SMEM) {  // uniform for the grid: the base was not 1024-byte aligned
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, NTB_ERR_LAUNCH);
+    return;
+  }
   uint8_t* sK = smem;
   uint8_t* sV = sK + KV_TILE_BYTES;
-  uint8_t* sQ = sV + KV_TILE_BYTES;           // 2 stages
-  uint8_t* sdO = sQ + 2 * Q_TILE_BYTES;       // 2 stages
-  uint8_t* sPT = sdO + 2 * Q_TILE_BYTES;      // 2 buffers
-  uint8_t* sdST = sPT + 2 * PT_BYTES;         // 2 buffers
-  float* s_stats = reinterpret_cast<float*>(sdST + 2 * PT_BYTES);  // [8 warps][2 buffers][32 (-lse log2 e) | 32 (delta scale)]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_stats) + 4096);
+  uint8_t* sQ = sV + KV_TILE_BYTES;                   // QDO_STAGES stages
+  uint8_t* sdO = sQ + QDO_STAGES * Q_TILE_BYTES;      // QDO_STAGES stages
+  uint8_t* sPT = sdO + QDO_STAGES * Q_TILE_BYTES;     // 2 buffers
+  uint8_t* sdST = sPT + 2 * PT_BYTES;                 // 2 buffers
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // [2]
-  uint64_t* qdo_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;     // 1
-  uint64_t* pds_full = bars + 6;     // 1
-  uint64_t* mma_done = bars + 7;     // [2] (dV, dK, dQ^T products of a step finished; steps alternate between the two)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* qdo_full = bars + 1;     // [QDO_STAGES]
+  uint64_t* qdo_empty = bars + 4;    // [QDO_STAGES]
+  uint64_t* sdp_full = bars + 7;     // 1
+  uint64_t* pds_full = bars + 8;     // 1
+  uint64_t* mma_done = bars + 9;     // [2] (dV, dK, dQ^T products of a step finished; steps alternate between the two)
+  uint64_t* dq_free = bars + 11;     // [2] (dQ^T buffer read out by the four read-out warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,7 +185,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; s++) {
+    for (int s = 0; s < QDO_STAGES; s++) {
       ptx::mbar_init(&qdo_full[s], 1);
       ptx::mbar_init(&qdo_empty[s], 1);
     }
@@ -181,6 +193,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     ptx::mbar_init(pds_full, 8);
     ptx::mbar_init(&mma_done[0], 1);
     ptx::mbar_init(&mma_done[1], 1);
+    ptx::mbar_init(&dq_free[0], 4);
+    ptx::mbar_init(&dq_free[1], 4);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tmap(&tmap_q);
@@ -210,8 +224,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ptx::tma_load_3d(sV, map_v, kv_full, 0, hk, kv_row);
       ptx::tma_load_3d(sV + KV_PANEL, map_v, kv_full, 64, hk, kv_row);
       for (int n = 0; n < n_steps; n++) {
-        const int s = n & 1;
-        const uint32_t ph = (n >> 1) & 1;
+        const int s = n % QDO_STAGES;
+        const uint32_t ph = (n / QDO_STAGES) & 1;
         const int h = hk * group + n / tiles_per_head;
         int sq0, sm0;
         step_pos(n % tiles_per_head, sq0, sm0);
@@ -232,8 +246,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t aK = ptx::smem_u32(sK), aV = ptx::smem_u32(sV), aPT = ptx::smem_u32(sPT), adST = ptx::smem_u32(sdST);
       bool ok = ptx::mbar_wait(kv_full, 0, abort_flag);
       auto issue_s = [&](int n) -> bool {
-        const int s = n & 1;
-        if (!ptx::mbar_wait(&qdo_full[s], (n >> 1) & 1, abort_flag)) return false;
+        const int s = n % QDO_STAGES;
+        if (!ptx::mbar_wait(&qdo_full[s], (n / QDO_STAGES) & 1, abort_flag)) return false;
         ptx::tc_fence_after();
         const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
 #pragma unroll
@@ -261,7 +275,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (n + 1 < n_steps) {
           if (!issue_s(n + 1)) { ok = false; break; }
         }
-        const uint32_t aQ = ptx::smem_u32(sQ + s * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + s * Q_TILE_BYTES);
+        const int qs = n % QDO_STAGES;
+        const uint32_t aQ = ptx::smem_u32(sQ + qs * Q_TILE_BYTES), adO = ptx::smem_u32(sdO + qs * Q_TILE_BYTES);
         const uint32_t aPTs = aPT + s * PT_BYTES, adSTs = adST + s * PT_BYTES;
         // dV += P^T dO ; dK += dS^T Q   (K dimension = 64 queries: 4 steps of 16 rows)
 #pragma unroll
@@ -272,12 +287,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int k = 0; k < BQ / 16; k++) {
           ptx::umma_f16(tm_dK, ptx::make_smem_desc(adSTs + k * 32, 16, 1024), ptx::make_smem_desc(aQ + k * 16 * 128, Q_PANEL, 1024), idesc_dv, (n | k) != 0);
         }
-        // dQ^T = K^T dS^T   (K dimension = 128 keys: 8 steps of 16 rows), into the dQ^T buffer of this step's parity
+        // dQ^T = K^T dS^T   (K dimension = 128 keys: 8 steps of 16 rows), into the dQ^T buffer of this step's parity, once the
+        // read-out warps are done with step n - 2
+        if (n >= 2) {
+          if (!ptx::mbar_wait(&dq_free[s], ((n - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after();
+        }
 #pragma unroll
         for (int k = 0; k < BK / 16; k++) {
           ptx::umma_f16(tm_dQT + s * BQ, ptx::make_smem_desc(aK + k * 16 * 128, KV_PANEL, 1024), ptx::make_smem_desc(adSTs + k * 16 * 128, PT_BYTES, 1024), idesc_dq, k != 0);
         }
-        ptx::umma_commit(&qdo_empty[s]);
+        ptx::umma_commit(&qdo_empty[qs]);
         ptx::umma_commit(&mma_done[s]);
       }
     }
@@ -289,32 +309,47 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int kpos = k0 + r;
     const bool key_valid = kpos < k_len;
     bool ok = true;
-    int prev_h = 0, prev_q0 = 0;
-    // Two warpgroups split the 64 query columns of a step: warpgroup `wg` owns columns [32 wg, 32 wg + 32) of S^T / dP^T / P^T /
-    // dS^T / dQ^T for all 128 key (or head-dim) rows, and after the last step writes out dK (wg 0) or dV (wg 1).
+    // Warps 2-9: two warpgroups split the 64 query columns of a step: warpgroup `wg` owns columns [32 wg, 32 wg + 32) of S^T /
+    // dP^T / P^T / dS^T for all 128 key rows, and after the last step writes out dK (wg 0) or dV (wg 1).
+    // Warps 10-13: read dQ^T (128 head-dim rows x 64 queries) of every step out of tensor memory into the fp32 dQ buffer.
     const int wg = (warp - 2) >> 2;
-    auto flush_dq = [&](int h, int q0, int par) {
-      // dQ^T[r = head-dim index][my 32 queries] -> dq_acc[(q_begin + q0 + col), h, r]: a warp's 32 lanes add 32 consecutive floats
+    if (wg == 2) {
+      int hi = 0, ti = 0;
       const int64_t stride = static_cast<int64_t>(p.num_heads) * HD;
-      float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0 + wg * 32) * p.num_heads + h) * HD + r;
-      const int nq = min(32, q_len - q0 - wg * 32);
-      uint32_t v[32];
-      ptx::tmem_ld_32x32(tm_dQT + lane_addr + par * BQ + wg * 32, v);
-      ptx::tmem_ld_wait();
-      if (nq == 32) {
+      for (int n = 0; n < n_steps && ok; n++) {
+        int q0, m0;
+        step_pos(ti, q0, m0);
+        const int h = hk * group + hi;
+        if (++ti == tiles_per_head) { ti = 0; hi++; }
+        if (!ptx::mbar_wait(&mma_done[n & 1], (n >> 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+        // dQ^T[r = head-dim index][64 queries] -> dq_acc[(q_begin + q0 + col), h, r]: a warp's 32 lanes add 32 consecutive floats
+#pragma unroll 1
+        for (int c = 0; c < 2; c++) {
+          float* ptr = p.dq_acc + (static_cast<int64_t>(q_begin + q0 + c * 32) * p.num_heads + h) * HD + r;
+          const int nq = min(32, q_len - q0 - c * 32);
+          uint32_t v[32];
+          ptx::tmem_ld_32x32(tm_dQT + lane_addr + (n & 1) * BQ + c * 32, v);
+          ptx::tmem_ld_wait();
+          if (nq == 32) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
-      } else {
+            for (int i = 0; i < 32; i++) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
+          } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++)
-          if (i < nq) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
+            for (int i = 0; i < 32; i++)
+              if (i < nq) red_add_f32(ptr + i * stride, __uint_as_float(v[i]));
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&dq_free[n & 1]);
       }
-    };
+    } else {
     // row statistics of my 32 query columns of a step: (-lse log2 e, delta * scale), fetched one step ahead
-    auto fetch_stats = [&](int n, float& nl, float& ds) {
-      const int h = hk * group + n / tiles_per_head;
+    auto fetch_stats = [&](int hi, int ti, float& nl, float& ds) {
+      const int h = hk * group + hi;
       int q0, m0;
-      step_pos(n % tiles_per_head, q0, m0);
+      step_pos(ti, q0, m0);
       const int qpos = q0 + wg * 32 + lane;
       const bool in = qpos < q_len;
       const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
@@ -322,18 +357,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ds = in ? p.delta[idx] * p.scale : 0.f;
     };
     float nl_next = 0.f, ds_next = 0.f;
-    if (n_steps > 0) fetch_stats(0, nl_next, ds_next);
+    if (n_steps > 0) fetch_stats(0, 0, nl_next, ds_next);
+    int hi = 0, ti = 0;
     for (int n = 0; n < n_steps && ok; n++) {
-      const int h = hk * group + n / tiles_per_head;
       int q0, m0;
-      step_pos(n % tiles_per_head, q0, m0);
+      step_pos(ti, q0, m0);
+      if (++ti == tiles_per_head) { ti = 0; hi++; }  // (hi, ti) now name the next step
       // per-warp copy of the 32 row statistics of this step (no cross-warp synchronisation needed)
-      float* lse_s = s_stats + ((warp - 2) * 2 + (n & 1)) * 64;
+      float* lse_s = s_stats + (warp - 2) * 64;
       float* delta_s = lse_s + 32;
       lse_s[lane] = nl_next;
       delta_s[lane] = ds_next;
       __syncwarp();
-      if (n + 1 < n_steps) fetch_stats(n + 1, nl_next, ds_next);  // in flight during this step
+      if (n + 1 < n_steps) fetch_stats(hi, ti, nl_next, ds_next);  // in flight during this step
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t pk_p[16], pk_ds[16];  // 32 bf16 each
@@ -376,7 +412,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           pk_ds[i / 2 + 1] = *reinterpret_cast<uint32_t*>(&hd1);
         }
       }
-      // P^T / dS^T buffer of this step's parity: its last readers were the products of step n - 2, awaited during step n - 1
+      // P^T / dS^T buffer of this step's parity: its last readers were the products of step n - 2.  (mma_done[b] completes one
+      // phase per two steps and the products of step n cannot start before this warp's arrival below, so the barrier is never
+      // more than one phase ahead of this wait.)
+      if (n >= 2) {
+        if (!ptx::mbar_wait(&mma_done[n & 1], ((n - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+      }
       uint8_t* prow = sPT + (n & 1) * PT_BYTES + r * 128;
       uint8_t* drow = sdST + (n & 1) * PT_BYTES + r * 128;
 #pragma unroll
@@ -389,20 +430,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ptx::fence_proxy_async();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(pds_full);
-      // off the critical path: dQ^T of the previous step (the tensor core is busy with this step's scores / products meanwhile).
-      // mma_done[b] completes one phase per two steps and the products of step n + 1 cannot start before this warp's next
-      // arrival, so the barrier is never more than one phase ahead of this wait.
-      if (n > 0) {
-        if (!ptx::mbar_wait(&mma_done[(n - 1) & 1], ((n - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after();
-        flush_dq(prev_h, prev_q0, (n - 1) & 1);
-      }
-      prev_h = h;
-      prev_q0 = q0;
     }
     if (ok && n_steps > 0 && ptx::mbar_wait(&mma_done[(n_steps - 1) & 1], ((n_steps - 1) >> 1) & 1, abort_flag)) {
       ptx::tc_fence_after();
-      flush_dq(prev_h, prev_q0, (n_steps - 1) & 1);
       // dK, dV rows of this key.  Every lane issues the warp-aligned TMEM loads; only the stores depend on key_valid.
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
       const int64_t acc_off = (static_cast<int64_t>(kv_row + r) * p.num_kv_heads + hk) * HD;  // context parallel: row in the owner's accumulators
@@ -447,6 +477,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         *reinterpret_cast<uint4*>(p.dv + off + c) = make_uint4(0, 0, 0, 0);
       }
     }
+    }  // softmax warpgroups
   }
 
   ptx::tc_fence_before();
