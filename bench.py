@@ -134,6 +134,7 @@ def run_native(args):
         raise SystemExit("bench.py needs a CUDA device")
     torch.cuda.set_device(local_rank)
     ops.set_gemm(args.gemm)
+    ops.set_attention(args.attention)
     from nanotron_b200.ops import native_gemm
 
     native_gemm.set_variant(args.gemm_variant)
@@ -234,6 +235,7 @@ def main():
     ap.add_argument("--accum", type=int, default=8)
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "cublas"], help="auto / tcgen05: every linear-layer product on the in-tree tcgen05 kernels; cublas: library GEMMs (wgrad then needs a separate fp32 add)")
+    ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"], help="auto / sdpa: library attention; native: the in-tree tcgen05 flash-attention kernels")
     ap.add_argument("--gemm-variant", default="pair", choices=["single", "pair"], help="in-tree GEMM kernel: one CTA per 128x256 tile, or CTA pairs (cta_group::2) per 256x256 tile")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence-parallel mode); dp = gpus / (tp * pp)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (1F1B)")

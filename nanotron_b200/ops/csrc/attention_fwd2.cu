@@ -6,15 +6,18 @@
 //   warp 1      MMA issuer, one elected thread.  Steady state per key tile j:
 //                   O0 += P0(j) V(j);  S0 = Q0 K(j+1)^T;  O1 += P1(j) V(j);  S1 = Q1 K(j+1)^T
 //               so while the softmax of one query tile runs, the tensor core works on the other tile.
-//               P is the A operand FROM TENSOR MEMORY: the softmax warps overwrite the first 64 columns of S_t with the bf16
-//               probabilities (two per 32-bit column), so P never goes through shared memory and S_t / P_t share storage.
+//               P is the A operand FROM TENSOR MEMORY: the softmax warps overwrite part of S_t with the bf16 probabilities
+//               (two per 32-bit column), so P never goes through shared memory and S_t / P_t share storage.
 //               MMAs of one thread execute in issue order, which is what makes the reuse of S_t safe without a barrier:
 //               S_t(j+1) is issued after the P_t(j) V(j) product that reads the same columns.
-//   warps 2-5   softmax of query tile 0, warps 6-9 of tile 1: thread r owns query row r of its tile and reads the whole
-//               128-column score row into registers with one wait.  In steady state there is NO row maximum: the exponentials
-//               are taken relative to the reference maximum of the earlier tiles and the row sum (needed anyway) shows whether
-//               that was good enough; if not (a row sums to more than 1024, or is not finite) the warp computes the exact
-//               maximum from its registers, rescales O and l, and recomputes the tile.  The final O / l is exact either way.
+//   warps 2-17  softmax: warps 2-9 serve query tile 0, warps 10-17 tile 1; inside a tile two warps share 32 query rows (a TMEM
+//               lane quarter), one per half of the key columns (64 scores each, read 32 at a time) and per half of O's columns.
+//               In steady state there is NO row maximum: the exponentials are taken relative to the reference maximum of the
+//               earlier tiles and the row sum (needed anyway) shows whether that was good enough; if not (a half row sums to
+//               more than 1024, or is not finite) both warps of the rows compute the exact maximum (halves exchanged through
+//               shared memory behind a 64-thread named barrier), rescale O and l, and recompute the tile: P is only stored
+//               after that decision, so the scores can be read again.  The final O / l is exact either way.  P_t is stored
+//               over columns 0-31 and 64-95 of S_t (each warp inside its own half).
 //               `s_full[t]` firing also means P_t(j-1) V(j-1) has completed (a commit covers every earlier MMA of the thread),
 //               so O_t may be rescaled as soon as S_t(j) can be read.
 // Epilogue: O_t / l from TMEM straight to global memory (rows past the end of the sequence are not written), LSE to global.
