@@ -54,6 +54,13 @@ struct Fwd2Params {
   float* lse;          // [Hq, T]
   int total_q;
   int* status;
+  int cp, cp_me, cp_chunk;  // context parallel: group size (0 = off), this rank, tokens per chunk (multiple of 128)
+};
+
+constexpr int CP_MAX = 8;
+struct Cp2Maps {
+  CUtensorMap k[CP_MAX];
+  CUtensorMap v[CP_MAX];
 };
 
 __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -139,7 +146,7 @@ __device__ __forceinline__ void exp2_poly_pair(float y0, float y1, float& x0, fl
 template <int POLY_PAIRS>
 __global__ void __maxnreg__(96)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                  const Fwd2Params p) {
+                  const Fwd2Params p, const __grid_constant__ Cp2Maps cpm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;  // two tiles
@@ -163,22 +170,33 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   // grid: x = (sequence, head), y = query-tile pair.  Blocks are handed out x-fastest, so all (sequence, head) instances of the
   // heaviest pair start first and the light ones fill the tail
   const int b = blockIdx.x / p.num_heads, h = blockIdx.x % p.num_heads;
-  const int q_begin = p.cu_q[b];
-  const int q_len = p.cu_q[b + 1] - q_begin;
-  const int k_begin = p.cu_k[b];
-  const int k_len = p.cu_k[b + 1] - k_begin;
+  // Context-parallel mode (p.cp > 0): the sequence is split in 2 * cp chunks and this rank holds chunks cp_me and 2 cp - 1 - cp_me
+  // of every batch row, one after the other.  Keys / values stay with their owners (peer-mapped buffers, one tensor map per rank)
+  // and are read tile by tile over NVLink by the TMA producer; masks use global positions.
+  const bool cpm_on = p.cp > 0;
+  const int q_begin = cpm_on ? b * 2 * p.cp_chunk : p.cu_q[b];
+  const int q_len = cpm_on ? 2 * p.cp_chunk : p.cu_q[b + 1] - q_begin;
+  const int k_begin = cpm_on ? 0 : p.cu_k[b];
+  const int k_len = cpm_on ? 2 * p.cp * p.cp_chunk : p.cu_k[b + 1] - k_begin;
   // heavy (late) query tiles first: with a causal mask they have the most key tiles
   const int pair = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
   const int q0 = pair * 2 * BM;
   if (q0 >= q_len) return;  // uniform for the CTA
-  const int shift = k_len - q_len;  // bottom-right aligned causal mask
+  const int shift = cpm_on ? 0 : k_len - q_len;  // bottom-right aligned causal mask
+  // position of a query tile's first row for the masks: the local one, or the global one under context parallelism
+  auto mask_pos = [&](int qt) -> int {
+    if (!cpm_on) return qt;
+    const int half = qt / p.cp_chunk;
+    const int chunk = half == 0 ? p.cp_me : 2 * p.cp - 1 - p.cp_me;
+    return chunk * p.cp_chunk + (qt - half * p.cp_chunk);
+  };
   // key range of the CTA: from the first key tile query tile 0 may see to the last one query tile 1 may see
   int kv_start = 0;
-  if (p.window > 0) kv_start = max(0, (q0 + shift - p.window + 1) / BN * BN);
+  if (p.window > 0) kv_start = max(0, (mask_pos(q0) + shift - p.window + 1) / BN * BN);
   auto tiles_of = [&](int t) -> int {
     const int qt = q0 + t * BM;
     int kv_end = k_len;
-    if (p.causal) kv_end = min(k_len, qt + BM + shift);
+    if (p.causal) kv_end = min(k_len, mask_pos(qt) + BM + shift);
     return (qt < q_len && kv_end > kv_start) ? (kv_end - kv_start + BN - 1) / BN : 0;
   };
   const int n_t0 = tiles_of(0), n_t1 = tiles_of(1);
@@ -225,16 +243,27 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ptx::tma_load_3d(sQ + t * TILE_BYTES + PANEL_BYTES, &tmap_q, q_full, 64, h, q_begin + q0 + t * BM);
       }
       for (int j = 0; j < n_max; j++) {
-        const int krow = k_begin + kv_start + j * BN;
+        int krow = k_begin + kv_start + j * BN;
+        const CUtensorMap* mk = &tmap_k;
+        const CUtensorMap* mv = &tmap_v;
+        if (cpm_on) {
+          // global key tile -> the rank that stores it and the row inside that rank's [batch, 2 chunks] buffer
+          const int gk = kv_start + j * BN;
+          const int chunk = gk / p.cp_chunk;
+          const int owner = chunk < p.cp ? chunk : 2 * p.cp - 1 - chunk;
+          krow = b * 2 * p.cp_chunk + (chunk < p.cp ? 0 : p.cp_chunk) + (gk - chunk * p.cp_chunk);
+          mk = &cpm.k[owner];
+          mv = &cpm.v[owner];
+        }
         const int ks = j % K_STAGES, vs = j % V_STAGES;
         if (!ptx::mbar_wait(&k_empty[ks], ((j / K_STAGES) & 1) ^ 1, abort_flag)) break;
         ptx::mbar_expect_tx(&k_full[ks], TILE_BYTES);
-        ptx::tma_load_3d(sK + ks * TILE_BYTES, &tmap_k, &k_full[ks], 0, hk, krow);
-        ptx::tma_load_3d(sK + ks * TILE_BYTES + PANEL_BYTES, &tmap_k, &k_full[ks], 64, hk, krow);
+        ptx::tma_load_3d(sK + ks * TILE_BYTES, mk, &k_full[ks], 0, hk, krow);
+        ptx::tma_load_3d(sK + ks * TILE_BYTES + PANEL_BYTES, mk, &k_full[ks], 64, hk, krow);
         if (!ptx::mbar_wait(&v_empty[vs], ((j / V_STAGES) & 1) ^ 1, abort_flag)) break;
         ptx::mbar_expect_tx(&v_full[vs], TILE_BYTES);
-        ptx::tma_load_3d(sV + vs * TILE_BYTES, &tmap_v, &v_full[vs], 0, hk, krow);
-        ptx::tma_load_3d(sV + vs * TILE_BYTES + PANEL_BYTES, &tmap_v, &v_full[vs], 64, hk, krow);
+        ptx::tma_load_3d(sV + vs * TILE_BYTES, mv, &v_full[vs], 0, hk, krow);
+        ptx::tma_load_3d(sV + vs * TILE_BYTES + PANEL_BYTES, mv, &v_full[vs], 64, hk, krow);
       }
     }
   } else if (warp == 1) {
@@ -295,7 +324,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     if (n_tiles > 0) {
       const int quarter = warp & 3;            // TMEM lane quarter this warp may access
       const int r = quarter * 32 + lane;       // query row inside the tile
-      const int qpos = q0 + t * BM + r;        // position inside the sequence
+      const int qpos = q0 + t * BM + r;        // position inside the (local) sequence: validity and output row
+      const int mpos = mask_pos(q0 + t * BM) + r;  // position used by the masks
       const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tS = tmem_base + lane_addr + t * BN + hh * 64;       // my 64 score columns; my P goes to their first 32
       const uint32_t tO = tmem_base + lane_addr + 256 + t * HD + hh * 64; // my 64 columns of O
@@ -309,9 +339,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (!ptx::mbar_wait(&s_full[t], j & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
         int hi = k_len - k0;
-        if (p.causal) hi = min(hi, qpos + shift - k0 + 1);
+        if (p.causal) hi = min(hi, mpos + shift - k0 + 1);
         int lo = 0;
-        if (p.window > 0) lo = max(0, qpos + shift - p.window + 1 - k0);
+        if (p.window > 0) lo = max(0, mpos + shift - p.window + 1 - k0);
         const bool need_mask = (hi < 64) || (lo > 0);
         // one 32-column chunk of my half of the score row at a time (register budget: 18 warps share the register file)
         auto load_chunk = [&](int c, uint32_t (&v)[32]) {
@@ -481,6 +511,25 @@ bool f2_make_map(CUtensorMap* m, const void* ptr, int64_t tokens, int heads, int
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int f2_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const Fwd2Params& p, const Cp2Maps& maps, dim3 grid, cudaStream_t stream) {
+  static int poly = -1;
+  if (poly < 0) {
+    const char* e = getenv("NTB_FA_POLY_PAIRS");  // 0..2 of every four pairs on the FMA pipe (tuning knob; measured: no gain)
+    int v = e ? atoi(e) : 0;
+    v = v < 0 ? 0 : (v > 2 ? 2 : v);
+    if (cudaFuncSetAttribute(flash_fwd2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess)
+      return NTB_ERR_LAUNCH;
+    poly = v;
+  }
+  if (grid.y > 65535) return NTB_ERR_ARG;
+  if (poly == 0) flash_fwd2_kernel<0><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
+  else if (poly == 1) flash_fwd2_kernel<1><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
+  else flash_fwd2_kernel<2><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
+  return ntb_check_launch();
+}
+
 }  // namespace
 
 // Same contract as ntb_flash_attn_fwd.  q: [total_q, Hq, 128], k/v: [total_k, Hkv, 128] bf16 (token / head strides in elements,
@@ -496,17 +545,6 @@ NTB_EXPORT int ntb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   if (!f2_make_map(&tq, q, total_q, num_heads, q_stride_t, q_stride_h) || !f2_make_map(&tk, k, total_k, num_kv_heads, k_stride_t, k_stride_h) ||
       !f2_make_map(&tv, v, total_k, num_kv_heads, v_stride_t, v_stride_h))
     return NTB_ERR_ARG;
-  static int poly = -1;
-  if (poly < 0) {
-    const char* e = getenv("NTB_FA_POLY_PAIRS");  // 0..2 of every four pairs on the FMA pipe (tuning knob)
-    int v = e ? atoi(e) : 0;
-    v = v < 0 ? 0 : (v > 2 ? 2 : v);
-    if (cudaFuncSetAttribute(flash_fwd2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess)
-      return NTB_ERR_LAUNCH;
-    poly = v;
-  }
   Fwd2Params p;
   p.num_heads = num_heads;
   p.num_kv_heads = num_kv_heads;
@@ -520,10 +558,47 @@ NTB_EXPORT int ntb_flash_attn_fwd2(const void* q, const void* k, const void* v, 
   p.lse = lse;
   p.total_q = total_q;
   p.status = status;
-  dim3 grid(num_heads * batch, (max_seqlen_q + 2 * BM - 1) / (2 * BM), 1);
-  if (grid.y > 65535) return NTB_ERR_ARG;
-  if (poly == 0) flash_fwd2_kernel<0><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
-  else if (poly == 1) flash_fwd2_kernel<1><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
-  else flash_fwd2_kernel<2><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p);
-  return ntb_check_launch();
+  p.cp = 0;
+  p.cp_me = 0;
+  p.cp_chunk = 0;
+  static const Cp2Maps no_cp = {};
+  return f2_launch(tq, tk, tv, p, no_cp, dim3(num_heads * batch, (max_seqlen_q + 2 * BM - 1) / (2 * BM), 1), stream);
+}
+
+// Context-parallel forward.  q: this rank's [batch * 2 * chunk, Hq, 128] (chunk r then chunk 2 cp - 1 - r of every batch row);
+// k_ptrs / v_ptrs: device addresses of every rank's [batch * 2 * chunk, Hkv, 128] K and V (peer-mapped, same strides everywhere,
+// filled and made visible by a cross-rank barrier before this launch).  Causal only.  out / lse as in ntb_flash_attn_fwd2.
+NTB_EXPORT int ntb_flash_attn_fwd2_cp(const void* q, const uint64_t* k_ptrs, const uint64_t* v_ptrs, void* out, float* lse, int batch, int chunk, int cp, int me,
+                                      int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t kv_stride_t, int64_t kv_stride_h,
+                                      float softmax_scale, int* status, cudaStream_t stream) {
+  if (!f2_get_encode() || batch <= 0 || chunk <= 0 || chunk % BM || cp < 1 || cp > CP_MAX || me < 0 || me >= cp || num_heads % num_kv_heads) return NTB_ERR_ARG;
+  if ((q_stride_t | q_stride_h | kv_stride_t | kv_stride_h) % 8) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 15) return NTB_ERR_ARG;
+  const int total = batch * 2 * chunk;
+  CUtensorMap tq;
+  Cp2Maps maps = {};
+  if (!f2_make_map(&tq, q, total, num_heads, q_stride_t, q_stride_h)) return NTB_ERR_ARG;
+  for (int r = 0; r < cp; r++) {
+    if ((k_ptrs[r] | v_ptrs[r]) & 15) return NTB_ERR_ARG;
+    if (!f2_make_map(&maps.k[r], reinterpret_cast<const void*>(k_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h) ||
+        !f2_make_map(&maps.v[r], reinterpret_cast<const void*>(v_ptrs[r]), total, num_kv_heads, kv_stride_t, kv_stride_h))
+      return NTB_ERR_ARG;
+  }
+  Fwd2Params p;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.causal = 1;
+  p.window = 0;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.cu_q = nullptr;
+  p.cu_k = nullptr;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.total_q = total;
+  p.status = status;
+  p.cp = cp;
+  p.cp_me = me;
+  p.cp_chunk = chunk;
+  return f2_launch(tq, maps.k[me], maps.v[me], p, maps, dim3(num_heads * batch, (2 * chunk + 2 * BM - 1) / (2 * BM), 1), stream);
 }

@@ -34,6 +34,9 @@ def _lib():
     if not _DECLARED:
         L.ntb_flash_attn_fwd_cp.restype = c_int
         L.ntb_flash_attn_fwd_cp.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_int64] * 4 + [c_float, c_void_p, c_void_p]
+        if hasattr(L, "ntb_flash_attn_fwd2_cp"):  # two query tiles per CTA (ops/csrc/attention_fwd2.cu), same contract
+            L.ntb_flash_attn_fwd2_cp.restype = c_int
+            L.ntb_flash_attn_fwd2_cp.argtypes = L.ntb_flash_attn_fwd_cp.argtypes
         L.ntb_flash_attn_bwd_cp.restype = c_int
         L.ntb_flash_attn_bwd_cp.argtypes = [c_void_p] * 11 + [c_int] * 6 + [c_int64] * 5 + [c_float, c_void_p, c_void_p]
         L.ntb_cast_f32_to_bf16_rows.restype = c_int
@@ -100,7 +103,10 @@ class _FusedCPAttention(torch.autograd.Function):
         out = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((Hq, T), dtype=torch.float32, device=q.device)
         status = native_gemm.status_word(q.device)
-        rc = L.ntb_flash_attn_fwd_cp(q.data_ptr(), cctx.k.ptrs, cctx.v.ptrs, out.data_ptr(), lse.data_ptr(), batch, chunk, cctx.world, cctx.rank, Hq, Hkv,
+        from nanotron_b200.ops import native_attn
+
+        fwd = L.ntb_flash_attn_fwd2_cp if (hasattr(L, "ntb_flash_attn_fwd2_cp") and native_attn.FWD_VARIANT["kernel"] == "two_tile") else L.ntb_flash_attn_fwd_cp
+        rc = fwd(q.data_ptr(), cctx.k.ptrs, cctx.v.ptrs, out.data_ptr(), lse.data_ptr(), batch, chunk, cctx.world, cctx.rank, Hq, Hkv,
                                      q.stride(0), q.stride(1), Hkv * D, D, scale, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
         native._check(rc, "flash_attn_fwd_cp")
         cctx.alloc.barrier()  # every rank has finished reading K / V: the buffers may be reused
