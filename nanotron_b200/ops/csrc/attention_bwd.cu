@@ -345,19 +345,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (lane == 0) ptx::mbar_arrive(&dq_free[n & 1]);
       }
     } else {
-    // row statistics of my 32 query columns of a step: (-lse log2 e, delta * scale), fetched one step ahead
-    auto fetch_stats = [&](int hi, int ti, float& nl, float& ds) {
+    // Row statistics (lse, delta) of my 32 query columns, fetched one step ahead.  Only the loads are issued here: a warp issues
+    // in order, so any arithmetic on the loaded values would stall it for the whole global-memory latency.  The values are
+    // turned into (-lse log2 e, delta * scale) when they are stored to shared memory at the top of the next step.
+    auto fetch_stats = [&](int hi, int ti, float& raw_lse, float& raw_delta) {
       const int h = hk * group + hi;
       int q0, m0;
       step_pos(ti, q0, m0);
-      const int qpos = q0 + wg * 32 + lane;
-      const bool in = qpos < q_len;
+      const int qpos = min(q0 + wg * 32 + lane, q_len - 1);  // rows past the end read the last valid row; masked at use
       const int64_t idx = static_cast<int64_t>(h) * p.total_q + q_begin + qpos;
-      nl = in ? -p.lse[idx] * 1.4426950408889634f : -INFINITY;  // exp2(s c - lse) = 0 for rows past the end
-      ds = in ? p.delta[idx] * p.scale : 0.f;
+      raw_lse = p.lse[idx];
+      raw_delta = p.delta[idx];
     };
-    float nl_next = 0.f, ds_next = 0.f;
-    if (n_steps > 0) fetch_stats(0, 0, nl_next, ds_next);
+    float lse_next = 0.f, delta_next = 0.f;
+    if (n_steps > 0) fetch_stats(0, 0, lse_next, delta_next);
     int hi = 0, ti = 0;
     for (int n = 0; n < n_steps && ok; n++) {
       int q0, m0;
@@ -366,10 +367,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // per-warp copy of the 32 row statistics of this step (no cross-warp synchronisation needed)
       float* lse_s = s_stats + (warp - 2) * 64;
       float* delta_s = lse_s + 32;
-      lse_s[lane] = nl_next;
-      delta_s[lane] = ds_next;
+      {
+        const bool in = q0 + wg * 32 + lane < q_len;
+        lse_s[lane] = in ? -lse_next * 1.4426950408889634f : -INFINITY;  // exp2(s c - lse) = 0 for rows past the end
+        delta_s[lane] = in ? delta_next * p.scale : 0.f;
+      }
       __syncwarp();
-      if (n + 1 < n_steps) fetch_stats(hi, ti, nl_next, ds_next);  // in flight during this step
+      if (n + 1 < n_steps) fetch_stats(hi, ti, lse_next, delta_next);  // in flight during this step
       if (!ptx::mbar_wait(sdp_full, n & 1, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t pk_p[16], pk_ds[16];  // 32 bf16 each
