@@ -15,7 +15,7 @@
 //               In steady state there is NO row maximum: the exponentials are taken relative to the reference maximum of the
 //               earlier tiles and the row sum (needed anyway) shows whether that was good enough; if not (a half row sums to
 //               more than 1024, or is not finite) both warps of the rows compute the exact maximum (halves exchanged through
-//               shared memory behind a 64-thread named barrier), rescale O and l, and recompute the tile: P is only stored
+//               shared memory behind a two-arrival mbarrier with a bounded wait), rescale O and l, and recompute the tile: P is only stored
 //               after that decision, so the scores can be read again.  The final O / l is exact either way.  P_t is stored
 //               over columns 0-31 and 64-95 of S_t (each warp inside its own half).
 //               `s_full[t]` firing also means P_t(j-1) V(j-1) has completed (a commit covers every earlier MMA of the thread),
@@ -161,7 +161,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* s_full = v_empty + V_STAGES;        // [2] per query tile
   uint64_t* p_full = s_full + 2;                // [2]
   uint64_t* o_done = p_full + 2;                // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+  uint64_t* pair_sync = o_done + 2;             // [2 tiles][4 quarters]: the two warps that share 32 query rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_sync + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);            // [2 slots][2][4][2][32]
   volatile int* xflag = reinterpret_cast<volatile int*>(xch + 2 * 2 * 4 * 2 * 32);          // [2 slots][2][4][2]
@@ -217,6 +218,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       ptx::mbar_init(&s_full[t], 1);
       ptx::mbar_init(&p_full[t], 8);
       ptx::mbar_init(&o_done[t], 1);
+      for (int q = 0; q < 4; q++) ptx::mbar_init(&pair_sync[t * 4 + q], 2);
     }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -329,7 +331,17 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tS = tmem_base + lane_addr + t * BN + hh * 64;       // my 64 score columns; my P goes to their first 32
       const uint32_t tO = tmem_base + lane_addr + 256 + t * HD + hh * 64; // my 64 columns of O
-      const int pair_bar = 1 + t * 4 + quarter;                          // named barrier of the two warps of these rows
+      // Rendezvous of the two warps of these rows: an mbarrier with two arrivals and a bounded wait (a named barrier would hang
+      // the partner if one warp gave up on a timeout).  Both warps take the same branches, so they count the same phases.
+      uint64_t* pair_bar = &pair_sync[t * 4 + quarter];
+      uint32_t pair_phase = 0;
+      auto pair_rendezvous = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(pair_bar);
+        const bool done = ptx::mbar_wait(pair_bar, pair_phase & 1, abort_flag);
+        pair_phase++;
+        return done;
+      };
       auto xslot = [&](int slot, int half) -> float* { return xch + ((((slot * 2 + t) * 4 + quarter) * 2 + half) * 32) + lane; };
       auto fslot = [&](int slot, int half) -> volatile int* { return xflag + (((slot * 2 + t) * 4 + quarter) * 2 + half); };
       float m_ref = -INFINITY, l_run = 0.f;  // m_ref: the maximum the stored probabilities and O are relative to (same in both warps)
@@ -380,7 +392,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
               mine = max3(mine, m0, m1);
             }
             *xslot(j & 1, hh) = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (!pair_rendezvous()) { ok = false; break; }
             const float m_new = fmaxf(m_ref, fmaxf(mine, *xslot(j & 1, hh ^ 1)));
             const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;
             alpha = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_fin) * p.scale_log2);
@@ -431,10 +443,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           // both warps of these rows must take the same decision
           const bool bad = __any_sync(0xffffffffu, !(sum <= SUM_LIMIT));
           if (lane == 0) *fslot(j & 1, hh) = bad ? 1 : 0;
-          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+          if (!pair_rendezvous()) { ok = false; break; }
           if (!(bad || *fslot(j & 1, hh ^ 1) != 0)) break;
           slow = true;
         }
+        if (!ok) break;
         // the scores are not needed any more: P over the first 32 columns of my half
         tmem_st_32x16(tS, pk[0]);
         tmem_st_32x16(tS + 16, pk[1]);
@@ -449,10 +462,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (ok && ptx::mbar_wait(&o_done[t], 0, abort_flag)) {
         ptx::tc_fence_after();
         *xslot(n_tiles & 1, hh) = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        const bool met = pair_rendezvous();
         const float l_tot = l_run + *xslot(n_tiles & 1, hh ^ 1);
         const float inv_l = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        const bool valid = qpos < q_len;
+        const bool valid = met && qpos < q_len;
         const int64_t tok = static_cast<int64_t>(q_begin) + qpos;
         __nv_bfloat16* orow = p.out + (tok * p.num_heads + h) * HD + hh * 64;
 #pragma unroll 1
