@@ -27,7 +27,7 @@ def _unavailable(why: str):
 
 def run_reference(args):
     if not os.path.isdir(os.path.join(REF, "nanotron")):
-        return _unavailable("baseline/_ref is missing: install with `pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <copy of /root/reference>`")
+        return _unavailable("baseline/_ref is missing: install with `pip install --no-index --no-build-isolation --no-deps --target baseline/_ref <copy of the reference source tree>`")
     sys.path.insert(0, SHIMS)
     sys.path.insert(0, REF)
     os.environ.setdefault("WANDB_MODE", "disabled")
