@@ -255,3 +255,23 @@ def test_device_side_wait_gives_up_and_reports():
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
+
+
+def test_rms_norm_return_input_sums_the_skip_gradient_in_the_kernel():
+    """`ops.rms_norm(x, return_input=True)` on the native path: the gradient reaching the second output (the skip connection) is
+    added by the norm's backward kernel.  Compared with fp32 autograd where `x` feeds the norm and the skip separately."""
+    torch.manual_seed(4)
+    T, H = 384, 1024
+    x0 = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w0 = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    gy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    gs = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    x, w = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    y, skip = ops.rms_norm(x, w, 1e-5, return_input=True)
+    torch.autograd.backward([y, skip], [gy, gs])
+    xr, wr = x0.float().requires_grad_(True), w0.float().requires_grad_(True)
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    torch.autograd.backward([yr, xr * 1.0], [gy.float(), gs.float()])
+    torch.testing.assert_close(y.float(), yr.detach(), atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=5e-2, rtol=5e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.5, rtol=5e-2)
