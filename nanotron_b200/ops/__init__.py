@@ -274,8 +274,19 @@ class _Rope(torch.autograd.Function):
 
 def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool = False, inplace: bool = False, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x: [T, H, D] (may be a strided view into a fused qkv buffer, last dim contiguous).  cos/sin fp32: either
-    per-token rows [T, D/2], or whole tables [P, D/2] indexed by ``positions`` [T] inside the kernel."""
+    per-token rows [T, D/2], or whole tables [P, D/2] indexed by ``positions`` [T] inside the kernel.
+    The kernel wants head dims that are multiples of 16 and 16-byte aligned rows; other shapes (toy models) take the PyTorch
+    composition, which autograd differentiates."""
+    if x.is_cuda and _MODE != "torch" and not _rope_kernel_ok(x):
+        if positions is not None:
+            cos, sin = cos.index_select(0, positions.long()), sin.index_select(0, positions.long())
+        return ref.rope_apply(x, cos, sin, interleaved)
     return _Rope.apply(x, cos, sin, interleaved, inplace, positions)
+
+
+def _rope_kernel_ok(x: torch.Tensor) -> bool:
+    return (x.dim() == 3 and x.shape[-1] % 16 == 0 and x.stride(-1) == 1 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+            and x.data_ptr() % 16 == 0 and x.dtype in (torch.bfloat16, torch.float16, torch.float32))
 
 
 # ============================================================================ SwiGLU
@@ -481,8 +492,8 @@ def fused_qkv_attention(qkv, cos_table, sin_table, positions, n_heads, n_kv, hea
 
 def fused_qkv_library_attention_supported(qkv: torch.Tensor, head_dim: int, window, cu_seqlens) -> bool:
     """Equal-length causal sequences (no packed documents, no window) on CUDA in bf16 / fp16 with the native element-wise kernels."""
-    return (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.is_contiguous() and head_dim % 8 == 0
-            and window is None and cu_seqlens is None)
+    return (_use_native(qkv) and qkv.dtype in (torch.bfloat16, torch.float16) and qkv.is_contiguous() and head_dim % 16 == 0
+            and qkv.data_ptr() % 16 == 0 and window is None and cu_seqlens is None)
 
 
 def fused_qkv_library_attention(qkv, cos_table, sin_table, positions, n_heads, n_kv, head_dim, batch, seqlen, softmax_scale=None, interleaved=False, use_rope=True):

@@ -275,3 +275,19 @@ def test_rms_norm_return_input_sums_the_skip_gradient_in_the_kernel():
     torch.testing.assert_close(y.float(), yr.detach(), atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(x.grad.float(), xr.grad, atol=5e-2, rtol=5e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.5, rtol=5e-2)
+
+
+def test_rotary_on_a_toy_head_dim_takes_the_composition():
+    """Head dim 4 (the toy example config) is outside the RoPE kernel's contract (multiples of 16, 16-byte rows): `apply_rotary`
+    must still work on the GPU, forward and backward, through the PyTorch composition."""
+    torch.manual_seed(1)
+    T, H, D = 32, 4, 4
+    qkv = torch.randn(T, 3 * H * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    q = qkv[:, : H * D].view(T, H, D)
+    pos = torch.arange(T, device="cuda")
+    cos, sin = ref.rope_cos_sin(torch.arange(64, device="cuda"), D, 10000.0)
+    out = ops.apply_rotary(q, cos, sin, False, False, positions=pos)
+    exp = ref.rope_apply(q.detach().float(), cos[pos], sin[pos], False)
+    torch.testing.assert_close(out.float(), exp, atol=2e-2, rtol=2e-2)
+    out.float().sum().backward()
+    assert qkv.grad is not None and torch.isfinite(qkv.grad).all()
