@@ -525,21 +525,13 @@ bool f2_make_map(CUtensorMap* m, const void* ptr, int64_t tokens, int heads, int
 }
 
 int f2_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const Fwd2Params& p, const Cp2Maps& maps, dim3 grid, cudaStream_t stream) {
-  static int poly = -1;
-  if (poly < 0) {
-    const char* e = getenv("NTB_FA_POLY_PAIRS");  // 0..2 of every four pairs on the FMA pipe (tuning knob; measured: no gain)
-    int v = e ? atoi(e) : 0;
-    v = v < 0 ? 0 : (v > 2 ? 2 : v);
-    if (cudaFuncSetAttribute(flash_fwd2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess)
-      return NTB_ERR_LAUNCH;
-    poly = v;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_fwd2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, F2_SMEM) != cudaSuccess) return NTB_ERR_LAUNCH;
+    configured = true;
   }
   if (grid.y > 65535) return NTB_ERR_ARG;
-  if (poly == 0) flash_fwd2_kernel<0><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
-  else if (poly == 1) flash_fwd2_kernel<1><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
-  else flash_fwd2_kernel<2><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
+  flash_fwd2_kernel<0><<<grid, F2_THREADS, F2_SMEM, stream>>>(tq, tk, tv, p, maps);
   return ntb_check_launch();
 }
 

@@ -359,11 +359,6 @@ bool p_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld
 
 template <bool A_MN, bool B_MN, int OUT, int ST = P_MAX_STAGES>
 int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream) {
-  if (ST == P_MAX_STAGES) {
-    // experiment knob: NTB_PAIR_STAGES=3 runs the forward layout with a 3-stage ring (same shared-memory footprint)
-    const char* e = getenv("NTB_PAIR_STAGES");
-    if (e && atoi(e) == 3 && !A_MN && !B_MN && OUT == P_OUT_BF16) return p_launch<false, false, P_OUT_BF16, 3>(ta, tb, td, M, N, K, status, num_sms, stream);
-  }
   auto kern = gemm2_tcgen05_kernel<A_MN, B_MN, OUT, ST>;
   static bool configured = false;
   if (!configured) {

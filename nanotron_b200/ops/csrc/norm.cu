@@ -284,12 +284,14 @@ NTB_EXPORT int ntb_norm_bwd(int is_rms, int dtype, const void* dy, const void* p
 // The regular entry point above needs a caller-provided fp32 scratch of [partials, cols] for the per-CTA partial sums of
 // dW.  Some callers cannot provide one: library hooks invoked from inside another framework's allocator callbacks, and
 // runtimes that pre-plan every byte of device memory and forbid cudaMalloc (and torch's caching allocator) after start-up.  For them this variant keeps the
-// scratch in a fixed array that is part of the loaded library image: every GPU that loads the library holds
-// NTB_NOALLOC_PARTIALS * NTB_NOALLOC_MAX_COLS * 4 bytes (4.6 MiB) from load until exit.
+// scratch in a fixed array that is part of the loaded library image: every GPU on which this module gets loaded holds
+// NTB_NOALLOC_PARTIALS * NTB_NOALLOC_MAX_COLS * 4 bytes (4.6 MiB) from that moment until the process exits.  The CUDA
+// runtime loads modules lazily, so "that moment" is the first use of this library's kernels or symbols on the device.
 //
 // The array's name is only a host-side handle; the device address is looked up with cudaGetSymbolAddress the first time
-// the entry point is called on each device (with that device current).  That first call should therefore come before
-// any stream capture.  All calls share the one array: two calls whose kernels overlap on the GPU (different streams
+// the entry point is called on each device (with that device current).  That first call should therefore come at
+// start-up: before memory is frozen (it may be what loads the module and reserves the array) and before any stream
+// capture.  The per-device address table below is written without a lock; racing first calls store the same value.  All calls share the one array: two calls whose kernels overlap on the GPU (different streams
 // without ordering) would mix their partial sums.  Nothing in the array has to start at zero: every launch rewrites
 // the rows it reads back.
 constexpr int NTB_NOALLOC_PARTIALS = 148;

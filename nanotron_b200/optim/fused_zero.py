@@ -52,8 +52,28 @@ class FusedDataParallelStep:
             self.n = max(0, min(per, total - self.start))
         dev = allocator.device
         self.partials = torch.empty(native.lib().ntb_dp_num_partials(), dtype=torch.float32, device=dev)
+        # flat ranges (inside this rank's reduced slice) of tied parameters whose squares another member of the tie group already counts
+        self.duplicate_ranges = []
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = None
+
+    def exclude_tied_duplicates(self, named_params, world_rank: int):
+        """A tied parameter (norm weights replicated over tp, embeddings tied across pipeline stages) has one gradient copy per
+        member of its tie group.  The global norm counts it once, on the first rank of the group, as ``clip_grad_norm`` does
+        (reference src/nanotron/optim/clip_grads.py:43-53): every other member records the part of the copy that lies in its
+        reduced slice here, and ``step`` removes those squares from its partial sum before the all-reduce."""
+        layout = self.acc.layout
+        lo, hi = self.start, self.start + self.n
+        self.duplicate_ranges = []
+        for name, p in named_params:
+            if not (p.requires_grad and getattr(p, "is_tied", False)):
+                continue
+            ranks = sorted(p.get_tied_info().global_ranks)
+            if len(ranks) <= 1 or world_rank == ranks[0] or name not in layout.offsets:
+                continue
+            a, b = max(layout.offsets[name], lo), min(layout.offsets[name] + layout.numels[name], hi)
+            if b > a:
+                self.duplicate_ranges.append((a, b))
 
     def step(self):
         """Everything between the last backward and the next forward.  Returns the pre-clip gradient norm (or None)."""
@@ -63,6 +83,9 @@ class FusedDataParallelStep:
         rc = L.ntb_dp_reduce_scatter(self.grad_sym.ptrs, self.rank, self.world, self.start, self.n, 1.0 / self.world, 0 if self.zero else 1, self.partials.data_ptr(), self.sumsq.data_ptr(), stream)
         native._check(rc, "dp_reduce_scatter")
         total = self.sumsq.clone()
+        if self.duplicate_ranges:
+            flat = self.acc._contiguous_fp32_grad_buffer
+            total -= torch.stack([flat[a:b].pow(2).sum() for a, b in self.duplicate_ranges]).sum()
         # every rank holds the squares of a disjoint slice: sum over dp, then over model-parallel ranks
         dist.all_reduce(total, group=self.dp_pg)
         if self.mp_pg is not None and self.mp_pg.size() > 1:

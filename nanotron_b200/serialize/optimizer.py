@@ -101,11 +101,22 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
     ckp_dp = int(ckp_cfg["parallelism"]["dp_size"])
     is_zero_ckp = "ZeroDistributedOptimizer" in ckp_cfg["type"]
     is_zero_now = optimizer.inherit_from(ZeroDistributedOptimizer)
-    same_topology = ckp_pp == parallel_context.pp_pg.size() and ckp_tp == parallel_context.tp_pg.size() and (not is_zero_ckp or ckp_dp == parallel_context.dp_pg.size()) and is_zero_ckp == is_zero_now
+    ckp_ep = int(ckp_cfg["parallelism"].get("expert_parallel_size", 1))
+    same_topology = (
+        ckp_pp == parallel_context.pp_pg.size() and ckp_tp == parallel_context.tp_pg.size() and ckp_ep == parallel_context.expert_parallel_size
+        and (not is_zero_ckp or ckp_dp == parallel_context.dp_pg.size()) and is_zero_ckp == is_zero_now
+    )
     if same_topology:
         state_dict = torch.load(root_folder / optimizer_filename(parallel_context, is_zero=is_zero_now), map_location=map_location, weights_only=False)
         optimizer.load_state_dict(state_dict, map_location=map_location)
         return
+    if ckp_ep > 1 or parallel_context.expert_parallel_size > 1:
+        # the merge below keys shards by (pp, tp) only: states of expert-sharded parameters from different expert ranks would overwrite each other
+        raise NotImplementedError(
+            f"optimizer states saved with expert_parallel_size={ckp_ep} can only be resumed under the same tp / pp / dp / ep topology "
+            f"(now tp={parallel_context.tp_pg.size()} pp={parallel_context.pp_pg.size()} dp={parallel_context.dp_pg.size()} ep={parallel_context.expert_parallel_size}); "
+            "resume with `checkpoints.load_optimizer: false` or under the saved topology"
+        )
     if ckp_pp != parallel_context.pp_pg.size():
         warnings.warn("You are resuming in a different PP size, so optimizer states need to be checked. Feel free to open a PR if you work on this!")
     assert model is not None, "loading optimizer states under a different topology needs the model (for the parameters' slice maps)"
@@ -124,17 +135,30 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
     state_keys = ["exp_avg", "exp_avg_sq"]
     new_state = {}
     my_dp = dist.get_rank(parallel_context.dp_pg)
+    my_tp = dist.get_rank(parallel_context.tp_pg)
+    my_pp = dist.get_rank(parallel_context.pp_pg)
+    same_tp = ckp_tp == parallel_context.tp_pg.size()
+
+    def holders(name):
+        """Checkpoint state dicts that hold ``name``, as [((pp, tp), state dict, index)].  With an unchanged tp size only this
+        rank's own tp shard qualifies (every tp rank of the checkpoint holds the name, each with different data); the
+        stage that matches this rank's pipeline rank comes first (a tied parameter lives on two stages)."""
+        found = []
+        for (pp_rank, tp_rank), sd in per_pp_tp.items():
+            if same_tp and tp_rank != my_tp:
+                continue
+            ckp_idx = next((k for k, v in sd["names"].items() if v == name), None)
+            if ckp_idx is not None:
+                found.append(((pp_rank, tp_rank), sd, ckp_idx))
+        found.sort(key=lambda e: (e[0][0] != my_pp, e[0]))
+        return found
+
     for idx, name in new_names.items():
         param = name_to_param[name]
-        shards = []
-        step = None
-        for (pp_rank, tp_rank), sd in per_pp_tp.items():
-            ckp_idx = next((k for k, v in sd["names"].items() if v == name), None)
-            if ckp_idx is None:
-                continue
-            shards.append((tp_rank, sd["state"][ckp_idx]))
-            step = sd["state"][ckp_idx]["step"]
-        assert shards, f"optimizer state of {name} not found in checkpoint"
+        found = holders(name)
+        assert found, f"optimizer state of {name} not found in checkpoint"
+        shards = [(key[1], sd["state"][ckp_idx]) for key, sd, ckp_idx in found]
+        step = shards[0][1]["step"]
         entry = {"step": step}
         for sk in state_keys:
             if isinstance(param, NanotronParameter) and param.is_sharded and ckp_tp != parallel_context.tp_pg.size():
@@ -163,11 +187,13 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
         for name in new_sd["gradient_accumulator"]:
             param = name_to_param[name]
             src = None
-            for sd in per_pp_tp.values():
+            for (pp_rank, tp_rank), sd in sorted(per_pp_tp.items(), key=lambda e: (e[0][0] != my_pp, e[0])):
+                if same_tp and tp_rank != my_tp:
+                    continue
                 if "gradient_accumulator" in sd and name in sd["gradient_accumulator"]:
                     src = sd["gradient_accumulator"][name]
                     break
-            if src is None or ckp_tp != parallel_context.tp_pg.size():
+            if src is None or not same_tp:
                 # masters can always be rebuilt from the (already loaded) parameters
                 full = param.detach().float().cpu()
             else:

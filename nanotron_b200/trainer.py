@@ -115,9 +115,10 @@ class DistributedTrainer:
         set_ranks_logging_level(parallel_context=self.parallel_context, logging_config=self.config.logging)
         log_libraries_versions(logger=logger)
         log_rank("Config:\n" + pformat(self.config), logger=logger, level=logging.DEBUG, rank=0)
-        # distinct seed per tp rank so sharded weights are not initialised identically
-        set_random_seed(self.config.general.seed + dist.get_rank(self.parallel_context.tp_pg) * 0)
+        # the named random states (tp_synced) are drawn from the configured seed on every rank ...
+        set_random_seed(self.config.general.seed)
         self.random_states = init_random_states(parallel_config=par, tp_pg=self.parallel_context.tp_pg)
+        # ... while the default generator differs per tp / pp rank so that sharded weights are not initialised identically
         set_random_seed(self.config.general.seed + dist.get_rank(self.parallel_context.tp_pg) + 1000 * dist.get_rank(self.parallel_context.pp_pg))
         self.model = self.init_model()
         self.unwrapped_model: NanotronModel = self.model
@@ -136,6 +137,7 @@ class DistributedTrainer:
 
             if isinstance(self.optimizer.get_base_optimizer(), FusedAdamW) and self.grad_accumulator is not None:
                 self.fused_dp = FusedDataParallelStep(symm_alloc, self.grad_accumulator, self.optimizer, self.parallel_context.dp_pg, self.parallel_context.mp_pg, self.config.optimizer.clip_grad)
+                self.fused_dp.exclude_tied_duplicates(self.unwrapped_model.get_named_params_with_correct_tied(), dist.get_rank(self.parallel_context.world_pg))
                 log_rank("Data-parallel step: in-kernel NVLink reduce-scatter + AdamW + all-gather", logger=logger, level=logging.INFO, rank=0)
         if self.init_checkpoint_path is not None and self.config.checkpoints.load_optimizer:
             load_optimizer(optimizer=self.optimizer, parallel_context=self.parallel_context, root_folder=self.init_checkpoint_path, param_shard_metadata=self.param_shard_metadata, model=self.unwrapped_model, map_location="cpu")
@@ -374,11 +376,14 @@ class DistributedTrainer:
             )
         after_tbi_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator)
         fused = self.fused_dp is not None
+        # tied / replicated-by-design parameters (norm weights under sequence parallelism, tied embeddings).  This sum runs BEFORE the
+        # data-parallel reduction: under ZeRO-1 that reduction is an in-place reduce-scatter after which only this rank's flat shard is
+        # valid, and two pipeline stages that tie a parameter own different slices of it.  Both reductions are linear, so the order
+        # does not change the result (the reference all-reduces whole gradients over dp first, trainer.py:643-661).
+        sync_tied_weights_gradients(module=self.unwrapped_model, parallel_context=self.parallel_context, grad_accumulator=self.grad_accumulator)
         if not fused:
             with nanotron_timer("sync_gradients"), torch.profiler.record_function("sync_gradients"):
                 self._sync_gradients()
-        # tied / replicated-by-design parameters (norm weights under sequence parallelism, tied embeddings)
-        sync_tied_weights_gradients(module=self.unwrapped_model, parallel_context=self.parallel_context, grad_accumulator=self.grad_accumulator)
         self.grad_norm_unclipped = None
         if self.config.optimizer.clip_grad is not None and not fused:
             with nanotron_timer("clip_gradients"), torch.profiler.record_function("clip_gradients"):
@@ -526,7 +531,7 @@ class DistributedTrainer:
                 rng = self.optimizer.param_name_to_dp_rank_offsets[n].get(me) if hasattr(self.optimizer, "param_name_to_dp_rank_offsets") else None
                 if rng is None:
                     continue
-                if p.is_tied and world_rank % 1 == 0:
+                if p.is_tied:
                     ranks = p.get_tied_info().global_ranks
                     # a tied parameter is counted by the first rank of its tie group (same dp rank by construction)
                     if ctx.get_local_ranks(world_rank)["dp"] == me and world_rank != sorted(ranks)[0] and len(ranks) > 1:

@@ -95,3 +95,17 @@ def test_resume_under_another_topology(tmp_path):
     resumed = _losses(tmp_path, "dp_resumed", 1, ckpt_dir=ckpt_dp, steps=2, first_step=2, resume=ckpt_dp)
     for a, b in zip(resumed, full[2:]):
         assert abs(a - b) < 3e-4, (resumed, full)
+
+
+def test_resume_same_tp_other_optimizer_layout(tmp_path):
+    """tp stays 2 while the optimizer layout changes (ZeRO-1 over dp 2 -> one replica, and -> no ZeRO): every tp rank must get
+    its own shard of the moments and fp32 masters back, not tp rank 0's."""
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4)
+    ckpt = str(tmp_path / "ckpt_tp2dp2")
+    _losses(tmp_path, "first", 4, ckpt_dir=ckpt, steps=2, save=True, tp=2, dp=2, zero=1, tp_mode="reduce_scatter")
+    resumed = _losses(tmp_path, "resumed_dp1", 2, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, tp=2, tp_mode="reduce_scatter")
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
+    resumed = _losses(tmp_path, "resumed_dp2_zero0", 4, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, tp=2, dp=2, zero=0, tp_mode="reduce_scatter")
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)

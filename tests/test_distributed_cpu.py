@@ -160,7 +160,10 @@ def _deterministic_init(model):
     with torch.no_grad():
         for name, p in model.get_named_params_with_correct_tied():
             shape = tuple(p.get_sharded_info().unsharded_shape) if p.is_sharded else tuple(p.shape)
-            g = torch.Generator().manual_seed(zlib.crc32(name.encode()))
+            seed_name = name
+            if getattr(getattr(model, "config", None), "tie_word_embeddings", False) and ("token_embedding" in name or "lm_head" in name):
+                seed_name = "tied_word_embeddings"  # one matrix under two names (one per pipeline stage)
+            g = torch.Generator().manual_seed(zlib.crc32(seed_name.encode()))
             full = torch.randn(shape, generator=g, dtype=torch.float32) * 0.05
             if "layernorm" in name or "layer_norm" in name or "ln_" in name:
                 full = 1.0 + full
@@ -185,7 +188,8 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
     if topology.get("cp", 1) > 1:
         topology["fp32_accum"] = True
     accum = total_mbs // (dp * mbs)
-    mc = tiny_llama_config() if model == "llama" else tiny_qwen_config()
+    tie = topology.pop("tie", False)
+    mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie)
     cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
     t = DistributedTrainer(cfg)
     t.prepare_training()
@@ -196,6 +200,14 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
         t.iteration_step += 1
         if loss is not None:
             losses.append(float(loss))
+    if tie and t.parallel_context.pp_pg.size() > 1:
+        # the two copies of the tied matrix (embedding on the first stage, lm head on the last) must still be equal
+        pp_pg = t.parallel_context.pp_pg
+        mine = [p for n, p in t.unwrapped_model.named_parameters() if "token_embedding" in n or "lm_head" in n]
+        assert len(mine) == 1, [n for n, _ in t.unwrapped_model.named_parameters()]
+        copies = [torch.empty_like(mine[0].data) for _ in range(pp_pg.size())]
+        dist.all_gather(copies, mine[0].data.contiguous(), group=pp_pg)
+        torch.testing.assert_close(copies[0], copies[-1], atol=0, rtol=0)
     if dist.get_rank(t.parallel_context.world_pg) == t.logger_ranks[0]:
         torch.save(losses, out_file)
     dist.barrier()
@@ -237,6 +249,15 @@ def test_3d_and_qwen_topologies(tmp_path):
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4, (got, base)
     got = _losses_for(tmp_path, 2, "qcp", model="qwen", cp=2)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 2e-4, (got, base)
+
+
+def test_tied_embeddings_across_stages_with_zero1(tmp_path):
+    """Embedding and lm head tied across two pipeline stages, each stage data-parallel with ZeRO-1: the tie-group sum of the
+    gradients must see whole (not reduce-scattered) gradients, or the two copies drift apart."""
+    base = _losses_for(tmp_path, 1, "tbase", tie=True)
+    got = _losses_for(tmp_path, 4, "tpp2dp2", tie=True, pp=2, dp=2, zero=1, pp_engine="1f1b")
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4, (got, base)
 

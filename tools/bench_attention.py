@@ -1,15 +1,21 @@
 """Flash attention micro-benchmark: in-tree tcgen05 forward vs the library (SDPA) forward on Llama-3-8B shapes.
 
-    python -m nanotron_b200.ops.bench_attention
+    python tools/bench_attention.py
 FLOPs are counted for the causal half (2 * 2 * H * S^2 * D / 2 per sequence).
 """
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import math
 
 import torch
 
-from nanotron_b200.ops.bench_kernels import _peaks, time_fn
+from bench_kernels import _peaks, time_fn
 
 
 def main():

@@ -1,6 +1,6 @@
 """Throughput of the fused compute + collective kernels against their rooflines and against the NCCL + library path.
 
-    torchrun --nproc-per-node N --master-addr 127.0.0.1 -m nanotron_b200.ops.bench_fused [tp] [dp] [ep] [cp]
+    torchrun --nproc-per-node N --master-addr 127.0.0.1 tools/bench_fused.py [tp] [dp] [ep] [cp]
 
 Every number is CUDA-event time on the launching stream, 3 warm-up + 10 timed iterations, maximum over ranks.
 Roofline of a fused kernel = the slower of (FLOPs / measured GEMM peak) and (bytes that must cross NVLink per GPU / 770 GB/s,
@@ -8,9 +8,13 @@ the measured peer-copy bandwidth per direction); for the optimizer step also loc
 """
 from __future__ import annotations
 
-import json
 import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import json
 
 import torch
 import torch.distributed as tdist
@@ -19,7 +23,7 @@ NVLINK_GBS = 770.0
 
 
 def _peaks():
-    for p in (os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json"),):
+    for p in (os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "MEASURED_PEAKS.json"),):
         if os.path.exists(p):
             d = json.load(open(p))
             return {"bf16_tflops": float(d.get("bf16_tflops", 1590.0)), "hbm_gbs": float(d.get("hbm_gbs", 6650.0))}

@@ -1,23 +1,27 @@
 """Micro-benchmarks of the in-tree kernels against their roofline (run on a B200).
 
-    python -m nanotron_b200.ops.bench_kernels gemm            # tcgen05 GEMM vs the library GEMM on Llama-3-8B shapes
-    python -m nanotron_b200.ops.bench_kernels elementwise     # HBM-bound kernels vs measured copy bandwidth
-    python -m nanotron_b200.ops.bench_kernels attention
+    python tools/bench_kernels.py gemm            # tcgen05 GEMM vs the library GEMM on Llama-3-8B shapes
+    python tools/bench_kernels.py elementwise     # HBM-bound kernels vs measured copy bandwidth
+    python tools/bench_kernels.py attention
 
 Timing: CUDA events, 3 warm-up + 10 timed launches; operands are rotated through several buffers so that consecutive
 launches do not find their inputs in L2 (total footprint > 126 MB).
 """
 from __future__ import annotations
 
-import json
 import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import json
 
 import torch
 
 
 def _peaks():
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             return json.load(f)
@@ -217,6 +221,6 @@ if __name__ == "__main__":
     elif what == "moe":
         bench_moe()
     elif what == "attention":
-        from nanotron_b200.ops.bench_attention import main
+        from bench_attention import main
 
         main()

@@ -1,12 +1,17 @@
 """Small, self-ending workloads for profiler captures: each in-tree kernel runs twice (one warm-up, one measured) on inputs
 larger than the L2 cache but well under a gigabyte or two in total, so a counter capture replays quickly.
 
-    python -m nanotron_b200.ops.profile_cases [gemm|norm|elementwise|attention|moe|optim|all]
+    python tools/profile_cases.py [gemm|norm|elementwise|attention|moe|optim|all]
 """
 from __future__ import annotations
 
-import math
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import math
 
 import torch
 
