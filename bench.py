@@ -235,7 +235,7 @@ def main():
     ap.add_argument("--accum", type=int, default=8)
     ap.add_argument("--recompute", action="store_true")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "cublas"], help="auto / tcgen05: every linear-layer product on the in-tree tcgen05 kernels; cublas: library GEMMs (wgrad then needs a separate fp32 add)")
-    ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"], help="auto / sdpa: library attention; native: the in-tree tcgen05 flash-attention kernels")
+    ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"], help="auto / native: the in-tree tcgen05 flash-attention kernels; sdpa: library attention (comparison runs)")
     ap.add_argument("--gemm-variant", default="pair", choices=["single", "pair"], help="in-tree GEMM kernel: one CTA per 128x256 tile, or CTA pairs (cta_group::2) per 256x256 tile")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (sequence-parallel mode); dp = gpus / (tp * pp)")
     ap.add_argument("--pp", type=int, default=1, help="pipeline-parallel size (1F1B)")

@@ -29,6 +29,9 @@ class ParallelismArgs:
     tp_recompute_allgather: bool = True
     expert_parallel_size: int = 1
     context_parallel_size: int = 1
+    # pipeline stages exchange tensor headers only during the first micro-batch and replay the learnt shapes afterwards
+    # (every micro-batch of a data stage has the same geometry); False sends a header with every activation
+    pp_static_shapes: bool = True
 
     def __post_init__(self):
         if self.pp_engine is None:

@@ -114,7 +114,7 @@ class Qwen2Attention(nn.Module, LogMixin):
         """hidden_states: [T_local, h] (T_local = b*s/tp under sequence parallelism); position_ids: [b, s_local]."""
         qkv = self.qkv_proj(hidden_states)  # [T, local_q + 2*local_kv]
         T = qkv.shape[0]
-        if self.cp_size == 1 and self.attn_impl == "flash_attention_2" and ops._ATTN == "native" and ops.fused_qkv_attention_supported(qkv, self.local_heads, self.local_kv_heads, self.head_dim, self.sliding_window_size):
+        if self.cp_size == 1 and self.attn_impl in ("flash_attention_2", "sdpa") and ops.fused_qkv_attention_supported(qkv, self.local_heads, self.local_kv_heads, self.head_dim, self.sliding_window_size):
             b, s = position_ids.shape
             cu = cu_seqlens if cu_seqlens is not None else regular_cu_seqlens(b, s, hidden_states.device)
             if self.use_rope:

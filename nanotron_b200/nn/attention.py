@@ -1,8 +1,8 @@
 """Attention backends registry (parity: reference src/nanotron/nn/attention.py:42-238).
 
 All backends take packed tensors q [T, Hq, D], k/v [T, Hkv, D] plus ``cu_seqlens`` and return [T, Hq, D].
-``flash_attention_2`` is the in-tree flash attention kernel on CUDA.  ``sdpa`` and ``flex_attention`` are the
-PyTorch masked-softmax formulation (document / sliding-window / causal masks).  The ring variants dispatch to
+``flash_attention_2``, ``sdpa`` and ``flex_attention`` all end in ``ops.flash_attn_varlen``: the in-tree flash attention kernel on
+CUDA (document / sliding-window / causal masks are its native inputs), the fp32 masked-softmax oracle on CPU.  The ring variants dispatch to
 ``nanotron_b200.parallel.context_parallel``.
 """
 from __future__ import annotations
@@ -12,7 +12,6 @@ from typing import Callable, Dict, Optional
 import torch
 
 from nanotron_b200 import ops
-from nanotron_b200.ops import reference as ref
 
 
 def get_attention_mask(position_ids: torch.Tensor, seq_length: int):
@@ -36,17 +35,25 @@ def flash_attention_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, m
 
 
 def sdpa_attention_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True, softmax_scale=None, sliding_window=None, **_):
-    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=softmax_scale, window=sliding_window)
+    """The "sdpa" backend name of the reference (src/nanotron/nn/attention.py:200-209).  Same computation as ``flash_attention_2``:
+    CUDA tensors run the in-tree kernel (or, outside its contract, the library kernel with an explicit mask), CPU tensors the
+    fp32 masked-softmax oracle."""
+    return ops.flash_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=causal, softmax_scale=softmax_scale, window=sliding_window)
 
 
-def flex_attention_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True, softmax_scale=None, sliding_window=None, flex_attention_mask: Optional[str] = None, **_):
-    """Mask kinds "sliding_window", "document", "sliding_window_document" map onto (cu_seqlens, window)."""
-    if flex_attention_mask == "sliding_window":
-        total_q = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
-        total_k = torch.tensor([0, k.shape[0]], dtype=torch.int32, device=q.device)
-        return ref.attention_varlen(q, k, v, total_q, total_k, causal=causal, softmax_scale=softmax_scale, window=sliding_window)
-    window = sliding_window if flex_attention_mask in ("sliding_window_document",) or flex_attention_mask is None else None
-    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=softmax_scale, window=window)
+def flex_attention_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True, softmax_scale=None, sliding_window=None, flex_attention_mask: Optional[str] = None, softcap: Optional[float] = None, **_):
+    """Mask-programmable attention (reference src/nanotron/nn/attention.py:120-129 + nn/flex_attention.py).  The mask kinds the
+    reference builds block masks for -- "causal", "sliding_window", "document", "sliding_window_document" -- are all of the form
+    (document boundaries, causal, window), which is what the in-tree kernel takes directly: ``nn.flex_attention.BlockMask``
+    carries that description instead of a dense block table.  Score soft-capping has no kernel and runs the fp32 formulation."""
+    from nanotron_b200.nn.flex_attention import block_mask_for
+
+    bm = block_mask_for(flex_attention_mask, cu_seqlens_q, cu_seqlens_k, total_q=q.shape[0], total_k=k.shape[0], max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k, causal=causal, sliding_window=sliding_window)
+    if softcap is not None:
+        from nanotron_b200.nn.flex_attention import softcapped_attention
+
+        return softcapped_attention(q, k, v, bm, softcap=softcap, softmax_scale=softmax_scale)
+    return ops.flash_attn_varlen(q, k, v, bm.cu_seqlens_q, bm.cu_seqlens_k, bm.max_seqlen_q, bm.max_seqlen_k, causal=bm.causal, softmax_scale=softmax_scale, window=bm.window)
 
 
 def _ring(kind: str) -> Callable:

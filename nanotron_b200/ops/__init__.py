@@ -18,7 +18,7 @@ from nanotron_b200.ops import reference as ref
 
 _MODE = os.environ.get("NTB_OPS", "auto")  # auto | torch
 _GEMM = os.environ.get("NTB_GEMM", "auto")  # auto | cublas | tcgen05
-_ATTN = os.environ.get("NTB_ATTN", "auto")  # auto | native | sdpa
+_ATTN = os.environ.get("NTB_ATTN", "auto")  # auto | native (both: the in-tree tcgen05 kernels) | sdpa (library kernel, for comparison)
 LAUNCH_COUNTER = {"n": 0}
 
 
@@ -353,29 +353,87 @@ class _FlashAttnVarlen(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None, None
 
 
+_WARNED = set()
+
+
+def _warn_once(msg: str):
+    if msg not in _WARNED:
+        _WARNED.add(msg)
+        import warnings
+
+        warnings.warn(msg, stacklevel=3)
+
+
+def _band_mask(lq: int, lk: int, causal: bool, window: Optional[int], device) -> Optional[torch.Tensor]:
+    """Boolean [lq, lk] mask (True = attend) with the causal diagonal aligned to the bottom-right corner: query i sees keys
+    j <= i + (lk - lq), and with a window only the last ``window`` of them, itself included (the convention of
+    ``reference.attention_varlen`` and of the in-tree kernels)."""
+    window = window if window else None
+    if not causal and window is None:
+        return None
+    qi = torch.arange(lq, device=device).unsqueeze(1) + (lk - lq)
+    kj = torch.arange(lk, device=device).unsqueeze(0)
+    m = torch.ones(lq, lk, dtype=torch.bool, device=device)
+    if causal:
+        m &= kj <= qi
+    if window is not None:
+        m &= kj > qi - window
+    return m
+
+
 def _sdpa_varlen(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, window):
-    """Library attention for CUDA tensors when the in-tree kernel does not cover the case."""
+    """Library attention for CUDA tensors: the comparison path (``set_attention("sdpa")``) and shapes outside the in-tree kernel's
+    contract (head dims other than 128, dtypes other than bf16).  Equal-length square causal batches take the library's own
+    causal kernel; every other case (queries shorter than keys, windows, packed documents) runs the library kernel per
+    document with an explicit bottom-right aligned mask, so the result always matches ``reference.attention_varlen``."""
     B = cu_q.numel() - 1
     Tq, Hq, D = q.shape
-    if B * max_q == Tq and B * max_k == k.shape[0] and window is None:
+    Hkv = k.shape[1]
+    sdpa = torch.nn.functional.scaled_dot_product_attention
+    if B * max_q == Tq and B * max_k == k.shape[0]:
+        # equal-length rows (what a non-packed batch gives): no host read of cu_seqlens needed
         qb = q.view(B, max_q, Hq, D).transpose(1, 2)
-        kb = k.view(B, max_k, k.shape[1], D).transpose(1, 2)
-        vb = v.view(B, max_k, v.shape[1], D).transpose(1, 2)
-        o = torch.nn.functional.scaled_dot_product_attention(qb, kb, vb, is_causal=causal and max_q == max_k, scale=scale, enable_gqa=Hq != k.shape[1])
+        kb = k.view(B, max_k, Hkv, D).transpose(1, 2)
+        vb = v.view(B, max_k, Hkv, D).transpose(1, 2)
+        if window is None and (not causal or max_q == max_k):
+            o = sdpa(qb, kb, vb, is_causal=causal, scale=scale, enable_gqa=Hq != Hkv)
+        else:
+            o = sdpa(qb, kb, vb, attn_mask=_band_mask(max_q, max_k, causal, window, q.device), scale=scale, enable_gqa=Hq != Hkv)
         return o.transpose(1, 2).reshape(Tq, Hq, D)
-    return ref.attention_varlen(q, k, v, cu_q, cu_k, causal=causal, softmax_scale=scale, window=window)
+    _warn_once("ragged documents outside the in-tree attention kernel's contract: running the library kernel once per document")
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    outs = []
+    for b in range(B):
+        qd = q[cq[b] : cq[b + 1]].transpose(0, 1).unsqueeze(0)
+        kd = k[ck[b] : ck[b + 1]].transpose(0, 1).unsqueeze(0)
+        vd = v[ck[b] : ck[b + 1]].transpose(0, 1).unsqueeze(0)
+        lq, lk = qd.shape[2], kd.shape[2]
+        if lq == 0:
+            continue
+        if lk == 0:
+            outs.append(torch.zeros(lq, Hq, D, dtype=q.dtype, device=q.device))
+            continue
+        o = sdpa(qd, kd, vd, attn_mask=_band_mask(lq, lk, causal, window, q.device), scale=scale, enable_gqa=Hq != Hkv)
+        outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, dim=0)
 
 
 def flash_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, causal: bool = True, softmax_scale: Optional[float] = None, window: Optional[int] = None) -> torch.Tensor:
-    """Variable-length attention over packed sequences.  q: [Tq,Hq,D]; k,v: [Tk,Hkv,D]; cu_seqlens int32 [B+1]."""
+    """Variable-length attention over packed sequences.  q: [Tq,Hq,D]; k,v: [Tk,Hkv,D]; cu_seqlens int32 [B+1].
+    Causal masks are aligned to the bottom-right corner when a sequence has fewer queries than keys.
+
+    On CUDA the in-tree tcgen05 kernels run whenever their contract holds (bf16, head dim 128): packed documents, sliding windows
+    and ``lq != lk`` included.  ``set_attention("sdpa")`` selects the library kernel for comparison runs; shapes outside the
+    contract (toy head dims, fp32) also use it, with an explicit mask where one is needed.  The fp32 PyTorch oracle only runs
+    on CPU tensors or under ``set_mode("torch")``."""
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if q.is_cuda and _MODE != "torch":
         from nanotron_b200.ops import native
 
-        if _ATTN == "native" and native.flash_attn_supported(q, k, v, window):
+        if _ATTN != "sdpa" and native.flash_attn_supported(q, k, v, window):
             return _FlashAttnVarlen.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
         return _sdpa_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)
-    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=scale, window=window)
+    return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=softmax_scale, window=window)
 
 
 class _FusedQKVAttention(torch.autograd.Function):

@@ -34,7 +34,7 @@ class GradientAccumulator(ABC):
         ...
 
     @abstractmethod
-    def backward(self, loss: torch.Tensor):
+    def backward(self, loss, grad_tensors=None):
         ...
 
     @abstractmethod
@@ -176,8 +176,10 @@ class FP32GradientAccumulator(GradientAccumulator):
             self._hooks.append(p.register_post_accumulate_grad_hook(hook))
 
     # ------------------------------------------------------------------ training-step API
-    def backward(self, loss: torch.Tensor):
-        loss.backward()
+    def backward(self, loss, grad_tensors=None):
+        """``loss``: a scalar, or a list of roots with matching ``grad_tensors`` (pipeline stages backpropagate from the activations
+        they sent onwards, seeded with the gradients received for them)."""
+        torch.autograd.backward(loss, grad_tensors)
         # gradients were folded into the fp32 buffer by hooks / GEMM epilogues
 
     @torch.no_grad()

@@ -83,7 +83,14 @@ class ParallelContext:
         self.tp_pg = self.create_new_group(ranks.reshape((-1, tp)))
         self.cp_pg = self.create_new_group(ranks.transpose((4, 0, 1, 2, 3)).reshape((-1, cp)))
         self.dp_pg = self.create_new_group(ranks.transpose((3, 4, 0, 1, 2)).reshape((-1, dp)))
-        self.pp_pg = self.create_new_group(ranks.transpose((2, 3, 4, 0, 1)).reshape((-1, pp)))
+        pp_groups = ranks.transpose((2, 3, 4, 0, 1)).reshape((-1, pp))
+        self.pp_pg = self.create_new_group(pp_groups)
+        if pp > 1:
+            # pipeline traffic: one process group per direction (activations forward, gradients backward), see pipeline_parallel/p2p.py
+            from nanotron_b200.parallel.pipeline_parallel.p2p import register_lanes
+
+            self.pp_lane_pgs = tuple(self._create_private_group(pp_groups) for _ in range(2))
+            register_lanes(self.pp_pg, *self.pp_lane_pgs)
         # expert parallel overlay: dp axis split as (dp // ep, ep)
         r6 = ranks.reshape((pp, dp // ep, ep, cp, tp))
         self.ep_pg = self.create_new_group(r6.transpose((0, 1, 3, 4, 2)).reshape((-1, ep)))
@@ -110,6 +117,17 @@ class ParallelContext:
                 self.world_ranks_to_pg[key] = dist.new_group(ranks=list(key), backend=dist.get_backend())
             if rank in key:
                 mine = self.world_ranks_to_pg[key]
+        return mine
+
+    def _create_private_group(self, all_groups_ranks) -> dist.ProcessGroup:
+        """Like ``create_new_group`` but never shared with another axis that happens to span the same ranks."""
+        rank = int(os.environ.get("RANK", "0"))
+        mine = None
+        for group_ranks in all_groups_ranks:
+            key = sorted(int(r) for r in group_ranks)
+            g = dist.new_group(ranks=key, backend=dist.get_backend())
+            if rank in key:
+                mine = g
         return mine
 
     # ------------------------------------------------------------------ misc

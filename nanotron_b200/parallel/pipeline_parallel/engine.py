@@ -1,13 +1,16 @@
-"""Pipeline schedules: all-forward-all-backward and one-forward-one-backward.
+"""Pipeline schedules: all-forward-all-backward (AFAB) and one-forward-one-backward (1F1B).
 
-Parity: reference src/nanotron/parallel/pipeline_parallel/engine.py:24-348.  A model wrapper may expose
-``no_sync()`` (context manager that suppresses gradient synchronisation) and ``trigger_grad_sync()``; the engine
-enters ``no_sync`` for every micro-batch but the last so data-parallel reduction happens once per step and can
-overlap the last backward.
+Capability parity: reference src/nanotron/parallel/pipeline_parallel/engine.py:24-348 (same class names and
+``train_batch_iter`` / ``validate_batch_iter`` entry points).  A schedule here is only an order of ``forward`` and
+``backward`` calls: communication needs no scheduling of its own because activations and gradients travel on separate
+one-directional lanes and are sent the moment they exist (``p2p.py``, ``state.py``).
+
+Data-parallel hooks: if the model (or the gradient accumulator) exposes ``no_sync()`` it is entered for every backward but the
+last, and ``prepare_last_backward()`` (a context manager) wraps the last one, which is where gradient reduction that
+overlaps the backward pass is armed.
 """
 from __future__ import annotations
 
-import contextlib
 from abc import ABC, abstractmethod
 from typing import Dict, Iterable, List, Optional, Union
 
@@ -17,11 +20,12 @@ from torch import nn as torch_nn
 from nanotron_b200 import distributed as dist
 from nanotron_b200.logging import get_logger
 from nanotron_b200.parallel.pipeline_parallel.context_manager import attach_pipeline_state_to_model
-from nanotron_b200.parallel.pipeline_parallel.state import PipelineEvalBatchState, PipelineTrainBatchState
+from nanotron_b200.parallel.pipeline_parallel.state import PipelineTrainBatchState
 from nanotron_b200.parallel.pipeline_parallel.tensor_pointer import TensorPointer
 from nanotron_b200.utils import ContextManagers
 
 logger = get_logger(__name__)
+MicroBatch = Dict[str, Union[torch.Tensor, TensorPointer]]
 
 
 class PipelineEngine(ABC):
@@ -34,133 +38,103 @@ class PipelineEngine(ABC):
     def __hash__(self):
         return hash(type(self).__name__)
 
-    def forward(self, context: ContextManagers, state: PipelineTrainBatchState, micro_batch: Dict[str, Union[torch.Tensor, TensorPointer]], model: torch_nn.Module):
-        state.new_micro_batch_forward()
+    # ------------------------------------------------------------------ one micro-batch
+    def forward(self, context: ContextManagers, state: PipelineTrainBatchState, micro_batch: MicroBatch, model: torch_nn.Module) -> Dict:
+        state.begin_micro_batch()
         with context:
             output = model(**micro_batch)
         if not isinstance(output, dict):
             output = {"loss": output}
-        for k, v in output.items():
-            if not isinstance(v, TensorPointer):
-                output[k] = v / self.nb_microbatches
-        # the loss tensor is what backward starts from on the last stage
-        if not isinstance(output["loss"], TensorPointer):
-            assert output["loss"].requires_grad or not torch.is_grad_enabled()
-            state.register_activation_requiring_backward(output["loss"])
+        # every micro-batch contributes 1 / nb_microbatches of the step's loss (and of its gradient)
+        output = {k: (v if isinstance(v, TensorPointer) else v / self.nb_microbatches) for k, v in output.items()}
+        loss = output["loss"]
+        if not isinstance(loss, TensorPointer):
+            assert loss.requires_grad or not torch.is_grad_enabled()
+            if loss.requires_grad:
+                state.register_activation_requiring_backward(loss)
         return output
 
     @staticmethod
     def _get_fwd_context(model: torch_nn.Module):
         return ContextManagers([])
 
-    def backward(self, context: ContextManagers, state: PipelineTrainBatchState, grad_accumulator=None):
-        if len(state.microbatches_activations_requiring_backward) == 0:
-            return
-        with context:
-            activations = state.pop_last_activations_requiring_backward()
-            if len(activations) == 0:
-                return
-            if grad_accumulator is None:
-                sum(activations).backward()
-            else:
-                grad_accumulator.backward(sum(activations))
-        # tensors sent in forward that turned out unused raise here rather than hang
-        state.nb_backwards += 1
-
     def _get_bwd_context(self, model: torch_nn.Module, nb_backwards: int, grad_accumulator=None):
-        is_last = nb_backwards == self.nb_microbatches - 1
-        cms = []
-        if hasattr(model, "no_sync") and not is_last:
-            cms.append(model.no_sync())
-        elif is_last and hasattr(model, "prepare_last_backward"):
-            cms.append(model.prepare_last_backward())
-        return ContextManagers(cms)
+        last = nb_backwards == self.nb_microbatches - 1
+        managers = []
+        for owner in (model, grad_accumulator):
+            if owner is None:
+                continue
+            if not last and hasattr(owner, "no_sync"):
+                managers.append(owner.no_sync())
+            elif last and hasattr(owner, "prepare_last_backward"):
+                managers.append(owner.prepare_last_backward())
+        return ContextManagers(managers)
 
+    def backward(self, context: ContextManagers, state: PipelineTrainBatchState, grad_accumulator=None):
+        with context:
+            state.backward_micro_batch(grad_accumulator=grad_accumulator)
+
+    def _one_forward(self, model, state, micro_batch, outputs: List[Dict]):
+        output = self.forward(context=self._get_fwd_context(model=model), state=state, micro_batch=micro_batch, model=model)
+        if not isinstance(output["loss"], TensorPointer):
+            output = {k: v.detach() for k, v in output.items()}
+        outputs.append(output)
+
+    def _one_backward(self, model, state, grad_accumulator):
+        context = self._get_bwd_context(model=model, nb_backwards=state.nb_backwards, grad_accumulator=grad_accumulator)
+        self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
+
+    # ------------------------------------------------------------------ whole batches
     @abstractmethod
-    def train_batch_iter(self, model: torch_nn.Module, pg: dist.ProcessGroup, batch: Iterable[Dict[str, Union[torch.Tensor, TensorPointer]]], nb_microbatches: int, grad_accumulator=None) -> Iterable[Dict[str, Union[torch.Tensor, TensorPointer]]]:
+    def train_batch_iter(self, model: torch_nn.Module, pg: dist.ProcessGroup, batch: Iterable[MicroBatch], nb_microbatches: int, grad_accumulator=None) -> Iterable[Dict]:
         ...
 
     @torch.inference_mode()
-    def validate_batch_iter(self, model: torch_nn.Module, batch: Iterable[Dict[str, Union[torch.Tensor, TensorPointer]]], nb_microbatches: int) -> Iterable[Dict[str, Union[torch.Tensor, TensorPointer]]]:
+    def validate_batch_iter(self, model: torch_nn.Module, batch: Iterable[MicroBatch], nb_microbatches: int) -> Iterable[Dict]:
         state = PipelineTrainBatchState()
         self.nb_microbatches = nb_microbatches
-        outputs = []
+        outputs: List[Dict] = []
         with attach_pipeline_state_to_model(model=model, pipeline_state=state):
             for micro_batch in batch:
-                context = self._get_fwd_context(model=model)
-                output = self.forward(context=context, state=state, micro_batch=micro_batch, model=model)
-                for _ in range(len(state.microbatches_activations_to_send)):
-                    state.microbatches_activations_to_send.popleft()()
-                if not isinstance(output, dict):
-                    output = {"loss": output}
-                if not isinstance(output["loss"], TensorPointer):
-                    output = {k: v.detach() for k, v in output.items()}
-                outputs.append(output)
-                # nothing is backpropagated in validation
-                state.microbatches_activations_requiring_backward.clear()
+                self._one_forward(model, state, micro_batch, outputs)
+            state.drop_pending()
+            state.finish()
         return outputs
 
 
 class AllForwardAllBackwardPipelineEngine(PipelineEngine):
     def train_batch_iter(self, model, pg, batch, nb_microbatches, grad_accumulator=None):
-        state = PipelineTrainBatchState()
         self.nb_microbatches = nb_microbatches
-        outputs = []
+        state = PipelineTrainBatchState()
+        outputs: List[Dict] = []
         with attach_pipeline_state_to_model(model=model, pipeline_state=state):
             for micro_batch in batch:
-                context = self._get_fwd_context(model=model)
-                output = self.forward(context=context, state=state, micro_batch=micro_batch, model=model)
-                # send what this stage produced right away so the next stage can start
-                for _ in range(len(state.microbatches_activations_to_send)):
-                    state.microbatches_activations_to_send.popleft()()
-                if not isinstance(output["loss"], TensorPointer):
-                    output = {k: v.detach() for k, v in output.items()}
-                outputs.append(output)
-            for _ in range(len(state.microbatches_activations_requiring_backward)):
-                context = self._get_bwd_context(model=model, nb_backwards=state.nb_backwards, grad_accumulator=grad_accumulator)
-                self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
-                for _ in range(len(state.microbatches_grads_to_send)):
-                    state.microbatches_grads_to_send.popleft()()
-            state.check_buffers_empty()
+                self._one_forward(model, state, micro_batch, outputs)
+            for _ in range(len(outputs)):
+                self._one_backward(model, state, grad_accumulator)
+            state.finish()
         return outputs
 
 
 class OneForwardOneBackwardPipelineEngine(PipelineEngine):
     def train_batch_iter(self, model, pg, batch, nb_microbatches, grad_accumulator=None):
-        """Warm-up of ``pp_size - rank - 1`` forwards, then alternate one forward / one backward, then drain."""
+        """Stage r of p runs ``p - r - 1`` forwards ahead (so the last stage alternates from the start), then one forward and one
+        backward per remaining micro-batch, then the backwards it still owes.  At most ``p - r`` micro-batches of activations are
+        alive on a stage, against all of them under AFAB."""
         self.nb_microbatches = nb_microbatches
-        assert self.nb_microbatches >= pg.size() - 1, f"Number of microbatches ({self.nb_microbatches}) must be at least PP_SIZE-1={pg.size() - 1} when using the OneForwardOneBackwardPipelineEngine"
+        stages, me = pg.size(), dist.get_rank(pg)
+        assert nb_microbatches >= stages - 1, f"Number of microbatches ({nb_microbatches}) must be at least PP_SIZE-1={stages - 1} when using the OneForwardOneBackwardPipelineEngine"
+        ahead = min(stages - me - 1, nb_microbatches)
         state = PipelineTrainBatchState()
-        outputs = []
-        batch = iter(batch)
-        current_pp_rank = dist.get_rank(pg)
+        outputs: List[Dict] = []
+        feed = iter(batch)
         with attach_pipeline_state_to_model(model=model, pipeline_state=state):
-            for _ in range(pg.size() - current_pp_rank - 1):
-                micro_batch = next(batch)
-                context = self._get_fwd_context(model=model)
-                output = self.forward(context=context, state=state, micro_batch=micro_batch, model=model)
-                for _ in range(len(state.microbatches_activations_to_send)):
-                    state.microbatches_activations_to_send.popleft()()
-                if not isinstance(output["loss"], TensorPointer):
-                    output = {k: v.detach() for k, v in output.items()}
-                outputs.append(output)
-            for micro_batch in batch:
-                context = self._get_fwd_context(model=model)
-                output = self.forward(context=context, state=state, micro_batch=micro_batch, model=model)
-                # only activations: the next stage may not be ready to hand gradients back yet
-                state.run_communication(send_only_activation=True)
-                if not isinstance(output["loss"], TensorPointer):
-                    output = {k: v.detach() for k, v in output.items()}
-                outputs.append(output)
-                context = self._get_bwd_context(model=model, nb_backwards=state.nb_backwards, grad_accumulator=grad_accumulator)
-                self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
-            state.run_communication()
-            assert len(state.microbatches_activations_to_send) == 0
-            # cool-down: remaining backwards
-            for _ in range(len(state.microbatches_activations_requiring_backward)):
-                context = self._get_bwd_context(model=model, nb_backwards=state.nb_backwards, grad_accumulator=grad_accumulator)
-                self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
-                for _ in range(len(state.microbatches_grads_to_send)):
-                    state.microbatches_grads_to_send.popleft()()
-            state.check_buffers_empty()
+            for _ in range(ahead):
+                self._one_forward(model, state, next(feed), outputs)
+            for micro_batch in feed:
+                self._one_forward(model, state, micro_batch, outputs)
+                self._one_backward(model, state, grad_accumulator)
+            for _ in range(ahead):
+                self._one_backward(model, state, grad_accumulator)
+            state.finish()
         return outputs

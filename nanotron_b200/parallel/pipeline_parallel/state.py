@@ -1,212 +1,168 @@
-"""Per-batch bookkeeping of pipeline communication (parity: reference src/nanotron/parallel/pipeline_parallel/state.py).
+"""Per-batch pipeline bookkeeping: which tensors crossed a stage boundary in each micro-batch, and the exchange of their
+gradients (capability parity: reference src/nanotron/parallel/pipeline_parallel/state.py).
 
-Sends and receives requested by ``PipelineBlock`` during a forward/backward are queued here and executed by
-``run_communication`` in a fixed order (send activations, recv activations, send grads, recv grads), which is
-what keeps every pair of neighbouring stages matched.
+The design follows from the two one-directional lanes of ``p2p.py``:
+
+* Nothing is queued.  An activation is sent the moment its ``PipelineBlock`` hands it over (asynchronously, never waited
+  on by the computing stream) and received the moment the consuming block asks for it.
+* A received activation that requires grad is an autograd *leaf*.  After the backward of its micro-batch its ``.grad`` is
+  the gradient the producer stage needs, so no custom autograd function and no placeholder tensors are involved: the
+  backward of a micro-batch is ONE ``torch.autograd.backward`` call whose roots are the local loss terms plus the
+  activations this stage sent onwards, seeded with the gradients received for them.
+* Gradients carry no header (shape and dtype are the activation's) and cross each boundary in the order the activations
+  crossed it; both sides derive that order from the same per-micro-batch records, so it does not depend on the order in
+  which autograd happens to visit nodes.  A received activation that took no part in the loss still gets a (zero)
+  gradient sent back, which keeps the two sides matched instead of hanging.
+
+Engines drive a state with ``begin_micro_batch`` / ``backward_micro_batch`` / ``finish``.
 """
 from __future__ import annotations
 
 import collections
 import dataclasses
 from abc import ABC, abstractmethod
-from typing import List
+from typing import Deque, List, Optional, Tuple
 
 import torch
 
-from nanotron_b200 import distributed as dist
 from nanotron_b200.logging import get_logger
-from nanotron_b200.parallel.pipeline_parallel.p2p import P2P
+from nanotron_b200.parallel.pipeline_parallel.p2p import BWD, FWD, P2P
 
 logger = get_logger(__name__)
 
 
 @dataclasses.dataclass
-class SendActivation:
-    activation: torch.Tensor
-    to_rank: int
-    p2p: P2P
+class MicroBatchRecord:
+    """What one micro-batch's forward left behind on this stage."""
 
-    def __call__(self):
-        self.p2p.send_tensors([self.activation], to_rank=self.to_rank)
-
-
-@dataclasses.dataclass
-class RecvActivation:
-    from_rank: int
-    p2p: P2P
-
-    def __call__(self) -> torch.Tensor:
-        return self.p2p.recv_tensors(num_tensors=1, from_rank=self.from_rank)[0]
-
-
-@dataclasses.dataclass
-class SendGrad:
-    grad: torch.Tensor
-    to_rank: int
-    p2p: P2P
-
-    def __call__(self):
-        self.p2p.send_tensors([self.grad], to_rank=self.to_rank)
-
-
-@dataclasses.dataclass
-class RecvGrad:
-    from_rank: int
-    p2p: P2P
-
-    def __call__(self) -> torch.Tensor:
-        return self.p2p.recv_tensors(num_tensors=1, from_rank=self.from_rank)[0]
+    index: int
+    roots: List[torch.Tensor] = dataclasses.field(default_factory=list)  # local scalars to differentiate (the loss)
+    sent: List[Tuple[torch.Tensor, int, P2P]] = dataclasses.field(default_factory=list)  # (activation, to_rank, p2p), grad expected back
+    received: List[Tuple[torch.Tensor, int, P2P]] = dataclasses.field(default_factory=list)  # (leaf, from_rank, p2p), grad owed
 
 
 class PipelineBatchState(ABC):
-    activations_buffer = collections.deque()
+    """What ``PipelineBlock`` needs from the schedule that is running."""
 
     @abstractmethod
-    def register_activation_requiring_backward(self, activation: torch.Tensor):
+    def send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P) -> None:
         ...
 
     @abstractmethod
-    def register_send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P):
+    def recv_activation(self, from_rank: int, p2p: P2P) -> torch.Tensor:
         ...
 
     @abstractmethod
-    def register_recv_activation(self, from_rank: int, p2p: P2P):
-        ...
-
-    @abstractmethod
-    def register_send_grad(self, grad: torch.Tensor, to_rank: int, p2p: P2P):
-        ...
-
-    @abstractmethod
-    def register_recv_grad(self, from_rank: int, p2p: P2P):
-        ...
-
-    @abstractmethod
-    def run_communication(self, send_only_activation: bool = False):
-        ...
-
-    @abstractmethod
-    def new_micro_batch_forward(self):
-        ...
-
-    @abstractmethod
-    def pop_last_activations_requiring_backward(self) -> List[torch.Tensor]:
+    def register_activation_requiring_backward(self, activation: torch.Tensor) -> None:
         ...
 
 
-@dataclasses.dataclass
 class PipelineTrainBatchState(PipelineBatchState):
-    microbatches_activations_to_send = collections.deque()
-    microbatches_activations_to_recv = collections.deque()
-    microbatches_grads_to_send = collections.deque()
-    microbatches_grads_to_recv = collections.deque()
-    grads_buffer = collections.deque()
-    activations_buffer = collections.deque()
-    microbatches_activations_requiring_backward = collections.deque()
-    nb_backwards: int = 0
-    nb_forwards: int = 0
+    def __init__(self):
+        self.pending: Deque[MicroBatchRecord] = collections.deque()  # forwarded, not yet backwarded (oldest first)
+        self.current: Optional[MicroBatchRecord] = None
+        self.nb_forwards = 0
+        self.nb_backwards = 0
+        self._p2ps: List[P2P] = []
 
-    def __post_init__(self):
-        # dataclass class-level deques would be shared between instances: give each instance its own
-        self.microbatches_activations_to_send = collections.deque()
-        self.microbatches_activations_to_recv = collections.deque()
-        self.microbatches_grads_to_send = collections.deque()
-        self.microbatches_grads_to_recv = collections.deque()
-        self.grads_buffer = collections.deque()
-        self.activations_buffer = collections.deque()
-        self.microbatches_activations_requiring_backward = collections.deque()
+    # ------------------------------------------------------------------ forward side
+    def _note(self, p2p: P2P):
+        if all(p is not p2p for p in self._p2ps):
+            self._p2ps.append(p2p)
+            p2p.begin_round()  # first use in this batch: it is at a micro-batch boundary (shapes learnt in earlier batches replay)
 
-    def new_micro_batch_forward(self):
-        self.microbatches_activations_requiring_backward.append(collections.deque())
+    def begin_micro_batch(self) -> MicroBatchRecord:
+        for p in self._p2ps:
+            p.begin_round()
+        self.current = MicroBatchRecord(index=self.nb_forwards)
+        self.pending.append(self.current)
+        self.nb_forwards += 1
+        return self.current
 
-    def register_activation_requiring_backward(self, activation: torch.Tensor):
-        self.microbatches_activations_requiring_backward[-1].append(activation)
+    def register_activation_requiring_backward(self, activation: torch.Tensor) -> None:
+        self.current.roots.append(activation)
 
-    def register_send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P):
-        self.microbatches_activations_to_send.append(SendActivation(activation=activation, to_rank=to_rank, p2p=p2p))
+    def send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P) -> None:
+        self._note(p2p)
+        p2p.send(activation, to_rank, FWD)
+        if activation.requires_grad and torch.is_grad_enabled():
+            self.current.sent.append((activation, to_rank, p2p))
 
-    def register_recv_activation(self, from_rank: int, p2p: P2P):
-        self.microbatches_activations_to_recv.append(RecvActivation(from_rank=from_rank, p2p=p2p))
+    def recv_activation(self, from_rank: int, p2p: P2P) -> torch.Tensor:
+        self._note(p2p)
+        ticket = p2p.recv(from_rank, FWD)
+        wants_grad = ticket.requires_grad and torch.is_grad_enabled()
+        ticket.requires_grad = wants_grad
+        tensor = ticket.wait()
+        if wants_grad:
+            self.current.received.append((tensor, from_rank, p2p))
+        return tensor
 
-    def register_send_grad(self, grad: torch.Tensor, to_rank: int, p2p: P2P):
-        self.microbatches_grads_to_send.append(SendGrad(grad=grad, to_rank=to_rank, p2p=p2p))
+    # ------------------------------------------------------------------ backward side
+    def backward_micro_batch(self, grad_accumulator=None) -> bool:
+        """Backward of the oldest micro-batch still pending.  Returns False when there was nothing to differentiate."""
+        if not self.pending:
+            return False
+        mb = self.pending.popleft()
+        if self.current is mb:
+            self.current = None
+        # gradients of what went downstream, in the order it went
+        tickets = [p2p.recv_like(act, to_rank, BWD) for act, to_rank, p2p in mb.sent]
+        roots = list(mb.roots) + [act for act, _, _ in mb.sent]
+        seeds = [None] * len(mb.roots) + [t.wait() for t in tickets]
+        did = False
+        if roots:
+            if grad_accumulator is None:
+                torch.autograd.backward(roots, seeds)
+            else:
+                grad_accumulator.backward(roots, seeds)
+            did = True
+        # gradients owed upstream, in the order the activations arrived
+        for leaf, from_rank, p2p in mb.received:
+            g = leaf.grad
+            if g is None:
+                g = torch.zeros_like(leaf)  # took no part in the loss: keep the exchange matched
+            p2p.send_raw(g, from_rank, BWD)
+            leaf.grad = None
+        self.nb_backwards += 1
+        return did
 
-    def register_recv_grad(self, from_rank: int, p2p: P2P):
-        self.microbatches_grads_to_recv.append(RecvGrad(from_rank=from_rank, p2p=p2p))
+    def drop_pending(self):
+        """Forward-only use (validation): forget the records, nothing will be differentiated."""
+        self.pending.clear()
+        self.current = None
 
-    def run_communication(self, send_only_activation: bool = False):
-        """Drain the queues.  ``send_only_activation``: used at the end of a forward when peers are not yet ready
-        to exchange gradients."""
-        logger.debug(
-            f"run_communication: act_send={len(self.microbatches_activations_to_send)} act_recv={len(self.microbatches_activations_to_recv)} "
-            f"grad_send={len(self.microbatches_grads_to_send)} grad_recv={len(self.microbatches_grads_to_recv)}"
-        )
-        while len(self.microbatches_activations_to_send) > 0:
-            self.microbatches_activations_to_send.popleft()()
-        if send_only_activation:
-            return
-        while len(self.microbatches_activations_to_recv) > 0:
-            self.activations_buffer.append(self.microbatches_activations_to_recv.popleft()())
-        while len(self.microbatches_grads_to_send) > 0:
-            self.microbatches_grads_to_send.popleft()()
-        while len(self.microbatches_grads_to_recv) > 0:
-            self.grads_buffer.append(self.microbatches_grads_to_recv.popleft()())
+    def finish(self):
+        """End of the batch: every micro-batch was differentiated; retire the sends."""
+        assert not self.pending, f"{len(self.pending)} micro-batches were forwarded but never backwarded"
+        for p in self._p2ps:
+            p.drain()
 
-    def pop_last_activations_requiring_backward(self) -> List[torch.Tensor]:
-        return self.microbatches_activations_requiring_backward.popleft()
-
-    def check_buffers_empty(self):
-        assert len(self.microbatches_activations_requiring_backward) == 0, f"There are still activations that require backward: {len(self.microbatches_activations_requiring_backward)}"
-        assert len(self.microbatches_activations_to_send) == 0, "There are activations left for me to send still"
-        assert len(self.microbatches_activations_to_recv) == 0, "There are activations left for me to recv still"
-        assert len(self.microbatches_grads_to_send) == 0, "There are gradients left for me to send still"
-        assert len(self.microbatches_grads_to_recv) == 0, "There are gradients left for me to recv still"
+    # name kept for callers written against the reference engine
+    check_buffers_empty = finish
 
 
-@dataclasses.dataclass
 class PipelineEvalBatchState(PipelineBatchState):
-    """Inference: only activations travel, nothing is kept for backward."""
+    """Inference (generation): activations only, exchanged eagerly and always with a header because shapes change from one
+    decoding step to the next.  The last stage feeds the first one inside the decoding loop; sending at once is what
+    keeps that cycle from waiting on itself."""
 
-    microbatches_activations_to_send = collections.deque()
-    microbatches_activations_to_recv = collections.deque()
-    activations_buffer = collections.deque()
+    def __init__(self):
+        self._p2ps: List[P2P] = []
 
-    def __post_init__(self):
-        self.microbatches_activations_to_send = collections.deque()
-        self.microbatches_activations_to_recv = collections.deque()
-        self.activations_buffer = collections.deque()
+    def send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P) -> None:
+        p2p.send_tensors([activation], to_rank=to_rank)
 
-    def new_micro_batch_forward(self):
+    def recv_activation(self, from_rank: int, p2p: P2P) -> torch.Tensor:
+        return p2p.recv_tensors(num_tensors=1, from_rank=from_rank)[0].requires_grad_(False)
+
+    def register_activation_requiring_backward(self, activation: torch.Tensor) -> None:
         pass
 
-    def register_activation_requiring_backward(self, activation: torch.Tensor):
+    def begin_micro_batch(self):
+        return None
+
+    def finish(self):
         pass
 
-    def register_send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P):
-        self.microbatches_activations_to_send.append(SendActivation(activation=activation, to_rank=to_rank, p2p=p2p))
-        # sending eagerly avoids a cyclic wait when the last stage feeds the first one (decoding loop)
-        self.microbatches_activations_to_send.popleft()()
-
-    def register_recv_activation(self, from_rank: int, p2p: P2P):
-        self.microbatches_activations_to_recv.append(RecvActivation(from_rank=from_rank, p2p=p2p))
-        self.activations_buffer.append(self.microbatches_activations_to_recv.popleft()())
-
-    def register_send_grad(self, grad: torch.Tensor, to_rank: int, p2p: P2P):
-        raise NotImplementedError("You can't register a send grad in pipeline eval mode")
-
-    def register_recv_grad(self, from_rank: int, p2p: P2P):
-        raise NotImplementedError("You can't register a recv grad in pipeline eval mode")
-
-    def run_communication(self, send_only_activation: bool = False):
-        while len(self.microbatches_activations_to_send) > 0:
-            self.microbatches_activations_to_send.popleft()()
-        while len(self.microbatches_activations_to_recv) > 0:
-            self.activations_buffer.append(self.microbatches_activations_to_recv.popleft()())
-
-    def pop_last_activations_requiring_backward(self) -> List[torch.Tensor]:
-        return []
-
-    def check_buffers_empty(self):
-        assert len(self.microbatches_activations_to_send) == 0
-        assert len(self.microbatches_activations_to_recv) == 0
-        assert len(self.activations_buffer) == 0
+    check_buffers_empty = finish

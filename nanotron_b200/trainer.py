@@ -122,6 +122,7 @@ class DistributedTrainer:
         set_random_seed(self.config.general.seed + dist.get_rank(self.parallel_context.tp_pg) + 1000 * dist.get_rank(self.parallel_context.pp_pg))
         self.model = self.init_model()
         self.unwrapped_model: NanotronModel = self.model
+        self._configure_pipeline_p2p()
         parametrization_method = ParametrizationMethod.SPECTRAL_MUP if hasattr(self.config.model.init_method, "use_mup") else ParametrizationMethod.STANDARD
         symm_alloc = self._maybe_enable_symmetric_buffers()
         try:
@@ -163,6 +164,23 @@ class DistributedTrainer:
         self._stop_requested = False
         self._kill_switch_path = Path(os.environ["NANOTRON_KILL_SWITCH"]) if os.environ.get("NANOTRON_KILL_SWITCH") else None
         self.post_init()
+
+    def _pipeline_p2ps(self):
+        from nanotron_b200.parallel.pipeline_parallel.block import PipelineBlock
+
+        seen = {}
+        for m in self.unwrapped_model.modules():
+            if isinstance(m, PipelineBlock):
+                seen[id(m.p2p)] = m.p2p
+        return list(seen.values())
+
+    def _configure_pipeline_p2p(self):
+        """Micro-batches of a data stage all have the same geometry: let pipeline stages learn the shapes they exchange during the
+        first micro-batch and send bare payloads afterwards (``pp_static_shapes``)."""
+        if self.parallel_context.pp_pg.size() == 1:
+            return
+        for p2p in self._pipeline_p2ps():
+            p2p.expect_static(bool(getattr(self.config.parallelism, "pp_static_shapes", True)))
 
     def _maybe_enable_symmetric_buffers(self):
         """Put the flat gradient / parameter buffers in peer-mapped memory when the fused data-parallel step applies."""
@@ -282,7 +300,11 @@ class DistributedTrainer:
                 dl = dl() if callable(dl) else dl
                 self.current_base_dl = dl
                 self.current_dataloader = self._wrap(dl)
-                self.sequence_length = stage.sequence_length or self.config.tokens.sequence_length
+                new_len = stage.sequence_length or self.config.tokens.sequence_length
+                if new_len != self.sequence_length and self.parallel_context.pp_pg.size() > 1:
+                    for p2p in self._pipeline_p2ps():
+                        p2p.reset_static()  # every rank switches stage at the same step: the next micro-batch re-learns the shapes
+                self.sequence_length = new_len
                 break
         assert self.current_dataloader is not None, "no data stage applies to the current step"
 

@@ -171,3 +171,80 @@ def test_fused_qkv_library_attention_matches_composition():
     with torch.no_grad():
         out2 = ops.fused_qkv_library_attention(qkv0.clone(), cos, sin, positions, Hq, Hkv, D, B, S)
     torch.testing.assert_close(out2, out.detach())
+
+
+@pytest.mark.parametrize("mode", ["auto", "sdpa"])
+@pytest.mark.parametrize("lq,lk,window", [(64, 192, None), (128, 384, None), (256, 256, 100), (128, 512, 200)])
+def test_default_path_causal_mask_is_bottom_right_aligned(mode, lq, lk, window):
+    """Fewer queries than keys (what context parallelism produces): query i of a row sees keys <= i + lk - lq, on the default
+    path (in-tree kernel) and on the library path alike; both must match the fp32 oracle, forward and gradients."""
+    from nanotron_b200 import ops
+
+    B, Hq, Hkv, D = 2, 4, 2, 128
+    torch.manual_seed(lq + lk)
+    q = torch.randn(B * lq, Hq, D, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(B * lk, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(B * lk, Hkv, D, device=DEV, dtype=torch.bfloat16)
+    cu_q = torch.arange(0, (B + 1) * lq, lq, dtype=torch.int32, device=DEV)
+    cu_k = torch.arange(0, (B + 1) * lk, lk, dtype=torch.int32, device=DEV)
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ops.set_attention(mode)
+    try:
+        out = ops.flash_attn_varlen(qg, kg, vg, cu_q, cu_k, lq, lk, causal=True, window=window)
+        g = torch.randn_like(out)
+        out.backward(g)
+    finally:
+        ops.set_attention("auto")
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    exp = ref.attention_varlen(qf, kf, vf, cu_q, cu_k, causal=True, window=window)
+    exp.backward(g.float())
+    torch.testing.assert_close(out.float(), exp.detach(), atol=2e-2, rtol=2e-2)
+    for name, a, b in (("dq", qg.grad, qf.grad), ("dk", kg.grad, kf.grad), ("dv", vg.grad, vf.grad)):
+        err = (a.float() - b).abs().max().item()
+        assert err < 3e-2 * max(b.abs().max().item(), 1.0), f"{name}: {err}"
+
+
+@pytest.mark.parametrize("mode", ["auto", "sdpa"])
+def test_default_path_ragged_documents_and_toy_head_dim(mode):
+    """Packed documents of unequal length: head dim 128 runs the in-tree kernel, head dim 64 (outside its contract) the library
+    kernel per document -- neither may fall back to anything that differs from the oracle."""
+    from nanotron_b200 import ops
+
+    lens = [100, 37, 300, 75]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    ops.set_attention(mode)
+    try:
+        for D in (128, 64):
+            torch.manual_seed(D)
+            q = torch.randn(T, 4, D, device=DEV, dtype=torch.bfloat16)
+            k = torch.randn(T, 2, D, device=DEV, dtype=torch.bfloat16)
+            v = torch.randn(T, 2, D, device=DEV, dtype=torch.bfloat16)
+            import warnings
+
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                out = ops.flash_attn_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=True, window=64)
+            exp = ref.attention_varlen(q, k, v, cu, cu, causal=True, window=64)
+            torch.testing.assert_close(out.float(), exp.float(), atol=2e-2, rtol=2e-2)
+    finally:
+        ops.set_attention("auto")
+
+
+def test_registry_backends_agree_on_cuda():
+    """"flash_attention_2", "sdpa" and "flex_attention" (document + window mask) give the oracle's result on CUDA tensors."""
+    from nanotron_b200.nn.attention import ALL_ATTENTION_FUNCTIONS
+
+    lens = [256, 128, 200]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _qkv(T, 4, 2, seed=21)
+    exp = ref.attention_varlen(q, k, v, cu, cu, causal=True, window=96)
+    for name, kw in (("flash_attention_2", {}), ("sdpa", {}), ("flex_attention", {"flex_attention_mask": "sliding_window_document"})):
+        out = ALL_ATTENTION_FUNCTIONS[name](q, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens), causal=True, sliding_window=96, **kw)
+        torch.testing.assert_close(out.float(), exp.float(), atol=2e-2, rtol=2e-2)
+    # the window-only mask ignores the document boundaries
+    one = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    exp = ref.attention_varlen(q, k, v, one, one, causal=True, window=96)
+    out = ALL_ATTENTION_FUNCTIONS["flex_attention"](q, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens), causal=True, sliding_window=96, flex_attention_mask="sliding_window")
+    torch.testing.assert_close(out.float(), exp.float(), atol=2e-2, rtol=2e-2)

@@ -38,3 +38,9 @@ def test_fused_expert_parallel_moe_matches_nccl():
 def test_fused_context_parallel_attention_matches_full_attention():
     r = _torchrun("tests/multigpu/check_fused_cp.py", 2, 29734)
     assert r.returncode == 0 and "FUSED_CP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_default_context_parallel_attention_matches_full_attention():
+    r = _torchrun("tests/multigpu/check_cp_default.py", 2, 29735)
+    assert r.returncode == 0 and "CP_DEFAULT_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
