@@ -1,11 +1,15 @@
 """Reference arm of ``bench.py``: runs the UNMODIFIED huggingface/nanotron installed under ``baseline/_ref`` through its
-own ``DistributedTrainer`` on the same model / batch / parallelism as the native arm and prints the same JSON line.
+own ``DistributedTrainer`` on the same model, batch and parallel layout (tp / pp by GPU count, sequence-parallel tensor
+parallelism with its asynchronous-communication linears, 1F1B) as the native arm and prints the same JSON line.
 
 Nothing of this repository's models, kernels or engine is on that path.  The only additions are import stand-ins under
 ``baseline/shims`` for third-party packages that cannot be installed offline (``dacite``, ``torchtyping``,
-``grouped_gemm``; the latter two are import-time only for a dense Llama).  Timing: the trainer's public
-``post_train_step`` hook is used to place CUDA events after the last warm-up step and after the last timed step,
-with a barrier + synchronize at both points; max over ranks.
+``grouped_gemm``; the latter two are import-time only for a dense Llama), and the dataloader handed to
+``DistributedTrainer.train``: the reference accepts any iterator of batches, and this one builds every micro-batch in
+pinned host memory and copies it to the device (the same end-to-end input path as the native arm) in the batch format
+of the reference's own dummy generator.  Timing: the trainer's public ``post_train_step`` hook places CUDA events after
+the last warm-up step and after the last timed step, with a barrier + synchronize at both points; max over ranks.  The
+reference reads the loss on the host every step (``iteration_step_info_interval=1``), so its timed region is end to end.
 """
 from __future__ import annotations
 
@@ -23,6 +27,45 @@ def _unavailable(why: str):
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
     return 0
+
+
+def _host_batches(trainer, input_pp_rank: int, output_pp_rank: int, counter: dict):
+    """Micro-batches in the format of the reference's ``dummy_infinite_data_generator(use_position_ids=True)``
+    (src/nanotron/data/dataloader.py:100-227: the first row packs documents of 4, 6 and seq - 10 tokens), built on the host in
+    pinned memory and copied to the device; ``counter`` accumulates the bytes copied."""
+    import torch
+    from nanotron import distributed as dist
+    from nanotron.parallel.pipeline_parallel.tensor_pointer import TensorPointer
+
+    ctx = trainer.parallel_context
+    mbs, seq, vocab = trainer.micro_batch_size, trainer.sequence_length, trainer.model_config.vocab_size
+    pp_rank = dist.get_rank(ctx.pp_pg)
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(42 * (1 + dist.get_rank(ctx.dp_pg)))
+    lengths = [[4, 6, seq - 10]] + [[seq]] * (mbs - 1)
+    position_ids = torch.cat([torch.cat([torch.arange(n) for n in row]).unsqueeze(0) for row in lengths]).long()
+
+    def to_device(t):
+        counter["bytes"] += t.numel() * t.element_size()
+        return t.pin_memory().to("cuda", non_blocking=True)
+
+    while True:
+        tokens = torch.randint(0, vocab, (mbs, seq + 1), dtype=torch.long, generator=gen)
+        batch = {}
+        if pp_rank == input_pp_rank:
+            batch["input_ids"] = to_device(tokens[:, :-1].contiguous())
+            batch["position_ids"] = to_device(position_ids)
+        else:
+            batch["input_ids"] = TensorPointer(group_rank=input_pp_rank)
+            batch["position_ids"] = TensorPointer(group_rank=input_pp_rank)
+        if pp_rank == output_pp_rank:
+            batch["label_ids"] = to_device(tokens[:, 1:].contiguous())
+            batch["label_mask"] = to_device(torch.ones(mbs, seq, dtype=torch.bool))
+        else:
+            batch["label_ids"] = TensorPointer(group_rank=output_pp_rank)
+            batch["label_mask"] = TensorPointer(group_rank=output_pp_rank)
+        counter["batches"] += 1
+        yield batch
 
 
 def run_reference(args):
@@ -52,16 +95,24 @@ def run_reference(args):
             AdamWOptimizerArgs, CheckpointsArgs, Config, DataArgs, DatasetStageArgs, GeneralArgs, LoggingArgs, Qwen2Config,
             LRSchedulerArgs, ModelArgs, OptimizerArgs, ParallelismArgs, RandomInit, TokenizerArgs, TokensArgs,
         )
-        from nanotron.data.dataloader import dummy_infinite_data_generator
         from nanotron.parallel.pipeline_parallel.utils import get_input_output_pp_ranks
         from nanotron.trainer import DistributedTrainer
     except Exception as e:  # import problems of the reference or of its dependencies
         return _unavailable(f"reference does not import here: {type(e).__name__}: {str(e)[:200]}")
 
-    from bench import BASELINE_TOK_S_PER_GPU, MODELS, ClockSampler
+    from bench import BASELINE_TOK_S_PER_GPU, MODELS, ClockSampler, layout_label, resolve_layout
 
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
+    tp, pp, dp = resolve_layout(args, world)
+    if args.model == "qwen-moe":
+        return _unavailable("the reference has no expert parallelism in src/ (nn/moe.py never communicates, parallel/context.py asserts tp*pp*cp*dp == world) and needs the grouped_gemm package, which cannot be installed offline")
+    if world // (tp * pp * dp) > 1:
+        return _unavailable("the reference cannot random-init a model under context parallelism (trainer.py:1052-1053 raises) and there is no checkpoint to load offline")
+    if dp > 1 and args.model == "llama3-8b":
+        # measured on this pool: with fp32 accumulation the reference's ZeRO-1 hook raises NotImplementedError
+        # (optim/gradient_accumulator.py:354-355) and its replicated-optimizer path needs more than the 180 GB of a B200 for 8B parameters
+        return _unavailable("the reference cannot hold a data-parallel replica of an 8B model on a 180 GB GPU (ZeRO-1 with fp32 accumulation is not implemented in its DDP hook; the replicated optimizer runs out of memory)")
     m = dict(MODELS[args.model])
     # The reference's `LlamaForTraining.init_model_randomly` fails on its stock path (models/llama.py:1095 hands
     # `config.model` to a parametrizator that reads `config.model.init_method`: AttributeError), so the Llama-3-8B shape
@@ -73,7 +124,7 @@ def run_reference(args):
     config = Config(
         general=GeneralArgs(project="bench", run="reference", seed=42, ignore_sanity_checks=True),
         checkpoints=CheckpointsArgs(checkpoints_path=ckpt_dir, checkpoint_interval=10**9, save_final_state=False),
-        parallelism=ParallelismArgs(dp=world, pp=1, tp=1, pp_engine="1f1b", tp_mode="REDUCE_SCATTER", tp_linear_async_communication=False, recompute_layer=bool(args.recompute)),
+        parallelism=ParallelismArgs(dp=dp, pp=pp, tp=tp, pp_engine="1f1b", tp_mode="REDUCE_SCATTER", tp_linear_async_communication=tp > 1, recompute_layer=bool(args.recompute)),
         model=ModelArgs(init_method=RandomInit(std=0.02), model_config=model_config),
         tokenizer=TokenizerArgs(tokenizer_name_or_path=None),
         optimizer=OptimizerArgs(
@@ -115,11 +166,8 @@ def run_reference(args):
     try:
         trainer = TimedTrainer(cfg_path)
         input_pp_rank, output_pp_rank = get_input_output_pp_ranks(model=trainer.model)
-        dataloader = dummy_infinite_data_generator(
-            micro_batch_size=trainer.micro_batch_size, sequence_length=trainer.sequence_length, input_pp_rank=input_pp_rank,
-            output_pp_rank=output_pp_rank, vocab_size=trainer.model_config.vocab_size, seed=42, parallel_context=trainer.parallel_context,
-            use_position_ids=True, cp_pg=trainer.parallel_context.cp_pg,
-        )()
+        h2d = {"bytes": 0, "batches": 0}
+        dataloader = _host_batches(trainer, input_pp_rank, output_pp_rank, h2d)
         trainer.train({"bench": dataloader})
     except torch.cuda.OutOfMemoryError as e:
         return _unavailable(f"reference ran out of GPU memory on this config: {str(e)[:160]}")
@@ -131,19 +179,23 @@ def run_reference(args):
     ms = torch.tensor([state["start"].elapsed_time(state["end"])], dtype=torch.float64, device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
-    tokens_per_step = args.mbs * args.seq * args.accum * world
+    tokens_per_step = args.mbs * args.seq * args.accum * dp
     value = tokens_per_step / (ms / args.steps / 1000.0)
+    per_batch = torch.tensor([h2d["bytes"] / max(h2d["batches"], 1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(per_batch, op=dist.ReduceOp.MAX)  # the rank that feeds both inputs and labels (or the larger of the two stages)
+    h2d_per_step = int(per_batch.item()) * args.accum
     if rank == 0:
         out = {
             "metric": "Llama-3-8B training tokens/sec (whole job), bf16, seq 4096" if args.model == "llama3-8b" else f"{args.model} training tokens/sec",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if args.model == "llama3-8b" else None,
+            "higher_is_better": True, "scaling": "weak" if dp == world else "strong", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if args.model == "llama3-8b" else None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference", "tokens_per_sec_per_gpu": value / world,
-            "config": {"model": args.model, "global_batch": args.mbs * args.accum * world, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
-                       "parallelism": f"dp{world}" + ("+zero1" if world > 1 else ""), "fp32_grad_accum": True, "optimizer": "AdamW (torch fused)", "clip_grad": 1.0,
-                       "l2": "inputs larger than L2; no explicit flush"},
+            "config": {"model": args.model, "global_batch": args.mbs * args.accum * dp, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
+                       "parallelism": layout_label(tp, pp, dp, 0), "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
+                       "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush"},
             "clocks": state["clocks"],
-            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4, "note": "the reference's stock loop: tokens drawn on the device by its dummy generator, loss read on the host every step"},
+            "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps, "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": 4,
+                    "note": "the reference's training loop has one mode: inputs copied from pinned host memory every micro-batch, loss read on the host every step; value and e2e are the same measurement"},
             "gpu_launches": 0,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9,
         }

@@ -17,7 +17,7 @@ from nanotron_b200.config import (  # noqa: E402
 
 model_config = Qwen2Config(
     bos_token_id=1, eos_token_id=2, hidden_size=2048, intermediate_size=5632, max_position_embeddings=4096, num_attention_heads=16, num_hidden_layers=24,
-    num_key_value_heads=16, rms_norm_eps=1e-06, rope_theta=1000000.0, tie_word_embeddings=False, vocab_size=151936,
+    num_key_value_heads=4, rms_norm_eps=1e-06, rope_theta=1000000.0, tie_word_embeddings=False, vocab_size=151936,
     moe_config=MoEConfig(num_experts=64, top_k=4, moe_intermediate_size=1408, shared_expert_intermediate_size=5632, enable_shared_expert=True, router_aux_loss_coef=0.01),
 )
 config = Config(

@@ -48,6 +48,12 @@ struct BwdParams {
   int total_q;
   int* status;
   int cp, cp_me, cp_chunk;  // context parallel: group size (0 = off), this rank, tokens per chunk
+  // Split mode: one CTA per (key tile, QUERY head) instead of per (key tile, kv head).  The query heads of a group then add their
+  // dK / dV into fp32 accumulators [total_k, Hkv, 128] (zero-filled by the caller, cast by a post-pass).  Used when key tiles x kv
+  // heads would not fill the GPU (few kv heads per GPU under tensor parallelism, short sequences).
+  int split;
+  float* dk_split;
+  float* dv_split;
 };
 
 constexpr int CP_MAX = 8;
@@ -137,16 +143,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, hk = blockIdx.y;
+  // Grid: x = (sequence, kv head), y = key tile.  CTAs are handed out x first, so all CTAs of key tile 0 start before any of tile 1:
+  // under a causal mask the first key tiles are seen by the most queries, and starting the longest CTAs first keeps the tail of
+  // the launch short (with the key tile in x, late CTAs of tile 0 ran alone at the end).
+  const int group_all = p.num_heads / p.num_kv_heads;
+  const int heads_x = p.split ? p.num_heads : p.num_kv_heads;
+  const int b = blockIdx.x / heads_x, hx = blockIdx.x % heads_x;
+  const int hk = p.split ? hx / group_all : hx;
+  const int h_first = p.split ? hx : hk * group_all;  // first query head this CTA walks
   const bool cpm_on = p.cp > 0;
   const int q_begin = cpm_on ? b * 2 * p.cp_chunk : p.cu_q[b];
   const int q_len = cpm_on ? 2 * p.cp_chunk : p.cu_q[b + 1] - q_begin;
   const int k_begin = cpm_on ? 0 : p.cu_k[b];
   const int k_len = cpm_on ? 2 * p.cp * p.cp_chunk : p.cu_k[b + 1] - k_begin;
-  const int k0 = blockIdx.x * BK;  // first key of the tile: local position, or the global one under context parallelism
+  const int k0 = blockIdx.y * BK;  // first key of the tile: local position, or the global one under context parallelism
   if (k0 >= k_len) return;
   const int shift = cpm_on ? 0 : k_len - q_len;
-  const int group = p.num_heads / p.num_kv_heads;
+  const int group = p.split ? 1 : group_all;  // query heads this CTA walks
   // Runs of 64-query steps that can see at least one key of this tile: one run normally, up to two (one per local chunk) under
   // context parallelism.  seg_q0 = local position of the run's first query, seg_m0 = its position for the masks.
   int seg_q0[2] = {0, 0}, seg_m0[2] = {0, 0}, seg_n[2] = {0, 0};
@@ -226,7 +239,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       for (int n = 0; n < n_steps; n++) {
         const int s = n % QDO_STAGES;
         const uint32_t ph = (n / QDO_STAGES) & 1;
-        const int h = hk * group + n / tiles_per_head;
+        const int h = h_first + n / tiles_per_head;
         int sq0, sm0;
         step_pos(n % tiles_per_head, sq0, sm0);
         const int row = q_begin + sq0;
@@ -319,7 +332,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       for (int n = 0; n < n_steps && ok; n++) {
         int q0, m0;
         step_pos(ti, q0, m0);
-        const int h = hk * group + hi;
+        const int h = h_first + hi;
         if (++ti == tiles_per_head) { ti = 0; hi++; }
         if (!ptx::mbar_wait(&mma_done[n & 1], (n >> 1) & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
@@ -349,7 +362,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // in order, so any arithmetic on the loaded values would stall it for the whole global-memory latency.  The values are
     // turned into (-lse log2 e, delta * scale) when they are stored to shared memory at the top of the next step.
     auto fetch_stats = [&](int hi, int ti, float& raw_lse, float& raw_delta) {
-      const int h = hk * group + hi;
+      const int h = h_first + hi;
       int q0, m0;
       step_pos(ti, q0, m0);
       const int qpos = min(q0 + wg * 32 + lane, q_len - 1);  // rows past the end read the last valid row; masked at use
@@ -444,14 +457,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int which = wg;  // warpgroup 0 writes dK, warpgroup 1 dV
         __nv_bfloat16* dst = (which == 0 ? p.dk : p.dv) + off;
         float* acc = cpm_on ? (which == 0 ? cpb.dk_acc[kv_owner] : cpb.dv_acc[kv_owner]) + acc_off : nullptr;
+        if (p.split) acc = (which == 0 ? p.dk_split : p.dv_split) + (static_cast<int64_t>(k_begin + kpos) * p.num_kv_heads + hk) * HD;
         const uint32_t src = (which == 0 ? tm_dK : tm_dV) + lane_addr;
 #pragma unroll 1
         for (int c = 0; c < 4; c++) {
           uint32_t v[32];
           ptx::tmem_ld_32x32(src + c * 32, v);
           ptx::tmem_ld_wait();
-          if (cpm_on) {
-            // partial sums of the queries of THIS rank: reduce into the key owner's fp32 rows (16-byte reductions, local or over NVLink)
+          if (cpm_on || p.split) {
+            // partial sums (of this rank's queries / of this query head): reduce into fp32 rows (16-byte reductions; under context
+            // parallelism the rows belong to the key owner and may sit across NVLink)
             if (key_valid) {
 #pragma unroll
               for (int u = 0; u < 8; u++)
@@ -473,7 +488,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
       }
-    } else if (n_steps == 0 && key_valid && !cpm_on) {
+    } else if (n_steps == 0 && key_valid && !cpm_on && !p.split) {
       // no query sees these keys: their gradients are zero
       const int64_t off = static_cast<int64_t>(k_begin + kpos) * p.dk_stride_t + static_cast<int64_t>(hk) * HD;
       for (int c = 0; c < HD; c += 8) {
@@ -520,10 +535,12 @@ bool make_map(CUtensorMap* m, const void* ptr, int64_t tokens, int heads, int64_
 // dout / out: [total_q, Hq, 128] contiguous.  q, k, v: strided like the forward (v shares k's strides).  delta: fp32 [Hq, total_q]
 // scratch; dq_acc: fp32 [total_q, Hq, 128] zero-filled scratch.  dq / dk / dv: bf16 outputs with token strides dq_stride_t /
 // dk_stride_t (head stride 128), e.g. views of one fused [T, Hq + 2 Hkv, 128] buffer.
-NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, float* dq_acc,
-                                  void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int max_seqlen_k, int total_q,
-                                  int total_k, int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
-                                  int64_t dq_stride_t, int64_t dk_stride_t, float softmax_scale, int causal, int window, int* status, cudaStream_t stream) {
+// dkv_split: nullptr, or fp32 [2, total_k, Hkv, 128] zero-filled scratch that selects the split mode (one CTA per key tile and QUERY
+// head; see BwdParams::split).  ntb_flash_attn_bwd_wants_split says when that pays.
+static int flash_attn_bwd_impl(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, float* dq_acc,
+                               void* dq, void* dk, void* dv, float* dkv_split, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int max_seqlen_k, int total_q,
+                               int total_k, int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
+                               int64_t dq_stride_t, int64_t dk_stride_t, float softmax_scale, int causal, int window, int* status, cudaStream_t stream) {
   if (!bwd_get_encode() || batch <= 0 || total_q <= 0 || total_k <= 0 || num_heads % num_kv_heads) return NTB_ERR_ARG;
   if ((q_stride_t | q_stride_h | k_stride_t | k_stride_h | dq_stride_t | dk_stride_t) % 8) return NTB_ERR_ARG;
   CUtensorMap tq, tdo, tk, tv;
@@ -556,7 +573,11 @@ NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k
   p.dk_stride_t = dk_stride_t;
   p.total_q = total_q;
   p.status = status;
-  dim3 grid((max_seqlen_k + BK - 1) / BK, num_kv_heads, batch);
+  p.split = dkv_split != nullptr;
+  p.dk_split = dkv_split;
+  p.dv_split = dkv_split ? dkv_split + static_cast<int64_t>(total_k) * num_kv_heads * HD : nullptr;
+  dim3 grid((p.split ? num_heads : num_kv_heads) * batch, (max_seqlen_k + BK - 1) / BK, 1);
+  if (grid.y > 65535) return NTB_ERR_ARG;
   p.cp = 0;
   p.cp_me = 0;
   p.cp_chunk = 0;
@@ -566,7 +587,38 @@ NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k
   if (rc) return rc;
   const int64_t n8 = static_cast<int64_t>(total_q) * num_heads * HD / 8;
   cast_dq_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), total_q, num_heads, dq_stride_t);
+  if (p.split) {
+    const int64_t k8 = static_cast<int64_t>(total_k) * num_kv_heads * HD / 8;
+    cast_dq_kernel<<<(unsigned)((k8 + 255) / 256), 256, 0, stream>>>(p.dk_split, reinterpret_cast<__nv_bfloat16*>(dk), total_k, num_kv_heads, dk_stride_t);
+    cast_dq_kernel<<<(unsigned)((k8 + 255) / 256), 256, 0, stream>>>(p.dv_split, reinterpret_cast<__nv_bfloat16*>(dv), total_k, num_kv_heads, dk_stride_t);
+  }
   return ntb_check_launch();
+}
+
+NTB_EXPORT int ntb_flash_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, float* dq_acc,
+                                  void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int max_seqlen_k, int total_q,
+                                  int total_k, int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
+                                  int64_t dq_stride_t, int64_t dk_stride_t, float softmax_scale, int causal, int window, int* status, cudaStream_t stream) {
+  return flash_attn_bwd_impl(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, nullptr, cu_q, cu_k, batch, max_seqlen_q, max_seqlen_k, total_q, total_k, num_heads,
+                             num_kv_heads, q_stride_t, q_stride_h, k_stride_t, k_stride_h, dq_stride_t, dk_stride_t, softmax_scale, causal, window, status, stream);
+}
+
+// 1 when (key tiles x kv heads x sequences) CTAs would leave most of the GPU idle and splitting the query heads of a group over
+// CTAs (with fp32 dK / dV accumulation) gives the launch enough parallelism.
+NTB_EXPORT int ntb_flash_attn_bwd_wants_split(int batch, int max_seqlen_k, int num_heads, int num_kv_heads) {
+  if (num_heads == num_kv_heads) return 0;
+  const int64_t ctas = static_cast<int64_t>((max_seqlen_k + BK - 1) / BK) * num_kv_heads * batch;
+  return ctas < 148 + 74 ? 1 : 0;
+}
+
+NTB_EXPORT int ntb_flash_attn_bwd_split(const void* dout, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta, float* dq_acc,
+                                        void* dq, void* dk, void* dv, float* dkv_split, const int* cu_q, const int* cu_k, int batch, int max_seqlen_q, int max_seqlen_k,
+                                        int total_q, int total_k, int num_heads, int num_kv_heads, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t,
+                                        int64_t k_stride_h, int64_t dq_stride_t, int64_t dk_stride_t, float softmax_scale, int causal, int window, int* status,
+                                        cudaStream_t stream) {
+  if (dkv_split == nullptr || (reinterpret_cast<uintptr_t>(dkv_split) & 15)) return NTB_ERR_ARG;
+  return flash_attn_bwd_impl(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, dkv_split, cu_q, cu_k, batch, max_seqlen_q, max_seqlen_k, total_q, total_k, num_heads,
+                             num_kv_heads, q_stride_t, q_stride_h, k_stride_t, k_stride_h, dq_stride_t, dk_stride_t, softmax_scale, causal, window, status, stream);
 }
 
 // Context-parallel backward (zig-zag layout, causal).  k_ptrs / v_ptrs: every rank's K / V as in ntb_flash_attn_fwd_cp; dk_acc_ptrs /
@@ -620,7 +672,11 @@ NTB_EXPORT int ntb_flash_attn_bwd_cp(const void* dout, const void* q, const uint
   p.cp = cp;
   p.cp_me = me;
   p.cp_chunk = chunk;
-  dim3 grid(2 * cp * chunk / BK, num_kv_heads, batch);
+  p.split = 0;
+  p.dk_split = nullptr;
+  p.dv_split = nullptr;
+  dim3 grid(num_kv_heads * batch, 2 * cp * chunk / BK, 1);
+  if (grid.y > 65535) return NTB_ERR_ARG;
   flash_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tq, tdo, cpb.k[me], cpb.v[me], p, cpb);
   int rc = ntb_check_launch();
   if (rc) return rc;

@@ -10,6 +10,7 @@ import torch
 
 _HAS = {"fwd": False, "fwd2": False, "bwd": False}
 FWD_VARIANT = {"kernel": "two_tile"}  # "two_tile" | "one_tile"
+BWD_SPLIT = {"mode": "auto"}  # "auto" (by launch size) | "on" | "off": one backward CTA per query head instead of per kv head
 
 
 def set_forward_variant(name: str):
@@ -30,6 +31,10 @@ def declare(L):
     if _HAS["bwd"]:
         L.ntb_flash_attn_bwd.restype = c_int
         L.ntb_flash_attn_bwd.argtypes = [c_void_p] * 13 + [c_int] * 7 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
+        L.ntb_flash_attn_bwd_split.restype = c_int
+        L.ntb_flash_attn_bwd_split.argtypes = [c_void_p] * 14 + [c_int] * 7 + [c_int64] * 6 + [c_float, c_int, c_int, c_void_p, c_void_p]
+        L.ntb_flash_attn_bwd_wants_split.restype = c_int
+        L.ntb_flash_attn_bwd_wants_split.argtypes = [c_int] * 4
 
 
 def _ok(t: torch.Tensor) -> bool:
@@ -83,12 +88,21 @@ def flash_attn_bwd(dout, q, k, v, out, lse, cu_q, cu_k, max_q: int, max_k: int, 
     delta = torch.empty((Hq, Tq), dtype=torch.float32, device=q.device)
     cu_q = cu_q.to(torch.int32)
     cu_k = cu_k.to(torch.int32)
+    L = native.lib()
+    batch = cu_q.numel() - 1
+    split = BWD_SPLIT["mode"] == "on" or (BWD_SPLIT["mode"] == "auto" and L.ntb_flash_attn_bwd_wants_split(batch, int(max_k), Hq, Hkv) == 1)
+    tail = (
+        cu_q.data_ptr(), cu_k.data_ptr(), batch, int(max_q), int(max_k), Tq, Tk, Hq, Hkv,
+        q.stride(0), q.stride(1), k.stride(0), k.stride(1), dq.stride(0), dk.stride(0), float(scale), int(bool(causal)), int(window or 0),
+        status_word(q.device).data_ptr(), torch.cuda.current_stream(q.device).cuda_stream,
+    )
+    head = (dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr())
     with torch.cuda.device(q.device):
-        rc = native.lib().ntb_flash_attn_bwd(
-            dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-            cu_q.data_ptr(), cu_k.data_ptr(), cu_q.numel() - 1, int(max_q), int(max_k), Tq, Tk, Hq, Hkv,
-            q.stride(0), q.stride(1), k.stride(0), k.stride(1), dq.stride(0), dk.stride(0), float(scale), int(bool(causal)), int(window or 0),
-            status_word(q.device).data_ptr(), torch.cuda.current_stream(q.device).cuda_stream,
-        )
+        if split and Hq != Hkv:
+            # too few (key tile, kv head) pairs to fill the GPU: one CTA per query head, dK / dV summed in fp32 scratch
+            dkv_acc = torch.zeros((2, Tk, Hkv, D), dtype=torch.float32, device=q.device)
+            rc = L.ntb_flash_attn_bwd_split(*head, dkv_acc.data_ptr(), *tail)
+        else:
+            rc = L.ntb_flash_attn_bwd(*head, *tail)
     native._check(rc, "flash_attn_bwd")
     return dq, dk, dv

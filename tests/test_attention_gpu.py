@@ -76,12 +76,16 @@ def test_flash_fwd_sliding_window(fwd_variant):
     torch.testing.assert_close(out.float(), exp.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("split", ["off", "on"])
 @pytest.mark.parametrize("lens,Hq,Hkv,causal", [([128], 1, 1, True), ([256], 2, 1, True), ([200, 56, 333], 4, 2, True), ([384, 100], 2, 2, False), ([1024], 8, 2, True)])
-def test_flash_bwd_matches_oracle(lens, Hq, Hkv, causal):
+def test_flash_bwd_matches_oracle(lens, Hq, Hkv, causal, split, monkeypatch):
+    """``split``: one backward CTA per kv head (dK / dV in tensor memory to the end) or per query head (fp32 accumulation across the
+    query heads of a group, what small launches select by themselves)."""
     from nanotron_b200 import ops
-    from nanotron_b200.ops import native, native_gemm
+    from nanotron_b200.ops import native, native_attn, native_gemm
 
     native.lib()
+    monkeypatch.setitem(native_attn.BWD_SPLIT, "mode", split)
     T = sum(lens)
     q, k, v = _qkv(T, Hq, Hkv, seed=5)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
