@@ -30,6 +30,30 @@ class MLP(_q.Qwen2MLP):
     pass
 
 
+def padding_cu_seqlens(sequence_mask: torch.Tensor) -> Optional[torch.Tensor]:
+    """Document boundaries that keep padding out of the attention of real tokens, for batches padded on the LEFT (generation,
+    evaluation): every padding token becomes a document of its own and the real tokens of a row form one document.  Returns None
+    for a mask without padding.  Right padding needs nothing (causal masking already hides it from the real tokens), which is why
+    training never calls this.  The result is cached on the mask tensor: every layer of a stage asks for the same one."""
+    cached = getattr(sequence_mask, "_ntb_padding_cu", False)
+    if cached is not False:
+        return cached
+    m = sequence_mask.bool()
+    if bool(m.all()):
+        cu = None
+    else:
+        b, s = m.shape
+        prev = torch.cat([torch.zeros(b, 1, dtype=torch.bool, device=m.device), m[:, :-1]], dim=1)
+        starts = (~m) | (~prev)  # a padding token, or the first token after padding / of the row
+        idx = torch.nonzero(starts.reshape(-1), as_tuple=False).flatten()
+        cu = torch.cat([idx, torch.tensor([b * s], device=m.device)]).to(torch.int32)
+    try:
+        sequence_mask._ntb_padding_cu = cu
+    except AttributeError:
+        pass
+    return cu
+
+
 class CausalSelfAttention(_q.Qwen2Attention):
     """Adds a KV-cache decode path (used by ``nanotron_b200.generation``) on top of the training path."""
 
@@ -40,6 +64,8 @@ class CausalSelfAttention(_q.Qwen2Attention):
         if store is not None:
             return self._forward_with_cache(hidden_states, sequence_mask, store)
         position_ids = (sequence_mask.long().cumsum(-1) - 1).clamp_(min=0)
+        if cu_seqlens is None and not self.training:
+            cu_seqlens = padding_cu_seqlens(sequence_mask)
         out = super().forward(hidden_states, position_ids, cu_seqlens)
         return {"hidden_states": out["hidden_states"], "sequence_mask": sequence_mask}
 

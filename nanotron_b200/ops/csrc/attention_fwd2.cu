@@ -504,6 +504,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn2 f2_get_encode() {
+  ntb_bind_context_to_thread();
   static EncodeTiledFn2 fn = nullptr;
   if (!fn) {
     void* ptr = nullptr;

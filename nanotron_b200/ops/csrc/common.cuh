@@ -12,6 +12,18 @@
 
 #define NTB_EXPORT extern "C" __attribute__((visibility("default")))
 
+// cuTensorMapEncodeTiled is a driver-API call and needs a CUDA context current on the CALLING THREAD.  The runtime binds the
+// device's primary context to a thread at its first runtime call that needs one; a fresh thread whose first CUDA work is one
+// of the tensor-map builders below has none yet (seen with autograd worker threads on device 0, where the framework skips
+// cudaSetDevice because device 0 is already the thread's default): the encode call then fails and the entry point would
+// report the arguments as unsupported.  Binding once per thread costs two runtime calls.
+static inline void ntb_bind_context_to_thread() {
+  static thread_local bool bound = false;
+  if (bound) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess && cudaFree(nullptr) == cudaSuccess) bound = true;
+}
+
 static inline int ntb_check_launch() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? NTB_OK : NTB_ERR_LAUNCH;

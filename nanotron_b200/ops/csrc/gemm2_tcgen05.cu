@@ -322,6 +322,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn p_get_encode() {
+  ntb_bind_context_to_thread();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -396,19 +397,25 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
 
 // Same contract as ntb_gemm_bf16 (gemm_tcgen05.cu); additionally M-major / N-major operands need M % 128 == 0 / N % 128 == 0 is NOT
 // required: edges are clipped by TMA.  a_mn / b_mn: 0 = K-major, 1 = MN-major.  out_mode: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate.
+// Which argument check rejected the last ntb_gemm2_bf16 call of this thread (0: none; for error messages).
+static thread_local int g_p_reject = 0;
+NTB_EXPORT int ntb_gemm2_last_reject() { return g_p_reject; }
+
 NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_mode,
                               int* status, int num_sms, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || !p_get_encode()) return NTB_ERR_ARG;
-  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
-  if (a_mn ? (lda % 64 || M % 64) : (lda % 8)) return NTB_ERR_ARG;
-  if (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) return NTB_ERR_ARG;
-  if (out_mode == P_OUT_BF16 ? (ldd % 8) : (ldd % 4)) return NTB_ERR_ARG;
+  g_p_reject = 0;
+#define NTB_P_REJECT(code) do { g_p_reject = (code); return NTB_ERR_ARG; } while (0)
+  if (M <= 0 || N <= 0 || K <= 0) NTB_P_REJECT(1);
+  if (!p_get_encode()) NTB_P_REJECT(2);
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) NTB_P_REJECT(3);
+  if (a_mn ? (lda % 64 || M % 64) : (lda % 8)) NTB_P_REJECT(4);
+  if (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) NTB_P_REJECT(5);
+  if (out_mode == P_OUT_BF16 ? (ldd % 8) : (ldd % 4)) NTB_P_REJECT(6);
   if (num_sms <= 1) num_sms = 148;
   CUtensorMap ta, tb, td;
-  bool ok = a_mn ? p_map_mnmajor(&ta, a, M, K, lda) : p_map_kmajor(&ta, a, M, K, lda);
-  ok = ok && (b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb));
-  ok = ok && p_map_out(&td, d, M, N, ldd, out_mode != P_OUT_BF16);
-  if (!ok) return NTB_ERR_ARG;
+  if (!(a_mn ? p_map_mnmajor(&ta, a, M, K, lda) : p_map_kmajor(&ta, a, M, K, lda))) NTB_P_REJECT(7);
+  if (!(b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb))) NTB_P_REJECT(8);
+  if (!p_map_out(&td, d, M, N, ldd, out_mode != P_OUT_BF16)) NTB_P_REJECT(9);
 #define NTB_P_CASE(AM, BM, OM) \
   if (a_mn == AM && b_mn == BM && out_mode == OM) return p_launch<AM != 0, BM != 0, OM>(ta, tb, td, M, N, K, status, num_sms, stream);
   NTB_P_CASE(0, 0, 0) NTB_P_CASE(0, 0, 1) NTB_P_CASE(0, 0, 2)
@@ -416,5 +423,6 @@ NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int 
   NTB_P_CASE(1, 1, 0) NTB_P_CASE(1, 1, 1) NTB_P_CASE(1, 1, 2)
   NTB_P_CASE(1, 0, 0) NTB_P_CASE(1, 0, 1) NTB_P_CASE(1, 0, 2)
 #undef NTB_P_CASE
-  return NTB_ERR_ARG;
+  NTB_P_REJECT(10);
+#undef NTB_P_REJECT
 }

@@ -386,6 +386,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode() {
+  ntb_bind_context_to_thread();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -92,7 +92,8 @@ def _launch(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode):
     with torch.cuda.device(dev):
         rc = fn(a.data_ptr(), b.data_ptr(), d.data_ptr(), M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(dev).data_ptr(), _sms(dev), torch.cuda.current_stream(dev).cuda_stream)
     if rc != 0:
-        what = (f"gemm_tcgen05[{VARIANT['kernel']}] M={M} N={N} K={K} lda={lda} ldb={ldb} ldd={ldd} a_mn={a_mn} b_mn={b_mn} out_mode={out_mode} "
+        reject = L.ntb_gemm2_last_reject() if hasattr(L, "ntb_gemm2_last_reject") else -1
+        what = (f"gemm_tcgen05[{VARIANT['kernel']}] check#{reject} M={M} N={N} K={K} lda={lda} ldb={ldb} ldd={ldd} a_mn={a_mn} b_mn={b_mn} out_mode={out_mode} "
                 f"a={tuple(a.shape)}/{a.stride()}/{a.dtype}/ptr%16={a.data_ptr() % 16} b={tuple(b.shape)}/{b.stride()}/{b.dtype}/ptr%16={b.data_ptr() % 16} "
                 f"d={tuple(d.shape)}/{d.stride()}/{d.dtype}/ptr%16={d.data_ptr() % 16}")
         native._check(rc, what)

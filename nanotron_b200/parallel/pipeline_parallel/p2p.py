@@ -245,33 +245,35 @@ class P2P:
         return Ticket(buf, [work], False)
 
     # ------------------------------------------------------------------ reference-style API (headers, forward lane)
-    def _isend(self, tensor: torch.Tensor, to_rank: int, tag: int) -> List[dist.Work]:
+    def _isend(self, tensor: torch.Tensor, to_rank: int, tag: int, static: Optional[bool] = None) -> List[dist.Work]:
+        static = self._static if static is None else static
         meta = P2PTensorMetaData.from_tensor(tensor)
         group = lane_group(self.pg, FWD)
         dst = dist.get_global_rank(self.pg, to_rank)
         key = ("send", to_rank, tag)
-        if not (self._static and self._tag_cache.get(key) == meta):
-            if self._static and key in self._tag_cache:
+        if not (static and self._tag_cache.get(key) == meta):
+            if static and key in self._tag_cache:
                 raise RuntimeError(f"p2p static-shape contract broken for peer {to_rank} tag {tag}: {self._tag_cache[key]} -> {meta}")
             dist.send(meta.to_header(self.device), dst=dst, group=group, tag=tag)
-            if self._static:
+            if static:
                 self._tag_cache[key] = meta
         payload = _wire_view(tensor.detach()).contiguous()
         work = dist.isend(payload, dst=dst, group=group, tag=tag)
         self._park(work, payload)
         return [work]
 
-    def _irecv(self, from_rank: int, tag: int) -> Tuple[torch.Tensor, List[dist.Work]]:
+    def _irecv(self, from_rank: int, tag: int, static: Optional[bool] = None) -> Tuple[torch.Tensor, List[dist.Work]]:
+        static = self._static if static is None else static
         group = lane_group(self.pg, FWD)
         src = dist.get_global_rank(self.pg, from_rank)
         key = ("recv", from_rank, tag)
-        if self._static and key in self._tag_cache:
+        if static and key in self._tag_cache:
             meta = self._tag_cache[key]
         else:
             header = torch.empty(HEADER_LEN, dtype=torch.long, device=self.device)
             dist.recv(header, src=src, group=group, tag=tag)
             meta = P2PTensorMetaData.from_header(header)
-            if self._static:
+            if static:
                 self._tag_cache[key] = meta
         buf = meta.create_empty_storage(self.device)
         work = dist.irecv(_wire_view(buf), src=src, group=group, tag=tag)
@@ -279,26 +281,27 @@ class P2P:
             buf.requires_grad_(True)
         return buf, [work]
 
-    def isend_tensors(self, tensors: List[torch.Tensor], to_rank: int, tag: int = 0) -> List[dist.Work]:
+    def isend_tensors(self, tensors: List[torch.Tensor], to_rank: int, tag: int = 0, static: Optional[bool] = None) -> List[dist.Work]:
+        """``static``: None follows ``expect_static``; False always sends the header (shapes that change from call to call)."""
         futures = []
         for t in tensors:
-            futures.extend(self._isend(t, to_rank, tag))
+            futures.extend(self._isend(t, to_rank, tag, static))
         return futures
 
-    def irecv_tensors(self, num_tensors: int, from_rank: int, tag: int = 0) -> Tuple[List[torch.Tensor], List[dist.Work]]:
+    def irecv_tensors(self, num_tensors: int, from_rank: int, tag: int = 0, static: Optional[bool] = None) -> Tuple[List[torch.Tensor], List[dist.Work]]:
         tensors, futures = [], []
         for _ in range(num_tensors):
-            t, f = self._irecv(from_rank, tag)
+            t, f = self._irecv(from_rank, tag, static)
             tensors.append(t)
             futures.extend(f)
         return tensors, futures
 
-    def send_tensors(self, tensors: List[torch.Tensor], to_rank: int, tag: int = 0):
-        for f in self.isend_tensors(tensors, to_rank, tag):
+    def send_tensors(self, tensors: List[torch.Tensor], to_rank: int, tag: int = 0, static: Optional[bool] = None):
+        for f in self.isend_tensors(tensors, to_rank, tag, static):
             f.wait()
 
-    def recv_tensors(self, num_tensors: int, from_rank: int, tag: int = 0) -> List[torch.Tensor]:
-        tensors, futures = self.irecv_tensors(num_tensors, from_rank, tag)
+    def recv_tensors(self, num_tensors: int, from_rank: int, tag: int = 0, static: Optional[bool] = None) -> List[torch.Tensor]:
+        tensors, futures = self.irecv_tensors(num_tensors, from_rank, tag, static)
         for f in futures:
             f.wait()
         return tensors

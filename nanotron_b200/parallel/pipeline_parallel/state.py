@@ -151,10 +151,10 @@ class PipelineEvalBatchState(PipelineBatchState):
         self._p2ps: List[P2P] = []
 
     def send_activation(self, activation: torch.Tensor, to_rank: int, p2p: P2P) -> None:
-        p2p.send_tensors([activation], to_rank=to_rank)
+        p2p.send_tensors([activation], to_rank=to_rank, static=False)
 
     def recv_activation(self, from_rank: int, p2p: P2P) -> torch.Tensor:
-        return p2p.recv_tensors(num_tensors=1, from_rank=from_rank)[0].requires_grad_(False)
+        return p2p.recv_tensors(num_tensors=1, from_rank=from_rank, static=False)[0].requires_grad_(False)
 
     def register_activation_requiring_backward(self, activation: torch.Tensor) -> None:
         pass

@@ -1,0 +1,92 @@
+"""The examples that show the extension API run end to end on CPU: a user-defined dataloader, and trainers that subclass
+``DistributedTrainer`` with their own model / config classes."""
+import importlib.util
+import os
+import sys
+
+import torch
+
+from helpers import make_config, run_distributed, single_process_env, tiny_llama_config
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(path, name):
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, path))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _custom_dataloader_run(out_file):
+    from nanotron_b200.trainer import DistributedTrainer
+
+    ex = _load("examples/custom_dataloader/run_train.py", "custom_dl_example")
+    cfg = make_config(tiny_llama_config(vocab_size=64), dp=2, seq=32, mbs=2, accum=1, steps=30, lr=3e-3)
+    cfg.logging.iteration_step_info_interval = 1
+    t = DistributedTrainer(cfg)
+    losses = []
+
+    orig = t.train_step_logs
+
+    def record(outputs, loss_avg, z_loss_avg=None):
+        if loss_avg is not None:
+            losses.append(float(loss_avg))
+        return orig(outputs=outputs, loss_avg=loss_avg, z_loss_avg=z_loss_avg)
+
+    t.train_step_logs = record
+    loader = ex.build_dataloader(t, num_steps=30, seed=1)
+    # the two data-parallel ranks must see different samples
+    first = next(iter(loader))["input_ids"]
+    import nanotron_b200.distributed as dist
+
+    gathered = [torch.empty_like(torch.as_tensor(first)) for _ in range(2)]
+    dist.all_gather(gathered, torch.as_tensor(first).contiguous(), group=t.parallel_context.dp_pg)
+    assert not torch.equal(gathered[0], gathered[1])
+    t.train({"stable": ex.build_dataloader(t, num_steps=30, seed=1)})
+    if dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save(losses, out_file)
+    t.parallel_context.destroy()
+
+
+def test_custom_dataloader_example_trains(tmp_path):
+    out = str(tmp_path / "losses.pt")
+    run_distributed(_custom_dataloader_run, 2, out_file=out)
+    losses = torch.load(out)
+    assert len(losses) == 30
+    assert losses[-1] < losses[0] - 0.25, losses  # counting sequences are learnable
+
+
+def _doremi_run(out_file):
+    sys.path.insert(0, os.path.join(ROOT, "examples", "doremi"))
+    import doremi as dr
+    import nanotron_b200.distributed as dist
+
+    train = _load("examples/doremi/train_doremi.py", "train_doremi_example")
+    t = dr.DoReMiTrainer(os.path.join(ROOT, "examples", "doremi", "config_tiny_doremi.yaml"))  # YAML with the extra section
+    assert isinstance(t.config, dr.DoReMiConfig) and t.config.doremi.domain_names == ["counting", "noise"]
+    assert isinstance(t.unwrapped_model, dr.LlamaForDoReMiTraining) and isinstance(t.ref_model, dr.LlamaReferenceForDoReMi)
+    assert all(not p.requires_grad for p in t.ref_model.parameters())
+    # proxy and reference start from different weights
+    a = next(iter(t.unwrapped_model.parameters())).detach().float()
+    b = next(iter(t.ref_model.parameters())).detach().float()
+    assert not torch.equal(a, b)
+    t.config.tokens.train_steps = 25
+    t.train({"proxy": train.domain_batches(t, seed=7)})
+    w = t.doremi_context.domain_weights
+    # same weights on both data-parallel ranks, still a distribution, moved away from uniform
+    both = [torch.empty_like(w) for _ in range(2)]
+    dist.all_gather(both, w.contiguous(), group=t.parallel_context.dp_pg)
+    torch.testing.assert_close(both[0], both[1])
+    assert abs(float(w.sum()) - 1.0) < 1e-5 and float((w - 0.5).abs().max()) > 1e-3, w
+    if dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save({"weights": w.cpu(), "n_updates": len(t.doremi_context.history)}, out_file)
+    t.parallel_context.destroy()
+
+
+def test_doremi_trainer_subclass_example(tmp_path):
+    out = str(tmp_path / "doremi.pt")
+    run_distributed(_doremi_run, 2, out_file=out)
+    res = torch.load(out)
+    assert res["n_updates"] == 26  # the initial weights + one update per step
