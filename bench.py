@@ -190,6 +190,7 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     ops.set_gemm(args.gemm)
     ops.set_attention(args.attention)
+    ops.set_linear(args.linear)
     from nanotron_b200.ops import native_gemm
 
     native_gemm.set_variant(args.gemm_variant)
@@ -263,7 +264,7 @@ def run_native(args):
             "metric": "Llama-3-8B training tokens/sec (whole job), bf16, seq 4096" if (args.model == "llama3-8b" and args.seq == 4096) else f"{args.config} training tokens/sec (whole job), bf16, seq {args.seq}",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak" if dp == world else "strong", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if (args.model == "llama3-8b" and args.seq == 4096) else None,
-            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "dtype": "bf16" if args.linear == "bf16" else "fp8 (block-scaled linears; bf16 elsewhere)", "data": "synthetic uniform-random tokens, random-init weights",
             "tokens_per_sec_per_gpu": value / world, "model_tflops_per_gpu": tflops_per_gpu, "mfu_of_measured_sustained_peak": tflops_per_gpu / peak,
             "loss": loss_val, "impl": "nanotron_b200",
             "config": {
@@ -273,7 +274,7 @@ def run_native(args):
                 "pp_p2p": "NCCL send/recv on one lane per direction, asynchronous" if pp > 1 else "n/a",
                 "dp_step": "in-tree NVLink kernels (reduce-scatter + AdamW + all-gather)" if getattr(trainer, "fused_dp", None) is not None else "NCCL", "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
                 "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush",
-                "gemm": ops._GEMM, "gemm_kernel": args.gemm_variant, "attention": ops._ATTN,
+                "gemm": ops._GEMM, "gemm_kernel": args.gemm_variant, "attention": ops._ATTN, "linear": ops.get_linear(),
             },
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * args.mbs * args.seq * 8 * args.accum, "d2h_bytes_per_step": 4},
@@ -301,6 +302,7 @@ def main():
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size, laid over the dp axis (-1: dp)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "cublas"], help="auto / tcgen05: every linear-layer product on the in-tree tcgen05 kernels; cublas: library GEMMs (wgrad then needs a separate fp32 add)")
     ap.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"], help="auto / native: the in-tree tcgen05 flash-attention kernels; sdpa: library attention (comparison runs)")
+    ap.add_argument("--linear", default="bf16", choices=["bf16", "fp8"], help="fp8: block-scaled fp8 operands (e4m3 forward, e5m2 gradients) for the linear-layer products")
     ap.add_argument("--gemm-variant", default="pair", choices=["single", "pair"], help="in-tree GEMM kernel: one CTA per 128x256 tile, or CTA pairs (cta_group::2) per 256x256 tile")
     ap.add_argument("--layout", default=None, choices=["model", "dp"], help="model: tp / pp by GPU count (1: none, 2: tp2, 4: tp4, 8: tp4 x pp2), same global batch at every N; dp: data parallel over all GPUs with ZeRO-1")
     ap.add_argument("--tp", type=int, default=None, help="tensor-parallel size (sequence-parallel mode), overrides --layout; dp = gpus / (tp * pp)")

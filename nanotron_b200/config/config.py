@@ -243,11 +243,14 @@ class ProfilerArgs:
 class KernelArgs:
     """Which implementation each hot op uses.  "auto": in-tree sm_100a kernels on CUDA, PyTorch math on CPU.
     "torch": always the PyTorch oracle.  ``gemm``: "cublas" routes plain GEMMs to the library, "tcgen05" to the
-    in-tree kernel."""
+    in-tree kernel.  ``attention``: "auto" / "native" run the in-tree flash-attention kernels, "sdpa" the library kernel."""
 
     ops: str = "auto"
     gemm: str = "auto"
     attention: str = "auto"
+    # operand precision of the linear-layer products: "bf16", or "fp8" = block-scaled fp8 (1 x 128 / 128 x 128 blocks, e4m3
+    # forward, e5m2 gradients) for every tensor-parallel linear whose dimensions are multiples of 128
+    linear: str = "bf16"
 
 
 @dataclass

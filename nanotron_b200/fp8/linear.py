@@ -33,43 +33,69 @@ def _transpose_blocks(t):
     return FP8BlockTensor(t.data.t().contiguous(), t.scale.t().contiguous(), t.block)
 
 
+def shapes_ok(x2: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Block scaling needs every dimension of the product to be a multiple of the 128-element block."""
+    return x2.dim() == 2 and weight.dim() == 2 and x2.shape[0] % 128 == 0 and x2.shape[1] % 128 == 0 and weight.shape[0] % 128 == 0 and x2.shape[1] == weight.shape[1]
+
+
+def fp8_forward(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """y = dq(q_e4m3^{1x128}(x)) @ dq(q_e4m3^{128x128}(W))^T."""
+    xq = quantize_1x128(x2, torch.float8_e4m3fn)
+    wq = quantize_128x128(weight, torch.float8_e4m3fn)
+    if _native_fp8(x2, weight):
+        from nanotron_b200.ops import native
+
+        return native.gemm_fp8_blockscaled(xq, wq)
+    return torch.nn.functional.linear(dequantize(xq, x2.dtype), dequantize(wq, weight.dtype))
+
+
+def fp8_dgrad(go: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """dx = dq(q_e5m2^{1x128}(dy)) @ dq(q_e4m3^{128x128}(W))."""
+    go = go.contiguous()
+    if go.is_cuda and go.dtype == torch.bfloat16 and _native_fp8(go, weight.t()):
+        from nanotron_b200.ops import native
+
+        goq = quantize_1x128(go, torch.float8_e5m2)
+        wq_t = _transpose_blocks(quantize_128x128(weight, torch.float8_e4m3fn))  # [K, N]: K-major for the dgrad reduction over N
+        return native.gemm_fp8_blockscaled(goq, wq_t)
+    goq = dequantize(quantize_1x128(go, torch.float8_e5m2), go.dtype)
+    wq = dequantize(quantize_128x128(weight, torch.float8_e4m3fn), weight.dtype)
+    return goq.matmul(wq)
+
+
+def fp8_wgrad(go: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
+    """dW = dy^T x with both operands quantised in 1 x 128 blocks along the token dimension (the reduction dimension of this
+    product).  Accumulates into ``weight.main_grad`` (fp32) when there is one and then returns None."""
+    go = go.contiguous()
+    main_grad = getattr(weight, "main_grad", None)
+    if go.is_cuda and go.dtype == torch.bfloat16 and _native_fp8(x2, weight):
+        from nanotron_b200.ops import native
+
+        go_t = quantize_1x128(go.t().contiguous(), torch.float8_e5m2)  # [N, M], blocks along the tokens
+        x_t = quantize_1x128(x2.t().contiguous(), torch.float8_e4m3fn)  # [K, M]
+        if main_grad is not None:
+            native.gemm_fp8_blockscaled(go_t, x_t, out=main_grad, accumulate_fp32=True)
+            return None
+        return native.gemm_fp8_blockscaled(go_t, x_t)
+    go_t = dequantize(quantize_1x128(go.t().contiguous(), torch.float8_e5m2), go.dtype)
+    x_t = dequantize(quantize_1x128(x2.t().contiguous(), torch.float8_e4m3fn), x2.dtype)
+    dw = go_t.matmul(x_t.t())
+    if main_grad is not None:
+        main_grad.add_(dw)
+        return None
+    return dw
+
+
 class _FP8Matmul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, weight):
-        xq = quantize_1x128(x2, torch.float8_e4m3fn)
-        wq = quantize_128x128(weight, torch.float8_e4m3fn)
         ctx.save_for_backward(x2, weight)
-        if _native_fp8(x2, weight):
-            from nanotron_b200.ops import native
-
-            return native.gemm_fp8_blockscaled(xq, wq)
-        return ops.linear_forward(dequantize(xq, x2.dtype), dequantize(wq, weight.dtype))
+        return fp8_forward(x2, weight)
 
     @staticmethod
     def backward(ctx, grad_out):
         x2, weight = ctx.saved_tensors
-        go = grad_out.contiguous()
-        if _native_fp8(x2, weight) and go.dtype == torch.bfloat16:
-            from nanotron_b200.ops import native
-
-            goq = quantize_1x128(go, torch.float8_e5m2)
-            wq_t = _transpose_blocks(quantize_128x128(weight, torch.float8_e4m3fn))  # [K, N]: K-major for the dgrad reduction over N
-            dx = native.gemm_fp8_blockscaled(goq, wq_t)
-            go_t = quantize_1x128(go.t().contiguous(), torch.float8_e5m2)  # [N, M], blocks along the tokens
-            x_t = quantize_1x128(x2.t().contiguous(), torch.float8_e4m3fn)  # [K, M]
-            main_grad = getattr(weight, "main_grad", None)
-            if main_grad is not None:
-                native.gemm_fp8_blockscaled(go_t, x_t, out=main_grad, accumulate_fp32=True)
-                return dx, None
-            return dx, native.gemm_fp8_blockscaled(go_t, x_t)
-        goq = dequantize(quantize_1x128(go, torch.float8_e5m2), go.dtype)
-        wq = dequantize(quantize_128x128(weight, torch.float8_e4m3fn), weight.dtype)
-        dx = ops.linear_dgrad(goq, wq)
-        # wgrad contracts over tokens: quantise both operands in blocks along that dimension (transposed 1x128)
-        go_t = dequantize(quantize_1x128(go.t().contiguous(), torch.float8_e5m2), go.dtype).t()
-        x_t = dequantize(quantize_1x128(x2.t().contiguous(), torch.float8_e4m3fn), x2.dtype).t()
-        dw = ops.linear_wgrad(go_t.contiguous(), x_t.contiguous(), weight)
-        return dx, dw
+        return fp8_dgrad(grad_out, weight), fp8_wgrad(grad_out, x2, weight)
 
 
 class FP8Linear(nn.Linear):

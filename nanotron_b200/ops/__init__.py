@@ -19,6 +19,7 @@ from nanotron_b200.ops import reference as ref
 _MODE = os.environ.get("NTB_OPS", "auto")  # auto | torch
 _GEMM = os.environ.get("NTB_GEMM", "auto")  # auto | cublas | tcgen05
 _ATTN = os.environ.get("NTB_ATTN", "auto")  # auto | native (both: the in-tree tcgen05 kernels) | sdpa (library kernel, for comparison)
+_LINEAR = os.environ.get("NTB_LINEAR", "bf16")  # bf16 | fp8 (block-scaled e4m3 forward / e5m2 gradients for the linear-layer products)
 LAUNCH_COUNTER = {"n": 0}
 
 
@@ -38,6 +39,19 @@ def set_attention(mode: str):
     global _ATTN
     assert mode in ("auto", "native", "sdpa")
     _ATTN = mode
+
+
+def set_linear(mode: str):
+    """Operand precision of the three products of every tensor-parallel linear layer: "bf16", or "fp8" = block-scaled fp8
+    (1 x 128 activation / gradient blocks, 128 x 128 weight blocks, e4m3 forward, e5m2 gradients; ``nanotron_b200.fp8``).  Products
+    whose shapes are not multiples of 128 (the padded lm head shard, toy models) stay in bf16."""
+    global _LINEAR
+    assert mode in ("bf16", "fp8")
+    _LINEAR = mode
+
+
+def get_linear() -> str:
+    return _LINEAR
 
 
 def get_mode() -> str:
@@ -85,6 +99,12 @@ def _tcgen05_ok(a: torch.Tensor, b: torch.Tensor, kind: str) -> bool:
 
 def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[M,N] = x2[M,K] @ weight[N,K]^T (+ bias)."""
+    if _LINEAR == "fp8":
+        from nanotron_b200.fp8 import linear as fp8_linear
+
+        if fp8_linear.shapes_ok(x2, weight):
+            y = fp8_linear.fp8_forward(x2, weight)
+            return y if bias is None else y + bias
     if _tcgen05_ok(x2, weight, "fwd"):
         from nanotron_b200.ops import native
 
@@ -95,6 +115,11 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
 
 def linear_dgrad(go2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """dx[M,K] = go2[M,N] @ weight[N,K]."""
+    if _LINEAR == "fp8":
+        from nanotron_b200.fp8 import linear as fp8_linear
+
+        if fp8_linear.shapes_ok(go2, weight.t()):
+            return fp8_linear.fp8_dgrad(go2, weight)
     if _tcgen05_ok(go2, weight, "dgrad"):
         from nanotron_b200.ops import native
 
@@ -106,6 +131,11 @@ def linear_wgrad(go2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor) -> O
     """dW[N,K] = go2[M,N]^T @ x2[M,K].  When the weight carries an fp32 ``main_grad`` buffer the product is
     accumulated into it and ``None`` is returned (autograd then leaves ``weight.grad`` unset)."""
     main_grad = getattr(weight, "main_grad", None)
+    if _LINEAR == "fp8":
+        from nanotron_b200.fp8 import linear as fp8_linear
+
+        if fp8_linear.shapes_ok(x2, weight) and go2.shape[0] % 128 == 0:
+            return fp8_linear.fp8_wgrad(go2, x2, weight)
     if main_grad is not None:
         if _tcgen05_ok(go2, x2, "wgrad_accum"):
             from nanotron_b200.ops import native

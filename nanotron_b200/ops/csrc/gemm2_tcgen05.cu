@@ -35,7 +35,28 @@ constexpr int P_EPI_BYTES = P_EPI_WARPS * 2 * P_EPI_BUF;
 constexpr int P_THREADS = 32 * (2 + P_EPI_WARPS);
 constexpr int P_SMEM = P_MAX_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 + 512;
 
-enum POut { P_OUT_BF16 = 0, P_OUT_F32 = 1, P_OUT_F32_ACCUM = 2 };
+enum POut { P_OUT_BF16 = 0, P_OUT_F32 = 1, P_OUT_F32_ACCUM = 2, P_OUT_PEER_BF16 = 3 };
+
+// Tensor-parallel fusion on the pair kernel (same protocol as the one-CTA kernel in gemm_tcgen05.cu; all off when world == 0):
+//  * all-gather -> GEMM: A is a gathered buffer of `world` row blocks of `ag_rows` rows that peers fill with plain stores;
+//    block r is valid once ag_flags[r] >= epoch.  Each CTA's TMA producer polls the word of the block its 128 rows belong to
+//    (bounded) before its first load from it; tile rows are visited starting with this rank's own block.
+//  * GEMM -> reduce-scatter (P_OUT_PEER_BF16): the epilogue TMA-stores every bf16 chunk into slot `me` of the staging area of the
+//    rank that owns those rows (one tensor map per owner); the last CTA of the grid to finish raises rs_flags[owner][me] everywhere.
+constexpr int P_TP_MAX = 8;
+struct PFuse {
+  int world = 0, me = 0;
+  uint32_t epoch = 0;
+  int m_rot = 0;                        // rotation of the tile rows, in 256-row pair tiles
+  const uint32_t* ag_flags = nullptr;   // local flag words [world]
+  int ag_rows = 0;                      // rows per gathered block (multiple of 128)
+  uint32_t* rs_flags[P_TP_MAX] = {};    // per-owner flag words [world]
+  int rs_rows = 0;                      // rows per owner (multiple of 32)
+  unsigned int* done_counter = nullptr; // local counter, zero before launch
+};
+struct PPeerMaps {
+  CUtensorMap m[P_TP_MAX];
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -110,7 +131,7 @@ __device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n, int 
 template <bool A_MN, bool B_MN, int OUT, int P_STAGES>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                     int M, int N, int K, int band, int* __restrict__ status) {
+                     int M, int N, int K, int band, int* __restrict__ status, const __grid_constant__ PFuse fuse, const __grid_constant__ PPeerMaps pmaps) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + P_MAX_STAGES * P_STAGE_BYTES;
@@ -162,10 +183,28 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     if (ptx::elect_one()) {
       int it = 0;
       bool ok = true;
+      uint32_t ag_ready = 0;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+        PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+        tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
         const int m0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M;           // this CTA's rows of A
         const int n0 = tc.n_blk * P_BLOCK_N + static_cast<int>(cta) * P_HALF_N;      // this CTA's half of B
+        if (fuse.ag_flags != nullptr && m0 < M) {
+          const int src = min(fuse.world - 1, m0 / fuse.ag_rows);  // ag_rows is a multiple of 128: one source per CTA row block
+          if (!(ag_ready & (1u << src))) {
+            const uint64_t t0 = ptx::globaltimer();
+            while (true) {
+              uint32_t v;
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(fuse.ag_flags + src) : "memory");
+              if (static_cast<int32_t>(v - fuse.epoch) >= 0) { ag_ready |= 1u << src; break; }
+              if (*abort_flag || ptx::globaltimer() - t0 > NTB_WAIT_LIMIT_NS) { *abort_flag = 1; ok = false; break; }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            // the block was written by peers with generic stores: make it visible to the async (TMA) proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1;
@@ -235,13 +274,14 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------------------------------------------ epilogue warps (both CTAs, own 128 rows)
     const int q = warp & 3;
     uint8_t* my_epi = epi_smem + (warp - 2) * 2 * P_EPI_BUF;
-    constexpr bool BF16_OUT = (OUT == P_OUT_BF16);
+    constexpr bool BF16_OUT = (OUT == P_OUT_BF16 || OUT == P_OUT_PEER_BF16);
     constexpr int CHUNK_COLS = BF16_OUT ? 64 : 32;
     constexpr int CHUNKS = P_BLOCK_N / CHUNK_COLS;
     int tile_it = 0, buf = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
-      const PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+      PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+      tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 1000)) { ok = false; break; }
@@ -289,7 +329,10 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 0) {
           const int x = tc.n_blk * P_BLOCK_N + c * CHUNK_COLS;
           if (x < N && row0 < M) {
-            if (OUT == P_OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
+            if (OUT == P_OUT_PEER_BF16) {
+              const int owner = row0 / fuse.rs_rows;  // rs_rows is a multiple of 32: the 32 rows of this warp share an owner
+              ptx::tma_store_2d(&pmaps.m[owner], stage_buf, x, fuse.me * fuse.rs_rows + (row0 - owner * fuse.rs_rows));
+            } else if (OUT == P_OUT_F32_ACCUM) ptx::tma_reduce_add_2d(&tmap_d, stage_buf, x, row0);
             else ptx::tma_store_2d(&tmap_d, stage_buf, x, row0);
           }
           ptx::tma_commit_group();
@@ -304,7 +347,14 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         else mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_empty[acc]), 0));
       }
     }
-    if (lane == 0) ptx::tma_wait_group<0>();
+    if (lane == 0) {
+      ptx::tma_wait_group<0>();
+      if (OUT == P_OUT_PEER_BF16) {
+        // the peer stores were made by the async proxy: order them before the generic-proxy flag store that follows the CTA barrier
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence_system();
+      }
+    }
     __syncwarp();
   }
 
@@ -314,6 +364,18 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (warp == 1) {
     ptx::tc_fence_after();
     tmem_dealloc2(tmem_base, 512);
+  }
+  if (OUT == P_OUT_PEER_BF16 && fuse.done_counter != nullptr && threadIdx.x == 0) {
+    // every store of this CTA is complete and fenced (epilogue warps, before the barrier above); the last CTA of the grid to get
+    // here tells every owner that this rank's partial sums are in place
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(fuse.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < fuse.world; r++)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(fuse.rs_flags[r] + fuse.me), "r"(fuse.epoch) : "memory");
+      *fuse.done_counter = 0;
+    }
   }
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, NTB_ERR_TIMEOUT);
 }
@@ -359,7 +421,10 @@ bool p_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld
 }
 
 template <bool A_MN, bool B_MN, int OUT, int ST = P_MAX_STAGES>
-int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream) {
+int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
+             const PFuse& fuse = PFuse(), const PPeerMaps* pmaps = nullptr) {
+  static const PPeerMaps no_maps = {};
+  const PPeerMaps& pm = pmaps ? *pmaps : no_maps;
   auto kern = gemm2_tcgen05_kernel<A_MN, B_MN, OUT, ST>;
   static bool configured = false;
   if (!configured) {
@@ -386,7 +451,7 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   if (band < 2) band = 2;
   if (band > tiles_m) band = tiles_m;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status, fuse, pm) != cudaSuccess) {
     cudaGetLastError();
     return NTB_ERR_LAUNCH;
   }
@@ -425,4 +490,57 @@ NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int 
 #undef NTB_P_CASE
   NTB_P_REJECT(10);
 #undef NTB_P_REJECT
+}
+
+// D = gathered_A @ B^T (or @ B when b_mn) where gathered_A = [world * ag_rows, K] is filled by ntb_tp_allgather_push on every rank
+// (same contract as ntb_gemm_bf16_ag; ag_rows must be a multiple of 128 here).
+NTB_EXPORT int ntb_gemm2_bf16_ag(const void* a_gathered, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int b_mn,
+                                 const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status, int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !p_get_encode() || world < 1 || world > P_TP_MAX || ag_rows <= 0 || ag_rows % P_BLOCK_M || ag_flags == nullptr) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a_gathered) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
+  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) || ldd % 8) return NTB_ERR_ARG;
+  if (num_sms <= 1) num_sms = 148;
+  CUtensorMap ta, tb, td;
+  if (!p_map_kmajor(&ta, a_gathered, M, K, lda)) return NTB_ERR_ARG;
+  if (!(b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb))) return NTB_ERR_ARG;
+  if (!p_map_out(&td, d, M, N, ldd, false)) return NTB_ERR_ARG;
+  PFuse f;
+  f.world = world;
+  f.me = me;
+  f.epoch = epoch;
+  f.ag_flags = ag_flags;
+  f.ag_rows = ag_rows;
+  const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
+  f.m_rot = ((me * ag_rows) / (2 * P_BLOCK_M)) % tiles_m;  // start with the rows this rank contributed itself
+  return b_mn ? p_launch<false, true, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f) : p_launch<false, false, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f);
+}
+
+// Partial product A @ B^T (or A @ B when b_mn) whose rows [r*rs_rows, (r+1)*rs_rows) are stored (bf16) into rank r's staging slot `me`
+// (same contract as ntb_gemm_bf16_rs).
+NTB_EXPORT int ntb_gemm2_bf16_rs(const void* a, const void* b, int M, int N, int K, int64_t lda, int64_t ldb, int b_mn, const uint64_t* staging_ptrs,
+                                 const uint64_t* flag_ptrs, int rs_rows, int me, int world, uint32_t epoch, unsigned int* done_counter, int* status, int num_sms,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || !p_get_encode() || world < 1 || world > P_TP_MAX || rs_rows * world != M || rs_rows % 32 || N % 8 || done_counter == nullptr) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) return NTB_ERR_ARG;
+  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8))) return NTB_ERR_ARG;
+  if (num_sms <= 1) num_sms = 148;
+  CUtensorMap ta, tb;
+  if (!p_map_kmajor(&ta, a, M, K, lda)) return NTB_ERR_ARG;
+  if (!(b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb))) return NTB_ERR_ARG;
+  PFuse f;
+  f.world = world;
+  f.me = me;
+  f.epoch = epoch;
+  f.rs_rows = rs_rows;
+  f.done_counter = done_counter;
+  PPeerMaps pm = {};
+  for (int r = 0; r < world; r++) {
+    if (staging_ptrs[r] & 15) return NTB_ERR_ARG;
+    if (!p_map_out(&pm.m[r], reinterpret_cast<void*>(staging_ptrs[r]), static_cast<int64_t>(world) * rs_rows, N, N, false)) return NTB_ERR_ARG;
+    f.rs_flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
+  f.m_rot = ((((me + 1) % world) * rs_rows) / (2 * P_BLOCK_M)) % tiles_m;  // the next rank's rows first, our own last
+  return b_mn ? p_launch<false, true, P_OUT_PEER_BF16>(ta, tb, ta, M, N, K, status, num_sms, stream, f, &pm)
+              : p_launch<false, false, P_OUT_PEER_BF16>(ta, tb, ta, M, N, K, status, num_sms, stream, f, &pm);
 }

@@ -68,6 +68,11 @@ def _declare(L):
             L.ntb_gemm_bf16_ag.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_int, c_void_p]
             L.ntb_gemm_bf16_rs.restype = c_int
             L.ntb_gemm_bf16_rs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_uint32, c_void_p, c_void_p, c_int, c_void_p]
+            if hasattr(L, "ntb_gemm2_bf16_ag"):
+                L.ntb_gemm2_bf16_ag.restype = c_int
+                L.ntb_gemm2_bf16_ag.argtypes = L.ntb_gemm_bf16_ag.argtypes
+                L.ntb_gemm2_bf16_rs.restype = c_int
+                L.ntb_gemm2_bf16_rs.argtypes = L.ntb_gemm_bf16_rs.argtypes
             L.ntb_tp_reduce_slots.restype = c_int
             L.ntb_tp_reduce_slots.argtypes = [c_void_p, c_void_p, c_void_p, c_int, ctypes.c_longlong, c_uint32, c_ull, c_void_p, c_void_p]
         L.ntb_dp_adamw_allgather.restype = c_int

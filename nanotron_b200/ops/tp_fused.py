@@ -4,7 +4,7 @@
 
 Fused path (``TPFusedContext``, needs the tp group inside one NVLink domain): buffers live in symmetric memory.
   all-gather -> GEMM : every rank pushes its block into slot `rank` of all peers' gather buffers with plain peer stores and
-      raises a flag there; the tcgen05 GEMM's TMA producer starts with the rows this rank wrote itself and polls the flag of
+      raises a flag there; the tcgen05 GEMM's TMA producer (CTA-pair kernel by default) starts with the rows this rank wrote itself and polls the flag of
       a peer's block right before its first load from it, so the transfer of late blocks hides behind the math of early ones.
   GEMM -> reduce-scatter : the GEMM epilogue stores each bf16 tile of partial sums directly into the owner rank's staging
       slot (peer stores from registers), the last CTA raises a flag at every owner, and a small kernel sums the slots in
@@ -77,6 +77,15 @@ class TPFusedContext:
         native._check(rc, "ce_combine_peers")
         return logz, loss
 
+    @staticmethod
+    def _entry(kind: str):
+        """The fused GEMMs exist on both in-tree GEMM kernels; the CTA-pair kernel (the default of ``native_gemm``) is the faster one."""
+        from nanotron_b200.ops import native, native_gemm
+
+        L = native.lib()
+        pair = native_gemm.VARIANT["kernel"] == "pair" and hasattr(L, "ntb_gemm2_bf16_ag")
+        return getattr(L, ("ntb_gemm2_bf16_" if pair else "ntb_gemm_bf16_") + kind)
+
     def _buf(self, pool, i: int, numel: int):
         cur = pool[i]
         if cur is None or cur.tensor.numel() < numel:
@@ -112,7 +121,7 @@ class TPFusedContext:
         N = weight.shape[1] if b_mn else weight.shape[0]
         K = x2.shape[1]
         out = torch.empty((self.world * M, N), dtype=x2.dtype, device=x2.device)
-        rc = native.lib().ntb_gemm_bf16_ag(gathered.data_ptr(), weight.data_ptr(), out.data_ptr(), self.world * M, N, K, K, weight.stride(0), N, int(b_mn), flags.tensor.data_ptr(), M, self.rank, self.world, epoch, self.status.data_ptr(), self.sms, torch.cuda.current_stream().cuda_stream)
+        rc = self._entry("ag")(gathered.data_ptr(), weight.data_ptr(), out.data_ptr(), self.world * M, N, K, K, weight.stride(0), N, int(b_mn), flags.tensor.data_ptr(), M, self.rank, self.world, epoch, self.status.data_ptr(), self.sms, torch.cuda.current_stream().cuda_stream)
         native._check(rc, "gemm_bf16_ag")
         return out, gathered
 
@@ -130,7 +139,7 @@ class TPFusedContext:
         flags = self.rs_flags[i]
         L = native.lib()
         stream = torch.cuda.current_stream().cuda_stream
-        rc = L.ntb_gemm_bf16_rs(x2.data_ptr(), weight.data_ptr(), M, N, K, x2.stride(0), weight.stride(0), int(b_mn), buf.ptrs, flags.ptrs, rows, self.rank, self.world, epoch, self.counter[1:2].data_ptr(), self.status.data_ptr(), self.sms, stream)
+        rc = self._entry("rs")(x2.data_ptr(), weight.data_ptr(), M, N, K, x2.stride(0), weight.stride(0), int(b_mn), buf.ptrs, flags.ptrs, rows, self.rank, self.world, epoch, self.counter[1:2].data_ptr(), self.status.data_ptr(), self.sms, stream)
         native._check(rc, "gemm_bf16_rs")
         out = torch.empty((rows, N), dtype=x2.dtype, device=x2.device)
         rc = L.ntb_tp_reduce_slots(buf.tensor.data_ptr(), out.data_ptr(), flags.tensor.data_ptr(), self.world, rows * N, epoch, self.alloc.wait_limit_ns, self.status.data_ptr(), stream)
@@ -158,6 +167,10 @@ def get_context(group) -> Optional[TPFusedContext]:
 
 
 def _fusable(x2: torch.Tensor, weight: torch.Tensor, rows_per_rank: int) -> bool:
+    from nanotron_b200 import ops
+
+    if ops.get_linear() == "fp8":
+        return False  # the fused kernels are bf16: fp8 products take the collective + local fp8 GEMM route
     return (
         x2.is_cuda and x2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x2.is_contiguous() and weight.is_contiguous()
         and rows_per_rank % 128 == 0 and x2.shape[1] % 64 == 0 and weight.shape[0] % 64 == 0 and weight.shape[1] % 64 == 0

@@ -107,6 +107,8 @@ class DistributedTrainer:
                 ops.set_gemm(self.config.kernels.gemm)
             if self.config.kernels.attention in ("auto", "native", "sdpa"):
                 ops.set_attention(self.config.kernels.attention)
+            if getattr(self.config.kernels, "linear", "bf16") in ("bf16", "fp8"):
+                ops.set_linear(self.config.kernels.linear)
         self.pre_init()
         if self.config.logging is None:
             from nanotron_b200.config import LoggingArgs

@@ -26,7 +26,7 @@ def check_ops(ctx):
 
     tp, rank = ctx.tp_pg.size(), dist.get_rank(ctx.tp_pg)
     torch.manual_seed(1234 + rank)
-    M, K, N = 256, 1024, 1536
+    M, K, N = 512, 1024, 1536
     results = {}
     for fused in (False, True):
         tp_fused.ENABLED = fused
@@ -89,7 +89,14 @@ def main():
         print("nccl  losses", ["%.4f" % l for l in base])
         print("fused losses", ["%.4f" % l for l in fused])
     assert all(abs(a - b) < 3e-2 for a, b in zip(base, fused)), (base, fused)
-    check_ops(ctx)
+    from nanotron_b200.ops import native_gemm
+
+    for variant in ("pair", "single"):  # the fused modes exist on both in-tree GEMM kernels
+        native_gemm.set_variant(variant)
+        if rank == 0:
+            print(f"GEMM kernel: {variant}")
+        check_ops(ctx)
+    native_gemm.set_variant("pair")
     if rank == 0:
         print("FUSED_TP_OK")
     import torch.distributed as tdist

@@ -94,3 +94,55 @@ def test_fp8_linear_native_path_matches_dequantised_path():
     for a, b, name in zip(res["auto"], res["torch"], ("y", "dx", "dW")):
         err = (a - b).abs().max() / b.abs().max()
         assert err < 2e-2, (name, float(err))
+
+
+def test_fp8_linear_mode_is_reachable_from_the_config_and_tracks_bf16():
+    """``kernels.linear: fp8`` routes the three products of every tensor-parallel linear through block-scaled fp8 operands; the
+    loss curve of a small model stays close to the full-precision one."""
+    import nanotron_b200.config as c
+    from helpers import make_config, single_process_env, tiny_llama_config
+    from nanotron_b200 import ops
+    from nanotron_b200.fp8 import linear as fp8_linear
+    from nanotron_b200.trainer import DistributedTrainer
+    from test_distributed_cpu import _deterministic_init
+
+    class T(DistributedTrainer):
+        def _load_model_checkpoint(self, model):
+            _deterministic_init(model)
+            return model
+
+    def run(linear):
+        single_process_env()
+        cfg = make_config(tiny_llama_config(hidden_size=128, intermediate_size=256, num_attention_heads=2, num_key_value_heads=2, vocab_size=256), seq=64, mbs=2, steps=6, lr=3e-3)
+        cfg.kernels = c.KernelArgs(linear=linear)
+        t = T(cfg)
+        t.prepare_training()
+        g = torch.Generator().manual_seed(0)
+        tokens = torch.randint(0, 256, (2, 65), generator=g)
+        batch = {"input_ids": tokens[:, :-1].contiguous(), "input_mask": torch.ones(2, 64, dtype=torch.bool), "label_ids": tokens[:, 1:].contiguous(), "label_mask": torch.ones(2, 64, dtype=torch.bool)}
+        losses = []
+        for _ in range(6):
+            _, loss, _ = t.training_step(iter([batch]))
+            t.iteration_step += 1
+            losses.append(float(loss))
+        t.parallel_context.destroy()
+        return losses
+
+    calls = {"n": 0}
+    orig = fp8_linear.fp8_forward
+
+    def counting(x2, w):
+        calls["n"] += 1
+        return orig(x2, w)
+
+    fp8_linear.fp8_forward = counting
+    try:
+        fp8 = run("fp8")
+    finally:
+        fp8_linear.fp8_forward = orig
+        ops.set_linear("bf16")
+    assert calls["n"] >= 6 * 2 * 4  # qkv, o, gate_up, down of both layers, every step
+    ref = run("bf16")
+    assert fp8[-1] < fp8[0] - 0.3, fp8
+    for a, b in zip(fp8, ref):
+        assert abs(a - b) < 0.05, (fp8, ref)

@@ -73,17 +73,21 @@ def bench_tp(group, rank, world, pk):
     def nccl_gemm_rs():
         tdist.reduce_scatter_tensor(out_rs, torch.nn.functional.linear(a, w_row), group=group)
 
+    from nanotron_b200.ops import native_gemm
+
     link_bytes = (world - 1) / world * T * h * 2
     f1 = 2.0 * T * (2 * ffn // world) * h
-    ms_f = timed(lambda: ctx.all_gather_gemm(x, w_col, b_mn=False))
-    ms_n = timed(nccl_ag_gemm)
-    roof = max(f1 / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
-    say(rank, f"tp{world} all-gather->GEMM   [{T}x{h}]x[{h}x{2 * ffn // world}]  fused {ms_f:7.3f} ms | NCCL+library {ms_n:7.3f} ms | roofline {roof:6.3f} ms -> {roof / ms_f:4.2f} of roofline")
     f2 = 2.0 * T * h * (ffn // world)
-    ms_f = timed(lambda: ctx.gemm_reduce_scatter(a, w_row, b_mn=False))
-    ms_n = timed(nccl_gemm_rs)
-    roof = max(f2 / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
-    say(rank, f"tp{world} GEMM->reduce-scatter [{T}x{ffn // world}]x[{ffn // world}x{h}]  fused {ms_f:7.3f} ms | NCCL+library {ms_n:7.3f} ms | roofline {roof:6.3f} ms -> {roof / ms_f:4.2f} of roofline")
+    ms_n1, ms_n2 = timed(nccl_ag_gemm), timed(nccl_gemm_rs)
+    for variant in ("pair", "single"):  # CTA-pair kernel (default) and one-CTA kernel
+        native_gemm.set_variant(variant)
+        ms_f = timed(lambda: ctx.all_gather_gemm(x, w_col, b_mn=False))
+        roof = max(f1 / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        say(rank, f"tp{world} all-gather->GEMM   [{T}x{h}]x[{h}x{2 * ffn // world}]  fused ({variant}) {ms_f:7.3f} ms | NCCL+library {ms_n1:7.3f} ms | roofline {roof:6.3f} ms -> {roof / ms_f:4.2f} of roofline")
+        ms_f = timed(lambda: ctx.gemm_reduce_scatter(a, w_row, b_mn=False))
+        roof = max(f2 / (pk["bf16_tflops"] * 1e9), link_bytes / (NVLINK_GBS * 1e6))
+        say(rank, f"tp{world} GEMM->reduce-scatter [{T}x{ffn // world}]x[{ffn // world}x{h}]  fused ({variant}) {ms_f:7.3f} ms | NCCL+library {ms_n2:7.3f} ms | roofline {roof:6.3f} ms -> {roof / ms_f:4.2f} of roofline")
+    native_gemm.set_variant("pair")
     ctx.alloc.check()
 
 
