@@ -340,6 +340,9 @@ class OptimizerArgs:
     # None: use the in-kernel NVLink reduce-scatter + AdamW + all-gather step whenever it applies (CUDA, dp > 1 inside one
     # node, fp32 accumulation, AdamW).  False: always the NCCL collectives.
     fused_zero_comm: Optional[bool] = None
+    # with the fused data-parallel step: start the gradient reduce-scatter of a layer while the last micro-batch's backward is still
+    # running on the layers below it
+    overlap_grad_reduce: bool = True
 
     def __post_init__(self):
         if self.weight_decay_exclude_named_params is None:

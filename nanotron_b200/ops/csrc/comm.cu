@@ -222,6 +222,31 @@ NTB_EXPORT int ntb_dp_reduce_scatter(const uint64_t* grad_ptrs, int me, int worl
   return ntb_check_launch();
 }
 
+namespace {
+__global__ void add_partials_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out) {
+  __shared__ float scratch[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += partial[i];
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) out[0] += s;
+}
+}  // namespace
+
+// The same reduction over one sub-range [start, start + n) of this rank's shard, for exchanges that are issued piece by piece
+// while the backward pass still runs: `blocks` (1 .. ntb_dp_num_partials()) bounds the SMs the transfer may occupy next to the
+// compute kernels, and the sum of squares is ADDED to sumsq_accum[0] (calls on one stream are ordered, so no atomics are needed).
+NTB_EXPORT int ntb_dp_reduce_scatter_range(const uint64_t* grad_ptrs, int me, int world, int64_t start, int64_t n, float scale, int broadcast,
+                                           float* sumsq_partial, float* sumsq_accum, int blocks, cudaStream_t stream) {
+  PeerPtrs g;
+  if (!fill_peers(g, grad_ptrs, world) || n <= 0 || n % 4 || start % 4 || blocks < 1 || blocks > ntb_dp_num_partials()) return NTB_ERR_ARG;
+  if (world <= 2) dp_reduce_scatter_kernel<4, 2><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else if (world <= 4) dp_reduce_scatter_kernel<2, 4><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else if (world <= 8) dp_reduce_scatter_kernel<2, 8><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  else dp_reduce_scatter_kernel<1, MAX_RANKS><<<blocks, COMM_THREADS, 0, stream>>>(g, me, world, start, n, scale, broadcast, sumsq_partial);
+  add_partials_kernel<<<1, 256, 0, stream>>>(sumsq_partial, blocks, sumsq_accum);
+  return ntb_check_launch();
+}
+
 NTB_EXPORT int ntb_dp_adamw_allgather(float* p, const float* g, float* m, float* v, const uint64_t* param_ptrs, int me, int world, int64_t start, int64_t n,
                                       const int64_t* seg_end, const float* seg_lr, const float* seg_wd, int nseg, float beta1, float beta2, float eps,
                                       float bias_correction1, float bias_correction2, const float* grad_scale, cudaStream_t stream) {

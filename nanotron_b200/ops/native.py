@@ -59,6 +59,9 @@ def _declare(L):
         L.ntb_symm_barrier.argtypes = [c_void_p, c_int, c_int, c_uint32, c_ull, c_void_p, c_void_p]
         L.ntb_dp_reduce_scatter.restype = c_int
         L.ntb_dp_reduce_scatter.argtypes = [c_void_p, c_int, c_int, c_int64, c_int64, c_float, c_int, c_void_p, c_void_p, c_void_p]
+        if hasattr(L, "ntb_dp_reduce_scatter_range"):
+            L.ntb_dp_reduce_scatter_range.restype = c_int
+            L.ntb_dp_reduce_scatter_range.argtypes = [c_void_p, c_int, c_int, c_int64, c_int64, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p]
         L.ntb_symm_wait.restype = c_int
         L.ntb_symm_wait.argtypes = [c_void_p, c_int, c_uint32, c_ull, c_void_p, c_void_p]
         if hasattr(L, "ntb_gemm_bf16_ag"):

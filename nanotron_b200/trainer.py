@@ -141,6 +141,11 @@ class DistributedTrainer:
             if isinstance(self.optimizer.get_base_optimizer(), FusedAdamW) and self.grad_accumulator is not None:
                 self.fused_dp = FusedDataParallelStep(symm_alloc, self.grad_accumulator, self.optimizer, self.parallel_context.dp_pg, self.parallel_context.mp_pg, self.config.optimizer.clip_grad)
                 self.fused_dp.exclude_tied_duplicates(self.unwrapped_model.get_named_params_with_correct_tied(), dist.get_rank(self.parallel_context.world_pg))
+                if self.config.optimizer.overlap_grad_reduce:
+                    early = self.fused_dp.install_overlap(self.unwrapped_model, list(self.unwrapped_model.get_named_params_with_correct_tied()))
+                    # the pipeline engines enter this context around the last micro-batch's backward
+                    self.grad_accumulator.prepare_last_backward = self.fused_dp.prepare_last_backward
+                    log_rank(f"Gradient reduce-scatter overlapped with the last backward: {early} buckets", logger=logger, level=logging.INFO, rank=0)
                 log_rank("Data-parallel step: in-kernel NVLink reduce-scatter + AdamW + all-gather", logger=logger, level=logging.INFO, rank=0)
         if self.init_checkpoint_path is not None and self.config.checkpoints.load_optimizer:
             load_optimizer(optimizer=self.optimizer, parallel_context=self.parallel_context, root_folder=self.init_checkpoint_path, param_shard_metadata=self.param_shard_metadata, model=self.unwrapped_model, map_location="cpu")

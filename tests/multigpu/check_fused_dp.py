@@ -14,14 +14,15 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from helpers import dummy_dataloader, make_config, tiny_llama_config  # noqa: E402
 
 
-def run(fused: bool, zero: int, steps: int = 5):
+def run(fused: bool, zero: int, steps: int = 5, overlap: bool = True, accum: int = 1):
     import nanotron_b200.distributed as dist
     from nanotron_b200.trainer import DistributedTrainer
 
     world = int(os.environ["WORLD_SIZE"])
     mc = tiny_llama_config(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=2, vocab_size=1024)
-    cfg = make_config(mc, dp=world, seq=128, mbs=2, steps=steps, dtype="bfloat16", zero=zero, lr=1e-3)
+    cfg = make_config(mc, dp=world, seq=128, mbs=2, accum=accum, steps=steps, dtype="bfloat16", zero=zero, lr=1e-3)
     cfg.optimizer.fused_zero_comm = None if fused else False
+    cfg.optimizer.overlap_grad_reduce = overlap
     torch.manual_seed(0)
     t = DistributedTrainer(cfg)
     assert (t.fused_dp is not None) == fused, f"fused path active={t.fused_dp is not None}, expected {fused}"
@@ -34,6 +35,8 @@ def run(fused: bool, zero: int, steps: int = 5):
         losses.append(float(loss))
     if t.fused_dp is not None:
         t.fused_dp.alloc.check()
+        early = t.fused_dp.overlapped_elems
+        assert (early > 0) == overlap, f"elements reduced during the backward: {early}, overlap requested: {overlap}"
     params = torch.cat([p.detach().float().reshape(-1) for _, p in sorted(t.unwrapped_model.named_parameters())])
     # replicas agree bit for bit
     ref = params.clone()
@@ -57,6 +60,15 @@ def main():
         assert all(abs(a - b) < 2e-2 for a, b in zip(base_losses, fused_losses)), (base_losses, fused_losses)
         assert diff < 2e-2, diff
         assert abs(base_norm - fused_norm) < 1e-2 * max(1.0, base_norm), (base_norm, fused_norm)
+        # the same step without starting the reduce-scatter during the backward, and with several micro-batches per step
+        # (only the last backward may launch buckets)
+        for accum in (1, 3):
+            late_losses, late_params, late_norm = run(fused=True, zero=zero, overlap=False, accum=accum)
+            early_losses, early_params, early_norm = run(fused=True, zero=zero, overlap=True, accum=accum)
+            d2 = (late_params - early_params).abs().max().item()
+            if rank == 0:
+                print(f"zero={zero} accum={accum} overlapped vs not: max |param diff| = {d2:.3e}, grad_norm {early_norm} vs {late_norm}")
+            assert d2 < 1e-3 and abs(early_norm - late_norm) < 1e-4 * max(1.0, late_norm), (d2, early_norm, late_norm)
     if rank == 0:
         print("FUSED_DP_OK")
     import torch.distributed as tdist
