@@ -93,18 +93,10 @@ class CausalSelfAttention(_q.Qwen2Attention):
         else:
             k_all, v_all, m_all = k, v, sequence_mask.bool()
         store.update({"key": k_all, "value": v_all, "mask": m_all, "past_len": past_len + sequence_mask.long().sum(-1)})
-        kv_len = k_all.shape[1]
-        rep = self.local_heads // self.local_kv_heads
-        qh = q.transpose(1, 2).float()
-        kh = k_all.transpose(1, 2).repeat_interleave(rep, dim=1).float()
-        vh = v_all.transpose(1, 2).repeat_interleave(rep, dim=1).float()
-        scores = torch.matmul(qh, kh.transpose(-1, -2)) / (self.head_dim**0.5)
-        qi = torch.arange(kv_len - qlen, kv_len, device=q.device).view(1, 1, qlen, 1)
-        ki = torch.arange(kv_len, device=q.device).view(1, 1, 1, kv_len)
-        allowed = (ki <= qi) & m_all.view(b, 1, 1, kv_len)
-        scores = scores.masked_fill(~allowed, float("-inf"))
-        p = torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
-        out = torch.matmul(p, vh).transpose(1, 2).reshape(T, self.local_q_size).to(hidden_states.dtype)
+        from nanotron_b200.nn.attention import cached_attention
+
+        out = cached_attention(q, k_all, v_all, sequence_mask.bool(), m_all, softmax_scale=1.0 / (self.head_dim**0.5), sliding_window=self.sliding_window_size)
+        out = out.reshape(T, self.local_q_size).to(hidden_states.dtype)
         return {"hidden_states": self.o_proj(out), "sequence_mask": sequence_mask}
 
 

@@ -69,6 +69,29 @@ class _Linear(nn.Module):
             nn.init.zeros_(self.bias)
 
 
+class _LocalLinear(torch.autograd.Function):
+    """y = x W^T (+ b) with the three products on ``ops.linear_*`` (the in-tree GEMM kernels on CUDA, fp32 main-grad accumulation)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.use_bias = bias is not None
+        return ops.linear_forward(x.reshape(-1, x.shape[-1]), weight, bias).view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, go):
+        x, weight = ctx.saved_tensors
+        go2 = go.reshape(-1, go.shape[-1]).contiguous()
+        gx = ops.linear_dgrad(go2, weight).view(x.shape) if ctx.needs_input_grad[0] else None
+        gw = ops.linear_wgrad(go2, x.reshape(-1, x.shape[-1]), weight)
+        gb = go2.sum(0) if ctx.use_bias else None
+        return gx, gw, gb
+
+
+def _linear(x, weight, bias):
+    return _LocalLinear.apply(x, weight, bias)
+
+
 class MQAColumnLinears(nn.Module):
     def __init__(self, in_features: int, q_out_features: int, kv_out_features: int, pg: dist.ProcessGroup, mode: TensorParallelLinearMode, bias=True, async_communication: bool = False):
         super().__init__()
@@ -86,7 +109,7 @@ class MQAColumnLinears(nn.Module):
             x = differentiable_all_gather(x, group=self.pg)
         else:
             x = differentiable_identity(x, group=self.pg)
-        return F.linear(x, self.q.weight, self.q.bias), F.linear(x, self.kv.weight, self.kv.bias)
+        return _linear(x, self.q.weight, self.q.bias), _linear(x, self.kv.weight, self.kv.bias)
 
 
 class _AttentionBase(nn.Module, AttachableStore):
@@ -103,13 +126,45 @@ class _AttentionBase(nn.Module, AttachableStore):
             self.rotary = None
 
     def _attend(self, q, k, v, sequence_mask):
-        """q [T,Hq,D], k/v [T,Hkv,D]; rows of ``sequence_mask`` [b,s] are whole sequences (right padding only)."""
+        """q [T,Hq,D], k/v [T,Hkv,D]; rows of ``sequence_mask`` [b,s] are whole sequences.  Training batches are padded on the right
+        (causal masking hides that from the real tokens); in evaluation mode left padding is kept out of the attention, and with a
+        key/value store attached (generation) only the new positions are computed against the cached keys and values
+        (reference: the flash_attn_with_kvcache paths, src/nanotron/models/starcoder2.py:832,1077)."""
         b, s = sequence_mask.shape
+        scale = (1.0 / math.sqrt(self.d_qk)) if self.config.scale_attn_weights else 1.0
+        store = self.get_local_store()
+        if store is not None:
+            return self._attend_cached(q, k, v, sequence_mask, store, scale)
         if self.rotary is not None:
             pos = (sequence_mask.long().cumsum(-1) - 1).clamp_(min=0).reshape(-1)
             q, k = self.rotary(q, k, pos)
-        cu = regular_cu_seqlens(b, s, q.device)
-        return ops.flash_attn_varlen(q, k, v, cu, cu, s, s, causal=True, softmax_scale=(1.0 / math.sqrt(self.d_qk)) if self.config.scale_attn_weights else 1.0, window=self.window)
+        cu = None
+        if not self.training:
+            from nanotron_b200.models.llama import padding_cu_seqlens
+
+            cu = padding_cu_seqlens(sequence_mask)
+        if cu is None:
+            cu = regular_cu_seqlens(b, s, q.device)
+        return ops.flash_attn_varlen(q, k, v, cu, cu, s, s, causal=True, softmax_scale=scale, window=self.window)
+
+    def _attend_cached(self, q, k, v, sequence_mask, store, scale):
+        from nanotron_b200.nn.attention import cached_attention
+
+        b, qlen = sequence_mask.shape
+        Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
+        past_len = store.get("past_len", torch.zeros(b, dtype=torch.long, device=q.device))
+        if self.rotary is not None:
+            pos = (past_len.unsqueeze(1) + (sequence_mask.long().cumsum(-1) - 1).clamp_(min=0)).reshape(-1)
+            q, k = self.rotary(q, k, pos)
+        kb, vb = k.reshape(b, qlen, Hkv, D), v.reshape(b, qlen, Hkv, D)
+        if "key" in store:
+            k_all, v_all = torch.cat([store["key"], kb], dim=1), torch.cat([store["value"], vb], dim=1)
+            m_all = torch.cat([store["mask"], sequence_mask.bool()], dim=1)
+        else:
+            k_all, v_all, m_all = kb, vb, sequence_mask.bool()
+        store.update({"key": k_all, "value": v_all, "mask": m_all, "past_len": past_len + sequence_mask.long().sum(-1)})
+        out = cached_attention(q.reshape(b, qlen, Hq, D), k_all, v_all, sequence_mask.bool(), m_all, softmax_scale=scale, sliding_window=self.window)
+        return out.reshape(b * qlen, Hq, D)
 
 
 class CausalSelfMQA(_AttentionBase):

@@ -56,6 +56,44 @@ def flex_attention_forward(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     return ops.flash_attn_varlen(q, k, v, bm.cu_seqlens_q, bm.cu_seqlens_k, bm.max_seqlen_q, bm.max_seqlen_k, causal=bm.causal, softmax_scale=softmax_scale, window=bm.window)
 
 
+def _packed_index(mask: torch.Tensor):
+    """(flat indices of the True positions, cu_seqlens int32 [b + 1]) of a [b, n] mask; cached on the mask tensor because every
+    layer of a decoding step asks for the same one (building it reads the mask back on the host once)."""
+    cached = getattr(mask, "_ntb_packed_index", None)
+    if cached is not None:
+        return cached
+    m = mask.bool()
+    idx = torch.nonzero(m.reshape(-1), as_tuple=False).flatten()
+    cu = torch.cat([torch.zeros(1, dtype=torch.int32, device=m.device), m.sum(-1).cumsum(0).to(torch.int32)])
+    try:
+        mask._ntb_packed_index = (idx, cu)
+    except AttributeError:
+        pass
+    return idx, cu
+
+
+def cached_attention(q: torch.Tensor, k_all: torch.Tensor, v_all: torch.Tensor, q_mask: torch.Tensor, kv_mask: torch.Tensor, softmax_scale: Optional[float] = None, sliding_window: Optional[int] = None) -> torch.Tensor:
+    """Attention of the new positions against the key/value cache (decoding; reference: ``flash_attn_with_kvcache`` call sites,
+    src/nanotron/models/llama.py:645-658, starcoder2.py:832,1077).
+
+    q: [b, q_len, Hq, D] (the positions being decoded now); k_all, v_all: [b, kv_len, Hkv, D] (cache including the new positions);
+    q_mask [b, q_len], kv_mask [b, kv_len]: which entries are real tokens (left padding on the first call).  The real queries of
+    a row are the LAST real keys of that row, which is what the bottom-right aligned causal mask of the variable-length kernel
+    expresses, so padded batches are packed and handed to ``ops.flash_attn_varlen`` (in-tree kernel on CUDA).  Returns
+    [b, q_len, Hq, D] with zeros at padded query positions."""
+    b, q_len, Hq, D = q.shape
+    kv_len = k_all.shape[1]
+    qi, cu_q = _packed_index(q_mask)
+    ki, cu_k = _packed_index(kv_mask)
+    qp = q.reshape(b * q_len, Hq, D).index_select(0, qi)
+    kp = k_all.reshape(b * kv_len, k_all.shape[2], D).index_select(0, ki)
+    vp = v_all.reshape(b * kv_len, v_all.shape[2], D).index_select(0, ki)
+    op = ops.flash_attn_varlen(qp, kp, vp, cu_q, cu_k, q_len, kv_len, causal=True, softmax_scale=softmax_scale, window=sliding_window)
+    out = torch.zeros((b * q_len, Hq, D), dtype=op.dtype, device=q.device)
+    out.index_copy_(0, qi, op)
+    return out.view(b, q_len, Hq, D)
+
+
 def _ring(kind: str) -> Callable:
     def fn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=True, softmax_scale=None, sliding_window=None, cp_pg=None, **kw):
         from nanotron_b200.parallel.context_parallel.ring_attention import ring_attention

@@ -21,8 +21,11 @@ def test_greedy_decode_cache_matches_recompute():
     a = decode_tokenized(ids, mask, t.unwrapped_model.model, t.parallel_context, max_new_tokens=6, use_cache=False)
     b = decode_tokenized(ids, mask, t.unwrapped_model.model, t.parallel_context, max_new_tokens=6, use_cache=True)
     assert a.generation_ids.shape == (2, 6)
-    # row 0 has no padding: the cached and recomputed paths must agree exactly
-    assert torch.equal(a.generation_ids[0], b.generation_ids[0])
+    # with and without the key/value cache, for the unpadded row and for the left-padded one (padding takes no part in attention)
+    assert torch.equal(a.generation_ids, b.generation_ids)
+    # a row decoded alone gives what it gives inside the padded batch
+    alone = decode_tokenized(ids[1:, 3:], mask[1:, 3:], t.unwrapped_model.model, t.parallel_context, max_new_tokens=6, use_cache=True)
+    assert torch.equal(alone.generation_ids[0], b.generation_ids[1])
     t.parallel_context.destroy()
 
 
@@ -45,3 +48,45 @@ def test_qwen_decode_and_samplers():
     assert TopPSampler(pg=None, p=0.9)(peaked).squeeze(1).tolist() == [7, 7]
     assert BasicSampler(pg=None)(peaked).squeeze(1).tolist() == [7, 7]
     t.parallel_context.destroy()
+
+
+def _pp_decode(out_file, tp, pp, use_cache):
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.generation.decode import decode_tokenized
+    from nanotron_b200.trainer import DistributedTrainer
+    from test_distributed_cpu import _deterministic_init
+
+    class T(DistributedTrainer):
+        def _load_model_checkpoint(self, model):
+            _deterministic_init(model)
+            return model
+
+    t = T(make_config(tiny_llama_config(), tp=tp, pp=pp, seq=32))
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 256, (3, 8), generator=g)
+    mask = torch.ones(3, 8, dtype=torch.bool)
+    mask[0, :5] = False
+    mask[2, :2] = False
+    out = decode_tokenized(ids, mask, t.unwrapped_model.model, t.parallel_context, max_new_tokens=7, use_cache=use_cache, returns_logits=True)
+    if dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save(out.generation_ids.cpu(), out_file)
+    # every rank (first stage, last stage, every tp rank) ends up with the same tokens
+    ref = out.generation_ids.clone()
+    dist.broadcast(ref, src=0)
+    assert torch.equal(ref, out.generation_ids)
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def test_decoding_through_pipeline_and_tensor_parallel_stages(tmp_path):
+    """Generation with the model split over two pipeline stages (activations cross stages every step, new tokens travel back to the
+    first stage) and two tensor-parallel ranks (sharded logits, sharded sampling) gives the tokens of a single process."""
+    from helpers import run_distributed
+
+    outs = {}
+    for name, world, kw in [("single", 1, dict(tp=1, pp=1, use_cache=False)), ("pp2", 2, dict(tp=1, pp=2, use_cache=False)), ("pp2_cache", 2, dict(tp=1, pp=2, use_cache=True)), ("tp2pp2", 4, dict(tp=2, pp=2, use_cache=True))]:
+        f = str(tmp_path / f"{name}.pt")
+        run_distributed(_pp_decode, world, out_file=f, **kw)
+        outs[name] = torch.load(f)
+    for name in ("pp2", "pp2_cache", "tp2pp2"):
+        assert torch.equal(outs[name], outs["single"]), (name, outs[name], outs["single"])
