@@ -145,6 +145,8 @@ def build_config(args, world: int):
         mc = c.Qwen2Config(moe_config=c.MoEConfig(**QWEN_MOE_EXPERTS), **QWEN_MOE)
     else:
         mc = c.LlamaConfig(**MODELS[args.model])
+    if args.layers is not None:
+        mc.num_hidden_layers = args.layers  # shortened model for trying a configuration on fewer GPUs: not a benchmark number
     tp, pp, dp = resolve_layout(args, world)
     cp = world // (tp * pp * dp)
     ep = dp if (args.ep or 1) < 0 else (args.ep or 1)
@@ -261,14 +263,14 @@ def run_native(args):
     peak = peaks.get("bf16_tflops_sustained", 1400.0)
     if rank == 0:
         out = {
-            "metric": "Llama-3-8B training tokens/sec (whole job), bf16, seq 4096" if (args.model == "llama3-8b" and args.seq == 4096) else f"{args.config} training tokens/sec (whole job), bf16, seq {args.seq}",
+            "metric": "Llama-3-8B training tokens/sec (whole job), bf16, seq 4096" if (args.model == "llama3-8b" and args.seq == 4096 and args.layers is None) else f"{args.config} training tokens/sec (whole job), bf16, seq {args.seq}",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak" if dp == world else "strong", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if (args.model == "llama3-8b" and args.seq == 4096) else None,
             "dtype": "bf16" if args.linear == "bf16" else "fp8 (block-scaled linears; bf16 elsewhere)", "data": "synthetic uniform-random tokens, random-init weights",
             "tokens_per_sec_per_gpu": value / world, "model_tflops_per_gpu": tflops_per_gpu, "mfu_of_measured_sustained_peak": tflops_per_gpu / peak,
             "loss": loss_val, "impl": "nanotron_b200",
             "config": {
-                "model": args.model, "global_batch": args.mbs * args.accum * dp, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
+                "model": args.model + (f" (shortened to {args.layers} layers)" if args.layers is not None else ""), "global_batch": args.mbs * args.accum * dp, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
                 "parallelism": layout_label(tp, pp, dp, 1 if (dp > 1 and ctx.expert_parallel_size == 1) else 0) + (f"xcp{ctx.cp_pg.size()}(zig-zag)" if ctx.cp_pg.size() > 1 else "") + (f"+ep{ctx.expert_parallel_size}(on the dp axis)" if ctx.expert_parallel_size > 1 else ""),
                 "tp_linears": "in-tree fused all-gather->GEMM / GEMM->reduce-scatter kernels over NVLink peer memory" if tp > 1 else "n/a",
                 "pp_p2p": "NCCL send/recv on one lane per direction, asynchronous" if pp > 1 else "n/a",
@@ -298,6 +300,7 @@ def main():
     ap.add_argument("--mbs", type=int, default=None)
     ap.add_argument("--accum", type=int, default=None)
     ap.add_argument("--recompute", action="store_true", default=None)
+    ap.add_argument("--layers", type=int, default=None, help="override the number of layers (for trying a configuration on fewer GPUs; the result is not a benchmark of the named model)")
     ap.add_argument("--cp", type=int, default=None, help="context-parallel size (-1: all GPUs)")
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size, laid over the dp axis (-1: dp)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "cublas"], help="auto / tcgen05: every linear-layer product on the in-tree tcgen05 kernels; cublas: library GEMMs (wgrad then needs a separate fp32 add)")

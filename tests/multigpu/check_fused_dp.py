@@ -63,12 +63,18 @@ def main():
         # the same step without starting the reduce-scatter during the backward, and with several micro-batches per step
         # (only the last backward may launch buckets)
         for accum in (1, 3):
+            nccl_losses, nccl_params, nccl_norm = run(fused=False, zero=zero, accum=accum)
             late_losses, late_params, late_norm = run(fused=True, zero=zero, overlap=False, accum=accum)
             early_losses, early_params, early_norm = run(fused=True, zero=zero, overlap=True, accum=accum)
-            d2 = (late_params - early_params).abs().max().item()
+            d_late = (late_params - nccl_params).abs().max().item()
+            d_early = (early_params - nccl_params).abs().max().item()
             if rank == 0:
-                print(f"zero={zero} accum={accum} overlapped vs not: max |param diff| = {d2:.3e}, grad_norm {early_norm} vs {late_norm}")
-            assert d2 < 1e-3 and abs(early_norm - late_norm) < 1e-4 * max(1.0, late_norm), (d2, early_norm, late_norm)
+                print(f"zero={zero} accum={accum} nccl        losses {['%.4f' % l for l in nccl_losses]} grad_norm {nccl_norm}")
+                print(f"zero={zero} accum={accum} fused       losses {['%.4f' % l for l in late_losses]} grad_norm {late_norm}  max |param diff| vs nccl {d_late:.3e}")
+                print(f"zero={zero} accum={accum} fused+early losses {['%.4f' % l for l in early_losses]} grad_norm {early_norm}  max |param diff| vs nccl {d_early:.3e}")
+            # bf16 parameters: one rounding step at magnitude 1 is 7.8e-3
+            assert d_late < 1e-2 and d_early < 1e-2, (d_late, d_early)
+            assert abs(early_norm - nccl_norm) < 1e-3 * max(1.0, nccl_norm) and abs(late_norm - nccl_norm) < 1e-3 * max(1.0, nccl_norm), (nccl_norm, late_norm, early_norm)
     if rank == 0:
         print("FUSED_DP_OK")
     import torch.distributed as tdist
