@@ -75,3 +75,43 @@ def test_checkpoint_converts_back_to_hf_folder(tmp_path):
         torch.testing.assert_close(out(input_ids=ids).logits, hf(input_ids=ids).logits, atol=1e-5, rtol=1e-5)
     assert (tmp_path / "hf" / "config.json").exists()
     torch.distributed.destroy_process_group()
+
+
+def test_qwen2_moe_logits_match_hugging_face():
+    """A random tiny ``Qwen2MoeForCausalLM`` (routed experts + gated shared expert, q / k / v biases) converted with
+    examples/inference/qwen_moe gives the same logits here, and the weight mapping round-trips."""
+    import importlib.util
+
+    from helpers import single_process_env
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("qwen_moe_convert", os.path.join(root, "examples", "inference", "qwen_moe", "convert.py"))
+    conv = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(conv)
+    from transformers import Qwen2MoeConfig, Qwen2MoeForCausalLM
+
+    cfg = Qwen2MoeConfig(vocab_size=160, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, moe_intermediate_size=16,
+                         shared_expert_intermediate_size=48, num_experts=4, num_experts_per_tok=2, norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[],
+                         max_position_embeddings=64, tie_word_embeddings=False, rope_theta=10000.0)
+    torch.manual_seed(0)
+    hf = Qwen2MoeForCausalLM(cfg).eval().float()
+    single_process_env()
+    nt_cfg = conv.nanotron_config_from_hf(hf.config)
+    assert nt_cfg.moe_config.num_experts == 4 and nt_cfg.moe_config.enable_shared_expert and nt_cfg.attention_bias
+    model, ctx = conv.build_single_process_model(nt_cfg)
+    state = conv.hf_state_to_nanotron(hf.state_dict(), nt_cfg)
+    conv.load_state_into(model, state)
+    model.eval()
+    ids = torch.randint(0, 160, (2, 19))
+    pos = torch.arange(19).unsqueeze(0).expand(2, -1).contiguous()
+    with torch.no_grad():
+        exp = hf(input_ids=ids).logits
+        got = model.model(input_ids=ids, position_ids=pos)
+    got = got[0] if isinstance(got, tuple) else got
+    torch.testing.assert_close(got.float().reshape(2, 19, -1), exp, atol=3e-4, rtol=1e-3)
+    back = conv.nanotron_state_to_hf(state, nt_cfg)
+    for k, v in hf.state_dict().items():
+        if "rotary" in k:
+            continue
+        assert torch.equal(back[k].to(v.dtype), v), k
+    ctx.destroy()
