@@ -2,6 +2,10 @@
 own ``DistributedTrainer`` on the same model, batch and parallel layout (tp / pp by GPU count, sequence-parallel tensor
 parallelism with its asynchronous-communication linears, 1F1B) as the native arm and prints the same JSON line.
 
+Where the native arm's layout has pipeline stages (8 GPUs: tp4 x pp2) the reference runs tensor parallelism over all the GPUs
+instead: its Qwen2 model, the only one that random-initialises on its stock path, raises on every stage but the first
+(see ``run_reference``).  A failure of one rank ends the whole job with the ``unavailable`` line (``_Guard``).
+
 Nothing of this repository's models, kernels or engine is on that path.  The only additions are import stand-ins under
 ``baseline/shims`` for third-party packages that cannot be installed offline (``dacite``, ``torchtyping``,
 ``grouped_gemm``; the latter two are import-time only for a dense Llama), and the dataloader handed to
@@ -27,6 +31,85 @@ def _unavailable(why: str):
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
     return 0
+
+
+class _Guard:
+    """Keeps a failure of one rank from leaving the others waiting in a collective until someone kills the job.
+
+    A rank whose training loop raised publishes the reason in the job's rendezvous store (host side, no collective); a daemon
+    thread on every rank polls the store and also watches a wall-clock deadline.  When either fires, rank 0 prints the
+    ``unavailable`` line and every rank leaves with ``os._exit(0)``: the ranks stuck in a collective never return to Python,
+    so nothing gentler would end them."""
+
+    KEY = "ntb_reference_failed"
+
+    def __init__(self, deadline_s: float):
+        self.deadline_s = deadline_s
+        self._stop = False
+        self._thread = None
+
+    @staticmethod
+    def _store():
+        import torch.distributed as tdist
+        from torch.distributed import distributed_c10d as c10d
+
+        return c10d._get_default_store() if tdist.is_initialized() else None
+
+    def start(self):
+        import threading
+        import time
+
+        store = self._store()
+        if store is None or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+            return
+        t_end = time.monotonic() + self.deadline_s
+
+        def watch():
+            while not self._stop:
+                time.sleep(2.0)
+                why = None
+                try:
+                    if store.check([self.KEY]):
+                        why = store.get(self.KEY).decode(errors="replace")
+                except Exception:
+                    continue
+                if why is None and time.monotonic() > t_end:
+                    why = f"the reference did not finish within {self.deadline_s:.0f} s on this layout (a rank is waiting in a collective)"
+                if why is not None and not self._stop:
+                    _unavailable(why)
+                    sys.stdout.flush()
+                    os._exit(0)
+
+        self._thread = threading.Thread(target=watch, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop = True
+
+    def fail(self, why: str):
+        """Called by the rank that failed: tell the others, give their watchers time to act, report."""
+        import time
+
+        self._stop = True
+        store = None
+        try:
+            store = self._store()
+        except Exception:
+            pass
+        if store is not None and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            try:
+                store.set(self.KEY, why)
+            except Exception:
+                pass
+            if int(os.environ.get("RANK", "0")) != 0:
+                time.sleep(6.0)  # rank 0's watcher prints the line
+                os._exit(0)
+        _unavailable(why)
+        sys.stdout.flush()
+        if store is not None and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            time.sleep(6.0)
+            os._exit(0)
+        return 0
 
 
 def _host_batches(trainer, input_pp_rank: int, output_pp_rank: int, counter: dict):
@@ -113,7 +196,18 @@ def run_reference(args):
         # measured on this pool: with fp32 accumulation the reference's ZeRO-1 hook raises NotImplementedError
         # (optim/gradient_accumulator.py:354-355) and its replicated-optimizer path needs more than the 180 GB of a B200 for 8B parameters
         return _unavailable("the reference cannot hold a data-parallel replica of an 8B model on a 180 GB GPU (ZeRO-1 with fp32 accumulation is not implemented in its DDP hook; the replicated optimizer runs out of memory)")
+    layout_note = None
+    if pp > 1:
+        # The reference's only model that random-initialises on its stock path, Qwen2, cannot run on more than one pipeline stage:
+        # Qwen2Model.forward calls position_ids.numel() on every stage (models/qwen.py:766) while its data path hands every stage
+        # but the first a TensorPointer (data/dataloader.py:164-166, data/clm_collator.py:194), so stage 1 raises
+        # AttributeError: 'TensorPointer' object has no attribute 'numel' and stage 0 waits for it forever (seen on 8 GPUs at
+        # tp4 x pp2).  The arm therefore spends the same GPUs on the layout it can run: tensor parallelism over all of them.
+        layout_note = f"requested tp{tp}xpp{pp}; the reference's Qwen2 model raises AttributeError on pipeline stages > 0 (models/qwen.py:766), so its arm runs tp{tp * pp}"
+        tp, pp = tp * pp, 1
     m = dict(MODELS[args.model])
+    if m["num_key_value_heads"] % tp or m["num_attention_heads"] % tp:
+        return _unavailable(f"the reference cannot split {m['num_key_value_heads']} key/value heads over tp={tp}")
     # The reference's `LlamaForTraining.init_model_randomly` fails on its stock path (models/llama.py:1095 hands
     # `config.model` to a parametrizator that reads `config.model.init_method`: AttributeError), so the Llama-3-8B shape
     # is run through its maintained decoder implementation, `Qwen2ForTraining`, which without attention bias is the same
@@ -163,19 +257,22 @@ def run_reference(args):
                     torch.cuda.synchronize()
                     state["clocks"] = state["sampler"].stop()
 
+    guard = _Guard(deadline_s=float(os.environ.get("NTB_REFERENCE_DEADLINE_S", "420")))
     try:
         trainer = TimedTrainer(cfg_path)
+        guard.start()
         input_pp_rank, output_pp_rank = get_input_output_pp_ranks(model=trainer.model)
         h2d = {"bytes": 0, "batches": 0}
         dataloader = _host_batches(trainer, input_pp_rank, output_pp_rank, h2d)
         trainer.train({"bench": dataloader})
     except torch.cuda.OutOfMemoryError as e:
-        return _unavailable(f"reference ran out of GPU memory on this config: {str(e)[:160]}")
+        return guard.fail(f"reference ran out of GPU memory on this config: {str(e)[:160]}")
     except Exception as e:
         import traceback
 
         traceback.print_exc(file=sys.stderr)
-        return _unavailable(f"reference failed on its stock path: {type(e).__name__}: {str(e)[:300]}")
+        return guard.fail(f"reference failed on its stock path: {type(e).__name__}: {str(e)[:300]}")
+    guard.stop()
     ms = torch.tensor([state["start"].elapsed_time(state["end"])], dtype=torch.float64, device="cuda")
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
@@ -191,7 +288,7 @@ def run_reference(args):
             "higher_is_better": True, "scaling": "weak" if dp == world else "strong", "vs_baseline": value / world / BASELINE_TOK_S_PER_GPU if args.model == "llama3-8b" else None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference", "tokens_per_sec_per_gpu": value / world,
             "config": {"model": args.model, "global_batch": args.mbs * args.accum * dp, "seq_len": args.seq, "micro_batch": args.mbs, "grad_accum": args.accum,
-                       "parallelism": layout_label(tp, pp, dp, 0), "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
+                       "parallelism": layout_label(tp, pp, dp, 0), **({"layout_note": layout_note} if layout_note else {}), "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
                        "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush"},
             "clocks": state["clocks"],
             "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms / args.steps, "h2d_bytes_per_step": h2d_per_step, "d2h_bytes_per_step": 4,

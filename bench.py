@@ -164,7 +164,7 @@ def build_config(args, world: int):
         tokens=c.TokensArgs(sequence_length=args.seq, train_steps=10**6, micro_batch_size=args.mbs, batch_accumulation_per_replica=args.accum),
         optimizer=c.OptimizerArgs(
             optimizer_factory=c.AdamWOptimizerArgs(adam_eps=1e-8, adam_beta1=0.9, adam_beta2=0.95, torch_adam_is_fused=True),
-            zero_stage=zero, weight_decay=0.01, clip_grad=1.0, accumulate_grad_in_fp32=True,
+            zero_stage=zero, weight_decay=0.01, clip_grad=1.0, accumulate_grad_in_fp32=True, overlap_grad_reduce=not args.no_grad_overlap,
             learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=3e-4, lr_warmup_steps=2, lr_decay_style="cosine", min_decay_lr=3e-5),
         ),
         data_stages=[c.DatasetStageArgs(name="bench", start_training_step=1, data=c.DataArgs(dataset=None, seed=42, num_loading_workers=0))],
@@ -274,7 +274,7 @@ def run_native(args):
                 "parallelism": layout_label(tp, pp, dp, 1 if (dp > 1 and ctx.expert_parallel_size == 1) else 0) + (f"xcp{ctx.cp_pg.size()}(zig-zag)" if ctx.cp_pg.size() > 1 else "") + (f"+ep{ctx.expert_parallel_size}(on the dp axis)" if ctx.expert_parallel_size > 1 else ""),
                 "tp_linears": "in-tree fused all-gather->GEMM / GEMM->reduce-scatter kernels over NVLink peer memory" if tp > 1 else "n/a",
                 "pp_p2p": "NCCL send/recv on one lane per direction, asynchronous" if pp > 1 else "n/a",
-                "dp_step": "in-tree NVLink kernels (reduce-scatter + AdamW + all-gather)" if getattr(trainer, "fused_dp", None) is not None else "NCCL", "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
+                "dp_step": ("in-tree NVLink kernels (reduce-scatter" + (" per layer during the last backward" if (trainer.fused_dp.buckets and not args.no_grad_overlap) else "") + " + AdamW + all-gather)") if getattr(trainer, "fused_dp", None) is not None else "NCCL", "fp32_grad_accum": True, "fp32_master_weights": True, "optimizer": "AdamW", "clip_grad": 1.0,
                 "recompute_layer": bool(args.recompute), "l2": "inputs larger than L2 (per-step working set is tens of GB); no explicit flush",
                 "gemm": ops._GEMM, "gemm_kernel": args.gemm_variant, "attention": ops._ATTN, "linear": ops.get_linear(),
             },
@@ -300,6 +300,7 @@ def main():
     ap.add_argument("--mbs", type=int, default=None)
     ap.add_argument("--accum", type=int, default=None)
     ap.add_argument("--recompute", action="store_true", default=None)
+    ap.add_argument("--no-grad-overlap", action="store_true", help="data-parallel runs: reduce-scatter all gradients after the last backward instead of per layer during it")
     ap.add_argument("--layers", type=int, default=None, help="override the number of layers (for trying a configuration on fewer GPUs; the result is not a benchmark of the named model)")
     ap.add_argument("--cp", type=int, default=None, help="context-parallel size (-1: all GPUs)")
     ap.add_argument("--ep", type=int, default=None, help="expert-parallel size, laid over the dp axis (-1: dp)")

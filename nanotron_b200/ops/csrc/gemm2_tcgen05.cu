@@ -58,6 +58,28 @@ struct PPeerMaps {
   CUtensorMap m[P_TP_MAX];
 };
 
+// Work units of a launch.  Tiles are dealt to the CTA pairs round robin; when the last round would leave most pairs idle, the
+// tiles of that round are cut along K into `split` chunks each, one unit per chunk, so the tail of the launch is shared by all
+// pairs.  A chunk stores its fp32 partial sums into a slab of its own in a workspace (no zero fill, no atomics); a small pass
+// then sums the slabs of a tile in chunk order and writes D (bf16 / fp32 store, or fp32 accumulate), so the result does not
+// depend on which chunk finished first.
+struct PSched {
+  int total_units = 0;  // grid-stride loop bound
+  int full_units = 0;   // units [0, full_units) are whole tiles with the same index
+  int split = 1;        // chunks per tile of the last round (1: nothing is split)
+  int kb_per = 0;       // k-blocks per chunk
+};
+struct PUnit {
+  int tile, kb0, kbs, ws;  // ws: workspace slab of this chunk (unit index within the last round), -1 for a whole tile
+};
+__device__ __forceinline__ PUnit decode_unit(int u, const PSched& sc, int k_blocks) {
+  if (u < sc.full_units || sc.split <= 1) return {u, 0, k_blocks, -1};
+  const int v = u - sc.full_units;
+  const int rt = v / sc.split, ch = v - rt * sc.split;
+  const int kb0 = ch * sc.kb_per;
+  return {sc.full_units + rt, kb0, min(sc.kb_per, k_blocks - kb0), v};
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -131,7 +153,8 @@ __device__ __forceinline__ PTile pair_tile(int t, int tiles_m, int tiles_n, int 
 template <bool A_MN, bool B_MN, int OUT, int P_STAGES>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
-                     int M, int N, int K, int band, int* __restrict__ status, const __grid_constant__ PFuse fuse, const __grid_constant__ PPeerMaps pmaps) {
+                     int M, int N, int K, int band, int* __restrict__ status, const __grid_constant__ PFuse fuse, const __grid_constant__ PPeerMaps pmaps,
+                     const __grid_constant__ PSched sched, const __grid_constant__ CUtensorMap tmap_ws) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + P_MAX_STAGES * P_STAGE_BYTES;
@@ -150,7 +173,6 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int num_pairs = gridDim.x >> 1;
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   const int tiles_n = (N + P_BLOCK_N - 1) / P_BLOCK_N;
-  const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + P_BLOCK_K - 1) / P_BLOCK_K;
 
   if (threadIdx.x == 0) {
@@ -184,8 +206,10 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int it = 0;
       bool ok = true;
       uint32_t ag_ready = 0;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+      for (int u = pair; u < sched.total_units && ok; u += num_pairs) {
+        const PUnit un = decode_unit(u, sched, k_blocks);
+        if (un.kbs <= 0) continue;
+        PTile tc = pair_tile(un.tile, tiles_m, tiles_n, band);
         tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
         const int m0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M;           // this CTA's rows of A
         const int n0 = tc.n_blk * P_BLOCK_N + static_cast<int>(cta) * P_HALF_N;      // this CTA's half of B
@@ -205,7 +229,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             asm volatile("fence.proxy.async.global;" ::: "memory");
           }
         }
-        for (int kb = 0; kb < k_blocks; kb++, it++) {
+        for (int kb = un.kb0; kb < un.kb0 + un.kbs; kb++, it++) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1;
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, 200)) { ok = false; break; }
@@ -245,13 +269,16 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         constexpr uint32_t idesc = ptx::make_idesc_bf16(2 * P_BLOCK_M, P_BLOCK_N, A_MN, B_MN);
         int it = 0, tile_it = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
+        for (int u = pair; u < sched.total_units && ok; u += num_pairs) {
+          const PUnit un = decode_unit(u, sched, k_blocks);
+          if (un.kbs <= 0) continue;
           const int acc = tile_it & 1;
           const uint32_t acc_ph = (tile_it >> 1) & 1;
+          tile_it++;
           if (!ptx::mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t tmem_d = tmem_base + acc * P_BLOCK_N;
-          for (int kb = 0; kb < k_blocks; kb++, it++) {
+          for (int kb = 0; kb < un.kbs; kb++, it++) {
             const int s = it % P_STAGES;
             const uint32_t ph = (it / P_STAGES) & 1;
             if (!ptx::mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
@@ -275,15 +302,21 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int q = warp & 3;
     uint8_t* my_epi = epi_smem + (warp - 2) * 2 * P_EPI_BUF;
     constexpr bool BF16_OUT = (OUT == P_OUT_BF16 || OUT == P_OUT_PEER_BF16);
-    constexpr int CHUNK_COLS = BF16_OUT ? 64 : 32;
-    constexpr int CHUNKS = P_BLOCK_N / CHUNK_COLS;
     int tile_it = 0, buf = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += num_pairs, tile_it++) {
-      PTile tc = pair_tile(t, tiles_m, tiles_n, band);
+    for (int u = pair; u < sched.total_units && ok; u += num_pairs) {
+      const PUnit un = decode_unit(u, sched, k_blocks);
+      if (un.kbs <= 0) continue;
+      PTile tc = pair_tile(un.tile, tiles_m, tiles_n, band);
       tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
+      tile_it++;
+      // a chunk of a split tile leaves as fp32 partial sums in its workspace slab, whatever the type of D
+      const bool to_ws = un.ws >= 0;
+      const bool bf16_path = BF16_OUT && !to_ws;
+      const int CHUNK_COLS = bf16_path ? 64 : 32;
+      const int CHUNKS = P_BLOCK_N / CHUNK_COLS;
       if (!ptx::mbar_wait(&tmem_full[acc], acc_ph, abort_flag, 1000)) { ok = false; break; }
       if (cta == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&tmem_full[acc]), 1));  // forward to the peer's epilogue
       ptx::tc_fence_after();
@@ -295,7 +328,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 0) ptx::tma_wait_group_read<1>();
         __syncwarp();
         uint8_t* my_row = stage_buf + lane * 128;
-        if (BF16_OUT) {
+        if (bf16_path) {
           uint32_t r0[32], r1[32];
           ptx::tmem_ld_32x32(taddr + c * 64, r0);
           ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
@@ -328,7 +361,9 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __syncwarp();
         if (lane == 0) {
           const int x = tc.n_blk * P_BLOCK_N + c * CHUNK_COLS;
-          if (x < N && row0 < M) {
+          if (to_ws) {
+            ptx::tma_store_2d(&tmap_ws, stage_buf, c * 32, un.ws * (2 * P_BLOCK_M) + static_cast<int>(cta) * P_BLOCK_M + q * 32);
+          } else if (x < N && row0 < M) {
             if (OUT == P_OUT_PEER_BF16) {
               const int owner = row0 / fuse.rs_rows;  // rs_rows is a multiple of 32: the 32 rows of this warp share an owner
               ptx::tma_store_2d(&pmaps.m[owner], stage_buf, x, fuse.me * fuse.rs_rows + (row0 - owner * fuse.rs_rows));
@@ -380,8 +415,76 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, NTB_ERR_TIMEOUT);
 }
 
+// Split tiles: D tile = (D tile +) the sum, in chunk order, of the tile's workspace slabs (256 x 256 fp32 each, complete once the
+// GEMM kernel has finished).  One block per split tile and 32-row group.  OUT as in the GEMM kernel.
+template <int OUT>
+__global__ void gemm2_split_fixup_kernel(const float* __restrict__ ws, void* __restrict__ d_, int64_t ldd, int M, int N, int k_blocks, PSched sched, int tiles_m,
+                                         int tiles_n, int band, int m_rot) {
+  const int rt = blockIdx.x >> 3, rg = blockIdx.x & 7;
+  PTile tc = pair_tile(sched.full_units + rt, tiles_m, tiles_n, band);
+  tc.m_blk = (tc.m_blk + m_rot) % tiles_m;
+  const int chunks = min(sched.split, (k_blocks + sched.kb_per - 1) / sched.kb_per);  // chunks past the end of K wrote nothing
+  const int64_t slab = static_cast<int64_t>(2 * P_BLOCK_M) * P_BLOCK_N;
+  const float* src = ws + static_cast<int64_t>(rt) * sched.split * slab + static_cast<int64_t>(rg) * 32 * P_BLOCK_N;
+  for (int i = threadIdx.x; i < 32 * P_BLOCK_N / 8; i += blockDim.x) {
+    const int r = i / (P_BLOCK_N / 8), c8 = (i % (P_BLOCK_N / 8)) * 8;
+    const int row = tc.m_blk * 2 * P_BLOCK_M + rg * 32 + r, col = tc.n_blk * P_BLOCK_N + c8;
+    if (row >= M || col >= N) continue;  // N is a multiple of 8 and rows of D start 16-byte aligned (checked by the host)
+    float f[8];
+    if (OUT == P_OUT_F32_ACCUM) {
+      const float* dp = reinterpret_cast<const float*>(d_) + static_cast<int64_t>(row) * ldd + col;
+      *reinterpret_cast<float4*>(f) = *reinterpret_cast<const float4*>(dp);
+      *reinterpret_cast<float4*>(f + 4) = *reinterpret_cast<const float4*>(dp + 4);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) f[j] = 0.f;
+    }
+    for (int ch = 0; ch < chunks; ch++) {
+      const float* p = src + ch * slab + r * P_BLOCK_N + c8;
+      const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+      f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+      f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+    }
+    if (OUT == P_OUT_BF16) {
+      Vec8<__nv_bfloat16> o;
+      o.from_float(f);
+      o.store(reinterpret_cast<__nv_bfloat16*>(d_) + static_cast<int64_t>(row) * ldd + col);
+    } else {
+      float* dp = reinterpret_cast<float*>(d_) + static_cast<int64_t>(row) * ldd + col;
+      *reinterpret_cast<float4*>(dp) = *reinterpret_cast<float4*>(f);
+      *reinterpret_cast<float4*>(dp + 4) = *reinterpret_cast<float4*>(f + 4);
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Per-device fp32 workspace for split tiles (caller-owned, ws_tiles slabs of 256 x 256 floats); see ntb_gemm2_set_workspace.
+static float* g_p_ws[64] = {};
+static int g_p_ws_tiles[64] = {};
+static cudaStream_t g_p_ws_stream[64] = {};
+static int g_p_split_enabled = 0;  // off by default: measured within +-5 % of whole tiles on Llama shapes (the step is power-bound, not round-bound)
+
+// How the tiles of a launch are dealt out (see PSched).  `ws_tiles`: workspace slabs available (0: never split).
+static PSched p_schedule(int num_tiles, int pairs_max, int k_blocks, int ws_tiles) {
+  PSched sc;
+  sc.total_units = sc.full_units = num_tiles;
+  sc.split = 1;
+  sc.kb_per = k_blocks;
+  if (!g_p_split_enabled || ws_tiles <= 0 || num_tiles <= 0) return sc;
+  const int rounds = num_tiles / pairs_max, rem = num_tiles % pairs_max;
+  if (rem == 0 || rem * 100 >= pairs_max * 85) return sc;  // the last round is (nearly) full already
+  int split = pairs_max / rem;
+  if (split > k_blocks / 4) split = k_blocks / 4;  // at least four k-blocks per chunk
+  if (split < 2) return sc;
+  if (rem * split > ws_tiles) return sc;
+  sc.full_units = rounds * pairs_max;
+  sc.split = split;
+  sc.kb_per = (k_blocks + split - 1) / split;
+  sc.total_units = sc.full_units + rem * split;
+  return sc;
+}
 
 EncodeTiledFn p_get_encode() {
   ntb_bind_context_to_thread();
@@ -422,7 +525,7 @@ bool p_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld
 
 template <bool A_MN, bool B_MN, int OUT, int ST = P_MAX_STAGES>
 int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
-             const PFuse& fuse = PFuse(), const PPeerMaps* pmaps = nullptr) {
+             const PFuse& fuse = PFuse(), const PPeerMaps* pmaps = nullptr, void* d_out = nullptr, int64_t ldd = 0) {
   static const PPeerMaps no_maps = {};
   const PPeerMaps& pm = pmaps ? *pmaps : no_maps;
   auto kern = gemm2_tcgen05_kernel<A_MN, B_MN, OUT, ST>;
@@ -432,8 +535,22 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
     configured = true;
   }
   const long long tiles = static_cast<long long>((M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M)) * ((N + P_BLOCK_N - 1) / P_BLOCK_N);
+  const int k_blocks = (K + P_BLOCK_K - 1) / P_BLOCK_K;
+  // every output mode but the peer stores of the reduce-scatter mode may cut the tiles of its last round along K, if a workspace
+  // was registered for this device and stream and D is known as a plain pointer (16-byte aligned rows for the fix-up pass)
+  int dev = 0, ws_tiles = 0;
+  float* ws = nullptr;
+  if (OUT != P_OUT_PEER_BF16 && d_out != nullptr && N % 8 == 0 && (OUT == P_OUT_BF16 || (ldd % 4 == 0 && (reinterpret_cast<uintptr_t>(d_out) & 15) == 0)) &&
+      cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && g_p_ws[dev] != nullptr && g_p_ws_stream[dev] == stream) {
+    ws = g_p_ws[dev];
+    ws_tiles = g_p_ws_tiles[dev];
+  }
+  const PSched sched = p_schedule(static_cast<int>(tiles), num_sms / 2, k_blocks, tiles > (1 << 30) ? 0 : ws_tiles);
+  CUtensorMap tws = td;  // placeholder when nothing goes through the workspace
+  const bool uses_ws = sched.split > 1;
+  if (uses_ws && !p_map_out(&tws, ws, static_cast<int64_t>(ws_tiles) * 2 * P_BLOCK_M, P_BLOCK_N, P_BLOCK_N, true)) return NTB_ERR_ARG;
   long long pairs = num_sms / 2;
-  if (tiles < pairs) pairs = tiles;
+  if (sched.total_units < pairs) pairs = sched.total_units;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
   cfg.blockDim = dim3(P_THREADS, 1, 1);
@@ -451,9 +568,14 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   if (band < 2) band = 2;
   if (band > tiles_m) band = tiles_m;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status, fuse, pm) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status, fuse, pm, sched, tws) != cudaSuccess) {
     cudaGetLastError();
     return NTB_ERR_LAUNCH;
+  }
+  if (uses_ws) {
+    const int split_tiles = static_cast<int>(tiles) - sched.full_units;
+    const int tiles_n = (N + P_BLOCK_N - 1) / P_BLOCK_N;
+    gemm2_split_fixup_kernel<OUT><<<split_tiles * 8, 256, 0, stream>>>(ws, d_out, ldd, M, N, k_blocks, sched, tiles_m, tiles_n, band, fuse.m_rot);
   }
   return ntb_check_launch();
 }
@@ -482,7 +604,7 @@ NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int 
   if (!(b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb))) NTB_P_REJECT(8);
   if (!p_map_out(&td, d, M, N, ldd, out_mode != P_OUT_BF16)) NTB_P_REJECT(9);
 #define NTB_P_CASE(AM, BM, OM) \
-  if (a_mn == AM && b_mn == BM && out_mode == OM) return p_launch<AM != 0, BM != 0, OM>(ta, tb, td, M, N, K, status, num_sms, stream);
+  if (a_mn == AM && b_mn == BM && out_mode == OM) return p_launch<AM != 0, BM != 0, OM>(ta, tb, td, M, N, K, status, num_sms, stream, PFuse(), nullptr, d, ldd);
   NTB_P_CASE(0, 0, 0) NTB_P_CASE(0, 0, 1) NTB_P_CASE(0, 0, 2)
   NTB_P_CASE(0, 1, 0) NTB_P_CASE(0, 1, 1) NTB_P_CASE(0, 1, 2)
   NTB_P_CASE(1, 1, 0) NTB_P_CASE(1, 1, 1) NTB_P_CASE(1, 1, 2)
@@ -512,8 +634,25 @@ NTB_EXPORT int ntb_gemm2_bf16_ag(const void* a_gathered, const void* b, void* d,
   f.ag_rows = ag_rows;
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   f.m_rot = ((me * ag_rows) / (2 * P_BLOCK_M)) % tiles_m;  // start with the rows this rank contributed itself
-  return b_mn ? p_launch<false, true, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f) : p_launch<false, false, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f);
+  return b_mn ? p_launch<false, true, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd)
+              : p_launch<false, false, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd);
 }
+
+// Registers (ws != nullptr) or removes the fp32 workspace that lets launches on the CURRENT device cut the tiles of
+// their last round along K: `tiles` slabs of 256 x 256 floats (contents do not matter), owned by the caller for as long as it is
+// registered.  Only launches on `stream` use it (launches on other streams run unsplit), so two launches never write it at once.
+// Returns 0, or NTB_ERR_ARG.
+NTB_EXPORT int ntb_gemm2_set_workspace(float* ws, int tiles, cudaStream_t stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || (ws != nullptr && (tiles <= 0 || (reinterpret_cast<uintptr_t>(ws) & 127)))) return NTB_ERR_ARG;
+  g_p_ws[dev] = ws;
+  g_p_ws_tiles[dev] = ws ? tiles : 0;
+  g_p_ws_stream[dev] = stream;
+  return NTB_OK;
+}
+
+// Non-zero switches the split of the last round on for every launch that has a workspace, 0 (the default) off.
+NTB_EXPORT void ntb_gemm2_enable_split(int on) { g_p_split_enabled = on != 0; }
 
 // Partial product A @ B^T (or A @ B when b_mn) whose rows [r*rs_rows, (r+1)*rs_rows) are stored (bf16) into rank r's staging slot `me`
 // (same contract as ntb_gemm_bf16_rs).

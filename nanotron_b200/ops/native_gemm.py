@@ -23,6 +23,38 @@ def set_variant(name: str):
     VARIANT["kernel"] = name
 _STATUS = {}
 _SMS = {}
+_WORKSPACE = {}  # device -> (fp32 tensor, stream handle) registered with the pair kernel
+SPLIT_SLABS = 74  # one workspace slab per CTA pair is the most a launch can use
+
+
+def ensure_workspace(device) -> None:
+    """The pair kernel cuts the tiles of a launch's last, partly filled round along K so that every CTA pair shares the tail;
+    each chunk parks its fp32 partial sums in a slab of this scratch (19 MB per device) and a fix-up pass sums them in a fixed
+    order.  The scratch belongs to the stream that first launched a GEMM on the device; launches on other streams run unsplit."""
+    key = str(device)
+    if key in _WORKSPACE or not _HAS["pair"]:
+        return
+    from nanotron_b200.ops import native
+
+    L = native.lib()
+    if not hasattr(L, "ntb_gemm2_set_workspace"):
+        _WORKSPACE[key] = None
+        return
+    ws = torch.empty(SPLIT_SLABS * 256 * 256, dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream(device).cuda_stream
+    with torch.cuda.device(device):
+        native._check(L.ntb_gemm2_set_workspace(ws.data_ptr(), SPLIT_SLABS, stream), "gemm2 workspace")
+    _WORKSPACE[key] = (ws, stream)
+
+
+def set_split(on: bool) -> None:
+    """True lets pair-kernel launches cut the tiles of their last round along K (off by default: on Llama-3-8B shapes it measured
+    within +-5 % of whole tiles, because a power-capped B200 is bound by total work rather than by rounds of tiles)."""
+    from nanotron_b200.ops import native
+
+    L = native.lib()
+    if hasattr(L, "ntb_gemm2_enable_split"):
+        L.ntb_gemm2_enable_split(1 if on else 0)
 
 
 def declare(L):
@@ -34,6 +66,11 @@ def declare(L):
     if _HAS["pair"]:
         L.ntb_gemm2_bf16.restype = c_int
         L.ntb_gemm2_bf16.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+        if hasattr(L, "ntb_gemm2_set_workspace"):
+            L.ntb_gemm2_set_workspace.restype = c_int
+            L.ntb_gemm2_set_workspace.argtypes = [c_void_p, c_int, c_void_p]
+            L.ntb_gemm2_enable_split.restype = None
+            L.ntb_gemm2_enable_split.argtypes = [c_int]
 
 
 def status_word(device) -> torch.Tensor:
@@ -88,7 +125,10 @@ def _launch(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode):
 
     dev = a.device
     L = native.lib()
-    fn = L.ntb_gemm2_bf16 if (VARIANT["kernel"] == "pair" and _HAS["pair"]) else L.ntb_gemm_bf16
+    pair = VARIANT["kernel"] == "pair" and _HAS["pair"]
+    fn = L.ntb_gemm2_bf16 if pair else L.ntb_gemm_bf16
+    if pair:
+        ensure_workspace(dev)
     with torch.cuda.device(dev):
         rc = fn(a.data_ptr(), b.data_ptr(), d.data_ptr(), M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(dev).data_ptr(), _sms(dev), torch.cuda.current_stream(dev).cuda_stream)
     if rc != 0:
@@ -97,6 +137,7 @@ def _launch(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode):
                 f"a={tuple(a.shape)}/{a.stride()}/{a.dtype}/ptr%16={a.data_ptr() % 16} b={tuple(b.shape)}/{b.stride()}/{b.dtype}/ptr%16={b.data_ptr() % 16} "
                 f"d={tuple(d.shape)}/{d.stride()}/{d.dtype}/ptr%16={d.data_ptr() % 16}")
         native._check(rc, what)
+    native._check(0, "gemm_tcgen05")  # counts the launch
     return d
 
 

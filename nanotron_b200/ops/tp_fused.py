@@ -121,6 +121,9 @@ class TPFusedContext:
         N = weight.shape[1] if b_mn else weight.shape[0]
         K = x2.shape[1]
         out = torch.empty((self.world * M, N), dtype=x2.dtype, device=x2.device)
+        from nanotron_b200.ops import native_gemm
+
+        native_gemm.ensure_workspace(x2.device)
         rc = self._entry("ag")(gathered.data_ptr(), weight.data_ptr(), out.data_ptr(), self.world * M, N, K, K, weight.stride(0), N, int(b_mn), flags.tensor.data_ptr(), M, self.rank, self.world, epoch, self.status.data_ptr(), self.sms, torch.cuda.current_stream().cuda_stream)
         native._check(rc, "gemm_bf16_ag")
         return out, gathered

@@ -64,6 +64,7 @@ def _doremi_run(out_file):
     import nanotron_b200.distributed as dist
 
     train = _load("examples/doremi/train_doremi.py", "train_doremi_example")
+    os.chdir(os.path.dirname(out_file))  # the example's relative checkpoints_path lands in the test's scratch directory
     t = dr.DoReMiTrainer(os.path.join(ROOT, "examples", "doremi", "config_tiny_doremi.yaml"))  # YAML with the extra section
     assert isinstance(t.config, dr.DoReMiConfig) and t.config.doremi.domain_names == ["counting", "noise"]
     assert isinstance(t.unwrapped_model, dr.LlamaForDoReMiTraining) and isinstance(t.ref_model, dr.LlamaReferenceForDoReMi)

@@ -186,3 +186,36 @@ def test_trainer_writes_heartbeats(tmp_path):
         t.parallel_context.destroy()
     finally:
         del os.environ["NANOTRON_HEARTBEAT_DIR"], os.environ["NANOTRON_HEARTBEAT_INTERVAL"]
+
+
+def _reference_arm_guard(marker_dir):
+    """Rank 1's "training loop" raises; rank 0 sits in a receive that nobody will match.  The guard of the benchmark's
+    reference arm must end both ranks with exit code 0 and rank 0 must be the one that reports."""
+    import sys
+
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.parallel import ParallelContext
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+    import run_reference
+
+    ctx = ParallelContext(1, 1, 2)
+    rank = dist.get_rank(ctx.world_pg)
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = str(rank), "2"
+    run_reference._unavailable = lambda why: open(os.path.join(marker_dir, f"reported_{rank}"), "w").write(why)
+    guard = run_reference._Guard(deadline_s=60.0)
+    guard.start()
+    if rank == 1:
+        guard.fail("reference failed on its stock path: Boom")
+        raise AssertionError("fail() returned on a rank other than 0 of a multi-rank job")
+    t = torch.ones(1)
+    torch.distributed.recv(t, src=1)  # never matched: only the guard's watcher can end this rank
+    raise AssertionError("unmatched receive returned")
+
+
+def test_reference_arm_guard_ends_every_rank_when_one_fails(tmp_path):
+    t0 = time.time()
+    run_distributed(_reference_arm_guard, 2, marker_dir=str(tmp_path))
+    assert time.time() - t0 < 60
+    assert os.listdir(tmp_path) == ["reported_0"]
+    assert "Boom" in open(tmp_path / "reported_0").read()

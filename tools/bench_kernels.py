@@ -1,6 +1,7 @@
 """Micro-benchmarks of the in-tree kernels against their roofline (run on a B200).
 
     python tools/bench_kernels.py gemm            # tcgen05 GEMM vs the library GEMM on Llama-3-8B shapes
+    python tools/bench_kernels.py gemm-split      # tensor-parallel per-rank shapes: last round split along K vs whole tiles
     python tools/bench_kernels.py elementwise     # HBM-bound kernels vs measured copy bandwidth
     python tools/bench_kernels.py attention
 
@@ -74,6 +75,45 @@ def bench_gemm(small: bool = False):
         for k, ms in rows.items():
             tf = flops / ms / 1e9
             print(f"{name:8s} M={M} N={N} K={K}  {k:42s} {ms:8.3f} ms  {tf:7.1f} TFLOP/s  {tf / peak:5.2f} of measured peak", flush=True)
+        g.check_status("cuda")
+        del xs, ws, dys, acc
+        torch.cuda.empty_cache()
+
+
+def bench_gemm_split():
+    """Per-rank Llama-3-8B shapes under tp 2 / tp 4, whose tile counts do not fill the last round of the 74 CTA pairs: the pair
+    kernel with and without the split of that round along K, against the library GEMM."""
+    from nanotron_b200.ops import native, native_gemm as g
+
+    native.lib()
+    peak = _peaks()["bf16_tflops"]
+    shapes = [("qkv tp4", 4096, 1536, 4096), ("qkv tp2", 4096, 3072, 4096), ("o tp4 dgrad-like", 4096, 4096, 1024), ("gate_up tp4", 4096, 7168, 4096),
+              ("gate_up tp2", 4096, 14336, 4096), ("down tp4", 4096, 4096, 3584), ("down tp2", 4096, 4096, 7168), ("qkv tp1", 4096, 6144, 4096)]
+    for name, M, N, K in shapes:
+        nbuf = max(2, int(300e6 // ((M * K + N * K) * 2)) + 1)
+        xs = [torch.randn(M, K, device="cuda", dtype=torch.bfloat16) for _ in range(nbuf)]
+        ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(nbuf)]
+        dys = [torch.randn(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        acc = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+        i = [0]
+
+        def nxt():
+            i[0] = (i[0] + 1) % nbuf
+            return i[0]
+
+        flops = 2.0 * M * N * K
+        rows = {}
+        for label, on in (("split", True), ("whole tiles", False)):
+            g.set_split(on)
+            rows[f"fwd   pair kernel, {label}"] = time_fn(lambda: g.gemm_nt(xs[nxt()], ws[i[0]]))
+            rows[f"dgrad pair kernel, {label}"] = time_fn(lambda: g.gemm_nn(dys[nxt() % 2], ws[i[0]]))
+            rows[f"wgrad pair kernel (+= fp32), {label}"] = time_fn(lambda: g.gemm_tn_accum_fp32(dys[nxt() % 2], xs[i[0]], acc))
+        g.set_split(False)
+        rows["fwd   library"] = time_fn(lambda: torch.nn.functional.linear(xs[nxt()], ws[i[0]]))
+        rows["dgrad library"] = time_fn(lambda: dys[nxt() % 2].matmul(ws[i[0]]))
+        for k, ms in rows.items():
+            tf = flops / ms / 1e9
+            print(f"{name:18s} M={M} N={N} K={K}  {k:42s} {ms:8.3f} ms  {tf:7.1f} TFLOP/s  {tf / peak:5.2f} of measured peak", flush=True)
         g.check_status("cuda")
         del xs, ws, dys, acc
         torch.cuda.empty_cache()
@@ -214,6 +254,8 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     if what == "gemm":
         bench_gemm(small="--small" in sys.argv)
+    elif what == "gemm-split":
+        bench_gemm_split()
     elif what == "elementwise":
         bench_elementwise()
     elif what == "fp8":
