@@ -50,6 +50,7 @@ struct PFuse {
   int m_rot = 0;                        // rotation of the tile rows, in 256-row pair tiles
   const uint32_t* ag_flags = nullptr;   // local flag words [world]
   int ag_rows = 0;                      // rows per gathered block (multiple of 128)
+  int ag_local = 0;                     // 1: this rank's own block is read through tmap_al (its source tensor) and needs no flag
   uint32_t* rs_flags[P_TP_MAX] = {};    // per-owner flag words [world]
   int rs_rows = 0;                      // rows per owner (multiple of 32)
   unsigned int* done_counter = nullptr; // local counter, zero before launch
@@ -154,7 +155,7 @@ template <bool A_MN, bool B_MN, int OUT, int P_STAGES>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_d,
                      int M, int N, int K, int band, int* __restrict__ status, const __grid_constant__ PFuse fuse, const __grid_constant__ PPeerMaps pmaps,
-                     const __grid_constant__ PSched sched, const __grid_constant__ CUtensorMap tmap_ws) {
+                     const __grid_constant__ PSched sched, const __grid_constant__ CUtensorMap tmap_ws, const __grid_constant__ CUtensorMap tmap_al) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + P_MAX_STAGES * P_STAGE_BYTES;
@@ -213,9 +214,12 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         tc.m_blk = (tc.m_blk + fuse.m_rot) % tiles_m;
         const int m0 = (tc.m_blk * 2 + static_cast<int>(cta)) * P_BLOCK_M;           // this CTA's rows of A
         const int n0 = tc.n_blk * P_BLOCK_N + static_cast<int>(cta) * P_HALF_N;      // this CTA's half of B
+        bool a_local = false;
         if (fuse.ag_flags != nullptr && m0 < M) {
           const int src = min(fuse.world - 1, m0 / fuse.ag_rows);  // ag_rows is a multiple of 128: one source per CTA row block
-          if (!(ag_ready & (1u << src))) {
+          if (fuse.ag_local && src == fuse.me) {
+            a_local = true;  // own rows come straight from the tensor they were pushed from: nothing to wait for
+          } else if (!(ag_ready & (1u << src))) {
             const uint64_t t0 = ptx::globaltimer();
             while (true) {
               uint32_t v;
@@ -242,6 +246,7 @@ gemm2_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           const uint32_t fb = map_to_cta(ptx::smem_u32(&full_bar[s]), 0);  // bytes of both CTAs are counted on the leader's barrier
           if (A_MN) tma2_load_3d(sa, &tmap_a, fb, 0, kb * P_BLOCK_K, m0 / 64);
+          else if (a_local) tma2_load_2d(sa, &tmap_al, fb, kb * P_BLOCK_K, m0 - fuse.me * fuse.ag_rows);
           else      tma2_load_2d(sa, &tmap_a, fb, kb * P_BLOCK_K, m0);
           if (B_MN) tma2_load_3d(sb, &tmap_b, fb, 0, kb * P_BLOCK_K, n0 / 64);
           else      tma2_load_2d(sb, &tmap_b, fb, kb * P_BLOCK_K, n0);
@@ -525,7 +530,7 @@ bool p_map_out(CUtensorMap* m, void* ptr, int64_t rows, int64_t cols, int64_t ld
 
 template <bool A_MN, bool B_MN, int OUT, int ST = P_MAX_STAGES>
 int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, int M, int N, int K, int* status, int num_sms, cudaStream_t stream,
-             const PFuse& fuse = PFuse(), const PPeerMaps* pmaps = nullptr, void* d_out = nullptr, int64_t ldd = 0) {
+             const PFuse& fuse = PFuse(), const PPeerMaps* pmaps = nullptr, void* d_out = nullptr, int64_t ldd = 0, const CUtensorMap* tal = nullptr) {
   static const PPeerMaps no_maps = {};
   const PPeerMaps& pm = pmaps ? *pmaps : no_maps;
   auto kern = gemm2_tcgen05_kernel<A_MN, B_MN, OUT, ST>;
@@ -568,7 +573,7 @@ int p_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   if (band < 2) band = 2;
   if (band > tiles_m) band = tiles_m;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status, fuse, pm, sched, tws) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, td, M, N, K, band, status, fuse, pm, sched, tws, tal ? *tal : ta) != cudaSuccess) {
     cudaGetLastError();
     return NTB_ERR_LAUNCH;
   }
@@ -616,14 +621,17 @@ NTB_EXPORT int ntb_gemm2_bf16(const void* a, const void* b, void* d, int M, int 
 
 // D = gathered_A @ B^T (or @ B when b_mn) where gathered_A = [world * ag_rows, K] is filled by ntb_tp_allgather_push on every rank
 // (same contract as ntb_gemm_bf16_ag; ag_rows must be a multiple of 128 here).
-NTB_EXPORT int ntb_gemm2_bf16_ag(const void* a_gathered, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int b_mn,
-                                 const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status, int num_sms, cudaStream_t stream) {
+static int p_gemm_ag(const void* a_gathered, const void* a_local, int64_t lda_local, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb,
+                     int64_t ldd, int b_mn, const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status, int num_sms,
+                     cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || !p_get_encode() || world < 1 || world > P_TP_MAX || ag_rows <= 0 || ag_rows % P_BLOCK_M || ag_flags == nullptr) return NTB_ERR_ARG;
-  if ((reinterpret_cast<uintptr_t>(a_gathered) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d)) & 15) return NTB_ERR_ARG;
-  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) || ldd % 8) return NTB_ERR_ARG;
+  if (me < 0 || me >= world || static_cast<int64_t>(ag_rows) * world != M) return NTB_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(a_gathered) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(a_local)) & 15) return NTB_ERR_ARG;
+  if (lda % 8 || (b_mn ? (ldb % 64 || N % 64) : (ldb % 8)) || ldd % 8 || (a_local != nullptr && lda_local % 8)) return NTB_ERR_ARG;
   if (num_sms <= 1) num_sms = 148;
-  CUtensorMap ta, tb, td;
+  CUtensorMap ta, tb, td, tal;
   if (!p_map_kmajor(&ta, a_gathered, M, K, lda)) return NTB_ERR_ARG;
+  if (a_local != nullptr && !p_map_kmajor(&tal, a_local, ag_rows, K, lda_local)) return NTB_ERR_ARG;
   if (!(b_mn ? p_map_mnmajor(&tb, b, N, K, ldb) : p_map_kmajor(&tb, b, N, K, ldb))) return NTB_ERR_ARG;
   if (!p_map_out(&td, d, M, N, ldd, false)) return NTB_ERR_ARG;
   PFuse f;
@@ -632,10 +640,28 @@ NTB_EXPORT int ntb_gemm2_bf16_ag(const void* a_gathered, const void* b, void* d,
   f.epoch = epoch;
   f.ag_flags = ag_flags;
   f.ag_rows = ag_rows;
+  f.ag_local = a_local != nullptr ? 1 : 0;
   const int tiles_m = (M + 2 * P_BLOCK_M - 1) / (2 * P_BLOCK_M);
   f.m_rot = ((me * ag_rows) / (2 * P_BLOCK_M)) % tiles_m;  // start with the rows this rank contributed itself
-  return b_mn ? p_launch<false, true, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd)
-              : p_launch<false, false, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd);
+  const CUtensorMap* pl = a_local != nullptr ? &tal : nullptr;
+  return b_mn ? p_launch<false, true, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd, pl)
+              : p_launch<false, false, P_OUT_BF16>(ta, tb, td, M, N, K, status, num_sms, stream, f, nullptr, d, ldd, pl);
+}
+
+// D = gathered_A @ B^T (or @ B when b_mn) where gathered_A = [world * ag_rows, K] is filled by ntb_tp_allgather_push on every rank.
+NTB_EXPORT int ntb_gemm2_bf16_ag(const void* a_gathered, const void* b, void* d, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int b_mn,
+                                 const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status, int num_sms, cudaStream_t stream) {
+  return p_gemm_ag(a_gathered, nullptr, 0, b, d, M, N, K, lda, ldb, ldd, b_mn, ag_flags, ag_rows, me, world, epoch, status, num_sms, stream);
+}
+
+// Same product, but rows [me * ag_rows, (me + 1) * ag_rows) are read from `a_local` (the tensor this rank pushes, row pitch
+// lda_local) instead of from the gather buffer.  The launch then depends on no kernel of its own GPU, so the caller may run this
+// rank's push on another stream at the same time; only the peers' blocks are waited for (bounded).
+NTB_EXPORT int ntb_gemm2_bf16_ag_local(const void* a_gathered, const void* a_local, int64_t lda_local, const void* b, void* d, int M, int N, int K, int64_t lda,
+                                       int64_t ldb, int64_t ldd, int b_mn, const uint32_t* ag_flags, int ag_rows, int me, int world, uint32_t epoch, int* status,
+                                       int num_sms, cudaStream_t stream) {
+  if (a_local == nullptr) return NTB_ERR_ARG;
+  return p_gemm_ag(a_gathered, a_local, lda_local, b, d, M, N, K, lda, ldb, ldd, b_mn, ag_flags, ag_rows, me, world, epoch, status, num_sms, stream);
 }
 
 // Registers (ws != nullptr) or removes the fp32 workspace that lets launches on the CURRENT device cut the tiles of

@@ -74,6 +74,10 @@ def _declare(L):
             if hasattr(L, "ntb_gemm2_bf16_ag"):
                 L.ntb_gemm2_bf16_ag.restype = c_int
                 L.ntb_gemm2_bf16_ag.argtypes = L.ntb_gemm_bf16_ag.argtypes
+                if hasattr(L, "ntb_gemm2_bf16_ag_local"):
+                    a = L.ntb_gemm_bf16_ag.argtypes
+                    L.ntb_gemm2_bf16_ag_local.restype = c_int
+                    L.ntb_gemm2_bf16_ag_local.argtypes = [a[0], c_void_p, c_int64] + list(a[1:])
                 L.ntb_gemm2_bf16_rs.restype = c_int
                 L.ntb_gemm2_bf16_rs.argtypes = L.ntb_gemm_bf16_rs.argtypes
             L.ntb_tp_reduce_slots.restype = c_int

@@ -28,8 +28,9 @@ def check_ops(ctx):
     torch.manual_seed(1234 + rank)
     M, K, N = 512, 1024, 1536
     results = {}
-    for fused in (False, True):
-        tp_fused.ENABLED = fused
+    for fused in (False, True, "overlapped push"):  # the last: this rank's push on a side stream beside the GEMM
+        tp_fused.ENABLED = bool(fused)
+        tp_fused.OVERLAP_PUSH = fused == "overlapped push"
         tp_fused._CONTEXTS.clear()
         torch.manual_seed(7 + rank)
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
@@ -48,12 +49,14 @@ def check_ops(ctx):
             assert c.ag_calls >= 2 and c.rs_calls >= 2, (c.ag_calls, c.rs_calls)  # forward + backward of each linear went through the fused kernels
             if rank == 0:
                 print(f"  fused kernel calls: all-gather(+GEMM) {c.ag_calls}, GEMM+reduce-scatter {c.rs_calls}")
+    tp_fused.OVERLAP_PUSH = False
     names = ["column out", "row out", "dx", "dW column", "dW row"]
-    for n, a, b in zip(names, results[True], results[False]):
-        e = rel(a, b)
-        if rank == 0:
-            print(f"  {n:12s} rel err fused vs nccl = {e:.3e}")
-        assert e < 2e-2, (n, e)
+    for key in (True, "overlapped push"):
+        for n, a, b in zip(names, results[key], results[False]):
+            e = rel(a, b)
+            if rank == 0:
+                print(f"  {n:12s} rel err fused{'' if key is True else ' (' + key + ')'} vs nccl = {e:.3e}")
+            assert e < 2e-2, (n, e)
 
 
 def train(fused: bool, steps=4):
