@@ -105,7 +105,7 @@ class Qwen2Attention(nn.Module, LogMixin):
             )
         self.attn_impl = config._attn_implementation or "flash_attention_2"
         if self.cp_size > 1 and self.attn_impl not in ("ring", "llama3_ring_attention", "ring_flash_triton", "ring_fused"):
-            self.attn_impl = "ring"
+            self.attn_impl = "llama3_ring_attention"  # the all-gather variant; "ring" passes K / V blocks around instead
         self.attention = ALL_ATTENTION_FUNCTIONS[self.attn_impl]
         self.sliding_window_size = getattr(config, "sliding_window_size", None)
         self.log_attn_probs = getattr(config, "log_attn_probs", False)

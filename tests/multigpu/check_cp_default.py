@@ -1,4 +1,5 @@
-"""Run with torchrun on 2+ GPUs: the default context-parallel attention (differentiable NCCL all-gather of K / V, then the
+"""Run with torchrun on 2+ GPUs: the context-parallel attention variants "allgather" (default) and "ring" (K / V blocks sent
+around the group, partial results merged by log-sum-exp).  The default context-parallel attention (differentiable NCCL all-gather of K / V, then the
 variable-length attention kernel on each zig-zag query chunk against the key prefix that ends with it) against full-sequence causal
 attention computed in fp32 -- forward output and the gradients of q, k and v.  Both attention selections are checked: the in-tree
 kernels (default) and the library kernel with its explicit bottom-right aligned mask.
@@ -46,15 +47,17 @@ def main():
             loc = lambda t: zigzag(t, rank, world, 1).reshape(B * 2 * chunk, t.shape[2], D).contiguous()
             ql, kl, vl = (loc(t).detach().requires_grad_(True) for t in (q, k, v))
             pos = torch.zeros(B, 2 * chunk, dtype=torch.long, device="cuda")  # only its shape is read
-            out = ring_attention(ql, kl, vl, cp_pg=group, causal=True, variant="allgather", position_ids=pos)
-            out.backward(loc(g))
-            torch.cuda.synchronize()
-            checks = {"out": (out, loc(ref_o)), "dq": (ql.grad, loc(ref_dq)), "dk": (kl.grad, loc(ref_dk)), "dv": (vl.grad, loc(ref_dv))}
-            for name, (got, exp) in checks.items():
-                err = ((got.float() - exp.float()).abs().max() / exp.float().abs().max()).item()
-                if rank == 0:
-                    print(f"attention={mode:5s} chunk {chunk:4d} {name:3s} rel err vs fp32 full attention = {err:.3e}")
-                assert err < 3e-2, (mode, chunk, name, err)
+            for variant in ("allgather", "ring"):
+                ql.grad = kl.grad = vl.grad = None
+                out = ring_attention(ql, kl, vl, cp_pg=group, causal=True, variant=variant, position_ids=pos)
+                out.backward(loc(g))
+                torch.cuda.synchronize()
+                checks = {"out": (out, loc(ref_o)), "dq": (ql.grad, loc(ref_dq)), "dk": (kl.grad, loc(ref_dk)), "dv": (vl.grad, loc(ref_dv))}
+                for name, (got, exp) in checks.items():
+                    err = ((got.float() - exp.float()).abs().max() / exp.float().abs().max()).item()
+                    if rank == 0:
+                        print(f"attention={mode:5s} {variant:9s} chunk {chunk:4d} {name:3s} rel err vs fp32 full attention = {err:.3e}")
+                    assert err < 3e-2, (mode, variant, chunk, name, err)
     ops.set_attention("auto")
     if rank == 0:
         print("CP_DEFAULT_OK")

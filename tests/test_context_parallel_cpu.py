@@ -3,23 +3,23 @@ import torch
 from helpers import run_distributed
 
 
-def _check_cp_attention():
+def _check_cp_attention(variant="allgather", cp=2):
     import nanotron_b200.distributed as dist
     from nanotron_b200.ops import reference as ref
     from nanotron_b200.parallel import ParallelContext
     from nanotron_b200.parallel.context_parallel.ring_attention import ring_attention
     from nanotron_b200.parallel.context_parallel.zigzag import zigzag_positions, zigzag_slice, zigzag_unshard
 
-    ctx = ParallelContext(tensor_parallel_size=1, pipeline_parallel_size=1, data_parallel_size=1, context_parallel_size=2)
-    rank, cp = dist.get_rank(ctx.cp_pg), 2
+    ctx = ParallelContext(tensor_parallel_size=1, pipeline_parallel_size=1, data_parallel_size=1, context_parallel_size=cp)
+    rank = dist.get_rank(ctx.cp_pg)
     torch.manual_seed(0)
-    b, S, Hq, Hkv, D = 2, 16, 4, 2, 8
+    b, S, Hq, Hkv, D = 2, 8 * cp, 4, 2, 8
     q = torch.randn(b, S, Hq, D, dtype=torch.float64)
     k = torch.randn(b, S, Hkv, D, dtype=torch.float64)
     v = torch.randn(b, S, Hkv, D, dtype=torch.float64)
     ql, kl, vl = (zigzag_slice(t, rank, cp, dim=1).reshape(-1, t.shape[2], D).clone().requires_grad_(True) for t in (q, k, v))
     pos = zigzag_positions(S, rank, cp).unsqueeze(0).expand(b, -1)
-    out = ring_attention(ql, kl, vl, cp_pg=ctx.cp_pg, position_ids=pos)
+    out = ring_attention(ql, kl, vl, cp_pg=ctx.cp_pg, position_ids=pos, variant=variant)
     # oracle: full attention on one device
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
     cu = torch.arange(0, (b + 1) * S, S, dtype=torch.int32)
@@ -40,6 +40,13 @@ def _check_cp_attention():
 
 def test_zigzag_context_parallel_attention_matches_full():
     run_distributed(_check_cp_attention, 2)
+
+
+def test_send_recv_ring_variant_matches_full_attention():
+    """K / V blocks passed around the group (registry names "ring", "ring_flash_triton"): forward and all three gradients
+    against full attention, on 2 ranks and on 4 (blocks from lower and from higher ranks, several hops)."""
+    run_distributed(_check_cp_attention, 2, variant="ring", cp=2)
+    run_distributed(_check_cp_attention, 4, variant="ring", cp=4)
 
 
 def test_merge_attention_states():
