@@ -458,6 +458,27 @@ def model_config_from_dict(d: dict):
     return from_dict(Qwen2Config, d)
 
 
+def _declared_model_config_class(config_class: Type) -> Optional[Type]:
+    """The dataclass a ``Config`` subclass declares for ``model.model_config`` (None when it keeps the stock union), so that
+    an extended config round-trips through YAML without the caller naming the class again."""
+    import dataclasses
+    import typing
+
+    def concrete(tp):
+        if typing.get_origin(tp) is Union:
+            args = [a for a in typing.get_args(tp) if a is not type(None)]
+            tp = args[0] if len(args) == 1 else None
+        return tp if (isinstance(tp, type) and dataclasses.is_dataclass(tp)) else None
+
+    try:
+        model_args = concrete(typing.get_type_hints(config_class).get("model"))
+        if model_args is None or model_args is ModelArgs:
+            return None
+        return concrete(typing.get_type_hints(model_args).get("model_config"))
+    except Exception:
+        return None
+
+
 def get_config_from_dict(config_dict: dict, config_class: Type = Config, skip_unused_config_keys: bool = False, skip_null_keys: bool = False, model_config_class: Optional[Type] = None):
     if skip_unused_config_keys:
         known = {f.name for f in fields(config_class)}
@@ -467,6 +488,8 @@ def get_config_from_dict(config_dict: dict, config_class: Type = Config, skip_un
     config_dict = dict(config_dict)
     # resolve the model config by discriminator before the strict loader sees the Union
     model = config_dict.get("model")
+    if model_config_class is None:
+        model_config_class = _declared_model_config_class(config_class)
     if isinstance(model, dict) and isinstance(model.get("model_config"), dict):
         model = dict(model)
         raw = model["model_config"]

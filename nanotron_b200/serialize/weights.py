@@ -149,6 +149,14 @@ def load_weights(model: nn.Module, parallel_context: ParallelContext, root_folde
         else:
             sharded_info, is_expert, exp_tp_pp = None, False, None
         path = get_path(base_name, type=ObjectType.MODEL, exp_tp_pp_rank_and_size=exp_tp_pp, prefix=param_root_folder, is_expert_sharded=is_expert)
+        if not path.exists() and param.is_tied and hasattr(model, "get_embeddings_lm_head_tied_names"):
+            # a tie across pipeline stages joins parameters with different names (embedding / lm head) and only the first rank
+            # of the tie group writes, under ITS name: the other members read that file
+            for other in model.get_embeddings_lm_head_tied_names():
+                alt = get_path(other, type=ObjectType.MODEL, exp_tp_pp_rank_and_size=exp_tp_pp, prefix=param_root_folder, is_expert_sharded=is_expert)
+                if other != base_name and (alt.exists() or alt.parent.exists()):
+                    base_name, path = other, alt
+                    break
         if path.exists():
             with safe_open(path, framework="pt", device=str(param_or_buffer.device)) as fi:
                 if param.is_sharded:
