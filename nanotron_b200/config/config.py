@@ -430,7 +430,8 @@ class Config:
             yaml.dump(config_dict, f, sort_keys=False)
         if sanity_checks:
             # re-parse what was written: a config that cannot be read back is a bug
-            get_config_from_file(file_path, config_class=self.__class__)
+            custom = type(self.model.model_config) if self.model is not None and type(self.model.model_config) not in (LlamaConfig, Qwen2Config, Starcoder2Config) else None
+            get_config_from_file(file_path, config_class=self.__class__, model_config_class=custom)
 
     def get_yaml(self) -> str:
         return yaml.dump(serialize(self), sort_keys=False)

@@ -95,7 +95,7 @@ class CausalSelfAttention(_q.Qwen2Attention):
         store.update({"key": k_all, "value": v_all, "mask": m_all, "past_len": past_len + sequence_mask.long().sum(-1)})
         from nanotron_b200.nn.attention import cached_attention
 
-        out = cached_attention(q, k_all, v_all, sequence_mask.bool(), m_all, softmax_scale=1.0 / (self.head_dim**0.5), sliding_window=self.sliding_window_size)
+        out = cached_attention(q, k_all, v_all, sequence_mask.bool(), m_all, softmax_scale=self.softmax_scale if self.softmax_scale is not None else 1.0 / (self.head_dim**0.5), sliding_window=self.sliding_window_size)
         out = out.reshape(T, self.local_q_size).to(hidden_states.dtype)
         return {"hidden_states": self.o_proj(out), "sequence_mask": sequence_mask}
 

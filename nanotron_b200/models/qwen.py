@@ -103,6 +103,8 @@ class Qwen2Attention(nn.Module, LogMixin):
                 dim=self.head_dim, max_seq_len=config.max_position_embeddings, base=config.rope_theta,
                 interleaved=config.rope_interleaved, seq_len_scaling_factor=getattr(config, "rope_seq_len_interpolation_factor", None),
             )
+        # spectral muP scales attention logits by 1 / head_dim instead of 1 / sqrt(head_dim) (reference models/llama.py:289)
+        self.softmax_scale = 1.0 / self.head_dim if getattr(config, "is_using_mup", False) else None
         self.attn_impl = config._attn_implementation or "flash_attention_2"
         if self.cp_size > 1 and self.attn_impl not in ("ring", "llama3_ring_attention", "ring_flash_triton", "ring_fused"):
             self.attn_impl = "llama3_ring_attention"  # the all-gather variant; "ring" passes K / V blocks around instead
@@ -123,10 +125,10 @@ class Qwen2Attention(nn.Module, LogMixin):
             else:
                 cos = sin = None
                 interleaved = False
-            out = ops.fused_qkv_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, cu, s, causal=True, window=self.sliding_window_size, interleaved=interleaved, use_rope=self.use_rope)
+            out = ops.fused_qkv_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, cu, s, causal=True, softmax_scale=self.softmax_scale, window=self.sliding_window_size, interleaved=interleaved, use_rope=self.use_rope)
             out = self.o_proj(out.reshape(T, self.local_q_size))
             return {"hidden_states": out, "position_ids": position_ids}
-        if self.cp_size == 1 and self.attn_impl == "flash_attention_2" and ops.fused_qkv_library_attention_supported(qkv, self.head_dim, self.sliding_window_size, cu_seqlens):
+        if self.cp_size == 1 and self.softmax_scale is None and self.attn_impl == "flash_attention_2" and ops.fused_qkv_library_attention_supported(qkv, self.head_dim, self.sliding_window_size, cu_seqlens):
             b, s = position_ids.shape
             if self.use_rope:
                 self.rotary_emb._ensure_tables(self.rotary_emb.max_seq_len, qkv.device)
@@ -150,7 +152,7 @@ class Qwen2Attention(nn.Module, LogMixin):
             max_len = s
         out = self.attention(
             q, k, v, cu_seqlens_q=cu_seqlens, cu_seqlens_k=cu_seqlens, max_seqlen_q=max_len, max_seqlen_k=max_len, causal=True,
-            sliding_window=self.sliding_window_size, cp_pg=self.cp_pg, position_ids=position_ids,
+            softmax_scale=self.softmax_scale, sliding_window=self.sliding_window_size, cp_pg=self.cp_pg, position_ids=position_ids,
             flex_attention_mask=getattr(self.config, "flex_attention_mask", None),
         )
         out = self.o_proj(out.reshape(T, self.local_q_size))

@@ -158,3 +158,75 @@ def test_mamba_example_under_tensor_and_pipeline_parallelism(tmp_path):
     run_distributed(_mamba_run, 4, out_file=out, tp=2, pp=2, steps=30)
     losses = torch.load(out)["losses"]
     assert losses[-1] < losses[0] and all(l == l for l in losses), losses[::5]
+
+
+def test_mup_example_keeps_logits_stable_across_widths(tmp_path, monkeypatch):
+    """examples/mup: under the spectral parametrisation the output logits of a freshly initialised model have the same size at
+    width 64 and at width 256; under the standard one (one std for every matrix) they grow with sqrt(width)."""
+    from helpers import dummy_dataloader, single_process_env
+
+    from nanotron_b200.trainer import DistributedTrainer
+
+    mup = _load("examples/mup/config_mup_llama.py", "config_mup_llama_example")
+    monkeypatch.chdir(tmp_path)
+    single_process_env()
+    stds = {}
+    for use_mup in (True, False):
+        for width in (64, 256):
+            cfg = mup.build(use_mup, hidden_size=width, layers=2, heads=4, vocab=512, seq=32, mbs=2, acc=1, dp=1, steps=2, lr=1e-3, dtype="float32")
+            cfg.checkpoints.checkpoint_interval = 10**6
+            cfg.checkpoints.save_final_state = False
+            t = DistributedTrainer(cfg)
+            assert t.model_config.is_using_mup == use_mup
+            torch.manual_seed(0)
+            ids = torch.randint(0, 512, (2, 32))
+            with torch.no_grad():
+                logits = t.unwrapped_model.model(input_ids=ids, input_mask=torch.ones(2, 32, dtype=torch.bool))
+            stds[(use_mup, width)] = float(logits.float().std())
+            if use_mup and width == 64:
+                t.prepare_training()
+                _, loss, _ = t.training_step(dummy_dataloader(t))
+                assert torch.isfinite(loss)
+            t.parallel_context.destroy()
+    assert 0.8 < stds[(True, 256)] / stds[(True, 64)] < 1.25, stds
+    assert 1.6 < stds[(False, 256)] / stds[(False, 64)] < 2.4, stds
+
+
+def _llamoe_run(out_file):
+    sys.path.insert(0, os.path.join(ROOT, "examples", "moe"))
+    import nanotron_b200.distributed as dist
+    from helpers import dummy_dataloader
+
+    cfgmod = _load("examples/moe/config_llamoe.py", "config_llamoe")
+    sys.modules["config_llamoe"] = cfgmod  # train_moe imports it by this name
+    train = _load("examples/moe/train_moe.py", "train_moe_example")
+    import llamoe
+
+    os.chdir(os.path.dirname(out_file))
+    cfg = cfgmod.build(hidden_size=32, layers=2, heads=4, experts=4, top_k=2, expert_size=32, vocab=64, seq=32, mbs=2, dp=2, ep=2, steps=12, dtype="float32", lr=3e-3)
+    path = os.path.join(os.path.dirname(out_file), f"llamoe_{dist.get_rank() if dist.is_initialized() else 0}.yaml")
+    cfg.save_as_yaml(path)
+    t = train.make_trainer(path)  # from the YAML file: the extra model-config fields survive the round trip
+    model = t.unwrapped_model
+    assert isinstance(model, llamoe.LlaMoEForTraining) and isinstance(t.model_config, cfgmod.LlaMoEConfig) and t.model_config.log_expert_load
+    no_decay = model.get_named_params_without_weight_decay()
+    assert any(".router." in n for n in no_decay)
+    t.prepare_training()
+    data = dummy_dataloader(t)
+    losses = []
+    for _ in range(12):
+        _, loss, _ = t.training_step(data)
+        t.iteration_step += 1
+        losses.append(float(loss))
+    report = model.expert_load_report()
+    assert len(report) == 2 and all(0.25 <= v <= 1.0 for v in report.values()), report  # one router per layer, 4 experts
+    if dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save({"losses": losses}, out_file)
+    t.parallel_context.destroy()
+
+
+def test_llamoe_example_trains_with_expert_parallelism(tmp_path):
+    out = str(tmp_path / "llamoe.pt")
+    run_distributed(_llamoe_run, 2, out_file=out)
+    losses = torch.load(out)["losses"]
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses
