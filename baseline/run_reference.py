@@ -56,23 +56,26 @@ class _Guard:
         return c10d._get_default_store() if tdist.is_initialized() else None
 
     def start(self):
+        """Starts the watcher.  The job's process group may not exist yet (the reference trainer creates it): the watcher waits
+        for it, the deadline runs from now."""
         import threading
         import time
 
-        store = self._store()
-        if store is None or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        if int(os.environ.get("WORLD_SIZE", "1")) == 1:
             return
         t_end = time.monotonic() + self.deadline_s
 
         def watch():
+            store = None
             while not self._stop:
                 time.sleep(2.0)
                 why = None
                 try:
-                    if store.check([self.KEY]):
+                    store = store or self._store()
+                    if store is not None and store.check([self.KEY]):
                         why = store.get(self.KEY).decode(errors="replace")
                 except Exception:
-                    continue
+                    pass
                 if why is None and time.monotonic() > t_end:
                     why = f"the reference did not finish within {self.deadline_s:.0f} s on this layout (a rank is waiting in a collective)"
                 if why is not None and not self._stop:
@@ -257,10 +260,10 @@ def run_reference(args):
                     torch.cuda.synchronize()
                     state["clocks"] = state["sampler"].stop()
 
-    guard = _Guard(deadline_s=float(os.environ.get("NTB_REFERENCE_DEADLINE_S", "420")))
+    guard = _Guard(deadline_s=float(os.environ.get("NTB_REFERENCE_DEADLINE_S", "300")))
+    guard.start()
     try:
         trainer = TimedTrainer(cfg_path)
-        guard.start()
         input_pp_rank, output_pp_rank = get_input_output_pp_ranks(model=trainer.model)
         h2d = {"bytes": 0, "batches": 0}
         dataloader = _host_batches(trainer, input_pp_rank, output_pp_rank, h2d)
