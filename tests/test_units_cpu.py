@@ -326,3 +326,60 @@ def test_s3_mover_state_machine_with_a_fake_s5cmd(tmp_path):
     bad.start_uploading()
     bad.wait_for_completion()
     assert bad.state == S3Mover.S3MoverState.IDLE and (local / "11" / "w.bin").exists()
+
+
+# ------------------------------------------------------------------------------------------------ optimizer parameter groups
+def test_param_groups_get_their_weight_decay_and_learning_rate(tmp_path):
+    """Norm gains (the model's own no-decay list) and names matched by ``weight_decay_exclude_named_params`` sit in groups with
+    weight decay 0, everything else decays; one AdamW step with zero gradients therefore shrinks exactly the decayed
+    parameters; under the spectral parametrisation matrices get learning rates scaled by their fan-in / fan-out."""
+    from nanotron_b200.config import SpectralMupInit
+    from nanotron_b200.trainer import DistributedTrainer
+
+    single_process_env()
+    cfg = make_config(tiny_llama_config(hidden_size=32, intermediate_size=64), seq=16, mbs=2, steps=2, dtype="float32", lr=1e-2)
+    cfg.optimizer.weight_decay = 0.5
+    cfg.optimizer.weight_decay_exclude_named_params = [r".*down_proj.*"]
+    cfg.optimizer.zero_stage = 0
+    cfg.optimizer.accumulate_grad_in_fp32 = False
+    cfg.checkpoints.checkpoints_path = tmp_path
+    t = DistributedTrainer(cfg)
+    base = t.optimizer.get_base_optimizer()
+    id_to_name = {id(p): n for n, p in t.unwrapped_model.named_parameters()}
+    decayed, spared = set(), set()
+    for group in base.param_groups:
+        for p in group["params"]:
+            (decayed if group["weight_decay"] > 0 else spared).add(id_to_name[id(p)])
+        assert group["lr"] == pytest.approx(1e-2) or group["lr"] == 0.0  # standard parametrisation: one learning rate (0 before warm-up starts)
+    assert any("down_proj" in n for n in spared) and not any("down_proj" in n for n in decayed)
+    assert all("norm" in n or "down_proj" in n for n in spared), spared
+    assert any("qkv_proj" in n for n in decayed) and any("token_embedding" in n for n in decayed)
+    before = {n: p.detach().clone() for n, p in t.unwrapped_model.named_parameters()}
+    for p in t.unwrapped_model.parameters():
+        p.grad = torch.zeros_like(p)
+    for group in base.param_groups:
+        group["lr"] = 1e-2
+    t.optimizer.step()
+    for n, p in t.unwrapped_model.named_parameters():
+        if n in spared:
+            assert torch.equal(p, before[n]), n  # zero gradient, no decay: untouched
+        else:
+            torch.testing.assert_close(p, before[n] * (1 - 1e-2 * 0.5))
+    t.parallel_context.destroy()
+    # spectral muP: per-matrix learning rates
+    cfg2 = make_config(tiny_llama_config(hidden_size=32, intermediate_size=128), seq=16, mbs=2, steps=2, dtype="float32", lr=1e-2)
+    cfg2.model.init_method = SpectralMupInit(use_mup=True)
+    cfg2.model.model_config._is_using_mup = True
+    cfg2.optimizer.zero_stage = 0
+    cfg2.optimizer.accumulate_grad_in_fp32 = False
+    cfg2.checkpoints.checkpoints_path = tmp_path
+    t2 = DistributedTrainer(cfg2)
+    lrs = {}
+    names = {id(p): n for n, p in t2.unwrapped_model.named_parameters()}
+    for group in t2.optimizer.get_base_optimizer().param_groups:
+        for p in group["params"]:
+            lrs[names[id(p)]] = group.get("initial_lr", group["lr"])
+    up = next(v for n, v in lrs.items() if "gate_up_proj" in n)  # fan_out 256 / fan_in 32
+    down = next(v for n, v in lrs.items() if "down_proj" in n)  # fan_out 32 / fan_in 128
+    assert up > down, (up, down)
+    t2.parallel_context.destroy()
