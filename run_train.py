@@ -142,8 +142,20 @@ def get_args():
     return parser.parse_args()
 
 
+def wait_for_debugger_if_asked():
+    """``NANOTRON_DEBUG_RANK=<r>``: rank r announces its pid and stops itself (SIGSTOP) before anything is initialised, so a
+    debugger can attach; ``kill -CONT <pid>`` lets it go on.  The other ranks wait for it at the first collective."""
+    import signal
+
+    want = os.environ.get("NANOTRON_DEBUG_RANK")
+    if want is not None and want == os.environ.get("RANK", "0"):
+        print(f"[rank {want}] pid {os.getpid()} stopped for a debugger; resume with: kill -CONT {os.getpid()}", flush=True)
+        os.kill(os.getpid(), signal.SIGSTOP)
+
+
 if __name__ == "__main__":
     args = get_args()
+    wait_for_debugger_if_asked()
     trainer = DistributedTrainer(args.config_file)
     dataloader = get_dataloader(trainer)
     trainer.train(dataloader)

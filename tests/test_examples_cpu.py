@@ -230,3 +230,32 @@ def test_llamoe_example_trains_with_expert_parallelism(tmp_path):
     run_distributed(_llamoe_run, 2, out_file=out)
     losses = torch.load(out)["losses"]
     assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_every_shipped_configuration_file_loads():
+    """All YAML files under examples/ parse with the strict loader (a renamed or removed config field shows up here), including
+    the ones with their own config classes."""
+    import glob
+
+    from nanotron_b200.config import Config, get_config_from_file
+
+    sys.path.insert(0, os.path.join(ROOT, "examples", "mamba"))
+    sys.path.insert(0, os.path.join(ROOT, "examples", "doremi"))
+    special = {}
+    from config import MambaConfig  # examples/mamba
+
+    special["config_mamba.yaml"] = dict(config_class=MambaConfig)
+    import doremi as dr
+
+    special["config_tiny_doremi.yaml"] = dict(config_class=dr.DoReMiConfig)
+    llamoe = _load("examples/moe/config_llamoe.py", "config_llamoe_for_load")
+    special["config_llamoe.yaml"] = dict(model_config_class=llamoe.LlaMoEConfig)
+    files = sorted(glob.glob(os.path.join(ROOT, "examples", "**", "*.yaml"), recursive=True))
+    assert len(files) >= 14, files
+    for path in files:
+        cfg = get_config_from_file(path, **special.get(os.path.basename(path), {}))
+        assert isinstance(cfg, Config) and cfg.parallelism.dp >= 1, path
+    variants = _load("examples/config_variants.py", "config_variants_example")
+    assert variants.resume().checkpoints.resume_checkpoint_path is not None
+    assert variants.s3_upload().s3_upload.upload_s3_path.startswith("s3://")
+    assert variants.nanoset().data_stages[1].data.dataset.dataset_weights == [0.8, 0.2]
