@@ -115,3 +115,35 @@ def test_qwen2_moe_logits_match_hugging_face():
             continue
         assert torch.equal(back[k].to(v.dtype), v), k
     ctx.destroy()
+
+
+def test_mamba_example_matches_the_hugging_face_model(tmp_path):
+    """examples/mamba against transformers' own Mamba (its sequential PyTorch path): same logits from the same weights, and a
+    checkpoint that goes Hugging Face -> this framework -> Hugging Face unchanged."""
+    import importlib.util
+    import os
+    import sys
+
+    transformers = pytest.importorskip("transformers")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "examples", "mamba"))
+    spec = importlib.util.spec_from_file_location("mamba_convert_hf", os.path.join(root, "examples", "mamba", "convert_hf.py"))
+    conv = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(conv)
+
+    torch.manual_seed(0)
+    hf_cfg = transformers.MambaConfig(vocab_size=96, hidden_size=32, state_size=8, num_hidden_layers=2, conv_kernel=4, expand=2, time_step_rank=4, use_mambapy=False,
+                                      pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    hf = transformers.MambaForCausalLM(hf_cfg).eval()
+    hf_dir = tmp_path / "hf"
+    hf.save_pretrained(hf_dir)
+    model, ctx = conv.to_nanotron(str(hf_dir), str(tmp_path / "nt"))
+    ids = torch.randint(3, 96, (2, 24))
+    with torch.no_grad():
+        want = hf(ids).logits
+        got = model.eval().model(input_ids=ids, input_mask=torch.ones(2, 24, dtype=torch.bool)).view(2, 24, -1)
+    torch.testing.assert_close(got, want, atol=2e-4, rtol=1e-4)
+    ctx.destroy()
+    back = conv.to_hf(str(tmp_path / "nt"), str(tmp_path / "hf_back"))
+    for name, p in hf.state_dict().items():
+        assert torch.equal(back.state_dict()[name], p), name
