@@ -22,8 +22,10 @@ def fs_open(file: Union[str, Path], mode="r"):
 
 def fs_copy(input_file: Union[str, Path], output_file: Union[str, Path]):
     """Copy between any two fsspec locations (downloads to / uploads from the local disk as needed)."""
+    import shutil
+
     with fs_open(input_file, mode="rb") as fi, fs_open(output_file, mode="wb") as fo:
-        fo.write(fi.read())
+        shutil.copyfileobj(fi, fo, length=16 << 20)  # streamed: checkpoint shards do not fit in host memory twice
 
 
 def check_path_is_local(path: Union[Path, str], storage_options=None) -> bool:
