@@ -383,3 +383,17 @@ def test_param_groups_get_their_weight_decay_and_learning_rate(tmp_path):
     down = next(v for n, v in lrs.items() if "down_proj" in n)  # fan_out 32 / fan_in 128
     assert up > down, (up, down)
     t2.parallel_context.destroy()
+
+
+def test_fsspec_helpers_copy_between_file_systems(tmp_path):
+    from nanotron_b200.s3_checkpoints import check_path_is_local, fs_copy, fs_open
+
+    src = tmp_path / "a.bin"
+    payload = bytes(range(256)) * 5000  # larger than nothing, smaller than a block
+    src.write_bytes(payload)
+    fs_copy(src, "memory://bucket/run/a.bin")
+    with fs_open("memory://bucket/run/a.bin", mode="rb") as f:
+        assert f.read() == payload
+    fs_copy("memory://bucket/run/a.bin", tmp_path / "back.bin")
+    assert (tmp_path / "back.bin").read_bytes() == payload
+    assert check_path_is_local(tmp_path) and not check_path_is_local("memory://bucket/run")
