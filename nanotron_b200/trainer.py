@@ -465,13 +465,9 @@ class DistributedTrainer:
             else:
                 self.grad_accumulator.sync_gradients_across_dp(ctx.dp_cp_pg, dist.ReduceOp.AVG, reduce_scatter=False)
             return
-        grads = [p.grad for p in self.unwrapped_model.parameters() if p.grad is not None]
-        by_dtype: Dict[torch.dtype, List[torch.Tensor]] = {}
-        for g in grads:
-            by_dtype.setdefault(g.dtype, []).append(g)
-        for gs in by_dtype.values():
-            dist.all_reduce_coalesced(gs, op=dist.ReduceOp.SUM, group=ctx.dp_cp_pg)
-            torch._foreach_div_(gs, ctx.dp_cp_pg.size())
+        from nanotron_b200.parallel.data_parallel import sync_gradients_across_dp
+
+        sync_gradients_across_dp(self.unwrapped_model, ctx.dp_cp_pg, reduce_op=dist.ReduceOp.AVG)
 
     def _sync_gradients_with_experts(self):
         """Expert weights are replicated over ``expert_dp`` only and saw tokens of all ``ep`` ranks: their gradients
@@ -485,15 +481,9 @@ class DistributedTrainer:
             if g is None:
                 continue
             (experts if self._param_is_expert(p) else dense).append(g)
-        if dense and ctx.dp_cp_pg.size() > 1:
-            dist.all_reduce_coalesced(dense, op=dist.ReduceOp.SUM, group=ctx.dp_cp_pg)
-            torch._foreach_div_(dense, ctx.dp_cp_pg.size())
-        if experts:
-            if ctx.expert_dp_pg.size() > 1:
-                dist.all_reduce_coalesced(experts, op=dist.ReduceOp.SUM, group=ctx.expert_dp_pg)
-            if ctx.cp_pg.size() > 1:
-                dist.all_reduce_coalesced(experts, op=dist.ReduceOp.SUM, group=ctx.cp_pg)
-            torch._foreach_div_(experts, ctx.dp_cp_pg.size())
+        from nanotron_b200.parallel.expert_parallel import sync_dense_and_expert_gradients
+
+        sync_dense_and_expert_gradients(dense, experts, ctx)
 
     def _clip_gradients_fused(self):
         """CUDA fast path: one flat sum-of-squares kernel over the fp32 gradient buffer (this rank's shard under
