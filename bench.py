@@ -96,7 +96,7 @@ class ClockSampler:
         return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-# Other BASELINE configurations, selected with --config (they set model / batch / layout flags; explicit flags still win):
+# Other target configurations, selected with --config (they set model / batch / layout flags; explicit flags still win):
 #   llama3.2-1b-dp8    Llama-3.2-1B, data parallel over all GPUs with ZeRO-1, micro-batch 4, one accumulation step
 #   qwen-moe-ep8       Qwen-style MoE (64 experts top-4 + shared expert, aux loss 0.01), expert parallel over all GPUs (on the dp axis), micro-batch 2
 #   llama3-8b-cp8-64k  Llama-3-8B at 65536 tokens, context parallel over all GPUs (zig-zag sharding), activation recompute
@@ -294,7 +294,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--config", default="llama3-8b", choices=sorted(CONFIGS), help="BASELINE configuration preset (sets --model / --layout / batch flags; flags given explicitly win)")
+    ap.add_argument("--config", default="llama3-8b", choices=sorted(CONFIGS), help="target configuration preset (sets --model / --layout / batch flags; flags given explicitly win)")
     ap.add_argument("--model", default=None, choices=sorted(MODELS) + ["qwen-moe"])
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--mbs", type=int, default=None)
