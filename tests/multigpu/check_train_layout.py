@@ -45,6 +45,7 @@ def main():
     ap.add_argument("--expect", default=None)
     ap.add_argument("--tol", type=float, default=0.05)
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--keep-gathered", action="store_true", help="tp_recompute_allgather off: column linears keep the gathered activations for their backward")
     args = ap.parse_args()
     os.environ.setdefault("RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1"), os.environ.setdefault("LOCAL_RANK", "0")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1"), os.environ.setdefault("MASTER_PORT", "29741")
@@ -65,6 +66,8 @@ def main():
     mc = tiny_llama_config(hidden_size=512, intermediate_size=1536, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, vocab_size=vocab, max_position_embeddings=seq)
     cfg = make_config(mc, tp=args.tp, pp=args.pp, dp=args.dp, seq=seq, mbs=1, accum=total_mbs // args.dp, steps=args.steps, dtype=args.dtype, lr=1e-3,
                       tp_mode="reduce_scatter" if args.tp > 1 else "all_reduce", async_tp=args.tp > 1, pp_engine=args.engine, zero=1 if args.dp > 1 else 0)
+    if args.keep_gathered:
+        cfg.parallelism.tp_recompute_allgather = False
     t = Trainer(cfg)
     t.prepare_training()
     ctx = t.parallel_context
