@@ -19,7 +19,7 @@ def _silent_rank(hb_dir, marker_dir):
     ctx = ParallelContext(1, 1, 3)
     rank = dist.get_rank(ctx.world_pg)
     hb = Heartbeat(hb_dir, rank, interval=0.1).start()
-    wd = Watchdog(hb_dir, rank, 3, timeout=1.0, startup_timeout=20.0)
+    wd = Watchdog(hb_dir, rank, 3, timeout=3.0, startup_timeout=30.0)  # generous against a loaded test machine: healthy ranks beat every 0.1 s
     t = torch.ones(1)
     for step in range(1, 4):  # three healthy steps
         wd.raise_if_failed()
@@ -31,7 +31,7 @@ def _silent_rank(hb_dir, marker_dir):
         os._exit(0)
     t0 = time.time()
     try:
-        while time.time() - t0 < 15:
+        while time.time() - t0 < 25:
             wd.raise_if_failed()  # the check every rank makes before launching the next step
             time.sleep(0.1)
         raise AssertionError("dead rank was not detected")
@@ -48,7 +48,7 @@ def test_rank_that_stops_between_steps_is_detected(tmp_path):
     marks.mkdir()
     run_distributed(_silent_rank, 3, hb_dir=str(hb), marker_dir=str(marks))
     assert sorted(os.listdir(marks)) == ["detected_0", "detected_1"]
-    assert all(float(open(marks / f).read()) < 10 for f in os.listdir(marks))
+    assert all(float(open(marks / f).read()) < 20 for f in os.listdir(marks))
 
 
 def _raising_rank(marker_dir):
