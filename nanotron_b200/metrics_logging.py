@@ -55,7 +55,7 @@ class MetricsLogger:
         self.log_detail_interval = ml.log_detail_interval if ml is not None else 10
 
     def _layer_of(self, name: str) -> Optional[int]:
-        m = re.search(r"\.decoder\.(\d+)\.", name)
+        m = re.search(r"(?:^|\.)decoder\.(\d+)\.", name)
         return int(m.group(1)) if m else None
 
     def _component_of(self, name: str) -> Optional[str]:

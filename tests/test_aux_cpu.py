@@ -1,0 +1,223 @@
+"""Auxiliary subsystems on CPU: timers, per-layer metrics, the block-local logging mixin, the decoding store, the evaluation
+job launcher, result collection for wandb, and the maintenance / preprocessing scripts."""
+import importlib.util
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(rel, name):
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, rel))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_timers_as_context_manager_decorator_and_registry():
+    from nanotron_b200.logging.timers import Timers, TimerType
+
+    timers = Timers()
+    timers.configure(timer_type=TimerType.CPU, enabled=True)
+    with timers("block"):
+        time.sleep(0.02)
+    with timers("block"):
+        time.sleep(0.02)
+    assert "block" in timers and timers["block"].call_count == 2
+    assert 0.03 < timers["block"].total_time < 1.0 and timers["block"].average_time == pytest.approx(timers["block"].total_time / 2)
+
+    @timers("decorated")
+    def work(n):
+        time.sleep(0.01)
+        return n + 1
+
+    assert work(1) == 2 and timers["decorated"].call_count == 1
+
+    @timers
+    def bare():
+        return 7
+
+    assert bare() == 7 and "bare" in timers
+    assert set(timers.get_all_elapsed()) == {"block", "decorated", "bare"}
+    timers.reset("block")
+    assert timers["block"].call_count == 0
+    # disabled timers cost nothing and record nothing
+    timers.disable()
+    with timers("off"):
+        pass
+    assert timers["off"].call_count == 0 and "off" not in timers.get_all_elapsed()
+
+
+def test_tensor_statistics_and_per_layer_metric_names():
+    from nanotron_b200.metrics_logging import STAT_NAMES, MetricsLogger, compute_tensor_stats
+
+    x = torch.tensor([0.0, 1.0, -1.0, 2.0])
+    stats = dict(zip(STAT_NAMES, compute_tensor_stats(x).tolist()))
+    assert stats["mean"] == pytest.approx(0.5) and stats["min"] == -1 and stats["max"] == 2
+    assert stats["l1"] == pytest.approx(4.0) and stats["l2"] == pytest.approx(6**0.5) and stats["zero_frac"] == pytest.approx(0.25)
+    assert compute_tensor_stats(torch.empty(0)).tolist() == [0.0] * len(STAT_NAMES)
+
+    class Attn(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv_proj, self.o_proj = nn.Linear(4, 12, bias=False), nn.Linear(4, 4, bias=False)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn, self.input_layernorm = Attn(), nn.LayerNorm(4)
+
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.decoder = nn.ModuleList([Block(), Block()])
+            self.lm_head = nn.Linear(4, 8, bias=False)
+
+    class Cfg:
+        class metrics_logging:
+            log_level, log_detail_interval = 1, 5
+
+    model = Tiny()
+    for p in model.parameters():
+        p.grad = torch.ones_like(p)
+    ml = MetricsLogger(Cfg)
+    detailed = ml.collect_all_metrics(model, iteration_step=10)
+    assert "global/weights_l2" in detailed
+    assert "weights/layer_1/attn/qkv_proj/std" in detailed and "grads/layer_0/attn/o_proj/l2" in detailed and "weights/lm_head/mean" in detailed
+    assert float(detailed["grads/layer_0/attn/o_proj/l2"]) == pytest.approx(4.0)  # 16 ones
+    assert set(ml.collect_all_metrics(model, iteration_step=11)) == {"global/weights_l2"}  # off the detail interval
+
+
+def test_block_local_logging_is_collected_from_the_model_tree():
+    from nanotron_b200.logging.logmixin import LoggingCollectorMixin, LogMixin
+
+    class Leaf(nn.Module, LogMixin):
+        def forward(self, x):
+            self.tbi_logger({"act_norm": x.norm()})
+            return x
+
+    class Model(nn.Module, LoggingCollectorMixin):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = Leaf(), Leaf()
+
+    m = Model()
+    m.a(torch.ones(4))
+    m.b(torch.full((4,), 2.0))
+    logs = m.get_tbi_logs()
+    assert {k.split(":")[0] if ":" in k else k for k in logs}  # something was collected
+    assert sorted(float(v) for v in logs.values()) == [2.0, 4.0]
+    m.clear_all_tbi_logs()
+    assert m.get_tbi_logs() == {}
+
+
+def test_decoding_store_attaches_per_module_state():
+    from nanotron_b200.generation.generate_store import AttachableStore, Store, attach_store
+
+    class Layer(nn.Module, AttachableStore):
+        def forward(self, x):
+            store = self.get_local_store()
+            if store is not None:
+                store["calls"] = store.get("calls", 0) + 1
+            return x
+
+    model = nn.Sequential(Layer(), Layer())
+    model(torch.zeros(1))  # no store attached: nothing is kept
+    store = Store()
+    with attach_store(model, store):
+        model(torch.zeros(1))
+        model(torch.zeros(1))
+        assert [s["calls"] for s in store.values()] == [2, 2]
+    assert model[0].get_local_store() is None
+    store.flush()
+    assert len(store) == 0
+
+
+def test_evaluation_job_script_is_rendered_from_the_upload_log(tmp_path):
+    from nanotron_b200.config import Config, GeneralArgs, LightEvalConfig, ParallelismArgs
+    from nanotron_b200.eval.one_job_runner import LightEvalRunner
+
+    cfg = Config.create_empty()
+    cfg.general = GeneralArgs(project="p", run="run7")
+    cfg.lighteval = LightEvalConfig(slurm_script_dir=tmp_path / "scripts", logs_path=tmp_path / "logs", local_checkpoint_dir=tmp_path / "ckpt", parallelism=ParallelismArgs(dp=1, pp=1, tp=2),
+                                    s3_save_path="s3://bucket/evals", upload_to_wandb=True, wandb_project="evals", eval_interval=100)
+    runner = LightEvalRunner(cfg)
+    log = '{"operation":"cp","success":true,"source":"/tmp/x","destination":"s3://bucket/ckpts/run7/200/model/model/lm_head/pp_block/model_weight.safetensors"}\n'
+    assert runner._checkpoint_from_upload_log(log) == "s3://bucket/ckpts/run7/200" and runner._step_from_path("s3://bucket/ckpts/run7/200") == 200
+    assert runner._checkpoint_from_upload_log("nothing useful") is None
+    script, out_log = runner.render_slurm_script("s3://bucket/ckpts/run7/200", 200)
+    text = open(script).read()
+    assert "#SBATCH --gpus-per-node=2" in text and "s5cmd cp --exclude 'optimizer/*'" in text and "run_evals.py --checkpoint-config-path" in text
+    assert "s3://bucket/evals/run7/200/" in text and "upload_to_wandb --wandb_project evals" in text and out_log.endswith(".out")
+    # a step off the evaluation interval launches nothing
+    assert runner.eval_single_checkpoint(log.replace("/200/", "/250/")) == (None, None)
+
+
+def test_result_files_are_flattened_for_wandb(tmp_path):
+    from nanotron_b200.eval.upload_to_wandb import collect_results
+
+    (tmp_path / "a").mkdir()
+    (tmp_path / "a" / "results_1.json").write_text(json.dumps({"results": {"arc:easy": {"acc": 0.5, "acc_stderr": 0.1, "note": "x"}, "piqa": {"acc_norm": 0.75}}}))
+    assert collect_results(str(tmp_path)) == {"arc:easy/acc": 0.5, "arc:easy/acc_stderr": 0.1, "piqa/acc_norm": 0.75}
+
+
+def test_badly_named_shards_get_their_extension_back(tmp_path, monkeypatch):
+    fix = _load("scripts/fix_checkpoint_bad_naming.py", "fix_naming")
+    assert fix.fixed_name("model_weight.safetensors_pp-rank-0-of-1_tp-rank-0-of-2") == "model_weight_pp-rank-0-of-1_tp-rank-0-of-2.safetensors"
+    assert fix.fixed_name("model_weight_pp-rank-0-of-1_tp-rank-0-of-2.safetensors") is None and fix.fixed_name("config.yaml") is None
+    d = tmp_path / "10" / "model"
+    d.mkdir(parents=True)
+    (d / "model_weight.safetensors_pp-rank-0-of-1_tp-rank-1-of-2").write_bytes(b"x")
+    (d / "model_bias_pp-rank-0-of-1_tp-rank-1-of-2.safetensors").write_bytes(b"y")
+    monkeypatch.setattr(sys, "argv", ["fix", str(tmp_path / "10")])
+    fix.main()
+    assert sorted(os.listdir(d)) == ["model_bias_pp-rank-0-of-1_tp-rank-1-of-2.safetensors", "model_weight_pp-rank-0-of-1_tp-rank-1-of-2.safetensors"]
+
+
+def test_preprocessed_token_shards_are_readable_by_the_dataset(tmp_path):
+    """tools/preprocess_data.py's writer produces the token file + index + metadata that the Nanoset reader opens."""
+    prep = _load("tools/preprocess_data.py", "preprocess_data_tool")
+    docs = [[5, 6, 7, 2], [8, 9, 2], [10, 11, 12, 13, 2]]
+    path = str(tmp_path / "part_000.ds")
+    assert prep.write_token_shard(path, docs, token_size=2, tokenizer_name="gpt2") == 12
+    assert np.fromfile(path, dtype=np.uint16).tolist() == [t for d in docs for t in d]
+    assert np.fromfile(path + ".index", dtype=np.uint64).tolist() == [4, 7, 12]
+    assert open(path + ".metadata").read().splitlines() == ["gpt2|2", "12"]
+    from nanotron_b200.data.tokenized_bytes import TokenizedBytesFileDataset
+
+    ds = TokenizedBytesFileDataset(path, seq_len=3, dtype=np.uint16)
+    assert len(ds) == 3  # 12 tokens in samples of seq_len + 1
+    first = ds[0]
+    tokens = first["input_ids"] if isinstance(first, dict) else first
+    assert torch.as_tensor(tokens).reshape(-1).tolist()[:4] == [5, 6, 7, 2]
+
+
+def test_scaling_sweep_generates_configs_and_job_scripts(tmp_path, monkeypatch):
+    import csv
+
+    sb = _load("scripts/scaling_benchmarks.py", "scaling_benchmarks_script")
+    assert sb.parse_layout("dp2tp4") == {"dp": 2, "tp": 4, "pp": 1}
+    assert set(sb.default_layouts(4)) >= {"dp4tp1pp1", "dp1tp4pp1", "dp1tp2pp2"}
+    layouts = sb.layouts_for(8)
+    assert all(dp * tp * pp == 8 for dp, tp, pp in layouts) and (1, 8, 1) in layouts and (8, 1, 1) in layouts
+    n = sb.estimate_num_params(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=128256, tie_word_embeddings=False)
+    assert 7.9e9 < n < 8.2e9
+    # generate mode: one config + one job script per experiment, and the experiment table
+    monkeypatch.setattr(sys, "argv", ["scaling_benchmarks.py", "generate", "--sizes", "8B", "--nodes", "1", "--limit", "3", "--configs-dir", str(tmp_path / "cfg"),
+                                      "--scripts-dir", str(tmp_path / "sh"), "--logs-dir", str(tmp_path / "logs"), "--benchmark-csv", str(tmp_path / "res.csv")])
+    sb.main()
+    rows = list(csv.DictReader(open(tmp_path / "cfg" / "experiments.csv")))
+    assert len(rows) == 3 and len(os.listdir(tmp_path / "sh")) == 3
+    from nanotron_b200.config import get_config_from_file
+
+    for row in rows:
+        cfg = get_config_from_file(row["config"])
+        assert cfg.parallelism.dp * cfg.parallelism.tp * cfg.parallelism.pp == 8
+        assert "run_train.py" in open(row["script"]).read() and "#SBATCH --nodes=1" in open(row["script"]).read()
