@@ -13,7 +13,8 @@ import torch
 from torch import nn
 
 from nanotron_b200 import ops
-from nanotron_b200.fp8.quantize import dequantize, quantize_1x128, quantize_128x128
+from nanotron_b200.fp8.parameter import weight_cache
+from nanotron_b200.fp8.quantize import dequantize, quantize_1x128
 
 
 def _native_fp8(x2: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -26,13 +27,6 @@ def _native_fp8(x2: torch.Tensor, weight: torch.Tensor) -> bool:
     return native.has_fp8_gemm() and K % 128 == 0 and N % 128 == 0 and M % 128 == 0
 
 
-def _transpose_blocks(t):
-    """Transposed view of a 128 x 128-block tensor as a new block tensor (payload and scales transposed)."""
-    from nanotron_b200.fp8.quantize import FP8BlockTensor
-
-    return FP8BlockTensor(t.data.t().contiguous(), t.scale.t().contiguous(), t.block)
-
-
 def shapes_ok(x2: torch.Tensor, weight: torch.Tensor) -> bool:
     """Block scaling needs every dimension of the product to be a multiple of the 128-element block."""
     return x2.dim() == 2 and weight.dim() == 2 and x2.shape[0] % 128 == 0 and x2.shape[1] % 128 == 0 and weight.shape[0] % 128 == 0 and x2.shape[1] == weight.shape[1]
@@ -41,7 +35,7 @@ def shapes_ok(x2: torch.Tensor, weight: torch.Tensor) -> bool:
 def fp8_forward(x2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """y = dq(q_e4m3^{1x128}(x)) @ dq(q_e4m3^{128x128}(W))^T."""
     xq = quantize_1x128(x2, torch.float8_e4m3fn)
-    wq = quantize_128x128(weight, torch.float8_e4m3fn)
+    wq = weight_cache.get(weight, torch.float8_e4m3fn)  # quantised once per optimizer step, not once per micro-batch
     if _native_fp8(x2, weight):
         from nanotron_b200.ops import native
 
@@ -56,10 +50,10 @@ def fp8_dgrad(go: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         from nanotron_b200.ops import native
 
         goq = quantize_1x128(go, torch.float8_e5m2)
-        wq_t = _transpose_blocks(quantize_128x128(weight, torch.float8_e4m3fn))  # [K, N]: K-major for the dgrad reduction over N
+        wq_t = weight_cache.get(weight, torch.float8_e4m3fn, transposed=True)  # [K, N]: K-major for the dgrad reduction over N
         return native.gemm_fp8_blockscaled(goq, wq_t)
     goq = dequantize(quantize_1x128(go, torch.float8_e5m2), go.dtype)
-    wq = dequantize(quantize_128x128(weight, torch.float8_e4m3fn), weight.dtype)
+    wq = dequantize(weight_cache.get(weight, torch.float8_e4m3fn), weight.dtype)
     return goq.matmul(wq)
 
 

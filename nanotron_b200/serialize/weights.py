@@ -124,6 +124,15 @@ def load_sharded_param_latest(param_or_buffer: torch.Tensor, sharded_info: Shard
     return unsharded
 
 
+def _forget_quantised_copies():
+    """Weights were overwritten in place: cached fp8 copies of them (fp8 linear mode) are stale."""
+    import sys
+
+    mod = sys.modules.get("nanotron_b200.fp8.parameter")
+    if mod is not None:
+        mod.weight_cache.invalidate()
+
+
 def load_weights(model: nn.Module, parallel_context: ParallelContext, root_folder: Path, filtered_state_dict: Optional[Dict[str, Any]] = None):
     """Load parameters in place.  ``filtered_state_dict`` restricts which entries are loaded (name -> tensor)."""
     param_root_folder = Path(root_folder) / "model"
@@ -177,6 +186,7 @@ def load_weights(model: nn.Module, parallel_context: ParallelContext, root_folde
                 checkpoint_version = get_checkpoint_version(parallel_context, root_folder, param_save_path=shards_path[0])
             with torch.no_grad():
                 load_sharded_param_latest(param_or_buffer=param_or_buffer, sharded_info=sharded_info, shards_path=shards_path, param_shard_metadata=param_shard_metadata[name])
+    _forget_quantised_copies()
     return param_shard_metadata
 
 

@@ -439,6 +439,12 @@ class DistributedTrainer:
             else:
                 self.optimizer.step()
             self.optimizer.zero_grad()
+        from nanotron_b200 import ops
+
+        if ops.get_linear() == "fp8":
+            from nanotron_b200.fp8 import weight_cache
+
+            weight_cache.invalidate()  # the weights moved: their quantised copies are recomputed on first use
         self.lr_scheduler.step()
         after_optim_step_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator)
         self.post_train_step()

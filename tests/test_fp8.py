@@ -146,3 +146,90 @@ def test_fp8_linear_mode_is_reachable_from_the_config_and_tracks_bf16():
     assert fp8[-1] < fp8[0] - 0.3, fp8
     for a, b in zip(fp8, ref):
         assert abs(a - b) < 0.05, (fp8, ref)
+
+
+def test_weight_copies_are_quantised_once_per_weights_generation():
+    """The e4m3 copy of a weight (and its transposed copy for the dgrad) is computed once and reused by every micro-batch until
+    the weights change: an in-place update (autograd version) or an explicit new generation (optimizer kernels that write
+    through raw pointers) makes the next use recompute it."""
+    from nanotron_b200.fp8 import QuantizedWeightCache, dequantize
+    from nanotron_b200.fp8 import linear as fp8_linear
+
+    cache = QuantizedWeightCache()
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(256, 384))
+    a = cache.get(w)
+    assert cache.get(w) is a and (cache.hits, cache.misses) == (1, 1)
+    t = cache.get(w, transposed=True)
+    assert t.data.shape == (384, 256) and torch.equal(t.data.t().float(), a.data.float()) and torch.equal(t.scale.t(), a.scale)
+    assert cache.get(w, transposed=True) is t
+    with torch.no_grad():
+        w.mul_(2.0)  # in-place update: the version counter moves
+    b = cache.get(w)
+    assert b is not a and torch.allclose(dequantize(b, torch.float32), 2 * dequantize(a, torch.float32), rtol=0, atol=1e-6)
+    w.data.copy_(torch.randn(256, 384))  # a raw write that autograd does not see ...
+    assert cache.get(w) is b  # ... is only caught by a new generation
+    cache.invalidate()
+    c = cache.get(w)
+    assert c is not b and not torch.equal(c.data.float(), b.data.float())
+    # the linear layer goes through the shared cache: several micro-batches, one quantisation; numerics unchanged
+    shared = fp8_linear.weight_cache
+    shared.invalidate()
+    h0, m0 = shared.hits, shared.misses
+    lin = torch.nn.Linear(384, 256, bias=False)
+    x = torch.randn(128, 384)
+    outs = [fp8_linear.fp8_forward(x, lin.weight) for _ in range(3)]
+    assert shared.misses - m0 == 1 and shared.hits - h0 == 2 and all(torch.equal(o, outs[0]) for o in outs)
+    shared.enabled = False
+    try:
+        assert torch.equal(fp8_linear.fp8_forward(x, lin.weight), outs[0])
+    finally:
+        shared.enabled = True
+
+
+def test_per_tensor_power_of_two_scaling_round_trips():
+    from nanotron_b200.fp8 import DTypes, FP8Tensor, convert_tensor_from_fp8
+    from nanotron_b200.fp8.tensor import compute_scale
+    from nanotron_b200.fp8.utils import is_overflow_underflow_nan, quantization_error
+
+    torch.manual_seed(1)
+    x = torch.randn(64, 64) * 3.0
+    for dtype, tol in ((DTypes.FP8E4M3, 0.07), (DTypes.FP8E5M2, 0.13)):
+        q = FP8Tensor(x, dtype)
+        scale = float(q.fp8_meta.scale)
+        assert scale == 2.0 ** round(torch.log2(torch.tensor(scale)).item())  # a power of two
+        assert float(x.abs().max()) * scale <= q.fp8_meta.fp8_max < float(x.abs().max()) * scale * 2  # the largest that fits
+        back = q.to_float()
+        assert not is_overflow_underflow_nan(back) and quantization_error(x, back)["max_rel"] < tol
+        assert torch.equal(back, convert_tensor_from_fp8(q.data, q.fp8_meta))
+    assert float(compute_scale(torch.tensor(0.0), DTypes.FP8E4M3)) == 1.0
+    q = FP8Tensor(x, DTypes.FP8E4M3)
+    old = float(q.fp8_meta.scale)
+    q.set_data(x * 1.1)  # still fits: the scale stays
+    assert float(q.fp8_meta.scale) == old or float(x.abs().max()) * 1.1 * old > q.fp8_meta.fp8_max
+    q.set_data(x * 64)  # would overflow: rescaled
+    assert float(q.fp8_meta.scale) < old and not is_overflow_underflow_nan(q.to_float())
+
+
+def test_cached_copy_dies_with_its_weight():
+    """A weight that was freed may give its address to a new tensor of the same shape: the new tensor must not inherit the copy."""
+    from nanotron_b200.fp8 import QuantizedWeightCache
+
+    cache = QuantizedWeightCache()
+    w = torch.randn(128, 128)
+    first = cache.get(w)
+    key_count = len(cache._entries)
+    ptr = w.data_ptr()
+    del w
+    for _ in range(50):  # try to land on the same address
+        v = torch.randn(128, 128)
+        if v.data_ptr() == ptr:
+            got = cache.get(v)
+            assert got is not first and cache.misses == 2
+            break
+        del v
+    assert len(cache._entries) >= key_count
+    # an alias of a live weight (what autograd hands back in backward) does share the copy
+    w2 = torch.nn.Parameter(torch.randn(128, 128))
+    c = cache.get(w2)
+    assert cache.get(w2.detach()) is c
