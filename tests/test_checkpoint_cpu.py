@@ -22,7 +22,7 @@ def _run(out_file, ckpt_dir, steps, first_step=0, save=False, resume=None, total
 
     dp = topology.get("dp", 1)
     accum = total_mbs // dp
-    mc = tiny_llama_config()
+    mc = tiny_llama_config(tie_word_embeddings=topology.pop("tied", False))
     cfg = make_config(mc, seq=16, mbs=1, accum=accum, steps=8, lr=1e-2, ckpt_path=ckpt_dir, **topology)
     if resume is not None:
         cfg.checkpoints.resume_checkpoint_path = resume
@@ -109,3 +109,20 @@ def test_resume_same_tp_other_optimizer_layout(tmp_path):
     resumed = _losses(tmp_path, "resumed_dp2_zero0", 4, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, tp=2, dp=2, zero=0, tp_mode="reduce_scatter")
     for a, b in zip(resumed, full[2:]):
         assert abs(a - b) < 3e-4, (resumed, full)
+
+
+def test_resume_with_embeddings_tied_across_pipeline_stages(tmp_path):
+    """Embedding (first stage) and lm head (last stage) share one weight: only the first member of the tie writes it, under the
+    embedding's name, and the lm head's stage must find it there when the run resumes, on the same layout and on a single process."""
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4, tied=True)
+    ckpt = str(tmp_path / "ckpt_pp")
+    first = _losses(tmp_path, "pp_first", 2, ckpt_dir=ckpt, steps=2, save=True, pp=2, tied=True)
+    for a, b in zip(first, full[:2]):
+        assert abs(a - b) < 3e-4, (first, full)
+    model_dir = os.path.join(ckpt, "2", "model", "model")
+    assert os.path.isdir(os.path.join(model_dir, "token_position_embeddings")) and not os.path.isdir(os.path.join(model_dir, "lm_head"))
+    same = _losses(tmp_path, "pp_resumed", 2, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, pp=2, tied=True)
+    single = _losses(tmp_path, "single_resumed", 1, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, tied=True)
+    for got in (same, single):
+        for a, b in zip(got, full[2:]):
+            assert abs(a - b) < 3e-4, (got, full)
