@@ -117,8 +117,6 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
             f"(now tp={parallel_context.tp_pg.size()} pp={parallel_context.pp_pg.size()} dp={parallel_context.dp_pg.size()} ep={parallel_context.expert_parallel_size}); "
             "resume with `checkpoints.load_optimizer: false` or under the saved topology"
         )
-    if ckp_pp != parallel_context.pp_pg.size():
-        warnings.warn("You are resuming in a different PP size, so optimizer states need to be checked. Feel free to open a PR if you work on this!")
     assert model is not None, "loading optimizer states under a different topology needs the model (for the parameters' slice maps)"
     # 1) unshard over dp (ZeRO) -> {(pp, tp): state dict with full-shard tensors}
     if is_zero_ckp:
@@ -153,6 +151,14 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
         found.sort(key=lambda e: (e[0][0] != my_pp, e[0]))
         return found
 
+    # the tensors the inner optimizer really steps (ZeRO: this rank's slice of each master, in whatever shape the optimizer holds it):
+    # torch numbers them consecutively over the parameter groups, which is the numbering of ``names``
+    stepped = [p for group in optimizer.get_base_optimizer().param_groups for p in group["params"]]
+
+    def shaped_like_stepped(idx, t: torch.Tensor) -> torch.Tensor:
+        target = stepped[idx] if isinstance(idx, int) and idx < len(stepped) else None
+        return t.view(target.shape) if target is not None and target.numel() == t.numel() else t
+
     for idx, name in new_names.items():
         param = name_to_param[name]
         found = holders(name)
@@ -179,7 +185,7 @@ def load_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
             if is_zero_now:
                 rng = optimizer.param_name_to_dp_rank_offsets[name].get(my_dp)
                 local = local.reshape(-1)[rng[0] : rng[1]] if rng is not None else local.reshape(-1)[0:0]
-            entry[sk] = local.clone()
+            entry[sk] = shaped_like_stepped(idx, local.clone())
         new_state[idx] = entry
     new_sd["state"] = new_state
     if "gradient_accumulator" in new_sd:

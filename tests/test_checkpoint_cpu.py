@@ -126,3 +126,18 @@ def test_resume_with_embeddings_tied_across_pipeline_stages(tmp_path):
     for got in (same, single):
         for a, b in zip(got, full[2:]):
             assert abs(a - b) < 3e-4, (got, full)
+
+
+def test_resume_from_another_pipeline_and_combined_layout(tmp_path):
+    """pp 2 -> 1 and (tp 2 x pp 2) -> dp 2 with ZeRO-1: file names carry the writer's pipeline rank, the reader finds the shards anyway."""
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4)
+    ckpt_pp = str(tmp_path / "ckpt_pp")
+    _losses(tmp_path, "pp_first", 2, ckpt_dir=ckpt_pp, steps=2, save=True, pp=2)
+    resumed = _losses(tmp_path, "pp_to_one", 1, ckpt_dir=ckpt_pp, steps=2, first_step=2, resume=ckpt_pp)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
+    ckpt_4 = str(tmp_path / "ckpt_4")
+    _losses(tmp_path, "tp2pp2_first", 4, ckpt_dir=ckpt_4, steps=2, save=True, tp=2, pp=2, tp_mode="reduce_scatter")
+    resumed = _losses(tmp_path, "to_dp2", 2, ckpt_dir=ckpt_4, steps=2, first_step=2, resume=ckpt_4, dp=2, zero=1)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
