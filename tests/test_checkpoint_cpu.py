@@ -141,3 +141,19 @@ def test_resume_from_another_pipeline_and_combined_layout(tmp_path):
     resumed = _losses(tmp_path, "to_dp2", 2, ckpt_dir=ckpt_4, steps=2, first_step=2, resume=ckpt_4, dp=2, zero=1)
     for a, b in zip(resumed, full[2:]):
         assert abs(a - b) < 3e-4, (resumed, full)
+
+
+def test_resume_into_larger_layouts(tmp_path):
+    """Growing instead of shrinking: ZeRO-1 over 2 ranks -> over 4, and a single process -> tp 2 x dp 2 with ZeRO-1 (weights and
+    optimizer moments are cut along tp, then partitioned over dp)."""
+    full = _losses(tmp_path, "full", 1, ckpt_dir=str(tmp_path / "unused"), steps=4)
+    ckpt_dp = str(tmp_path / "ckpt_dp2")
+    _losses(tmp_path, "dp2_first", 2, ckpt_dir=ckpt_dp, steps=2, save=True, dp=2, zero=1)
+    resumed = _losses(tmp_path, "dp4", 4, ckpt_dir=ckpt_dp, steps=2, first_step=2, resume=ckpt_dp, dp=4, zero=1)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
+    ckpt_one = str(tmp_path / "ckpt_one")
+    _losses(tmp_path, "one_first", 1, ckpt_dir=ckpt_one, steps=2, save=True)
+    resumed = _losses(tmp_path, "tp2dp2", 4, ckpt_dir=ckpt_one, steps=2, first_step=2, resume=ckpt_one, tp=2, dp=2, zero=1, tp_mode="reduce_scatter")
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 3e-4, (resumed, full)
