@@ -180,6 +180,13 @@ def init_optimizer_and_grad_accumulator(parametrization_method: ParametrizationM
     grad_accumulator: Optional[GradientAccumulator] = None
     dp_size = parallel_context.dp_pg.size()
     zero = optimizer_args.zero_stage > 0
+    if zero and parallel_context.expert_parallel_size > 1:
+        # ZeRO-1 cuts every parameter's optimizer state over the dp ranks and all-gathers the updated parameters over them; with
+        # experts laid over the dp axis those ranks hold DIFFERENT experts, so the gather would stitch unrelated experts together
+        raise ValueError(
+            f"zero_stage={optimizer_args.zero_stage} cannot be combined with expert_parallel_size={parallel_context.expert_parallel_size}: the expert-parallel ranks "
+            "are data-parallel ranks that own different experts.  Use zero_stage 0 (the optimizer state of the experts is already split over the expert-parallel ranks)."
+        )
     holder: Dict[str, Any] = {}
     if optimizer_args.accumulate_grad_in_fp32:
 

@@ -44,9 +44,18 @@ def lr_scheduler_filename(parallel_context: ParallelContext, is_zero: bool) -> s
     return optimizer_filename(parallel_context, is_zero).replace(ObjectType.OPTIMIZER.value + "_", ObjectType.LR_SCHEDULER.value + "_", 1)
 
 
+def _is_first_replica(parallel_context: ParallelContext) -> bool:
+    """One writer per distinct optimizer state: replicas over context parallelism and over the data-parallel ranks that hold the
+    SAME experts are identical, but with expert parallelism laid over the dp axis the dp ranks of different expert ranks are not."""
+    if dist.get_rank(parallel_context.cp_pg) > 0:
+        return False
+    replicas = parallel_context.expert_dp_pg if parallel_context.expert_parallel_size > 1 else parallel_context.dp_pg
+    return dist.get_rank(replicas) == 0
+
+
 def save_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelContext, root_folder: Path):
-    if not optimizer.inherit_from(ZeroDistributedOptimizer) and dist.get_rank(parallel_context.dp_cp_pg) > 0:
-        return  # identical on every dp replica: only the first writes
+    if not optimizer.inherit_from(ZeroDistributedOptimizer) and not _is_first_replica(parallel_context):
+        return  # identical on every replica: only the first writes
     if optimizer.inherit_from(ZeroDistributedOptimizer) and dist.get_rank(parallel_context.cp_pg) > 0:
         return
     root_folder = Path(root_folder) / "optimizer"
@@ -71,7 +80,7 @@ def save_optimizer(optimizer: optim.BaseOptimizer, parallel_context: ParallelCon
 
 
 def save_lr_scheduler(lr_scheduler, is_zero, parallel_context: ParallelContext, root_folder: Path):
-    if not is_zero and dist.get_rank(parallel_context.dp_cp_pg) > 0:
+    if not is_zero and not _is_first_replica(parallel_context):
         return
     if is_zero and dist.get_rank(parallel_context.cp_pg) > 0:
         return

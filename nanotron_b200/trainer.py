@@ -795,8 +795,10 @@ def mark_unsharded_params_as_tied_across_tp(model: NanotronModel, parallel_conte
             if isinstance(param, NanotronParameter):
                 if param.is_tied:
                     continue
-                if param.is_sharded:
-                    continue  # sharded over tp or over experts: distinct data per rank
+                if param.is_sharded and not (param.get_sharded_info().is_expert_sharded(parallel_context) and parallel_context.tp_pg.size() > 1):
+                    continue  # sharded over tp: distinct data per rank
+                # (sharded over the expert axis only: the tp ranks hold copies of the same local experts, and under sequence
+                # parallelism each copy sees a different token shard, so their gradients are summed like any replicated weight's)
             # ALL_REDUCE: activations are replicated so gradients are already identical (no reduction).
             # REDUCE_SCATTER: every tp rank saw different tokens, gradients must be summed.
             if parallel_config is None or parallel_config.tp_mode is TensorParallelLinearMode.ALL_REDUCE:

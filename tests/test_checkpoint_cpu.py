@@ -22,14 +22,22 @@ def _run(out_file, ckpt_dir, steps, first_step=0, save=False, resume=None, total
 
     dp = topology.get("dp", 1)
     accum = total_mbs // dp
-    mc = tiny_llama_config(tie_word_embeddings=topology.pop("tied", False))
+    uses_mask = True
+    if topology.pop("moe", False):
+        import nanotron_b200.config as c
+        from helpers import tiny_qwen_config
+
+        mc = tiny_qwen_config(moe_config=c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=16, shared_expert_intermediate_size=32, enable_shared_expert=True, router_aux_loss_coef=0.01))
+        uses_mask = False
+    else:
+        mc = tiny_llama_config(tie_word_embeddings=topology.pop("tied", False))
     cfg = make_config(mc, seq=16, mbs=1, accum=accum, steps=8, lr=1e-2, ckpt_path=ckpt_dir, **topology)
     if resume is not None:
         cfg.checkpoints.resume_checkpoint_path = resume
     t = DistributedTrainer(cfg)
     t.prepare_training()
     assert t.iteration_step == first_step + 1, (t.iteration_step, first_step)  # the step about to run
-    all_batches = _fixed_batches(t, first_step + steps, total_mbs, 16, mc.vocab_size, uses_mask=True)
+    all_batches = _fixed_batches(t, first_step + steps, total_mbs, 16, mc.vocab_size, uses_mask=uses_mask)
     per_step = len(all_batches) // (first_step + steps)
     batches = iter(all_batches[first_step * per_step :])
     losses = []
@@ -157,3 +165,19 @@ def test_resume_into_larger_layouts(tmp_path):
     resumed = _losses(tmp_path, "tp2dp2", 4, ckpt_dir=ckpt_one, steps=2, first_step=2, resume=ckpt_one, tp=2, dp=2, zero=1, tp_mode="reduce_scatter")
     for a, b in zip(resumed, full[2:]):
         assert abs(a - b) < 3e-4, (resumed, full)
+
+
+def test_expert_parallel_checkpoint_resumes(tmp_path):
+    """Experts split over two ranks (and replicated over two tp ranks): every expert rank writes its own expert shard, and the run
+    continues exactly after a resume on the same layout."""
+    kw = dict(dp=2, ep=2, tp=2, tp_mode="reduce_scatter", moe=True)
+    full = _losses(tmp_path, "moe_full", 4, ckpt_dir=str(tmp_path / "unused"), steps=4, **kw)
+    ckpt = str(tmp_path / "ckpt_moe")
+    first = _losses(tmp_path, "moe_first", 4, ckpt_dir=ckpt, steps=2, save=True, **kw)
+    assert first == full[:2]
+    experts = os.path.join(ckpt, "2", "model", "model", "decoder", "0", "pp_block", "mlp", "experts")
+    names = sorted(os.listdir(experts))
+    assert any("exp-rank-0-of-2" in n for n in names) and any("exp-rank-1-of-2" in n for n in names), names
+    resumed = _losses(tmp_path, "moe_resumed", 4, ckpt_dir=ckpt, steps=2, first_step=2, resume=ckpt, **kw)
+    for a, b in zip(resumed, full[2:]):
+        assert abs(a - b) < 1e-5, (resumed, full)

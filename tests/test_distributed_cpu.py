@@ -189,7 +189,13 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
         topology["fp32_accum"] = True
     accum = total_mbs // (dp * mbs)
     tie = topology.pop("tie", False)
-    mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie)
+    if model == "moe":
+        import nanotron_b200.config as c
+
+        moe = c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=16, shared_expert_intermediate_size=32, enable_shared_expert=True, router_aux_loss_coef=0.01)
+        mc = tiny_qwen_config(tie_word_embeddings=tie, moe_config=moe)
+    else:
+        mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie)
     cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
     t = DistributedTrainer(cfg)
     t.prepare_training()
@@ -279,3 +285,23 @@ def test_single_process_overfits_fixed_batch():
     t.parallel_context.destroy()
     assert all(b < a for a, b in zip(losses, losses[1:])), losses
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_expert_parallel_training_matches_replicated_experts(tmp_path):
+    """A Qwen2-MoE model on 2 data-parallel ranks: with the experts split over the two ranks (ep 2: tokens travel to their
+    experts, expert gradients are averaged over expert_dp and already contain both ranks' tokens) the loss curve is the one of
+    replicated experts (ep 1), also together with tensor parallelism.  ZeRO-1 over ranks that own different experts is refused."""
+    rep = _losses_for(tmp_path, 2, "moe_dp2", model="moe", dp=2)
+    assert rep[-1] < rep[0]
+    got = _losses_for(tmp_path, 2, "moe_ep2", model="moe", dp=2, ep=2)
+    for a, b in zip(got, rep):
+        assert abs(a - b) < 3e-4, (got, rep)
+    # with sequence-parallel tp every rank routes its own token shard (the load-balance loss is a statistic of that shard), so the
+    # like-for-like comparison is the same tp layout with replicated experts
+    rep_tp = _losses_for(tmp_path, 4, "moe_dp2_tp2", model="moe", dp=2, tp=2, tp_mode="reduce_scatter")
+    got = _losses_for(tmp_path, 4, "moe_ep2_tp2", model="moe", dp=2, ep=2, tp=2, tp_mode="reduce_scatter")
+    for a, b in zip(got, rep_tp):
+        assert abs(a - b) < 3e-4, (got, rep_tp)
+    assert abs(rep_tp[0] - rep[0]) < 5e-3  # the two layouts differ only in that statistic
+    with pytest.raises(AssertionError, match="cannot be combined with expert_parallel_size"):
+        _losses_for(tmp_path, 2, "moe_ep2_zero1", model="moe", dp=2, ep=2, zero=1)
