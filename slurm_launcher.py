@@ -142,6 +142,7 @@ def create_config(a) -> Config:
     assert a.dp * a.pp * a.tp * a.cp == a.nodes * a.gpus_per_node, f"dp*pp*tp*cp={a.dp * a.pp * a.tp * a.cp} != nodes*gpus_per_node={a.nodes * a.gpus_per_node}"
     assert nh % a.tp == 0 and nkv % a.tp == 0, f"tp={a.tp} must divide the {nh} query heads and the {nkv} key/value heads"
     assert L >= a.pp, f"{L} layers cannot fill {a.pp} pipeline stages"
+    assert not (a.ep > 1 and a.zero), "expert parallelism is laid over the data-parallel ranks: use --zero 0 with --ep > 1"
     extra = {"_attn_implementation": a.attention} if a.attention else {}
     model_config = Qwen2Config(hidden_size=h, num_hidden_layers=L, num_attention_heads=nh, num_key_value_heads=nkv, intermediate_size=inter, vocab_size=a.vocab_size, max_position_embeddings=a.seq, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=a.tie_word_embeddings, **extra)
     if a.dataset and a.text_column:
