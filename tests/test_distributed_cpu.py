@@ -305,3 +305,16 @@ def test_expert_parallel_training_matches_replicated_experts(tmp_path):
     assert abs(rep_tp[0] - rep[0]) < 5e-3  # the two layouts differ only in that statistic
     with pytest.raises(AssertionError, match="cannot be combined with expert_parallel_size"):
         _losses_for(tmp_path, 2, "moe_ep2_zero1", model="moe", dp=2, ep=2, zero=1)
+
+
+def test_expert_parallelism_with_pipeline_and_context_parallelism(tmp_path):
+    """Experts split over the data-parallel ranks inside a 2-stage pipeline, and under context parallelism (every cp rank routes
+    its own sequence shard): the same curves as with replicated experts."""
+    rep = _losses_for(tmp_path, 2, "moe_dp2_b", model="moe", dp=2)
+    got = _losses_for(tmp_path, 4, "moe_pp2_ep2", model="moe", dp=2, ep=2, pp=2, pp_engine="1f1b")
+    for a, b in zip(got, rep):
+        assert abs(a - b) < 3e-4, (got, rep)
+    rep_cp = _losses_for(tmp_path, 4, "moe_cp2", model="moe", dp=2, cp=2)
+    got = _losses_for(tmp_path, 4, "moe_cp2_ep2", model="moe", dp=2, ep=2, cp=2)
+    for a, b in zip(got, rep_cp):
+        assert abs(a - b) < 3e-4, (got, rep_cp)
