@@ -174,7 +174,7 @@ def _deterministic_init(model):
                 p.copy_(full.to(p.dtype))
 
 
-def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
+def _train_losses(out_file, steps=4, total_mbs=4, model="llama", norms_file=None, **topology):
     import nanotron_b200.distributed as dist
     from nanotron_b200.trainer import DistributedTrainer as _Base
 
@@ -200,12 +200,15 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", **topology):
     t = DistributedTrainer(cfg)
     t.prepare_training()
     batches = iter(_fixed_batches(t, steps, total_mbs, 16, mc.vocab_size, uses_mask=(model == "llama")))
-    losses = []
+    losses, norms = [], []
     for _ in range(steps):
         _, loss, _ = t.training_step(batches)
         t.iteration_step += 1
         if loss is not None:
             losses.append(float(loss))
+        norms.append(float(t.grad_norm_unclipped))
+    if norms_file is not None and dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save(norms, norms_file)
     if tie and t.parallel_context.pp_pg.size() > 1:
         # the two copies of the tied matrix (embedding on the first stage, lm head on the last) must still be equal
         pp_pg = t.parallel_context.pp_pg
@@ -318,3 +321,33 @@ def test_expert_parallelism_with_pipeline_and_context_parallelism(tmp_path):
     got = _losses_for(tmp_path, 4, "moe_cp2_ep2", model="moe", dp=2, ep=2, cp=2)
     for a, b in zip(got, rep_cp):
         assert abs(a - b) < 3e-4, (got, rep_cp)
+
+
+def test_gradient_norm_is_the_same_under_every_layout(tmp_path):
+    """The norm that gradient clipping uses counts every weight exactly once: tied / replicated weights on the first rank of their
+    tie group, tensor- and expert-sharded weights summed over their shards, ZeRO shards summed over dp."""
+    def norms(name, world, **kw):
+        f = str(tmp_path / f"{name}_norms.pt")
+        _losses_for(tmp_path, world, name, norms_file=f, steps=2, **kw)
+        return torch.load(f)
+
+    base = norms("n_base", 1)
+    for name, world, kw in (
+        ("n_tp2_sp", 2, dict(tp=2, tp_mode="reduce_scatter")),
+        ("n_pp2", 2, dict(pp=2, pp_engine="1f1b")),
+        ("n_dp2_zero1", 2, dict(dp=2, zero=1)),
+        ("n_pp2_tied", 2, dict(pp=2, tie=True)),
+    ):
+        ref = norms("n_base_tied", 1, tie=True) if kw.get("tie") else base
+        got = norms(name, world, **kw)
+        for a, b in zip(got, ref):
+            assert abs(a - b) < 2e-4 * b, (name, got, ref)
+    moe = norms("n_moe_dp2", 2, model="moe", dp=2)
+    for name, world, kw in (("n_moe_ep2", 2, dict(dp=2, ep=2)), ("n_moe_pp2_ep2", 4, dict(dp=2, ep=2, pp=2))):
+        got = norms(name, world, model="moe", **kw)
+        for a, b in zip(got, moe):
+            assert abs(a - b) < 2e-4 * b, (name, got, moe)
+    moe_tp = norms("n_moe_tp2", 4, model="moe", dp=2, tp=2, tp_mode="reduce_scatter")
+    got = norms("n_moe_tp2_ep2", 4, model="moe", dp=2, tp=2, ep=2, tp_mode="reduce_scatter")
+    for a, b in zip(got, moe_tp):
+        assert abs(a - b) < 2e-4 * b, (got, moe_tp)
