@@ -139,7 +139,15 @@ class Nanoset(torch.utils.data.Dataset):
         self.consumed[d] += self.sequence_length
         return self.datasets[d][s]
 
-    def get_consumption_stats(self) -> Dict[str, Dict[str, int]]:
+    def get_consumption_stats(self, consumed_samples: Optional[int] = None) -> Dict[str, Dict[str, int]]:
+        """Tokens drawn from every folder.  With ``consumed_samples`` (samples of this dataset consumed by the WHOLE job so far) the
+        answer comes from the sample index itself: the job walks the index in order, so the first ``consumed_samples`` entries are
+        what was read, whichever rank or loader worker read them.  Without it: what this process happened to fetch (diagnostic only,
+        it misses other ranks and loader workers and runs ahead by the prefetch depth)."""
+        if consumed_samples is not None:
+            n = min(int(consumed_samples), len(self.dataset_index))
+            counts = np.bincount(np.asarray(self.dataset_index[:n], dtype=np.int64), minlength=len(self.dataset_folders))
+            return {f: {"tokens": int(c) * self.sequence_length} for f, c in zip(self.dataset_folders, counts)}
         return {f: {"tokens": int(t)} for f, t in zip(self.dataset_folders, self.consumed)}
 
     def build_nanoset_index(self) -> Tuple[np.ndarray, np.ndarray]:

@@ -375,8 +375,17 @@ class DistributedTrainer:
                     stage.consumed_train_samples += self.global_batch_size
                     base = self.current_base_dl
                     ds = getattr(base, "dataset", None)
+                    if ds is not None and hasattr(ds, "update_consumption_metrics"):
+                        # blended token files: account this step's global batch (a range of the blend index) to its folders
+                        ds.update_consumption_metrics(start_idx=stage.consumed_train_samples - self.global_batch_size, end_idx=stage.consumed_train_samples, sequence_length=self.sequence_length)
                     if ds is not None and hasattr(ds, "get_consumption_stats"):
-                        for folder, s in ds.get_consumption_stats().items():
+                        import inspect
+
+                        if "consumed_samples" in inspect.signature(ds.get_consumption_stats).parameters:
+                            stats = ds.get_consumption_stats(consumed_samples=stage.consumed_train_samples)  # job-wide, from the sample index
+                        else:
+                            stats = ds.get_consumption_stats()
+                        for folder, s in stats.items():
                             stage.consumed_tokens_per_dataset_folder[folder] = s["tokens"]
                 if (self.iteration_step - 1) % self.config.logging.iteration_step_info_interval == 0:
                     self.train_step_logs(outputs=outputs, loss_avg=loss_avg, z_loss_avg=z_loss_avg)

@@ -1,0 +1,100 @@
+"""``run_train.py`` end to end on CPU (2 gloo ranks started by torchrun): pre-tokenised files written by the preprocessing tool,
+two data stages that read different folders, periodic checkpoints, and a resume in the middle of the second stage that must
+continue the interrupted run step for step (weights, optimizer, learning-rate schedule, and the position inside the data)."""
+import importlib.util
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _write_datasets(tmp_path):
+    spec = importlib.util.spec_from_file_location("preprocess_data_tool_e2e", os.path.join(ROOT, "tools", "preprocess_data.py"))
+    prep = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(prep)
+    rng = np.random.default_rng(0)
+    folders = []
+    for name, lo, hi in (("first", 3, 120), ("second", 130, 250)):  # disjoint token ranges: the stages cannot be confused
+        d = tmp_path / name
+        d.mkdir()
+        docs = [list(rng.integers(lo, hi, size=int(rng.integers(20, 60)))) + [2] for _ in range(120)]
+        prep.write_token_shard(str(d / "part_000.ds"), docs, token_size=2, tokenizer_name="none")
+        folders.append(str(d))
+    return folders
+
+
+def _config(tmp_path, folders, resume=None, streamed=False):
+    sys.path.insert(0, ROOT)
+    import nanotron_b200.config as c
+
+    model = c.Qwen2Config(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=256, max_position_embeddings=32,
+                          rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+
+    def stage(name, start, folder):
+        return c.DatasetStageArgs(name=name, start_training_step=start, data=c.DataArgs(dataset=c.NanosetDatasetsArgs(dataset_folder=folder, token_size_in_bytes=2, use_old_brrr_dataloader=streamed), seed=7, num_loading_workers=0))
+
+    cfg = c.Config(
+        general=c.GeneralArgs(project="e2e", run="e2e", seed=3),
+        checkpoints=c.CheckpointsArgs(checkpoints_path=str(tmp_path / "ckpt"), checkpoint_interval=4, save_final_state=True, resume_checkpoint_path=resume),
+        parallelism=c.ParallelismArgs(dp=2, pp=1, tp=1, pp_engine="1f1b", tp_mode="ALL_REDUCE", tp_linear_async_communication=False),
+        model=c.ModelArgs(model_config=model, init_method=c.RandomInit(std=0.05), dtype="float32"),
+        tokenizer=c.TokenizerArgs(tokenizer_name_or_path=None),
+        optimizer=c.OptimizerArgs(
+            optimizer_factory=c.AdamWOptimizerArgs(adam_eps=1e-8, adam_beta1=0.9, adam_beta2=0.95, torch_adam_is_fused=False), zero_stage=1, weight_decay=0.01, clip_grad=1.0,
+            accumulate_grad_in_fp32=True,
+            learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=5e-3, lr_warmup_steps=2, lr_warmup_style="linear", lr_decay_style="cosine", min_decay_lr=5e-4),
+        ),
+        logging=c.LoggingArgs(log_level="info", log_level_replica="error", iteration_step_info_interval=1),
+        tokens=c.TokensArgs(sequence_length=32, train_steps=7, micro_batch_size=2, batch_accumulation_per_replica=2),
+        data_stages=[stage("first", 1, folders[0]), stage("second", 4, folders[1])],
+    )
+    path = str(tmp_path / ("resume.yaml" if resume else "config.yaml"))
+    cfg.save_as_yaml(path)
+    return path
+
+
+def _train(config_path):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "run_train.py"), "--config-file", config_path]
+    out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    text = out.stdout + out.stderr
+    losses = {int(m.group(1)): float(m.group(2)) for m in re.finditer(r"iteration: (\d+) / \d+.*?lm_loss: ([\d.]+)", text)}
+    return losses, text
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("streamed", [False, True], ids=["nanoset", "streamed_token_files"])
+def test_run_train_with_data_stages_and_resume(tmp_path, streamed):
+    folders = _write_datasets(tmp_path)
+    full, log = _train(_config(tmp_path, folders, streamed=streamed))
+    assert sorted(full) == list(range(1, 8)), (sorted(full), log[-2000:])
+    assert "second" in log  # the stage switch was announced
+    assert sorted(d for d in os.listdir(tmp_path / "ckpt") if d.isdigit()) == ["4", "7"]
+    # the checkpoint knows how many tokens came from which folder, job-wide (2 ranks x 2 micro-batches x 2 sequences x 32 tokens per step)
+    import json
+
+    meta = json.load(open(tmp_path / "ckpt" / "4" / "checkpoint_metadata.json"))["metas"]
+    per_stage = [sum(s["consumed_tokens_per_dataset_folder"].values()) for s in meta["data_stages"]]
+    assert per_stage == [3 * 256, 1 * 256] and meta["consumed_tokens_total"] == 4 * 256, meta
+    # resume from step 4 (one step into the second stage): steps 5..7 must repeat the interrupted run
+    (tmp_path / "ckpt" / "latest.txt").write_text("4")
+    resumed, log2 = _train(_config(tmp_path, folders, resume=str(tmp_path / "ckpt"), streamed=streamed))
+    assert sorted(resumed) == [5, 6, 7], (sorted(resumed), log2[-2000:])
+    for step in (5, 6, 7):
+        assert abs(resumed[step] - full[step]) < 2e-3 * max(1.0, full[step]), (step, resumed, full)
