@@ -98,3 +98,11 @@ def test_run_train_with_data_stages_and_resume(tmp_path, streamed):
     assert sorted(resumed) == [5, 6, 7], (sorted(resumed), log2[-2000:])
     for step in (5, 6, 7):
         assert abs(resumed[step] - full[step]) < 2e-3 * max(1.0, full[step]), (step, resumed, full)
+    if not streamed:
+        # the same checkpoint (written by 2 data-parallel ranks) decodes under tensor parallelism 2 through run_generate.py
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+               os.path.join(ROOT, "run_generate.py"), "--ckpt-path", str(tmp_path / "ckpt" / "7"), "--tp", "2", "--max-new-tokens", "4"]
+        out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+        assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+        assert "generat" in (out.stdout + out.stderr).lower()
