@@ -118,7 +118,17 @@ def before_optim_step_sanity_checks(config, parallel_context: ParallelContext, u
     for name, param in sorted(unwrapped_model.named_parameters(), key=lambda x: x[0]):
         assert_tensor_synced_across_pg(param, _replica_group(param, parallel_context), msg=lambda err, name=name: f"{name} are not synchronized across DP {err}")
     if optimizer is not None and not zero:
-        check_optim_state_in_sync(optimizer.state_dict(), parallel_context.dp_pg)
+        # replicas of an optimizer state are the replicas of its parameter: all of dp, except for experts (their dp ranks of other
+        # expert ranks hold other experts)
+        by_name = dict(unwrapped_model.get_named_params_with_correct_tied()) if hasattr(unwrapped_model, "get_named_params_with_correct_tied") else dict(unwrapped_model.named_parameters())
+        state_dict = optimizer.state_dict()
+        names = state_dict.get("names", {})
+
+        def group_of(idx):
+            param = by_name.get(names.get(idx))
+            return _replica_group(param, parallel_context) if param is not None else parallel_context.dp_pg
+
+        check_optim_state_in_sync(state_dict, parallel_context.dp_pg, group_of=group_of)
     unwrapped_model.before_optim_step_sanity_checks()
 
 
@@ -131,9 +141,11 @@ def after_optim_step_sanity_checks(config, parallel_context: ParallelContext, un
     unwrapped_model.after_optim_step_sanity_checks()
 
 
-def check_optim_state_in_sync(optim_state_dict: dict, pg: dist.ProcessGroup):
-    for _, st in sorted(optim_state_dict["state"].items(), key=lambda x: x[0]):
+def check_optim_state_in_sync(optim_state_dict: dict, pg: dist.ProcessGroup, group_of=None):
+    """Every optimizer state tensor is identical on the ranks of ``pg`` (or of ``group_of(state index)`` when given)."""
+    for idx, st in sorted(optim_state_dict["state"].items(), key=lambda x: x[0]):
+        group = group_of(idx) if group_of is not None else pg
         for name, tensor in st.items():
             if name == "step" or not isinstance(tensor, torch.Tensor):
                 continue
-            assert_tensor_synced_across_pg(tensor, pg, msg=lambda err, name=name: f"{name} are not synced across DP {err}")
+            assert_tensor_synced_across_pg(tensor, group, msg=lambda err, name=name: f"{name} are not synced across DP {err}")

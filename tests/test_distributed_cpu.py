@@ -265,7 +265,7 @@ def test_topologies_agree_on_loss_curve(tmp_path):
 
 def test_3d_and_qwen_topologies(tmp_path):
     base = _losses_for(tmp_path, 1, "qbase", model="qwen")
-    got = _losses_for(tmp_path, 4, "q3d", model="qwen", dp=2, tp=2, tp_mode="reduce_scatter", zero=1)
+    got = _losses_for(tmp_path, 4, "q3d", model="qwen", dp=2, tp=2, tp_mode="reduce_scatter", zero=1, sanity=True)  # with the runtime invariant checks on
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4, (got, base)
     got = _losses_for(tmp_path, 4, "qpp", model="qwen", pp=2, tp=2, pp_engine="1f1b")
@@ -280,7 +280,7 @@ def test_tied_embeddings_across_stages_with_zero1(tmp_path):
     """Embedding and lm head tied across two pipeline stages, each stage data-parallel with ZeRO-1: the tie-group sum of the
     gradients must see whole (not reduce-scattered) gradients, or the two copies drift apart."""
     base = _losses_for(tmp_path, 1, "tbase", tie=True)
-    got = _losses_for(tmp_path, 4, "tpp2dp2", tie=True, pp=2, dp=2, zero=1, pp_engine="1f1b")
+    got = _losses_for(tmp_path, 4, "tpp2dp2", tie=True, pp=2, dp=2, zero=1, pp_engine="1f1b", sanity=True)
     for a, b in zip(got, base):
         assert abs(a - b) < 2e-4, (got, base)
     _same_norms(tmp_path, "tpp2dp2", "tbase")  # the tied matrix is counted once, not once per stage
@@ -318,7 +318,7 @@ def test_expert_parallel_training_matches_replicated_experts(tmp_path):
     # with sequence-parallel tp every rank routes its own token shard (the load-balance loss is a statistic of that shard), so the
     # like-for-like comparison is the same tp layout with replicated experts
     rep_tp = _losses_for(tmp_path, 4, "moe_dp2_tp2", model="moe", dp=2, tp=2, tp_mode="reduce_scatter")
-    got = _losses_for(tmp_path, 4, "moe_ep2_tp2", model="moe", dp=2, ep=2, tp=2, tp_mode="reduce_scatter")
+    got = _losses_for(tmp_path, 4, "moe_ep2_tp2", model="moe", dp=2, tp=2, ep=2, tp_mode="reduce_scatter", sanity=True)  # invariant checks know which ranks replicate an expert
     for a, b in zip(got, rep_tp):
         assert abs(a - b) < 3e-4, (got, rep_tp)
     _same_norms(tmp_path, "moe_ep2_tp2", "moe_dp2_tp2")  # the tp copies of an expert count once
