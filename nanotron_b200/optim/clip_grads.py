@@ -42,8 +42,13 @@ def clip_grad_norm(
     norm_type: float = 2.0,
     extra_reduce_group: Optional[dist.ProcessGroup] = None,
     grad_slices: Optional[Iterable[torch.Tensor]] = None,
+    scale_slices: Optional[Iterable[torch.Tensor]] = None,
 ) -> torch.Tensor:
-    """Scale gradients so their global norm is at most ``max_norm``.  Returns the norm before clipping (0-dim tensor)."""
+    """Scale gradients so their global norm is at most ``max_norm``.  Returns the norm before clipping (0-dim tensor).
+
+    ``grad_slices``: the tensors whose norm is taken (ZeRO-1: this rank's slices, each tied weight on one rank of its tie group
+    only).  ``scale_slices``: the tensors that are scaled; it defaults to ``grad_slices`` but must also hold the copies that the
+    norm skipped, or a tied weight would be clipped on one rank of its group and not on the others."""
     named_parameters = list(named_parameters)
     grads = list(grad_slices) if grad_slices is not None else _local_grads(named_parameters, grad_accumulator)
     device = grads[0].device if grads else (named_parameters[0][1].device if named_parameters else torch.device("cpu"))
@@ -63,7 +68,9 @@ def clip_grad_norm(
             dist.all_reduce(total, group=extra_reduce_group, op=dist.ReduceOp.SUM)
         total = total.pow(1.0 / norm_type)
     clip_coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
-    if grad_slices is not None:
+    if scale_slices is not None:
+        targets = list(scale_slices)
+    elif grad_slices is not None:
         targets = grads
     elif grad_accumulator is not None:
         targets = [grad_accumulator.get_grad_buffer(n) for n, _ in named_parameters]

@@ -102,13 +102,19 @@ def _canonical(name, param, model):
 def before_optim_step_sanity_checks(config, parallel_context: ParallelContext, unwrapped_model, grad_accumulator, optimizer) -> None:
     if config.general.ignore_sanity_checks:
         return
+    zero = optimizer is not None and optimizer.inherit_from(optim.ZeroDistributedOptimizer)
+    # After the in-place reduce-scatter of ZeRO-1 a gradient is only meaningful on the slice its rank optimises, and the members of
+    # a tie group (two pipeline stages, say) own different slices of the same weight: whole tensors cannot be compared then.
+    # Members on the same stage (tensor-parallel replicas) lay their buffers out identically and own the same slices: those stay comparable.
+    sliced = zero and parallel_context.dp_pg.size() > 1
     for (name, ranks), param in sorted(get_tied_id_to_param(list(unwrapped_model.parameters()), unwrapped_model).items(), key=lambda x: x[0]):
-        if not param.requires_grad or param.get_tied_info().reduce_op is None and False:
+        if not param.requires_grad:
+            continue
+        if sliced and len({parallel_context.get_local_ranks(world_rank=r)["pp"] for r in ranks}) > 1:
             continue
         grad = grad_accumulator.get_grad_buffer(name=name) if grad_accumulator is not None else param.grad
         group = parallel_context.world_ranks_to_pg[tuple(sorted(ranks))]
         assert_tensor_synced_across_pg(grad, group, msg=lambda err, name=name: f"[Before optimizer step] Tied weights grads for {name} are not synchronized. {err}")
-    zero = optimizer is not None and optimizer.inherit_from(optim.ZeroDistributedOptimizer)
     if not zero:
         for name, param in sorted(unwrapped_model.named_parameters(), key=lambda x: x[0]):
             if not param.requires_grad:

@@ -560,18 +560,21 @@ class DistributedTrainer:
             # gradients are only valid on this rank's shard: norm over the owned slices, summed over dp as well
             me = dist.get_rank(ctx.dp_pg)
             world_rank = dist.get_rank(ctx.world_pg)
-            slices = []
+            slices, owned = [], []
             for n, p in named:
                 rng = self.optimizer.param_name_to_dp_rank_offsets[n].get(me) if hasattr(self.optimizer, "param_name_to_dp_rank_offsets") else None
                 if rng is None:
                     continue
+                piece = self.grad_accumulator.get_grad_buffer(n).view(-1)[rng[0] : rng[1]]
+                owned.append(piece)  # every owned slice is scaled ...
                 if p.is_tied:
                     ranks = p.get_tied_info().global_ranks
-                    # a tied parameter is counted by the first rank of its tie group (same dp rank by construction)
+                    # ... but a tied parameter is counted in the norm by the first rank of its tie group only (same dp rank by construction)
                     if ctx.get_local_ranks(world_rank)["dp"] == me and world_rank != sorted(ranks)[0] and len(ranks) > 1:
                         continue
-                slices.append(self.grad_accumulator.get_grad_buffer(n).view(-1)[rng[0] : rng[1]])
-            return clip_grad_norm(mp_pg=ctx.mp_pg, named_parameters=named, grad_accumulator=self.grad_accumulator, max_norm=self.config.optimizer.clip_grad, extra_reduce_group=ctx.dp_pg, grad_slices=slices)
+                slices.append(piece)
+            return clip_grad_norm(mp_pg=ctx.mp_pg, named_parameters=named, grad_accumulator=self.grad_accumulator, max_norm=self.config.optimizer.clip_grad, extra_reduce_group=ctx.dp_pg,
+                                  grad_slices=slices, scale_slices=owned)
         extra = ctx.ep_pg if ctx.expert_parallel_size > 1 else None
         if extra is not None:
             # dense params are replicated over ep: count them on ep rank 0 only so the ep-sum is exact
