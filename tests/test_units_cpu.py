@@ -397,3 +397,37 @@ def test_fsspec_helpers_copy_between_file_systems(tmp_path):
     fs_copy("memory://bucket/run/a.bin", tmp_path / "back.bin")
     assert (tmp_path / "back.bin").read_bytes() == payload
     assert check_path_is_local(tmp_path) and not check_path_is_local("memory://bucket/run")
+
+
+def test_learning_rate_schedules_have_the_documented_shapes():
+    """Linear / constant warm-up, then cosine / linear / 1-sqrt decay to ``min_decay_lr`` over ``lr_decay_steps`` from ``lr_decay_starting_step``,
+    then flat; the default decay length is what is left of training after the warm-up."""
+    import math
+
+    import nanotron_b200.config as c
+    from nanotron_b200.helpers import lr_scheduler_builder
+
+    def curve(total=20, **kw):
+        p = torch.nn.Parameter(torch.zeros(1))
+        opt = torch.optim.SGD([p], lr=1.0)
+        sched = lr_scheduler_builder(opt, c.LRSchedulerArgs(learning_rate=1.0, **kw), total_training_steps=total)
+        out = []
+        for _ in range(total + 3):
+            out.append(opt.param_groups[0]["lr"])
+            opt.step()
+            sched.step()
+        return out
+
+    cos = curve(lr_warmup_steps=4, lr_warmup_style="linear", lr_decay_style="cosine", lr_decay_steps=10, lr_decay_starting_step=6, min_decay_lr=0.1)
+    assert cos[:5] == pytest.approx([0.0, 0.25, 0.5, 0.75, 1.0]) and cos[5] == cos[6] == pytest.approx(1.0)  # warm-up, then the plateau before the decay starts
+    assert cos[11] == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 5 / 10)))  # half way down the cosine
+    assert cos[16] == pytest.approx(0.1) and cos[-1] == pytest.approx(0.1)  # floor, kept after the decay ends
+    assert all(a >= b - 1e-12 for a, b in zip(cos[6:], cos[7:]))  # monotone from the plateau on
+    lin = curve(lr_warmup_steps=2, lr_warmup_style="constant", lr_decay_style="linear", lr_decay_steps=8, min_decay_lr=0.2)
+    assert lin[0] == lin[1] == pytest.approx(1.0)  # constant warm-up stays at the peak
+    assert lin[2 + 4] == pytest.approx(0.2 + 0.8 * 0.5) and lin[10] == pytest.approx(0.2)
+    sq = curve(lr_warmup_steps=0, lr_decay_style="1-sqrt", lr_decay_steps=16, min_decay_lr=0.0)
+    assert sq[4] == pytest.approx(1 - math.sqrt(4 / 16)) and sq[16] == pytest.approx(0.0)
+    # default decay length: total steps minus the warm-up
+    default = curve(total=12, lr_warmup_steps=2, lr_warmup_style="linear", lr_decay_style="linear", min_decay_lr=0.0)
+    assert default[2] == pytest.approx(1.0) and default[12] == pytest.approx(0.0) and default[7] == pytest.approx(0.5)
