@@ -157,11 +157,13 @@ def _deterministic_init(model):
     the element's position in the unsharded tensor."""
     import zlib
 
+    tied_names = getattr(model, "get_embeddings_lm_head_tied_names", lambda: [])()
+    tied_matrix = bool(tied_names) or getattr(getattr(model, "config", None), "tie_word_embeddings", False)
     with torch.no_grad():
         for name, p in model.get_named_params_with_correct_tied():
             shape = tuple(p.get_sharded_info().unsharded_shape) if p.is_sharded else tuple(p.shape)
             seed_name = name
-            if getattr(getattr(model, "config", None), "tie_word_embeddings", False) and ("token_embedding" in name or "lm_head" in name):
+            if tied_matrix and ("token_embedding" in name or "lm_head" in name):
                 seed_name = "tied_word_embeddings"  # one matrix under two names (one per pipeline stage)
             g = torch.Generator().manual_seed(zlib.crc32(seed_name.encode()))
             full = torch.randn(shape, generator=g, dtype=torch.float32) * 0.05

@@ -17,7 +17,7 @@ def _config(mq: bool, **over):
     return Starcoder2Config(**base)
 
 
-def _train(out_file, mq, steps=3, ckpt=None, resume=None, **topology):
+def _train(out_file, mq, steps=3, ckpt=None, resume=None, sanity=False, clip=1.0, **topology):
     import nanotron_b200.distributed as dist
     from nanotron_b200.trainer import DistributedTrainer as Base
 
@@ -28,7 +28,8 @@ def _train(out_file, mq, steps=3, ckpt=None, resume=None, **topology):
             _deterministic_init(model)
             return model
 
-    cfg = make_config(_config(mq), seq=16, mbs=1, accum=4, steps=8, lr=1e-2, ckpt_path=ckpt, **topology)
+    dp = topology.get("dp", 1)
+    cfg = make_config(_config(mq), seq=16, mbs=1, accum=4 // dp, steps=8, lr=1e-2, ckpt_path=ckpt, sanity=sanity, clip=clip, **topology)
     if resume:
         cfg.checkpoints.resume_checkpoint_path = resume
     t = T(cfg)
@@ -65,6 +66,19 @@ def test_mqa_and_gqa_match_one_process_under_tensor_parallelism(tmp_path):
             got = _losses(tmp_path, f"tp{mq}{mode}", 2, mq=mq, tp=2, tp_mode=mode)
             for a, b in zip(got, base):
                 assert abs(a - b) < 2e-4, (mq, mode, got, base)
+
+
+def test_mqa_and_gqa_match_one_process_under_3d_layouts_with_the_invariant_checks_on(tmp_path):
+    """Tied embeddings across pipeline stages, the single replicated kv head under tensor parallelism and sharded optimizer
+    states together, with active clipping and the runtime invariant checks."""
+    base = _losses(tmp_path, "base_mq", 1, mq=True, clip=0.05)
+    got = _losses(tmp_path, "mq_3d", 8, mq=True, dp=2, tp=2, pp=2, tp_mode="reduce_scatter", zero=1, pp_engine="1f1b", sanity=True, clip=0.05)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 3e-4, (got, base)
+    base = _losses(tmp_path, "base_gq", 1, mq=False, clip=0.05)
+    got = _losses(tmp_path, "gq_pp2_tp2", 4, mq=False, tp=2, pp=2, tp_mode="all_reduce", pp_engine="afab", sanity=True, clip=0.05)
+    for a, b in zip(got, base):
+        assert abs(a - b) < 3e-4, (got, base)
 
 
 def test_mqa_checkpoint_has_one_replicated_kv_projection_and_resumes(tmp_path):
