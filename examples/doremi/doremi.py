@@ -1,5 +1,6 @@
 """DoReMi (domain reweighting with minimax optimisation) on top of the framework's extension points
-(capability parity: reference examples/doremi/doremi/{config,doremi_context,loss,llama,trainer}.py).
+(capability parity: reference examples/doremi/doremi/{config,doremi_context,loss,llama,trainer}.py; the domain-weighted
+sampler and collator live in ``dataloader.py`` beside this file).
 
 A small *proxy* model is trained with a loss that re-weights data domains; the weights follow the per-domain *excess loss*
 of the proxy over a frozen *reference* model:
@@ -13,7 +14,10 @@ What this file shows about the framework:
   * ``LlamaForDoReMiTraining`` reuses the stock Llama decoder and replaces only the loss ``PipelineBlock``; the trainer gets it
     as ``model_class`` (the batch carries two extra keys, ``domain_idxs`` and ``ref_losses``);
   * ``DoReMiTrainer`` subclasses ``DistributedTrainer``: ``_init_model_instance`` builds the frozen reference model next to the
-    proxy, and the dataloader is wrapped so every micro-batch is scored by the reference first.
+    proxy, and the dataloader is wrapped so every micro-batch is scored by the reference first; the history of the domain
+    weights is written beside every checkpoint (``doremi_domain_weights_<step>.pt``) and read back on resume;
+  * ``ReferenceTrainer`` trains a plain model on a fixed mixture (step 1 and step 4 of the recipe) and logs the loss of every
+    domain.
 Pipeline parallelism is not supported by this example (the reference model's per-token losses are fed back as an input).
 """
 from __future__ import annotations
@@ -46,8 +50,17 @@ class DoReMiArgs:
     smoothing_param: float = 1e-3
     ref_model_resume_checkpoint_path: Optional[str] = None  # weights of the reference model; None: random init with ref_model_seed
     ref_model_seed: int = 1234
+    # True: the sampler follows the weights as they move (what the reference implementation does); False: the mixture of the
+    # batches stays at the initial weights and only the loss is re-weighted (Algorithm 1 of the paper)
+    sample_with_current_weights: bool = False
+    # one folder of tokenised ``.ds`` files per domain (same order as domain_names); None: the synthetic domains of ``utils.py``
+    domain_folders: Optional[List[str]] = None
+    token_size: int = 2  # bytes per token in those files
+    samples_per_synthetic_domain: int = 4096
 
     def __post_init__(self):
+        if self.domain_folders is not None:
+            assert len(self.domain_folders) == len(self.domain_names), "one folder per domain"
         if self.domain_weights is not None:
             assert len(self.domain_weights) == len(self.domain_names)
             assert abs(sum(self.domain_weights) - 1.0) < 1e-3, "domain weights must sum to 1"
@@ -72,6 +85,15 @@ class DoReMiContext:
     @property
     def num_domains(self) -> int:
         return len(self.domain_names)
+
+    def history_records(self) -> List[Dict[str, object]]:
+        return [{"update": i, "domain_names": self.domain_names, "domain_weights": w.detach().cpu()} for i, w in enumerate(self.history)]
+
+    def load_history(self, records: List[Dict[str, object]]) -> None:
+        assert list(records[0]["domain_names"]) == self.domain_names, "the saved weights belong to other domains"
+        device = self.domain_weights.device
+        self.history = [r["domain_weights"].to(device) for r in records]
+        self.domain_weights = self.history[-1].clone()
 
     def update(self, excess_per_domain: torch.Tensor):
         w = self.domain_weights * torch.exp(self.step_size * excess_per_domain)
@@ -147,6 +169,41 @@ class LlamaReferenceForDoReMi(LlamaForTraining):
         return self.loss(sharded_logits=logits, label_ids=label_ids, label_mask=label_mask)
 
 
+class PerDomainLoss(nn.Module):
+    """Plain mean cross entropy (what is optimised) plus the loss sum and token count of every domain (what is logged)."""
+
+    def __init__(self, tp_pg, num_domains: int):
+        super().__init__()
+        self.tp_pg, self.num_domains = tp_pg, num_domains
+
+    def forward(self, sharded_logits, label_ids, label_mask, domain_idxs):
+        losses = per_token_losses(sharded_logits, label_ids, self.tp_pg) * label_mask
+        loss = losses.sum() / label_mask.sum().clamp(min=1)
+        with torch.no_grad():
+            dom = domain_idxs.reshape(-1).long()
+            sums = torch.zeros(self.num_domains, dtype=torch.float32, device=losses.device).index_add_(0, dom, losses.detach().sum(-1))
+            tokens = torch.zeros(self.num_domains, dtype=torch.float32, device=losses.device).index_add_(0, dom, label_mask.sum(-1).float())
+        return {"loss": loss, "domain_loss_sums": sums, "domain_tokens": tokens}
+
+
+class LlamaForReferenceTraining(LlamaForTraining):
+    """The stock Llama trained on a fixed mixture; its loss block also reports every domain's loss."""
+
+    num_domains: Optional[int] = None  # set by ReferenceTrainer before the model is built
+
+    def __init__(self, config, parallel_context, parallel_config, random_states=None):
+        super().__init__(config=config, parallel_context=parallel_context, parallel_config=parallel_config, random_states=random_states)
+        assert type(self).num_domains is not None, "ReferenceTrainer sets LlamaForReferenceTraining.num_domains before building the model"
+        self.loss = PipelineBlock(
+            p2p=self.model.p2p, module_builder=PerDomainLoss, module_kwargs={"tp_pg": parallel_context.tp_pg, "num_domains": type(self).num_domains},
+            module_input_keys={"sharded_logits", "label_ids", "label_mask", "domain_idxs"}, module_output_keys={"loss", "domain_loss_sums", "domain_tokens"},
+        )
+
+    def forward(self, input_ids, input_mask, label_ids, label_mask, domain_idxs):
+        logits = self.model(input_ids=input_ids, input_mask=input_mask)
+        return self.loss(sharded_logits=logits, label_ids=label_ids, label_mask=label_mask, domain_idxs=domain_idxs)
+
+
 class LlamaForDoReMiTraining(LlamaForTraining):
     doremi_context: Optional[DoReMiContext] = None  # set by the trainer before the model is built
 
@@ -204,7 +261,76 @@ class DoReMiTrainer(DistributedTrainer):
     def _wrap(self, dl):
         return self._score_with_reference(super()._wrap(dl))
 
+    def sampling_weights(self) -> torch.Tensor:
+        """What a ``dataloader.DomainWeightedSampler`` of this run follows (its ``weights_fn``)."""
+        if self.config.doremi.sample_with_current_weights:
+            return self.doremi_context.domain_weights
+        return self.doremi_context.history[0]
+
     def train_step_logs(self, outputs, loss_avg, z_loss_avg=None):
         super().train_step_logs(outputs=outputs, loss_avg=loss_avg, z_loss_avg=z_loss_avg)
         w = ", ".join(f"{n}={float(v):.4f}" for n, v in zip(self.doremi_context.domain_names, self.doremi_context.domain_weights))
         log_rank(f"[DoReMi] domain weights: {w}", logger=logger, level=logging.INFO, rank=0)
+
+    # the weights are the product of proxy training: one file per checkpoint with every value they took so far
+    def post_init(self):
+        super().post_init()
+        if self.init_checkpoint_path is not None:
+            path = _weights_file(self.init_checkpoint_path.parent, self.metadata.last_train_step)
+            if path.exists():
+                self.doremi_context.load_history(torch.load(path, map_location="cpu"))
+                log_rank(f"[DoReMi] resumed the domain weights from {path}", logger=logger, level=logging.INFO, rank=0)
+
+    def post_save_checkpoint(self):
+        if dist.get_rank(self.parallel_context.world_pg) == 0:
+            torch.save(self.doremi_context.history_records(), _weights_file(self.config.checkpoints.checkpoints_path, self.iteration_step))
+        super().post_save_checkpoint()
+
+
+def _weights_file(checkpoints_path, step: int):
+    from pathlib import Path
+
+    return Path(checkpoints_path) / f"doremi_domain_weights_{step}.pt"
+
+
+def average_domain_weights(path) -> torch.Tensor:
+    """The tuned mixture: the mean of the weights over all updates of a proxy run (what the larger run is trained with)."""
+    records = torch.load(path, map_location="cpu")
+    return torch.stack([r["domain_weights"] for r in records]).mean(0)
+
+
+class ReferenceTrainer(DistributedTrainer):
+    """Training on a fixed mixture of the domains with per-domain loss logging: the small reference model of step 1, and the
+    large model of step 4 with the tuned weights (capability parity: reference examples/doremi/doremi/trainer.py:200-270)."""
+
+    def __init__(self, config_or_config_file: Union[DoReMiConfig, str], domain_weights: Optional[torch.Tensor] = None):
+        self._given_weights = domain_weights
+        super().__init__(config_or_config_file, config_class=DoReMiConfig, model_class=LlamaForReferenceTraining)
+
+    def pre_init(self):
+        super().pre_init()
+        assert self.config.doremi is not None, "the config needs a `doremi` section"
+        self.doremi_context = DoReMiContext(self.config.doremi, self.parallel_context.device)
+        if self._given_weights is not None:  # e.g. weights from the token counts of the datasets
+            w = torch.as_tensor(self._given_weights, dtype=torch.float32, device=self.parallel_context.device)
+            assert w.numel() == self.doremi_context.num_domains and abs(float(w.sum()) - 1.0) < 1e-3
+            self.doremi_context.domain_weights = w
+            self.doremi_context.history = [w.clone()]
+        LlamaForReferenceTraining.num_domains = self.doremi_context.num_domains
+        self.domain_losses: Optional[torch.Tensor] = None
+
+    def sampling_weights(self) -> torch.Tensor:
+        return self.doremi_context.domain_weights
+
+    def train_step_logs(self, outputs, loss_avg, z_loss_avg=None):
+        super().train_step_logs(outputs=outputs, loss_avg=loss_avg, z_loss_avg=z_loss_avg)
+        if not isinstance(outputs[0]["loss"], torch.Tensor):
+            return  # not the pipeline rank that holds the loss
+        stats = torch.stack([torch.stack([o["domain_loss_sums"] for o in outputs]).sum(0), torch.stack([o["domain_tokens"] for o in outputs]).sum(0)])
+        pg = self.parallel_context.dp_pg
+        if pg.size() > 1:
+            dist.all_reduce(stats, group=pg)
+        self.domain_losses = torch.where(stats[1] > 0, stats[0] / stats[1].clamp(min=1e-9), torch.full_like(stats[0], float("nan")))
+        if self.iteration_step % self.config.logging.iteration_step_info_interval == 0:
+            text = ", ".join(f"{n}={float(v):.4f}" for n, v in zip(self.doremi_context.domain_names, self.domain_losses))
+            log_rank(f"[DoReMi] domain losses: {text}", logger=logger, level=logging.INFO, rank=self.logger_ranks[0] if hasattr(self, "logger_ranks") else 0)

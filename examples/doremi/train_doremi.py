@@ -2,9 +2,10 @@
 
     torchrun --nproc-per-node 2 examples/doremi/train_doremi.py --config-file examples/doremi/config_tiny_doremi.yaml
 
-The synthetic data has one *learnable* domain (counting sequences) and one *noise* domain (uniform tokens): the proxy cannot
-beat the reference on noise, so the excess loss concentrates on ... whichever domain the proxy still lags the reference on, and the
-domain weights drift away from uniform, which is what the printed weights show.
+Without ``doremi.domain_folders`` in the config the data is synthetic: one *learnable* domain (counting sequences) and one
+*noise* domain (uniform tokens).  The excess loss concentrates on whichever domain the proxy still lags the reference on, and the
+domain weights drift away from uniform, which is what the printed weights show.  Batches come from the domain-weighted sampler of
+``dataloader.py``; ``domain_batches`` below is the smallest possible alternative (an endless generator, no datasets).
 """
 import argparse
 import os
@@ -16,7 +17,9 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
+from dataloader import get_dataloader  # noqa: E402
 from doremi import DoReMiTrainer  # noqa: E402
+from utils import get_domain_datasets  # noqa: E402
 
 from nanotron_b200 import distributed as dist  # noqa: E402
 
@@ -50,8 +53,8 @@ def main():
     ap.add_argument("--config-file", type=str, required=True)
     args = ap.parse_args()
     trainer = DoReMiTrainer(args.config_file)
-    stage = trainer.config.data_stages[-1]
-    trainer.train({s.name: domain_batches(trainer, seed=stage.data.seed) for s in trainer.config.data_stages})
+    datasets = get_domain_datasets(trainer)
+    trainer.train({s.name: get_dataloader(trainer, datasets, weights_fn=trainer.sampling_weights) for s in trainer.config.data_stages})
 
 
 if __name__ == "__main__":

@@ -4,6 +4,8 @@ import importlib.util
 import os
 import sys
 
+import pytest
+
 import torch
 
 from helpers import make_config, run_distributed, single_process_env, tiny_llama_config
@@ -259,3 +261,109 @@ def test_every_shipped_configuration_file_loads():
     assert variants.resume().checkpoints.resume_checkpoint_path is not None
     assert variants.s3_upload().s3_upload.upload_s3_path.startswith("s3://")
     assert variants.nanoset().data_stages[1].data.dataset.dataset_weights == [0.8, 0.2]
+
+
+def test_doremi_quotas_and_domain_weighted_sampler():
+    sys.path.insert(0, os.path.join(ROOT, "examples", "doremi"))
+    import numpy as np
+    from dataloader import CombinedDataset, DomainWeightedSampler, apportion, domain_weights_from_token_count
+    from utils import SyntheticDomain
+
+    # quotas: sum to the batch, within one sample of the exact share unless the floor binds, every domain keeps one sample
+    assert apportion([0.5, 0.3, 0.2], 10) == [5, 3, 2]
+    assert apportion([0.98, 0.01, 0.01], 16) == [14, 1, 1]
+    assert sum(apportion([0.37, 0.33, 0.30], 7)) == 7
+    rng = np.random.default_rng(0)
+    wins = np.zeros(3)
+    for _ in range(300):  # equal weights, 4 samples: the extra sample goes to every domain equally often with a random tie-break
+        wins += np.asarray(apportion([1, 1, 1], 4, rng=rng)) - 1
+    assert wins.sum() == 300 and wins.min() > 60
+    with pytest.raises(ValueError):
+        apportion([0.5, 0.5], 1)
+    # the sampler: both data-parallel ranks draw from one global batch that follows the weights; domains never repeat an item
+    # inside a pass; a change of the weights shows in the next global batch
+    domains = [SyntheticDomain("counting", 40, 9, 32), SyntheticDomain("noise", 24, 9, 32), SyntheticDomain("repeat", 16, 9, 32)]
+    combined = CombinedDataset(domains)
+    assert len(combined) == 80 and combined.locate(40) == (1, 0) and combined[63]["domain_idx"] == 1 and combined[64]["domain_idx"] == 2
+    torch.testing.assert_close(domain_weights_from_token_count(domains), torch.tensor([0.5, 0.3, 0.2]))
+    weights = {"w": [0.5, 0.25, 0.25]}
+    samplers = [DomainWeightedSampler(combined.lengths, micro_batch_size=2, num_microbatches=2, dp_size=2, dp_rank=r, weights_fn=lambda: weights["w"], seed=3) for r in range(2)]
+    its = [iter(s) for s in samplers]
+    seen = [[], [], []]
+    for step in range(4):
+        batch = [i for it in its for _ in range(2) for i in next(it)]  # 2 ranks x 2 micro-batches x 2 samples
+        assert len(batch) == 8 and len(set(batch)) == 8
+        doms = [combined.locate(i)[0] for i in batch]
+        assert [doms.count(d) for d in range(3)] == [4, 2, 2] == samplers[0].last_quotas
+        for i, d in zip(batch, doms):
+            seen[d].append(i)
+    assert all(len(set(s)) == len(s) for s in seen)
+    weights["w"] = [0.125, 0.75, 0.125]
+    batch = [i for it in its for _ in range(2) for i in next(it)]
+    assert [[combined.locate(i)[0] for i in batch].count(d) for d in range(3)] == [1, 6, 1]
+    # resumable: a new sampler with the saved counters continues with the same batches
+    state = samplers[0].state_dict()
+    fresh = DomainWeightedSampler(combined.lengths, 2, 2, 2, 0, lambda: weights["w"], seed=3)
+    fresh.load_state_dict(state)
+    assert [next(its[0]) for _ in range(4)] == [b for _, b in zip(range(4), iter(fresh))]
+    # an exhausted domain starts a new pass (default) or ends the epoch
+    stop = DomainWeightedSampler([3, 100], 2, 1, 1, 0, lambda: [0.5, 0.5], seed=0, on_exhausted="stop")
+    assert len(list(stop)) == 3
+    wrap = DomainWeightedSampler([3, 100], 2, 1, 1, 0, lambda: [0.5, 0.5], seed=0)
+    got = [b for _, b in zip(range(6), iter(wrap))]
+    assert wrap.passes[0] == 1 and sorted(i for b in got for i in b if i < 3) == [0, 0, 1, 1, 2, 2]
+
+
+def _doremi_reference_run(out_file, ckpt):
+    sys.path.insert(0, os.path.join(ROOT, "examples", "doremi"))
+    import doremi as dr
+    import nanotron_b200.distributed as dist
+    from dataloader import get_dataloader
+    from utils import get_domain_datasets
+
+    os.chdir(os.path.dirname(out_file))
+    cfg_path = os.path.join(ROOT, "examples", "doremi", "config_tiny_doremi.yaml")
+    # step 1 of the recipe: a reference model on a fixed 3:1 mixture, with the loss of every domain
+    ref = dr.ReferenceTrainer(cfg_path, domain_weights=torch.tensor([0.75, 0.25]))
+    ref.config.tokens.train_steps = 30
+    ref.config.checkpoints.checkpoints_path = ckpt + "/ref"
+    datasets = get_domain_datasets(ref)
+    ref.train({"proxy": get_dataloader(ref, datasets, weights_fn=ref.sampling_weights)})
+    assert ref.doremi_sampler.last_quotas == [6, 2]  # global batch 8
+    losses = ref.domain_losses
+    assert float(losses[0]) < float(losses[1]) - 0.5, losses  # counting is learnable, noise is not
+    del ref
+    # step 2: the proxy scores against that checkpoint; its weight history lands beside its own checkpoints and is resumed
+    t = dr.DoReMiTrainer(cfg_path)
+    assert t.config.doremi.ref_model_resume_checkpoint_path is None
+    t.config.doremi.ref_model_resume_checkpoint_path = ckpt + "/ref/30"
+    dr.load_weights(model=t.ref_model, parallel_context=t.parallel_context, root_folder=ckpt + "/ref/30")
+    t.config.tokens.train_steps = 6
+    t.config.checkpoints.checkpoints_path = ckpt + "/proxy"
+    t.train({"proxy": get_dataloader(t, get_domain_datasets(t), weights_fn=t.sampling_weights)})
+    assert t.doremi_sampler.last_quotas == [4, 4]  # sampling keeps the starting mixture, the loss is re-weighted
+    final = t.doremi_context.domain_weights.clone()
+    n = len(t.doremi_context.history)
+    dist.barrier()
+    avg = dr.average_domain_weights(ckpt + "/proxy/doremi_domain_weights_6.pt")
+    torch.testing.assert_close(avg, torch.stack(t.doremi_context.history).mean(0).cpu())
+    del t
+    from nanotron_b200.config import get_config_from_file
+
+    cfg = get_config_from_file(cfg_path, config_class=dr.DoReMiConfig)
+    cfg.checkpoints.checkpoints_path = ckpt + "/proxy"
+    cfg.checkpoints.resume_checkpoint_path = ckpt + "/proxy"
+    cfg.doremi.ref_model_resume_checkpoint_path = ckpt + "/ref/30"
+    resumed = dr.DoReMiTrainer(cfg)
+    torch.testing.assert_close(resumed.doremi_context.domain_weights, final)
+    assert len(resumed.doremi_context.history) == n and resumed.iteration_step == 6
+    if dist.get_rank(resumed.parallel_context.world_pg) == 0:
+        torch.save({"ref_domain_losses": losses.cpu(), "weights": final.cpu()}, out_file)
+    resumed.parallel_context.destroy()
+
+
+def test_doremi_reference_then_proxy_with_saved_domain_weights(tmp_path):
+    out = str(tmp_path / "doremi_ref.pt")
+    run_distributed(_doremi_reference_run, 2, out_file=out, ckpt=str(tmp_path / "ckpt"))
+    res = torch.load(out)
+    assert abs(float(res["weights"].sum()) - 1.0) < 1e-5
