@@ -294,10 +294,16 @@ class Qwen2Model(nn.Module):
 
     def get_flops_per_sec(self, iteration_time_in_sec, sequence_length, global_batch_size):
         world = self.parallel_context.world_pg.size()
+        c = self.config
+        moe = getattr(c, "moe_config", None)
+        moe_layers = 0
+        if moe is not None:
+            moe_layers = c.num_hidden_layers if -1 in moe.layers else len([i for i in moe.layers if 0 <= i < c.num_hidden_layers])
         model_flops, hardware_flops = get_flops(
-            num_layers=self.config.num_hidden_layers, hidden_size=self.config.hidden_size, num_heads=self.config.num_attention_heads,
-            num_key_value_heads=self.config.num_key_value_heads, vocab_size=self.config.vocab_size, ffn_hidden_size=self.config.intermediate_size,
-            seq_len=sequence_length, batch_size=global_batch_size,
+            num_layers=c.num_hidden_layers, hidden_size=c.hidden_size, num_heads=c.num_attention_heads,
+            num_key_value_heads=c.num_key_value_heads, vocab_size=c.vocab_size, ffn_hidden_size=c.intermediate_size,
+            seq_len=sequence_length, batch_size=global_batch_size, moe_config=moe, num_moe_layers=moe_layers,
+            recompute_layer=bool(getattr(self.parallel_config, "recompute_layer", False)),
         )
         return model_flops / (iteration_time_in_sec * world * 1e12), hardware_flops / (iteration_time_in_sec * world * 1e12)
 
@@ -414,20 +420,30 @@ class Qwen2ForTraining(NanotronModel):
         return self.model.get_flops_per_sec(iteration_time_in_sec, sequence_length, global_batch_size)
 
 
-def get_flops(num_layers, hidden_size, num_heads, num_key_value_heads, vocab_size, seq_len, ffn_hidden_size, batch_size=1):
-    """Model FLOPs of one forward+backward over ``batch_size`` sequences, counted the way the reference does
+def get_flops(num_layers, hidden_size, num_heads, num_key_value_heads, vocab_size, seq_len, ffn_hidden_size, batch_size=1, moe_config=None, num_moe_layers=0, recompute_layer=False):
+    """FLOPs of one forward+backward over ``batch_size`` sequences, counted the way the reference does
     (reference src/nanotron/models/qwen.py:1024-1091): full S^2 attention without causal discount, gated MLP
-    (3 matrices), lm head; backward = 2 x forward.  Returns (model_flops, hardware_flops) -- equal, no recompute term."""
+    (3 matrices), lm head; backward = 2 x forward.
+
+    Beyond the reference: a mixture-of-experts layer counts the experts a token actually visits (``top_k`` gated MLPs of
+    ``moe_intermediate_size``, the router, and the shared expert with its gate when enabled) instead of a dense MLP, and the
+    hardware figure adds the second forward of every decoder layer under full-layer recomputation.
+    Returns (model_flops, hardware_flops)."""
     head_dim = hidden_size // num_heads
     T = batch_size * seq_len
     qkv = 2 * T * hidden_size * (num_heads + 2 * num_key_value_heads) * head_dim
     qk = 2 * num_heads * T * seq_len * head_dim
     pv = 2 * num_heads * T * seq_len * head_dim
     out = 2 * T * num_heads * head_dim * hidden_size
-    gate_up = 4 * T * hidden_size * ffn_hidden_size
-    down = 2 * T * ffn_hidden_size * hidden_size
-    per_layer = qkv + qk + pv + out + gate_up + down
+    attention = qkv + qk + pv + out
+    dense_mlp = 6 * T * hidden_size * ffn_hidden_size
+    moe_mlp = 0
+    if moe_config is not None and num_moe_layers > 0:
+        moe_mlp = 6 * T * hidden_size * moe_config.moe_intermediate_size * moe_config.top_k + 2 * T * hidden_size * moe_config.num_experts
+        if moe_config.enable_shared_expert:
+            moe_mlp += 6 * T * hidden_size * moe_config.shared_expert_intermediate_size + 2 * T * hidden_size
+    layers_fwd = num_layers * attention + (num_layers - num_moe_layers) * dense_mlp + num_moe_layers * moe_mlp
     lm_head = 2 * T * hidden_size * vocab_size
-    fwd = num_layers * per_layer + lm_head
-    model_flops = 3 * fwd
-    return model_flops, model_flops
+    model_flops = 3 * (layers_fwd + lm_head)
+    hardware_flops = model_flops + (layers_fwd if recompute_layer else 0)
+    return model_flops, hardware_flops
