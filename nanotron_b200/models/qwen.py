@@ -116,7 +116,8 @@ class Qwen2Attention(nn.Module, LogMixin):
         """hidden_states: [T_local, h] (T_local = b*s/tp under sequence parallelism); position_ids: [b, s_local]."""
         qkv = self.qkv_proj(hidden_states)  # [T, local_q + 2*local_kv]
         T = qkv.shape[0]
-        if self.cp_size == 1 and self.attn_impl in ("flash_attention_2", "sdpa") and ops.fused_qkv_attention_supported(qkv, self.local_heads, self.local_kv_heads, self.head_dim, self.sliding_window_size):
+        log_stats = self.log_attn_probs and self.training and self.cp_size == 1
+        if not log_stats and self.cp_size == 1 and self.attn_impl in ("flash_attention_2", "sdpa") and ops.fused_qkv_attention_supported(qkv, self.local_heads, self.local_kv_heads, self.head_dim, self.sliding_window_size):
             b, s = position_ids.shape
             cu = cu_seqlens if cu_seqlens is not None else regular_cu_seqlens(b, s, hidden_states.device)
             if self.use_rope:
@@ -128,7 +129,7 @@ class Qwen2Attention(nn.Module, LogMixin):
             out = ops.fused_qkv_attention(qkv, cos, sin, position_ids.reshape(-1), self.local_heads, self.local_kv_heads, self.head_dim, cu, s, causal=True, softmax_scale=self.softmax_scale, window=self.sliding_window_size, interleaved=interleaved, use_rope=self.use_rope)
             out = self.o_proj(out.reshape(T, self.local_q_size))
             return {"hidden_states": out, "position_ids": position_ids}
-        if self.cp_size == 1 and self.softmax_scale is None and self.attn_impl == "flash_attention_2" and ops.fused_qkv_library_attention_supported(qkv, self.head_dim, self.sliding_window_size, cu_seqlens):
+        if not log_stats and self.cp_size == 1 and self.softmax_scale is None and self.attn_impl == "flash_attention_2" and ops.fused_qkv_library_attention_supported(qkv, self.head_dim, self.sliding_window_size, cu_seqlens):
             b, s = position_ids.shape
             if self.use_rope:
                 self.rotary_emb._ensure_tables(self.rotary_emb.max_seq_len, qkv.device)
@@ -150,6 +151,9 @@ class Qwen2Attention(nn.Module, LogMixin):
             max_len = s
         else:
             max_len = s
+        if log_stats:
+            # [local heads, tokens] log-sum-exp of the attention scores, collected by the trainer once per logged step
+            self.tbi_logger({"attn_probs": ops.attention_lse(q, k, v, cu_seqlens, cu_seqlens, max_len, max_len, causal=True, softmax_scale=self.softmax_scale, window=self.sliding_window_size)})
         out = self.attention(
             q, k, v, cu_seqlens_q=cu_seqlens, cu_seqlens_k=cu_seqlens, max_seqlen_q=max_len, max_seqlen_k=max_len, causal=True,
             softmax_scale=self.softmax_scale, sliding_window=self.sliding_window_size, cp_pg=self.cp_pg, position_ids=position_ids,

@@ -466,6 +466,20 @@ def flash_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, ma
     return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=softmax_scale, window=window)
 
 
+def attention_lse(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int, causal: bool = True, softmax_scale: Optional[float] = None, window: Optional[int] = None) -> torch.Tensor:
+    """log-sum-exp of the (scaled, masked) attention scores of every query: fp32 [Hq, Tq], no gradient.  A diagnostic (how
+    peaked each head's softmax is; what the reference logs under the name ``attn_probs``, src/nanotron/models/qwen.py:309-328):
+    it runs one extra attention forward."""
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    with torch.no_grad():
+        if q.is_cuda and _MODE != "torch":
+            from nanotron_b200.ops import native
+
+            if native.flash_attn_supported(q, k, v, window):
+                return native.flash_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, scale, window)[1]
+        return ref.attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, causal=causal, softmax_scale=softmax_scale, window=window, return_lse=True)[1].float()
+
+
 class _FusedQKVAttention(torch.autograd.Function):
     """RoPE (in place on the q / k parts of the fused projection output) + flash attention, with ONE gradient tensor for the
     whole qkv buffer: the attention backward writes dq / dk / dv into a single [T, (Hq + 2 Hkv) * D] buffer and the inverse

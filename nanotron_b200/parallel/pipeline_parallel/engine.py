@@ -22,7 +22,7 @@ from nanotron_b200.logging import get_logger
 from nanotron_b200.parallel.pipeline_parallel.context_manager import attach_pipeline_state_to_model
 from nanotron_b200.parallel.pipeline_parallel.state import PipelineTrainBatchState
 from nanotron_b200.parallel.pipeline_parallel.tensor_pointer import TensorPointer
-from nanotron_b200.utils import ContextManagers
+from nanotron_b200.utils import ContextManagers, annotate
 
 logger = get_logger(__name__)
 MicroBatch = Dict[str, Union[torch.Tensor, TensorPointer]]
@@ -75,14 +75,16 @@ class PipelineEngine(ABC):
             state.backward_micro_batch(grad_accumulator=grad_accumulator)
 
     def _one_forward(self, model, state, micro_batch, outputs: List[Dict]):
-        output = self.forward(context=self._get_fwd_context(model=model), state=state, micro_batch=micro_batch, model=model)
+        with annotate("micro_batch_forward"):
+            output = self.forward(context=self._get_fwd_context(model=model), state=state, micro_batch=micro_batch, model=model)
         if not isinstance(output["loss"], TensorPointer):
             output = {k: v.detach() for k, v in output.items()}
         outputs.append(output)
 
     def _one_backward(self, model, state, grad_accumulator):
         context = self._get_bwd_context(model=model, nb_backwards=state.nb_backwards, grad_accumulator=grad_accumulator)
-        self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
+        with annotate("micro_batch_backward"):
+            self.backward(context=context, state=state, grad_accumulator=grad_accumulator)
 
     # ------------------------------------------------------------------ whole batches
     @abstractmethod

@@ -50,6 +50,7 @@ from nanotron_b200.parallel.tensor_parallel.enum import TensorParallelLinearMode
 from nanotron_b200.parallel.tensor_parallel.nn import TensorParallelRowLinear
 from nanotron_b200.parallel.tied_parameters import create_pg_for_tied_weights, get_tied_id_to_param, sync_tied_weights_gradients, tie_parameters
 from nanotron_b200.random import set_random_seed
+from nanotron_b200.utils import annotate
 from nanotron_b200.sanity_checks import after_optim_step_sanity_checks, after_tbi_sanity_checks, before_optim_step_sanity_checks, before_tbi_sanity_checks
 from nanotron_b200.scaling.parametrization import ParametrizationMethod
 from nanotron_b200.serialize import load_lr_scheduler, load_meta, load_optimizer, load_weights, parse_ckpt_path, save, save_random_states
@@ -170,6 +171,12 @@ class DistributedTrainer:
         self.current_base_dl = None
         self._stop_requested = False
         self._kill_switch_path = Path(os.environ["NANOTRON_KILL_SWITCH"]) if os.environ.get("NANOTRON_KILL_SWITCH") else None
+        from nanotron_b200.metrics_logging import MetricsLogger
+
+        self.metrics_logging = MetricsLogger(self.config)
+        self._detailed_metrics: Optional[Dict[str, float]] = None
+        # NANOTRON_METRICS_JSONL=<file>: every logged step is also appended there as one JSON object (works without wandb)
+        self._metrics_jsonl = os.environ.get("NANOTRON_METRICS_JSONL")
         self.post_init()
 
     def _pipeline_p2ps(self):
@@ -232,18 +239,20 @@ class DistributedTrainer:
         metadata = self.metadata
         log_rank(f"Start training] datetime: {datetime.datetime.now()} | mbs: {self.micro_batch_size} | grad_accum: {self.n_micro_batches_per_batch} | global_batch_size: {self.global_batch_size} | sequence_length: {self.sequence_length} | train_steps: {self.config.tokens.train_steps} | start_iteration_step: {metadata.last_train_step} | consumed_train_samples: {metadata.consumed_train_samples}", logger=logger, level=logging.INFO, rank=0)
         self._wandb = None
-        if os.environ.get("WANDB_MODE", "disabled") != "disabled" and dist.get_rank(self.parallel_context.world_pg) == self.logger_ranks[0]:
+        is_logger = dist.get_rank(self.parallel_context.world_pg) == self.logger_ranks[0]
+        per_tp_runs = self._shard_suffix() != "" and self._is_metrics_rank()
+        if os.environ.get("WANDB_MODE", "disabled") != "disabled" and (is_logger or per_tp_runs):
             try:
                 import wandb
 
                 self._wandb = wandb
-                wandb.init(project=self.config.general.project, name=f"{self.config.general.run}", config={"nanotron_config": self.config.as_dict()})
+                # with detailed metrics every model shard (tp rank, pp stage) has a run of its own, grouped under the run name
+                name = f"{self.config.general.run}" + (f"_{self._shard_suffix()}" if per_tp_runs else "")
+                wandb.init(project=self.config.general.project, name=name, group=self.config.general.run if per_tp_runs else None, config={"nanotron_config": self.config.as_dict()})
             except ImportError:
                 self._wandb = None
 
     def post_train_step(self):
-        if hasattr(self.unwrapped_model, "clear_all_tbi_logs"):
-            self.unwrapped_model.clear_all_tbi_logs()
         if self.s3_mover is not None:
             self.s3_mover.update()
 
@@ -389,6 +398,9 @@ class DistributedTrainer:
                             stage.consumed_tokens_per_dataset_folder[folder] = s["tokens"]
                 if (self.iteration_step - 1) % self.config.logging.iteration_step_info_interval == 0:
                     self.train_step_logs(outputs=outputs, loss_avg=loss_avg, z_loss_avg=z_loss_avg)
+                if self._detailed_metrics is not None:  # a detailed-metrics step that is not a console step
+                    self._emit_metrics([LogItem(k, v, "human_format") for k, v in self._detailed_metrics.items()])
+                    self._detailed_metrics = None
                 stop = (self._kill_switch_path is not None or self._stop_requested) and self._should_stop()
                 if self.config.checkpoints is not None and (self.iteration_step % self.config.checkpoints.checkpoint_interval == 0 or stop):
                     self.save_checkpoint()
@@ -404,10 +416,12 @@ class DistributedTrainer:
         self.iteration_step = self.initial_iter_step
 
     def training_step(self, dataloader: Iterator[Dict[str, Union[torch.Tensor, TensorPointer]]]):
+        if hasattr(self.unwrapped_model, "clear_all_tbi_logs"):
+            self.unwrapped_model.clear_all_tbi_logs()  # what the modules recorded during the previous step stays readable until here
         before_tbi_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator, self.lr_scheduler)
         if self.iteration_step < self.initial_iter_step + 5:
             log_memory(logger=logger)
-        with nanotron_timer("train_batch_iter"), torch.profiler.record_function("train_batch_iter"):
+        with nanotron_timer("train_batch_iter"), annotate("train_batch_iter"):
             outputs = self.pipeline_engine.train_batch_iter(
                 model=self.model, pg=self.parallel_context.pp_pg, batch=(next(dataloader) for _ in range(self.n_micro_batches_per_batch)),
                 nb_microbatches=self.n_micro_batches_per_batch, grad_accumulator=self.grad_accumulator,
@@ -420,11 +434,11 @@ class DistributedTrainer:
         # does not change the result (the reference all-reduces whole gradients over dp first, trainer.py:643-661).
         sync_tied_weights_gradients(module=self.unwrapped_model, parallel_context=self.parallel_context, grad_accumulator=self.grad_accumulator)
         if not fused:
-            with nanotron_timer("sync_gradients"), torch.profiler.record_function("sync_gradients"):
+            with nanotron_timer("sync_gradients"), annotate("sync_gradients"):
                 self._sync_gradients()
         self.grad_norm_unclipped = None
         if self.config.optimizer.clip_grad is not None and not fused:
-            with nanotron_timer("clip_gradients"), torch.profiler.record_function("clip_gradients"):
+            with nanotron_timer("clip_gradients"), annotate("clip_gradients"):
                 self.grad_norm_unclipped = self._clip_gradients()
         # loss average over data (and context) parallel replicas, for logging
         loss_avg = z_loss_avg = None
@@ -442,7 +456,15 @@ class DistributedTrainer:
         if self.init_checkpoint_path is not None and self.config.checkpoints.load_optimizer and self.iteration_step == self.initial_iter_step:
             self._move_optimizer_state_to_device()
         before_optim_step_sanity_checks(self.config, self.parallel_context, self.unwrapped_model, self.grad_accumulator, self.optimizer)
-        with nanotron_timer("optimizer_step"), torch.profiler.record_function("optimizer_step"):
+        self._detailed_metrics = None
+        if self.metrics_logging.log_level > 0 and self.iteration_step % self.metrics_logging.log_detail_interval == 0 and self._is_metrics_rank():
+            # per-layer statistics of weights and of the gradients this step applies (after clipping, before they are cleared)
+            with torch.no_grad():
+                # gradient statistics only where this rank holds whole reduced gradients (a sharded exchange leaves it one slice)
+                sliced = fused or (self.config.optimizer.zero_stage > 0 and self.parallel_context.dp_pg.size() > 1)
+                collected = self.metrics_logging.collect_all_metrics(model=self.unwrapped_model, grad_accumulator=None if sliced else self.grad_accumulator, iteration_step=self.iteration_step)
+            self._detailed_metrics = {k: float(v) for k, v in collected.items()}
+        with nanotron_timer("optimizer_step"), annotate("optimizer_step"):
             if fused:
                 self.grad_norm_unclipped = self.fused_dp.step()
             else:
@@ -646,6 +668,8 @@ class DistributedTrainer:
                 LogItem("model_tflops_per_gpu", model_tflops, "human_format"),
                 LogItem("eta", str(datetime.timedelta(seconds=int(remaining * elapsed_ms / 1000))), None),
             ]
+            if hardware_tflops != model_tflops:
+                entries.append(LogItem("hardware_tflops_per_gpu", hardware_tflops, "human_format"))
             if nanotron_timer.is_enabled():
                 for name, t in nanotron_timer.items():
                     if name != "iteration_time" and t.call_count:
@@ -653,13 +677,80 @@ class DistributedTrainer:
             if not hasattr(self, "loggerwriter"):
                 self.loggerwriter = LoggerWriter(global_step=self.config.tokens.train_steps)
             self.loggerwriter.add_scalars_from_list(entries, self.iteration_step)
-            if getattr(self, "_wandb", None) is not None:
-                self._wandb.log({**{e.tag: e.scalar_value for e in entries}, "iteration_step": self.iteration_step})
+            # everything below goes to the metric sinks only (wandb, the JSONL file), not to the console line
+            entries += self._diagnostic_log_items()
+            if self._detailed_metrics is not None:
+                entries += [LogItem(k, v, "human_format") for k, v in self._detailed_metrics.items()]
+                self._detailed_metrics = None
+            self._emit_metrics(entries)
+        # (ranks other than the logger rank hold other shards and other layers: the training loop emits what they collected)
         if os.environ.get("NANOTRON_BENCHMARK", "0") == "1" and self.iteration_step == 4:
             log_throughput(self.config, ctx, model_tflops, hardware_tflops, tokens_per_sec, num_params=getattr(self, "num_params", {"total": 0, "local": 0}))
             log_rank("Throughput logging complete", logger=logger, level=logging.INFO, rank=0)
             if os.environ.get("NANOTRON_BENCHMARK_NO_EXIT", "0") != "1":
                 raise SystemExit(0)
+
+    def _is_metrics_rank(self) -> bool:
+        """The ranks that report detailed metrics: the first data / context-parallel replica of every tensor-parallel rank and
+        pipeline stage (each holds other shards and other layers; reference trainer.py:894-903)."""
+        ctx = self.parallel_context
+        return dist.get_rank(ctx.dp_pg) == 0 and dist.get_rank(ctx.cp_pg) == 0
+
+    def _shard_suffix(self) -> str:
+        """Names the model shard of this rank where several ranks report (detailed metrics under tp / pp > 1)."""
+        ctx = self.parallel_context
+        if self.metrics_logging.log_level == 0 or ctx.tp_pg.size() * ctx.pp_pg.size() == 1:
+            return ""
+        return f"pp{dist.get_rank(ctx.pp_pg)}_tp{dist.get_rank(ctx.tp_pg)}"
+
+    def _diagnostic_log_items(self) -> List[LogItem]:
+        """Optional entries: statistics of tensors that modules recorded with ``tbi_logger``, host memory (``DEBUG_CPU=1``),
+        tokens drawn from every dataset folder (``DEBUG_DL=1``), device and disk memory."""
+        items: List[LogItem] = []
+        if hasattr(self.unwrapped_model, "get_tbi_logs"):
+            for name, tensor in self.unwrapped_model.get_tbi_logs().items():
+                t = tensor.float()
+                if t.numel() == 0:
+                    continue
+                items += [LogItem(f"tbi_logs/{name}_{stat}", float(getattr(t, stat)()), "human_format") for stat in ("mean", "std", "max", "min")]
+                if t.dim() >= 2:  # [heads, tokens]: one set per head
+                    for h in range(t.shape[0]):
+                        items += [LogItem(f"tbi_logs/{name}/head_{h}_{stat}", float(getattr(t[h], stat)()), "human_format") for stat in ("mean", "std", "max", "min")]
+        if os.environ.get("DEBUG_CPU", "0") == "1":
+            try:
+                import psutil
+
+                vm, proc = psutil.virtual_memory(), psutil.Process()
+                items += [
+                    LogItem("cpu_memory/total", vm.total, "human_format"), LogItem("cpu_memory/available", vm.available, "human_format"),
+                    LogItem("cpu_memory/used_percent", vm.percent, ".1f"), LogItem("cpu_memory/process_rss", proc.memory_info().rss, "human_format"),
+                ]
+            except ImportError:
+                pass
+        if os.environ.get("DEBUG_DL", "0") == "1" and self.metadata.data_stages:
+            stage = self.metadata.data_stages[self.metadata.last_stage_idx]
+            items += [LogItem(f"dataloader/consumed_tokens/{folder}", tokens, "human_format") for folder, tokens in sorted(stage.consumed_tokens_per_dataset_folder.items())]
+        if self.parallel_context.device.type == "cuda":
+            items += [LogItem("cuda_memory_allocated", torch.cuda.memory_allocated(), "human_format"), LogItem("cuda_max_memory_reserved", torch.cuda.max_memory_reserved(), "human_format")]
+        if self._detailed_metrics is not None:
+            import shutil
+
+            total, used, free = shutil.disk_usage(str(Path(self.config.checkpoints.checkpoints_path).anchor or "/"))
+            items += [LogItem("hd_total_memory", total, "human_format"), LogItem("hd_used_memory", used, "human_format"), LogItem("hd_free_memory", free, "human_format")]
+        return items
+
+    def _emit_metrics(self, entries: List[LogItem]) -> None:
+        record = {e.tag: e.scalar_value for e in entries}
+        record["iteration_step"] = self.iteration_step
+        suffix = self._shard_suffix()
+        if suffix:
+            ctx = self.parallel_context
+            record.update(tp_rank=dist.get_rank(ctx.tp_pg), tp_group_size=ctx.tp_pg.size(), pp_rank=dist.get_rank(ctx.pp_pg))
+        if getattr(self, "_wandb", None) is not None:
+            self._wandb.log(record)
+        if self._metrics_jsonl:
+            with open(self._metrics_jsonl + (f".{suffix}" if suffix else ""), "a") as f:
+                f.write(json.dumps(record, default=str) + "\n")
 
     # ------------------------------------------------------------------ model construction
     def init_model(self) -> NanotronModel:

@@ -39,6 +39,21 @@ class ContextManagers:
 
 
 @contextmanager
+def annotate(name: str):
+    """Name a region for the profilers: a ``torch.profiler`` record and, on a CUDA build, an NVTX range (visible in Nsight
+    timelines beside the kernels launched inside)."""
+    nvtx = torch.cuda.is_available()
+    if nvtx:
+        torch.cuda.nvtx.range_push(name)
+    try:
+        with torch.profiler.record_function(name):
+            yield
+    finally:
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
+
+
+@contextmanager
 def main_rank_first(group):
     """Rank 0 of ``group`` runs the body first, the others after it finished."""
     import nanotron_b200.distributed as dist

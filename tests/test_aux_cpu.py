@@ -221,3 +221,49 @@ def test_scaling_sweep_generates_configs_and_job_scripts(tmp_path, monkeypatch):
         cfg = get_config_from_file(row["config"])
         assert cfg.parallelism.dp * cfg.parallelism.tp * cfg.parallelism.pp == 8
         assert "run_train.py" in open(row["script"]).read() and "#SBATCH --nodes=1" in open(row["script"]).read()
+
+
+def _metrics_run(out_dir):
+    import json
+
+    import nanotron_b200.config as c
+    import nanotron_b200.distributed as dist
+    from helpers import dummy_dataloader, make_config, tiny_qwen_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    os.environ["NANOTRON_METRICS_JSONL"] = os.path.join(out_dir, "metrics.jsonl")
+    os.environ["DEBUG_CPU"] = "1"
+    cfg = make_config(tiny_qwen_config(log_attn_probs=True), tp=2, seq=16, steps=4, tp_mode="reduce_scatter")
+    cfg.metrics_logging = c.MetricsLoggingArgs(log_level=1, log_detail_interval=2)
+    cfg.logging.iteration_step_info_interval = 3  # console steps 1 and 4, detailed steps 2 and 4
+    cfg.checkpoints.checkpoints_path = os.path.join(out_dir, "ckpt")
+    t = DistributedTrainer(cfg)
+    t.train(dummy_dataloader(t))
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def test_detailed_metrics_attention_statistics_and_diagnostics_reach_the_metric_file(tmp_path):
+    import json
+
+    from helpers import run_distributed
+
+    run_distributed(_metrics_run, 2, out_dir=str(tmp_path))
+    files = sorted(f for f in os.listdir(tmp_path) if f.startswith("metrics.jsonl"))
+    assert files == ["metrics.jsonl.pp0_tp0", "metrics.jsonl.pp0_tp1"]  # one stream per model shard
+    rows = {f: [json.loads(line) for line in open(tmp_path / f)] for f in files}
+    logger, other = rows["metrics.jsonl.pp0_tp0"], rows["metrics.jsonl.pp0_tp1"]
+    assert [r["iteration_step"] for r in logger] == [1, 2, 4] and [r["iteration_step"] for r in other] == [2, 4]
+    first, detailed, both = logger
+    assert "lm_loss" in first and "tokens_per_sec" in first and "weights/layer_0/attn/qkv_proj/mean" not in first
+    # attention statistics of every layer and head (two local heads per tensor-parallel rank), host memory
+    assert "tbi_logs/model.decoder.0.pp_block.attn/attn_probs_mean" in first and "tbi_logs/model.decoder.1.pp_block.attn/attn_probs/head_1_max" in first
+    assert "tbi_logs/model.decoder.0.pp_block.attn/attn_probs/head_2_max" not in first
+    assert first["cpu_memory/process_rss"] > 0
+    # a detailed step that is not a console step carries the per-layer statistics only; step 4 carries both
+    assert "lm_loss" not in detailed and "weights/layer_0/attn/qkv_proj/l2" in detailed and "grads/layer_1/mlp/down_proj/l2" in detailed
+    assert "lm_loss" in both and "weights/layer_1/mlp/gate_up_proj/std" in both and both["hd_total_memory"] > 0
+    assert detailed["tp_rank"] == 0 and other[0]["tp_rank"] == 1 and other[0]["tp_group_size"] == 2
+    # the two tensor-parallel ranks see different shards of a sharded matrix and the same replicated norm weight
+    assert other[0]["weights/layer_0/attn/qkv_proj/l2"] != detailed["weights/layer_0/attn/qkv_proj/l2"]
+    assert other[0]["weights/layer_0/input_layernorm/mean"] == detailed["weights/layer_0/input_layernorm/mean"]
