@@ -22,7 +22,8 @@ def clm_process(raw_dataset, tokenizer, text_column_name: str, dataset_processin
     """``datasets.Dataset`` of text -> dataset of packed ``input_ids`` windows (length ``sequence_length + 1``)."""
 
     def _tokenize_and_group(texts: List[str]) -> Dict[str, List[np.ndarray]]:
-        tokenized = tokenizer.batch_encode_plus(texts, return_attention_mask=False, return_token_type_ids=False)
+        # the plain call works with every transformers version (``batch_encode_plus`` is gone from the 5.x tokenizers)
+        tokenized = tokenizer(list(texts), return_attention_mask=False, return_token_type_ids=False)
         return group_texts(tokenized["input_ids"], sequence_length)
 
     from datasets import Features, Sequence, Value

@@ -106,3 +106,68 @@ def test_run_train_with_data_stages_and_resume(tmp_path, streamed):
         out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
         assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
         assert "generat" in (out.stdout + out.stderr).lower()
+
+
+def _write_text_datasets(tmp_path):
+    """A word-level tokenizer saved in the Hugging Face format, a folder of raw text and a folder of prompt / completion pairs
+    (both learnable: words count upwards)."""
+    import json
+
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    vocab = {"<pad>": 0, "<s>": 1, "</s>": 2, "<unk>": 3, **{f"w{i}": i + 4 for i in range(200)}}
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<s>", eos_token="</s>", unk_token="<unk>", pad_token="<pad>").save_pretrained(str(tmp_path / "tok"))
+    rng = np.random.default_rng(0)
+    (tmp_path / "text").mkdir()
+    (tmp_path / "sft").mkdir()
+    with open(tmp_path / "text" / "train.jsonl", "w") as f:
+        for _ in range(400):
+            start, stride = int(rng.integers(0, 200)), int(rng.integers(1, 4))
+            f.write(json.dumps({"text": " ".join(f"w{(start + stride * j) % 200}" for j in range(int(rng.integers(20, 60))))}) + "\n")
+    with open(tmp_path / "sft" / "train.jsonl", "w") as f:
+        for _ in range(300):
+            start = int(rng.integers(0, 200))
+            f.write(json.dumps({"prompt": " ".join(f"w{(start + j) % 200}" for j in range(6)), "completion": " ".join(f"w{(start + 6 + j) % 200}" for j in range(8))}) + "\n")
+
+
+@pytest.mark.parametrize("kind", ["text", "sft"])
+def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
+    """``PretrainDatasetsArgs`` (tokenise + pack on the fly, Llama with masks) and ``SFTDatasetsArgs`` (loss on the completion only,
+    Qwen2 with position ids) through ``run_train.py``: the datasets load from local folders, the loss falls."""
+    sys.path.insert(0, ROOT)
+    import nanotron_b200.config as c
+
+    _write_text_datasets(tmp_path)
+    shape = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=256, max_position_embeddings=64, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    if kind == "text":
+        model, dataset = c.LlamaConfig(**shape), c.PretrainDatasetsArgs(hf_dataset_or_datasets=str(tmp_path / "text"), text_column_name="text")
+    else:
+        model, dataset = c.Qwen2Config(**shape), c.SFTDatasetsArgs(hf_dataset_or_datasets=str(tmp_path / "sft"))
+    cfg = c.Config(
+        general=c.GeneralArgs(project="e2e", run=kind, seed=3),
+        checkpoints=c.CheckpointsArgs(checkpoints_path=str(tmp_path / "ckpt"), checkpoint_interval=1000, save_final_state=False),
+        parallelism=c.ParallelismArgs(dp=2, pp=1, tp=1),
+        model=c.ModelArgs(model_config=model, init_method=c.RandomInit(std=0.05), dtype="float32"),
+        tokenizer=c.TokenizerArgs(tokenizer_name_or_path=str(tmp_path / "tok")),
+        optimizer=c.OptimizerArgs(
+            optimizer_factory=c.AdamWOptimizerArgs(adam_eps=1e-8, adam_beta1=0.9, adam_beta2=0.95, torch_adam_is_fused=False), zero_stage=0, weight_decay=0.01, clip_grad=1.0,
+            accumulate_grad_in_fp32=True, learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=1e-2, lr_warmup_steps=2, lr_decay_style="cosine", min_decay_lr=1e-3),
+        ),
+        logging=c.LoggingArgs(log_level="info", log_level_replica="error", iteration_step_info_interval=1),
+        tokens=c.TokensArgs(sequence_length=32, train_steps=20, micro_batch_size=4, batch_accumulation_per_replica=1),
+        data_stages=[c.DatasetStageArgs(name="only", start_training_step=1, data=c.DataArgs(dataset=dataset, seed=7, num_loading_workers=0))],
+    )
+    path = str(tmp_path / f"{kind}.yaml")
+    cfg.save_as_yaml(path)
+    os.environ["HF_DATASETS_CACHE"] = str(tmp_path / "hf_cache")
+    os.environ["HF_HUB_OFFLINE"] = "1"
+    try:
+        losses, text = _train(path)
+    finally:
+        os.environ.pop("HF_DATASETS_CACHE")
+        os.environ.pop("HF_HUB_OFFLINE")
+    assert sorted(losses) == list(range(1, 21)), text[-2000:]
+    assert losses[20] < losses[1] - 1.0, losses
