@@ -148,7 +148,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
         model, dataset = c.Qwen2Config(**shape), c.SFTDatasetsArgs(hf_dataset_or_datasets=str(tmp_path / "sft"))
     cfg = c.Config(
         general=c.GeneralArgs(project="e2e", run=kind, seed=3),
-        checkpoints=c.CheckpointsArgs(checkpoints_path=str(tmp_path / "ckpt"), checkpoint_interval=1000, save_final_state=False),
+        checkpoints=c.CheckpointsArgs(checkpoints_path=str(tmp_path / "ckpt"), checkpoint_interval=1000, save_final_state=kind == "text"),
         parallelism=c.ParallelismArgs(dp=2, pp=1, tp=1),
         model=c.ModelArgs(model_config=model, init_method=c.RandomInit(std=0.05), dtype="float32"),
         tokenizer=c.TokenizerArgs(tokenizer_name_or_path=str(tmp_path / "tok")),
@@ -166,8 +166,20 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
     os.environ["HF_HUB_OFFLINE"] = "1"
     try:
         losses, text = _train(path)
+        generations = []
+        if kind == "text":
+            # the checkpoint names its tokenizer: run_generate.py decodes text prompts, with and without the key / value cache
+            for extra in ([], ["--use-cache"]):
+                cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+                       os.path.join(ROOT, "run_generate.py"), "--ckpt-path", str(tmp_path / "ckpt" / "20"), "--tp", "2", "--max-new-tokens", "5", "--prompt", "w3 w4 w5 w6", "--prompt", "w10 w12 w14"] + extra
+                out = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1"), cwd=ROOT, timeout=600)
+                assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+                generations.append(re.findall(r"generation: (.*)", out.stdout + out.stderr))
     finally:
         os.environ.pop("HF_DATASETS_CACHE")
         os.environ.pop("HF_HUB_OFFLINE")
     assert sorted(losses) == list(range(1, 21)), text[-2000:]
     assert losses[20] < losses[1] - 1.0, losses
+    if kind == "text":
+        assert len(generations[0]) == 2 and all(len(g.split()) == 5 and all(w.startswith("w") for w in g.split()) for g in generations[0]), generations
+        assert generations[0] == generations[1]
