@@ -141,6 +141,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
     import nanotron_b200.config as c
 
     _write_text_datasets(tmp_path)
+    steps = 40 if kind == "text" else 20
     shape = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=256, max_position_embeddings=64, rms_norm_eps=1e-5, tie_word_embeddings=False)
     if kind == "text":
         model, dataset = c.LlamaConfig(**shape), c.PretrainDatasetsArgs(hf_dataset_or_datasets=str(tmp_path / "text"), text_column_name="text")
@@ -157,7 +158,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
             accumulate_grad_in_fp32=True, learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=1e-2, lr_warmup_steps=2, lr_decay_style="cosine", min_decay_lr=1e-3),
         ),
         logging=c.LoggingArgs(log_level="info", log_level_replica="error", iteration_step_info_interval=1),
-        tokens=c.TokensArgs(sequence_length=32, train_steps=20, micro_batch_size=4, batch_accumulation_per_replica=1),
+        tokens=c.TokensArgs(sequence_length=32, train_steps=steps, micro_batch_size=4, batch_accumulation_per_replica=1),
         data_stages=[c.DatasetStageArgs(name="only", start_training_step=1, data=c.DataArgs(dataset=dataset, seed=7, num_loading_workers=0))],
     )
     path = str(tmp_path / f"{kind}.yaml")
@@ -171,14 +172,32 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
             # the checkpoint names its tokenizer: run_generate.py decodes text prompts, with and without the key / value cache
             for extra in ([], ["--use-cache"]):
                 cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-                       os.path.join(ROOT, "run_generate.py"), "--ckpt-path", str(tmp_path / "ckpt" / "20"), "--tp", "2", "--max-new-tokens", "5", "--prompt", "w3 w4 w5 w6", "--prompt", "w10 w12 w14"] + extra
+                       os.path.join(ROOT, "run_generate.py"), "--ckpt-path", str(tmp_path / "ckpt" / str(steps)), "--tp", "2", "--max-new-tokens", "5", "--prompt", "w3 w4 w5 w6", "--prompt", "w10 w12 w14"] + extra
                 out = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1"), cwd=ROOT, timeout=600)
                 assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
                 generations.append(re.findall(r"generation: (.*)", out.stdout + out.stderr))
+            # ... and run_evals.py scores a multiple-choice task from local files: the right continuation keeps counting
+            import json
+
+            rng = np.random.default_rng(1)
+            (tmp_path / "eval").mkdir()
+            with open(tmp_path / "eval" / "arc:easy.test.jsonl", "w") as f:
+                for i in range(24):
+                    start, pos = int(rng.integers(0, 150)), int(rng.integers(0, 4))
+                    wrong = [" ".join(f"w{int(x)}" for x in rng.integers(0, 200, size=3)) for _ in range(3)]
+                    texts = wrong[:pos] + [" ".join(f"w{start + 8 + j}" for j in range(3))] + wrong[pos:]
+                    f.write(json.dumps({"id": str(i), "question": " ".join(f"w{start + j}" for j in range(8)), "choices": {"text": texts, "label": list("ABCD")}, "answerKey": "ABCD"[pos]}) + "\n")
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+                   os.path.join(ROOT, "run_evals.py"), "--checkpoint-config-path", str(tmp_path / "ckpt" / str(steps) / "config.yaml"), "--tasks", "arc_cf:easy", "--data-dir", str(tmp_path / "eval"),
+                   "--tp", "2", "--max-length", "64", "--output", str(tmp_path / "eval" / "results.json")]
+            out = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1"), cwd=ROOT, timeout=600)
+            assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+            scores = json.load(open(tmp_path / "eval" / "results.json"))["results"]["arc_cf:easy|test"]
+            assert scores["num_samples"] == 24 and scores["acc_token"] >= 0.6, scores  # chance is 0.25
     finally:
         os.environ.pop("HF_DATASETS_CACHE")
         os.environ.pop("HF_HUB_OFFLINE")
-    assert sorted(losses) == list(range(1, 21)), text[-2000:]
+    assert sorted(losses) == list(range(1, steps + 1)), text[-2000:]
     assert losses[20] < losses[1] - 1.0, losses
     if kind == "text":
         assert len(generations[0]) == 2 and all(len(g.split()) == 5 and all(w.startswith("w") for w in g.split()) for g in generations[0]), generations
