@@ -44,7 +44,7 @@ logger = logging.get_logger(__name__)
 # ---------------------------------------------------------------------------- configuration
 @dataclass
 class DoReMiArgs:
-    domain_names: List[str] = field(default_factory=lambda: ["a", "b"])
+    domain_names: Union[List[str], str] = field(default_factory=lambda: ["a", "b"])  # a comma-separated string also works
     domain_weights: Optional[List[float]] = None  # initial weights (uniform when omitted)
     step_size: float = 1.0
     smoothing_param: float = 1e-3
@@ -59,6 +59,8 @@ class DoReMiArgs:
     samples_per_synthetic_domain: int = 4096
 
     def __post_init__(self):
+        if isinstance(self.domain_names, str):
+            self.domain_names = [name.strip() for name in self.domain_names.split(",")]
         if self.domain_folders is not None:
             assert len(self.domain_folders) == len(self.domain_names), "one folder per domain"
         if self.domain_weights is not None:

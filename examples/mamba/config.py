@@ -39,6 +39,10 @@ class MambaModelConfig:
     eos_token_id: Optional[int] = None
     tie_word_embeddings: bool = True
     scan_chunk: int = 32  # steps the state-space scan handles at once
+    # accepted so that configuration files of the reference example load: the parameter dtype comes from ``model.dtype``, and the
+    # residual add is always done together with the norm
+    dtype: Optional[str] = None
+    fused_add_norm: bool = True
 
     def ssm(self) -> dict:
         """The mixer's hyper-parameters with their defaults filled in."""

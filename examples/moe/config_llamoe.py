@@ -32,6 +32,16 @@ class LlaMoEConfig(Qwen2Config):
     moe_config: Optional[MoEConfig] = field(default_factory=lambda: MoEConfig(num_experts=8, top_k=2, moe_intermediate_size=256, enable_shared_expert=False, router_aux_loss_coef=0.01))
     router_weight_decay: bool = False  # routers are small and sensitive: excluded from weight decay unless asked for
     log_expert_load: bool = True  # keep the per-expert token fractions of the last forward for logging
+    # the spelling of the reference example's YAML files (examples/moe/config_llamoe.yaml): when given, they define the experts
+    # (every expert as wide as ``intermediate_size``).  Routing here never drops tokens, so the capacity factor has no effect.
+    moe_num_experts: Optional[int] = None
+    num_experts_per_tok: Optional[int] = None
+    moe_capacity_factor: Optional[float] = None
+
+    def __post_init__(self):
+        if self.moe_num_experts is not None:
+            self.moe_config = MoEConfig(num_experts=self.moe_num_experts, top_k=self.num_experts_per_tok or 1, moe_intermediate_size=self.intermediate_size, enable_shared_expert=False, router_aux_loss_coef=0.01)
+        super().__post_init__()
 
 
 def build(hidden_size=256, layers=4, heads=4, experts=8, top_k=2, expert_size=256, vocab=32000, seq=512, mbs=2, dp=4, ep=4, tp=1, steps=200, dtype="bfloat16", lr=3e-4) -> Config:

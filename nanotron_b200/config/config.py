@@ -480,7 +480,40 @@ def _declared_model_config_class(config_class: Type) -> Optional[Type]:
         return None
 
 
+_LEGACY_ADAM_KEYS = ("adam_beta1", "adam_beta2", "adam_eps", "torch_adam_is_fused")
+
+
+def upgrade_legacy_config_dict(config_dict: dict) -> dict:
+    """Rewrite spellings that older configuration files of the reference use into the current schema (a copy is returned; a
+    warning names every rewrite).  Several of the reference's own example files are still written this way
+    (examples/mup/configs/*.yaml, examples/config_nanoset.yaml, examples/config_resume_training.yaml):
+
+    * AdamW settings directly under ``optimizer`` instead of under ``optimizer.optimizer_factory``;
+    * ``dataset_folder`` as a mapping ``{folder: weight}`` instead of ``dataset_folder`` + ``dataset_weights`` lists;
+    * ``interleaved_rotary`` for ``rope_interleaved`` in a model configuration."""
+    import copy
+    import warnings
+
+    d = copy.deepcopy(config_dict)
+    opt = d.get("optimizer")
+    if isinstance(opt, dict) and "optimizer_factory" not in opt and any(k in opt for k in _LEGACY_ADAM_KEYS):
+        opt["optimizer_factory"] = {"name": "adamW", **{k: opt.pop(k) for k in _LEGACY_ADAM_KEYS if k in opt}}
+        warnings.warn("config: AdamW settings directly under `optimizer` moved to `optimizer.optimizer_factory`")
+    for stage in d.get("data_stages") or []:
+        dataset = (stage.get("data") or {}).get("dataset") if isinstance(stage, dict) else None
+        if isinstance(dataset, dict) and isinstance(dataset.get("dataset_folder"), dict):
+            mapping = dataset["dataset_folder"]
+            dataset["dataset_folder"], dataset["dataset_weights"] = list(mapping.keys()), [float(w) for w in mapping.values()]
+            warnings.warn("config: `dataset_folder` given as {folder: weight} split into `dataset_folder` and `dataset_weights`")
+    model_config = (d.get("model") or {}).get("model_config") if isinstance(d.get("model"), dict) else None
+    if isinstance(model_config, dict) and "interleaved_rotary" in model_config:
+        model_config.setdefault("rope_interleaved", model_config.pop("interleaved_rotary"))
+        warnings.warn("config: `interleaved_rotary` renamed to `rope_interleaved`")
+    return d
+
+
 def get_config_from_dict(config_dict: dict, config_class: Type = Config, skip_unused_config_keys: bool = False, skip_null_keys: bool = False, model_config_class: Optional[Type] = None):
+    config_dict = upgrade_legacy_config_dict(config_dict)
     if skip_unused_config_keys:
         known = {f.name for f in fields(config_class)}
         config_dict = {k: v for k, v in config_dict.items() if k in known}

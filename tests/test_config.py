@@ -61,3 +61,37 @@ def test_lr_scheduler_shapes():
     assert lrs[0] == 0.0 and abs(lrs[1] - 0.5) < 1e-9 and abs(lrs[2] - 1.0) < 1e-9
     assert abs(lrs[4] - 0.55) < 1e-9  # halfway through the cosine
     assert abs(lrs[6] - 0.1) < 1e-9 and abs(lrs[8] - 0.1) < 1e-9
+
+
+def test_older_spellings_of_the_reference_schema_still_load(tmp_path):
+    """AdamW settings directly under ``optimizer``, ``dataset_folder`` as {folder: weight}, ``interleaved_rotary``: files written for
+    older versions of the reference (several of its own examples among them) load with a warning and mean the same."""
+    import warnings
+
+    import yaml
+
+    from nanotron_b200.config.config import upgrade_legacy_config_dict
+
+    cfg = make_config(tiny_llama_config(), seq=16)
+    path = tmp_path / "new.yaml"
+    cfg.save_as_yaml(str(path))
+    new = yaml.safe_load(open(path))
+    old = yaml.safe_load(open(path))
+    factory = old["optimizer"].pop("optimizer_factory")
+    factory.pop("name")
+    old["optimizer"].update(factory)  # adam_beta1 / adam_beta2 / adam_eps / torch_adam_is_fused at the top level
+    old["model"]["model_config"]["interleaved_rotary"] = old["model"]["model_config"].pop("rope_interleaved")
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    for d in (new, old):
+        d["data_stages"][0]["data"]["dataset"] = {"dataset_folder": [str(tmp_path / "a"), str(tmp_path / "b")], "dataset_weights": [0.75, 0.25]}
+    old["data_stages"][0]["data"]["dataset"] = {"dataset_folder": {str(tmp_path / "a"): 0.75, str(tmp_path / "b"): 0.25}}
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        loaded_old = c.get_config_from_dict(old)
+    assert len([w for w in seen if str(w.message).startswith("config:")]) == 3
+    assert loaded_old == c.get_config_from_dict(new)
+    assert loaded_old.optimizer.optimizer_factory.adam_beta2 == 0.95 and loaded_old.data_stages[0].data.dataset.dataset_weights == [0.75, 0.25]
+    assert upgrade_legacy_config_dict(new) == new  # the current schema passes through untouched
+    with pytest.raises(Exception):
+        c.get_config_from_dict({**old, "optimizer": {**old["optimizer"], "adam_beta3": 0.5}})  # unknown keys are still errors
