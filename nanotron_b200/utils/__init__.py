@@ -38,18 +38,27 @@ class ContextManagers:
         self.stack.__exit__(*args, **kwargs)
 
 
+_NVTX = {"usable": None}
+
+
 @contextmanager
 def annotate(name: str):
     """Name a region for the profilers: a ``torch.profiler`` record and, on a CUDA build, an NVTX range (visible in Nsight
-    timelines beside the kernels launched inside)."""
-    nvtx = torch.cuda.is_available()
-    if nvtx:
-        torch.cuda.nvtx.range_push(name)
+    timelines beside the kernels launched inside).  A build without NVTX just loses the range."""
+    if _NVTX["usable"] is None:
+        _NVTX["usable"] = torch.cuda.is_available()
+    pushed = False
+    if _NVTX["usable"]:
+        try:
+            torch.cuda.nvtx.range_push(name)
+            pushed = True
+        except Exception:
+            _NVTX["usable"] = False
     try:
         with torch.profiler.record_function(name):
             yield
     finally:
-        if nvtx:
+        if pushed:
             torch.cuda.nvtx.range_pop()
 
 
