@@ -367,3 +367,48 @@ def test_doremi_reference_then_proxy_with_saved_domain_weights(tmp_path):
     run_distributed(_doremi_reference_run, 2, out_file=out, ckpt=str(tmp_path / "ckpt"))
     res = torch.load(out)
     assert abs(float(res["weights"].sum()) - 1.0) < 1e-5
+
+
+def test_doremi_loss_updates_the_domain_weights_as_specified():
+    """excess_d = mean over the tokens of domain d of max(proxy - reference, 0); w <- normalise(w * exp(step * excess)) mixed with the
+    uniform distribution; loss = sum_d w_d * (token losses of d) * n_domains / tokens."""
+    sys.path.insert(0, os.path.join(ROOT, "examples", "doremi"))
+    import doremi as dr
+    from nanotron_b200.parallel.context import ParallelContext
+
+    single_process_env()
+    ctx = ParallelContext(tensor_parallel_size=1, pipeline_parallel_size=1, data_parallel_size=1)
+    args = dr.DoReMiArgs(domain_names=["a", "b", "c"], domain_weights=[0.5, 0.3, 0.2], step_size=0.7, smoothing_param=0.01)
+    state = dr.DoReMiContext(args, torch.device("cpu"))
+    loss_block = dr.DoReMiLoss(ctx.tp_pg, ctx.dp_pg, state)
+    torch.manual_seed(0)
+    b, s, v = 4, 6, 11
+    logits = torch.randn(b * s, v, requires_grad=True)
+    labels = torch.randint(0, v, (b, s))
+    mask = torch.ones(b, s, dtype=torch.bool)
+    mask[1, 4:] = False
+    domains = torch.tensor([0, 2, 0, 1])
+    ref_losses = torch.rand(b, s) * 2.5 * mask
+    out = loss_block(logits, labels, mask, domains, ref_losses)
+    token_losses = torch.nn.functional.cross_entropy(logits.detach(), labels.reshape(-1), reduction="none").view(b, s) * mask
+    excess = (token_losses - ref_losses).clamp(min=0)
+    per_domain = torch.stack([excess[domains == d].sum() / mask[domains == d].sum() for d in range(3)])
+    torch.testing.assert_close(out["excess_losses"], per_domain)
+    w = torch.tensor([0.5, 0.3, 0.2]) * torch.exp(0.7 * per_domain)
+    w = 0.99 * w / w.sum() + 0.01 / 3
+    torch.testing.assert_close(state.domain_weights, w)
+    assert len(state.history) == 2 and abs(float(state.domain_weights.sum()) - 1) < 1e-6
+    expected = sum(w[d] * token_losses[domains == d].sum() for d in range(3)) * 3 / mask.sum()
+    torch.testing.assert_close(out["loss"], expected)
+    torch.testing.assert_close(out["ce_loss"], token_losses.sum() / mask.sum())
+    out["loss"].backward()
+    assert logits.grad is not None and float(logits.grad.view(b, s, v)[1, 4:].abs().sum()) == 0  # masked tokens carry no gradient
+    # evaluation (no gradient) reads the weights without moving them
+    with torch.no_grad():
+        loss_block(logits, labels, mask, domains, ref_losses)
+    assert len(state.history) == 2
+    # uniform weights reduce to the plain mean
+    uniform = dr.DoReMiContext(dr.DoReMiArgs(domain_names=["a", "b", "c"], step_size=0.0, smoothing_param=0.0), torch.device("cpu"))
+    plain = dr.DoReMiLoss(ctx.tp_pg, ctx.dp_pg, uniform)(logits, labels, mask, domains, ref_losses)
+    torch.testing.assert_close(plain["loss"], plain["ce_loss"])
+    ctx.destroy()
