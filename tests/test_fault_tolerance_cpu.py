@@ -163,7 +163,9 @@ class _Exploding(torch.utils.data.Dataset):
 
 
 def test_dataloader_worker_failure_propagates():
-    dl = torch.utils.data.DataLoader(_Exploding(), batch_size=1, num_workers=1)
+    # a spawned worker: forking this (by now multi-threaded) test process can deadlock the child; the timeout turns a stuck
+    # worker into an error instead of a hang
+    dl = torch.utils.data.DataLoader(_Exploding(), batch_size=1, num_workers=1, multiprocessing_context="spawn", timeout=120)
     with pytest.raises(Exception) as ei:
         for _ in dl:
             pass
