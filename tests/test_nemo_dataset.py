@@ -126,3 +126,62 @@ def test_blendable_datasets_follow_the_weights():
     me = MemoryEfficientBlendableDataset([a, b, c], [0.5, 0.3, 0.2], 1000, weight_bins=10)
     got = [me[i][0] for i in range(1000)]
     assert got.count("a") == 500 and got.count("b") == 300 and got.count("c") == 200
+
+
+class _CharTokenizer:
+    """One token per character (ids 10 ..), plus the five sentinel tokens the fill-in-the-middle transform needs."""
+
+    def __init__(self):
+        from nanotron_b200.data.nemo_dataset.gpt_dataset import EOD, FIM_MIDDLE, FIM_PAD, FIM_PREFIX, FIM_SUFFIX
+
+        self.vocab = {FIM_PREFIX: 1, FIM_MIDDLE: 2, FIM_SUFFIX: 3, FIM_PAD: 4, EOD: 0}
+
+    def decode(self, ids):
+        return "".join(chr(int(i) - 10 + ord("a")) for i in ids)
+
+    def encode(self, text):
+        return [ord(ch) - ord("a") + 10 for ch in text]
+
+
+def test_fill_in_the_middle_reorders_documents_without_losing_text(tmp_path):
+    from types import SimpleNamespace
+
+    from nanotron_b200.data.nemo_dataset import GPTDataset
+    from nanotron_b200.data.nemo_dataset.gpt_dataset import permute
+
+    tok = _CharTokenizer()
+    ids = dict(prefix_tok_id=1, middle_tok_id=2, suffix_tok_id=3, pad_tok_id=4)
+    doc = np.asarray(tok.encode("abcdefghijklmnopqrstuvwxyz"), dtype=np.int64)
+    rng = np.random.RandomState(0)
+    assert permute(doc, rng, 0.0, 0.5, tok, **ids) is doc  # rate 0: untouched
+    seen = set()
+    for _ in range(40):
+        out = permute(doc, rng, 1.0, 0.5, tok, truncate_or_pad=False, **ids)
+        assert len(out) == len(doc) + 3 and sorted(out.tolist()) == sorted(doc.tolist() + [1, 2, 3])
+        p, m, s = (int(np.flatnonzero(out == t)[0]) for t in (1, 2, 3))
+        if out[1] == 3:  # suffix-prefix-middle order: <prefix><suffix> s <middle> p m
+            seen.add("spm")
+            suffix, rest = out[2:m], out[m + 1 :]
+            assert p == 0 and s == 1 and tok.decode(rest) + tok.decode(suffix) == tok.decode(doc)
+        else:  # prefix-suffix-middle order: <prefix> p <suffix> s <middle> m
+            seen.add("psm")
+            assert p == 0 and p < s < m
+            assert tok.decode(out[1:s]) + tok.decode(out[m + 1 :]) + tok.decode(out[s + 1 : m]) == tok.decode(doc)
+    assert seen == {"spm", "psm"}
+    # keeping the length: the suffix is cut by the three sentinel tokens
+    out = permute(doc, np.random.RandomState(3), 1.0, 0.0, tok, truncate_or_pad=True, **ids)
+    assert len(out) == len(doc)
+    # through the dataset: samples keep their length, documents stay separated, sentinels appear
+    rs = np.random.RandomState(1)
+    docs = [list(rs.randint(10, 36, size=int(rs.randint(12, 30)))) + [0] for _ in range(40)]
+    prefix = _write(tmp_path, "fim", docs)
+    cfg = SimpleNamespace(fim_rate=1.0, fim_spm_rate=0.5)
+    g = GPTDataset(cfg, tok, "train", prefix, np.arange(40, dtype=np.int32), MMapIndexedDataset(prefix), 20, 48, seed=5)
+    plain = GPTDataset(None, None, "train", prefix, np.arange(40, dtype=np.int32), MMapIndexedDataset(prefix), 20, 48, seed=5)
+    changed = 0
+    for i in range(len(g)):
+        a, b = g[i]["input_ids"], plain[i]["input_ids"]
+        assert a.shape == b.shape == (49,)
+        changed += int(not np.array_equal(a, b))
+        assert {1, 2, 3} <= set(a.tolist())
+    assert changed == len(g)
