@@ -68,3 +68,69 @@ def test_get_tb_datasets_blends_folders(tmp_path):
     # resuming a later stage shifts the folder that was already consumed
     later, _ = get_tb_datasets(cfg, 9, 8, 10, 0, None, last_stages_consumed_tokens_per_dataset_folder={str(a): 90})
     assert int(later[0]["input_ids"][0]) == 90
+
+
+class _FakeBoto3:
+    """An in-memory object store with the three entry points the streaming helpers use."""
+
+    def __init__(self, objects):
+        self.objects = objects  # {(bucket, key): bytes}
+        outer = self
+
+        class _Body:
+            def __init__(self, data):
+                self.data = data
+
+            def iter_chunks(self, size):
+                for i in range(0, len(self.data), size):
+                    yield self.data[i : i + size]
+
+        class _Object:
+            def __init__(self, bucket_name, key):
+                self.data = outer.objects[(bucket_name, key)]
+                self.content_length = len(self.data)
+
+            def get(self, Range):
+                start = int(Range[len("bytes=") : -1])
+                return {"Body": _Body(self.data[start:])}
+
+        class _Resource:
+            Object = staticmethod(lambda bucket_name, key: _Object(bucket_name, key))
+
+        class _Paginator:
+            def paginate(self, Bucket, Prefix, Delimiter):
+                keys = sorted(k for (b, k) in outer.objects if b == Bucket and k.startswith(Prefix))
+                here = [k for k in keys if Delimiter not in k[len(Prefix) :]]
+                below = sorted({Prefix + k[len(Prefix) :].split(Delimiter)[0] + Delimiter for k in keys if Delimiter in k[len(Prefix) :]})
+                yield {"Contents": [{"Key": k} for k in here], "CommonPrefixes": [{"Prefix": p} for p in below]}
+
+        class _Client:
+            get_paginator = staticmethod(lambda name: _Paginator())
+
+        self.resource = lambda service: _Resource()
+        self.client = lambda service: _Client()
+
+
+def test_byte_range_streaming_from_files_and_from_an_object_store(tmp_path, monkeypatch):
+    from nanotron_b200.data import s3_utils
+
+    payload = bytes(range(256)) * 5
+    local = tmp_path / "tokens.ds"
+    local.write_bytes(payload)
+    assert s3_utils.file_size(str(local)) == 1280
+    assert b"".join(s3_utils._stream_file(str(local), chunk_size=100, offset=0)) == payload
+    assert b"".join(s3_utils._stream_file(str(local), chunk_size=100, offset=3)) == payload[300:]  # the offset counts chunks
+    assert s3_utils._get_s3_path_components("s3://bucket/a//b/c.ds") == ("bucket", "a/b/c.ds")
+    store = {("bucket", "data/a/000.ds"): payload, ("bucket", "data/a/001.ds"): payload[:700], ("bucket", "data/a/000.ds.index"): b"x",
+             ("bucket", "data/b/deep/002.ds"): payload[:10], ("bucket", "other/003.ds"): b"zz"}
+    monkeypatch.setattr(s3_utils, "boto3", _FakeBoto3(store))
+    monkeypatch.setattr(s3_utils, "BOTO3_AVAILABLE", True)
+    assert s3_utils.file_size("s3://bucket/data/a/001.ds") == 700
+    chunks = list(s3_utils._stream_file("s3://bucket/data/a/000.ds", chunk_size=512, offset=1))
+    assert b"".join(chunks) == payload[512:] and len(chunks[0]) == 512
+    assert s3_utils._get_s3_file_list("s3://bucket/data", pattern=r".*\.ds$") == ["s3://bucket/data/a/000.ds", "s3://bucket/data/a/001.ds", "s3://bucket/data/b/deep/002.ds"]
+    assert s3_utils._get_s3_file_list("s3://bucket/data", pattern=r".*\.ds$", max_recursion=1) == ["s3://bucket/data/a/000.ds", "s3://bucket/data/a/001.ds"]
+    assert s3_utils._get_s3_file_list("s3://bucket/data/a", recursive=False) == ["s3://bucket/data/a/000.ds", "s3://bucket/data/a/000.ds.index", "s3://bucket/data/a/001.ds"]
+    monkeypatch.setattr(s3_utils, "BOTO3_AVAILABLE", False)
+    with pytest.raises(ImportError):
+        s3_utils.file_size("s3://bucket/data/a/001.ds")
