@@ -134,3 +134,53 @@ def test_byte_range_streaming_from_files_and_from_an_object_store(tmp_path, monk
     monkeypatch.setattr(s3_utils, "BOTO3_AVAILABLE", False)
     with pytest.raises(ImportError):
         s3_utils.file_size("s3://bucket/data/a/001.ds")
+
+
+def test_token_file_streams_from_an_object_store_and_survives_a_dropped_connection(tmp_path, monkeypatch):
+    from nanotron_b200.data import s3_utils
+
+    tokens = np.arange(9 * 40, dtype=np.uint16)
+    fake = _FakeBoto3({("bucket", "run/000.ds"): tokens.tobytes()})
+    monkeypatch.setattr(s3_utils, "boto3", fake)
+    monkeypatch.setattr(s3_utils, "BOTO3_AVAILABLE", True)
+    ds = TokenizedBytesFileDataset("s3://bucket/run/000.ds", seq_len=8, skip_tokens=4)  # samples of 9 tokens after a skipped prefix
+    assert len(ds) == (360 - 4) // 9
+    assert ds[0]["input_ids"].tolist() == list(range(4, 13)) and ds[1]["input_ids"].tolist() == list(range(13, 22))
+    assert ds[5]["input_ids"].tolist() == list(range(4 + 45, 4 + 54))  # forward jump: the samples in between are consumed from the stream
+    assert ds[2]["input_ids"].tolist() == list(range(22, 31))  # backward jump: a new range request
+    # the connection drops in the middle of the stream: the dataset re-opens it at the sample it was about to serve
+    real_resource = fake.resource
+    state = {"opened": 0}
+
+    def flaky_resource(service):
+        res = real_resource(service)
+
+        class Wrapper:
+            @staticmethod
+            def Object(bucket_name, key):
+                obj = res.Object(bucket_name, key)
+                real_get = obj.get
+
+                def get(Range):
+                    state["opened"] += 1
+                    body = real_get(Range)["Body"]
+                    first = state["opened"] == 1
+
+                    class Body:
+                        def iter_chunks(self, size):
+                            for n, chunk in enumerate(body.iter_chunks(size)):
+                                if first and n == 2:
+                                    raise ConnectionError("connection reset")
+                                yield chunk
+
+                    return {"Body": Body()}
+
+                obj.get = get
+                return obj
+
+        return Wrapper()
+
+    monkeypatch.setattr(fake, "resource", flaky_resource)
+    fresh = TokenizedBytesFileDataset("s3://bucket/run/000.ds", seq_len=8)
+    got = [fresh[i]["input_ids"].tolist() for i in range(5)]
+    assert got == [list(range(9 * i, 9 * i + 9)) for i in range(5)] and state["opened"] == 2
