@@ -95,3 +95,38 @@ def test_older_spellings_of_the_reference_schema_still_load(tmp_path):
     assert upgrade_legacy_config_dict(new) == new  # the current schema passes through untouched
     with pytest.raises(Exception):
         c.get_config_from_dict({**old, "optimizer": {**old["optimizer"], "adam_beta3": 0.5}})  # unknown keys are still errors
+
+
+def test_parallelism_section_validates_sizes_and_describes_the_layout():
+    from nanotron_b200.parallel.pipeline_parallel.engine import AllForwardAllBackwardPipelineEngine, OneForwardOneBackwardPipelineEngine
+    from nanotron_b200.parallel.tensor_parallel.enum import TensorParallelLinearMode
+
+    p = c.ParallelismArgs(dp=2, pp=1, tp=1)
+    assert isinstance(p.pp_engine, AllForwardAllBackwardPipelineEngine) and p.tp_mode == TensorParallelLinearMode.ALL_REDUCE and p.tp_linear_async_communication is False
+    assert p.world_size == 2 and p.describe() == "dp2"
+    p = c.ParallelismArgs(dp=8, pp=2, tp=4, pp_engine="1f1b", tp_mode="reduce_scatter", tp_linear_async_communication=True, expert_parallel_size=4, context_parallel_size=2)
+    assert isinstance(p.pp_engine, OneForwardOneBackwardPipelineEngine) and p.tp_mode == TensorParallelLinearMode.REDUCE_SCATTER
+    assert p.world_size == 128 and p.describe() == "dp8 (ep4) x cp2 x tp4 (sequence parallel) x pp2 (OneForwardOneBackwardPipelineEngine)"
+    for bad in (dict(dp=0, pp=1, tp=1), dict(dp=1, pp=1, tp=-2), dict(dp=6, pp=1, tp=1, expert_parallel_size=4), dict(dp=1, pp=1, tp=1, context_parallel_size=0)):
+        with pytest.raises(ValueError):
+            c.ParallelismArgs(**bad)
+
+
+def test_evaluation_section_accepts_the_reference_keys_and_round_trips(tmp_path):
+    cfg = make_config(tiny_llama_config(), seq=16)
+    cfg.lighteval = c.LightEvalConfig(
+        batch_size=16, s3_save_path="s3://bucket/evals", upload_to_wandb=True, wandb_project="p", eval_interval=200,
+        logging=c.LightEvalLoggingArgs(local_output_path="eval_out", push_results_to_tensorboard=True, hub_repo_results="org/results", tensorboard_metric_prefix="e"),
+        tasks=c.LightEvalTasksArgs(tasks="early-signal", max_samples=1000, no_multichoice_continuations_start_space=True),
+        generation=c.GenerationArgs(sampler="top_p", top_p=0.9, temperature=0.7),
+    )
+    assert cfg.lighteval.output_dir == "eval_out" and str(cfg.lighteval.logging.local_output_path) == "eval_out" and cfg.lighteval.generation.seed == 42
+    path = tmp_path / "with_eval.yaml"
+    cfg.save_as_yaml(str(path))
+    again = c.get_config_from_file(str(path))
+    assert again.lighteval == cfg.lighteval and again.lighteval.parallelism.world_size == 1
+    assert c.LightEvalLoggingArgs(output_dir="x").local_output_path.name == "x"  # the newer spelling fills the reference's field
+    with pytest.raises(AssertionError):
+        c.LightEvalConfig(upload_to_wandb=True, wandb_project="p")  # nowhere to read the results from
+    with pytest.raises(ValueError):
+        c.LightEvalTasksArgs(multichoice_continuations_start_space=True, no_multichoice_continuations_start_space=True)
