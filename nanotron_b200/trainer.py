@@ -237,7 +237,7 @@ class DistributedTrainer:
     def pre_training(self, *args, **kwargs):
         self._install_signal_handlers()
         metadata = self.metadata
-        log_rank(f"Start training] datetime: {datetime.datetime.now()} | mbs: {self.micro_batch_size} | grad_accum: {self.n_micro_batches_per_batch} | global_batch_size: {self.global_batch_size} | sequence_length: {self.sequence_length} | train_steps: {self.config.tokens.train_steps} | start_iteration_step: {metadata.last_train_step} | consumed_train_samples: {metadata.consumed_train_samples}", logger=logger, level=logging.INFO, rank=0)
+        log_rank(f"Start training] datetime: {datetime.datetime.now()} | layout: {self.config.parallelism.describe()} | mbs: {self.micro_batch_size} | grad_accum: {self.n_micro_batches_per_batch} | global_batch_size: {self.global_batch_size} | sequence_length: {self.sequence_length} | train_steps: {self.config.tokens.train_steps} | start_iteration_step: {metadata.last_train_step} | consumed_train_samples: {metadata.consumed_train_samples}", logger=logger, level=logging.INFO, rank=0)
         self._wandb = None
         is_logger = dist.get_rank(self.parallel_context.world_pg) == self.logger_ranks[0]
         per_tp_runs = self._shard_suffix() != "" and self._is_metrics_rank()
