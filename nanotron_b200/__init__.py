@@ -7,4 +7,4 @@ under :mod:`nanotron_b200.ops`.  The same code also runs on CPU with the gloo
 backend, which is what the numerical oracles and the multi-rank logic tests use.
 """
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
