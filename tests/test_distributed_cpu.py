@@ -341,3 +341,47 @@ def test_expert_parallelism_with_pipeline_and_context_parallelism(tmp_path):
     got = _losses_for(tmp_path, 4, "moe_cp2_ep2", model="moe", dp=2, ep=2, cp=2)
     for a, b in zip(got, rep_cp):
         assert abs(a - b) < 3e-4, (got, rep_cp)
+
+
+def _two_stage_lengths(out_file, **topology):
+    import importlib.util
+
+    import nanotron_b200.config as c
+    import nanotron_b200.distributed as dist
+    from helpers import tiny_qwen_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("run_train_for_stage_test", os.path.join(root, "run_train.py"))
+    run_train = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(run_train)
+    cfg = make_config(tiny_qwen_config(max_position_embeddings=64), seq=16, mbs=2, accum=2, steps=5, lr=1e-2, sanity=True, **topology)
+    cfg.data_stages = [
+        c.DatasetStageArgs(name="short", start_training_step=1, data=c.DataArgs(dataset=None, seed=3)),
+        c.DatasetStageArgs(name="long", start_training_step=3, data=c.DataArgs(dataset=None, seed=4), sequence_length=32),
+    ]
+    t = DistributedTrainer(cfg)
+    seen = []
+    step = t.training_step
+
+    def spy(dataloader):
+        result = step(dataloader)
+        seen.append((t.iteration_step, t.sequence_length))
+        return result
+
+    t.training_step = spy
+    t.train(run_train.get_dataloader(t))
+    if dist.get_rank(t.parallel_context.world_pg) == t.logger_ranks[0]:
+        torch.save({"seen": seen, "tokens": t.metadata.consumed_tokens_total, "stages": [(s.name, s.consumed_train_samples, s.sequence_length) for s in t.metadata.data_stages]}, out_file)
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def test_data_stages_may_change_the_sequence_length_under_pipeline_parallelism(tmp_path):
+    """The second stage doubles the sequence length: pipeline stages that replay learnt activation shapes must learn the new ones
+    at the switch, and the token accounting follows the stage's length."""
+    out = str(tmp_path / "stages.pt")
+    run_distributed(_two_stage_lengths, 4, out_file=out, pp=2, tp=2, tp_mode="reduce_scatter", pp_engine="1f1b")
+    res = torch.load(out)
+    assert res["seen"] == [(1, 16), (2, 16), (3, 32), (4, 32), (5, 32)]
+    assert res["tokens"] == 2 * 4 * 16 + 3 * 4 * 32 and res["stages"] == [("short", 8, 16), ("long", 12, 32)]
