@@ -307,3 +307,74 @@ def test_flop_count_of_dense_and_mixture_models():
     model, _ = get_flops(**kw, moe_config=moe, num_moe_layers=1)
     moe_mlp = 6 * T * h * 32 * 2 + 2 * T * h * 8 + 6 * T * h * 64 + 2 * T * h
     assert model == 3 * (2 * attention + 6 * T * h * 256 + moe_mlp + 2 * T * h * 1000)
+
+
+# ---------------------------------------------------------------------------- less common options of the trainer
+def test_initial_checkpoint_weights_only_start_sgd_and_validation(tmp_path):
+    import os
+
+    import nanotron_b200.config as c
+    from helpers import dummy_dataloader
+    from nanotron_b200.trainer import DistributedTrainer
+
+    # save_initial_state writes step 0 before the first update
+    single_process_env()
+    cfg = make_config(tiny_llama_config(), seq=16, steps=3, ckpt_path=str(tmp_path / "a"), ckpt_interval=3)
+    cfg.checkpoints.save_initial_state = True
+    t = DistributedTrainer(cfg)
+    t.train(dummy_dataloader(t))
+    assert sorted(os.listdir(tmp_path / "a")) == ["0", "3", "latest.txt"] and open(tmp_path / "a" / "latest.txt").read() == "3"
+    trained = {k: v.detach().clone() for k, v in t.unwrapped_model.named_parameters()}
+    t.parallel_context.destroy()
+    # init_method.path starts a NEW run from those weights: step 0, fresh schedule and optimizer
+    single_process_env()
+    cfg = make_config(tiny_llama_config(), seq=16, steps=2, ckpt_path=str(tmp_path / "b"))
+    cfg.model.init_method = c.ExistingCheckpointInit(path=str(tmp_path / "a" / "3"))
+    t = DistributedTrainer(cfg)
+    assert all(torch.equal(v, dict(t.unwrapped_model.named_parameters())[k]) for k, v in trained.items())
+    assert t.iteration_step == 0 and t.metadata.consumed_train_samples == 0 and len(t.optimizer.get_base_optimizer().state) == 0
+    # validation: limit_val_batches forward passes without gradients; their outputs add up to the mean loss
+    t.config.tokens.limit_val_batches = t.limit_val_batches = 2
+    t.prepare_training()
+    outputs = t.validation_step(dummy_dataloader(t))
+    assert len(outputs) == 2 and all(not o["loss"].requires_grad for o in outputs) and 3.0 < float(sum(o["loss"] for o in outputs)) < 7.0
+    assert all(p.grad is None for p in t.unwrapped_model.parameters())
+    t.parallel_context.destroy()
+    # plain SGD from the config
+    single_process_env()
+    cfg = make_config(tiny_llama_config(), seq=16, steps=8, lr=0.5)
+    cfg.optimizer.optimizer_factory = c.SGDOptimizerArgs()
+    t = DistributedTrainer(cfg)
+    assert type(t.optimizer.get_base_optimizer()).__name__ == "SGD"
+    t.prepare_training()
+    batch = [next(dummy_dataloader(t))]
+    losses = []
+    for _ in range(6):
+        losses.append(float(t.training_step(iter(batch))[1]))
+        t.iteration_step += 1
+    assert losses[-1] < losses[0] - 0.5, losses
+    t.parallel_context.destroy()
+
+
+def test_rotary_options_layers_without_rope_and_frequency_scaling():
+    from helpers import dummy_dataloader
+    from nanotron_b200.trainer import DistributedTrainer
+
+    single_process_env()
+    t = DistributedTrainer(make_config(tiny_qwen_config(no_rope_layer=2), seq=16, steps=2))
+    assert [blk.pp_block.attn.use_rope for blk in t.unwrapped_model.model.decoder] == [True, False]  # every second layer is position-free
+    t.prepare_training()
+    assert torch.isfinite(t.training_step(dummy_dataloader(t))[1])
+    t.parallel_context.destroy()
+    single_process_env()
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    t = DistributedTrainer(make_config(tiny_llama_config(rope_scaling=scaling, max_position_embeddings=256, num_attention_heads=2, num_key_value_heads=2, hidden_size=64), seq=16, steps=2))
+    rot = t.unwrapped_model.model.decoder[0].pp_block.attn.rotary_emb
+    t.prepare_training()
+    assert torch.isfinite(t.training_step(dummy_dataloader(t))[1])
+    # long wavelengths are stretched by the factor, short ones are kept (the Llama-3.1 rule)
+    plain = 1.0 / (10000.0 ** (torch.arange(0, 32, 2).float() / 32))
+    got = rot.inv_freq.float().cpu() if hasattr(rot, "inv_freq") else None
+    if got is not None:
+        assert torch.allclose(got[0], plain[0]) and torch.allclose(got[-1], plain[-1] / 8.0, rtol=1e-4)
+    t.parallel_context.destroy()
