@@ -29,14 +29,30 @@ def nanotron_config_from_hf(hf_config, **overrides):
         params = getattr(hf_config, "rope_parameters", None) or {}
         kw["rope_theta"] = params.get("rope_theta", 10000.0)
     kw.setdefault("rope_interleaved", False)
+    scaling = _rope_scaling_of(hf_config)
+    if scaling is not None:
+        kw["rope_scaling"] = scaling
     kw.update(overrides)
     return LlamaConfig(**{k: v for k, v in kw.items() if v is not None or k == "pad_token_id"})
+
+
+def _rope_scaling_of(hf_config):
+    """The frequency-scaling rule of a Hugging Face configuration (``rope_scaling`` of older releases, ``rope_parameters`` of
+    newer ones) without the base frequency; None for plain rotary embeddings."""
+    params = getattr(hf_config, "rope_scaling", None) or getattr(hf_config, "rope_parameters", None)
+    if not params:
+        return None
+    rule = {k: v for k, v in dict(params).items() if k != "rope_theta"}
+    kind = rule.get("rope_type", rule.get("type", "default"))
+    return None if kind in (None, "default") else {**rule, "rope_type": kind}
 
 
 def hf_config_from_nanotron(nt_config):
     from transformers import LlamaConfig as HFLlamaConfig
 
     kw = {hf: getattr(nt_config, nt) for hf, nt in HF_TO_NT_CONFIG.items() if hasattr(nt_config, nt)}
+    if getattr(nt_config, "rope_scaling", None):
+        kw["rope_scaling"] = dict(nt_config.rope_scaling)
     return HFLlamaConfig(**kw, attention_bias=False, mlp_bias=False)
 
 

@@ -102,6 +102,7 @@ class Qwen2Attention(nn.Module, LogMixin):
             self.rotary_emb = RotaryEmbedding(
                 dim=self.head_dim, max_seq_len=config.max_position_embeddings, base=config.rope_theta,
                 interleaved=config.rope_interleaved, seq_len_scaling_factor=getattr(config, "rope_seq_len_interpolation_factor", None),
+                rope_scaling=getattr(config, "rope_scaling", None),
             )
         # spectral muP scales attention logits by 1 / head_dim instead of 1 / sqrt(head_dim) (reference models/llama.py:289)
         self.softmax_scale = 1.0 / self.head_dim if getattr(config, "is_using_mup", False) else None

@@ -15,8 +15,11 @@ from nanotron_b200.ops import reference as ref
 
 
 class RotaryEmbedding(nn.Module):
-    def __init__(self, dim: int, max_seq_len: int, base: float = 10000.0, interleaved: bool = False, seq_len_scaling_factor: Optional[float] = None, fused: bool = True):
+    def __init__(self, dim: int, max_seq_len: int, base: float = 10000.0, interleaved: bool = False, seq_len_scaling_factor: Optional[float] = None, fused: bool = True,
+                 rope_scaling: Optional[dict] = None):
         super().__init__()
+        self.rope_scaling = dict(rope_scaling) if rope_scaling else None
+        ref.rope_inverse_frequencies(dim, base, self.rope_scaling)  # an unsupported rule fails here, when the model is built
         self.dim = dim
         self.max_seq_len = max_seq_len
         self.base = base
@@ -30,8 +33,12 @@ class RotaryEmbedding(nn.Module):
         if self.cos_table.numel() == 0 or self.cos_table.shape[0] < needed_len or self.cos_table.device != device:
             n = max(needed_len, self.max_seq_len)
             pos = torch.arange(n, device=device)
-            cos, sin = ref.rope_cos_sin(pos, self.dim, self.base, self.seq_len_scaling_factor)
+            cos, sin = ref.rope_cos_sin(pos, self.dim, self.base, self.seq_len_scaling_factor, scaling=self.rope_scaling)
             self.cos_table, self.sin_table = cos.contiguous(), sin.contiguous()
+
+    @property
+    def inv_freq(self) -> torch.Tensor:
+        return ref.rope_inverse_frequencies(self.dim, self.base, self.rope_scaling)
 
     def get_cos_sin(self, positions: torch.Tensor, max_position: Optional[int] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """cos/sin rows [T, dim/2] for flat ``positions`` [T]."""
@@ -52,5 +59,6 @@ class RotaryEmbedding(nn.Module):
 class FlashRotaryEmbedding(RotaryEmbedding):
     """Same maths; keeps the reference name and its ``seq_len_interpolation_factor`` argument."""
 
-    def __init__(self, dim: int, base: float = 10000.0, interleaved: bool = False, seq_len_interpolation_factor: Optional[float] = None, max_seq_len: int = 4096, **_):
-        super().__init__(dim=dim, max_seq_len=max_seq_len, base=base, interleaved=interleaved, seq_len_scaling_factor=seq_len_interpolation_factor)
+    def __init__(self, dim: int, base: float = 10000.0, interleaved: bool = False, seq_len_interpolation_factor: Optional[float] = None, max_seq_len: int = 4096,
+                 rope_scaling: Optional[dict] = None, **_):
+        super().__init__(dim=dim, max_seq_len=max_seq_len, base=base, interleaved=interleaved, seq_len_scaling_factor=seq_len_interpolation_factor, rope_scaling=rope_scaling)

@@ -62,9 +62,36 @@ def layer_norm_bwd(dy, pre, weight, mean, rstd, dresidual=None, has_bias=True):
 
 
 # ------------------------------------------------------------------ rotary
-def rope_cos_sin(positions: torch.Tensor, dim: int, theta: float, interpolation_factor: Optional[float] = None, dtype=torch.float32):
+def rope_inverse_frequencies(dim: int, theta: float, scaling: Optional[dict] = None, device=None) -> torch.Tensor:
+    """The dim/2 rotation frequencies, with the ``rope_scaling`` rules of Hugging Face model configurations applied:
+
+    * ``linear``: every frequency divided by ``factor`` (position interpolation);
+    * ``llama3``: wavelengths longer than ``original_max_position_embeddings / low_freq_factor`` are stretched by ``factor``,
+      those shorter than ``original / high_freq_factor`` are kept, the band in between is blended linearly (Llama-3.1).
+
+    Other rules (``dynamic``, ``yarn``, ``longrope``) are not implemented and raise instead of training with silently different
+    positions.  (The reference carries ``rope_scaling`` in its configurations but never reads it.)"""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, device=device, dtype=torch.float32) / dim))
+    if not scaling:
+        return inv_freq
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    if kind in (None, "default"):
+        return inv_freq
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv_freq / factor
+    if kind == "llama3":
+        low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        original = float(scaling["original_max_position_embeddings"])
+        wavelen = 2 * math.pi / inv_freq
+        blend = ((original / wavelen - low) / (high - low)).clamp(0.0, 1.0)  # 0: long wavelengths (stretched), 1: short ones (kept)
+        return (1 - blend) * inv_freq / factor + blend * inv_freq
+    raise NotImplementedError(f"rope_scaling of type {kind!r} is not implemented (supported: linear, llama3)")
+
+
+def rope_cos_sin(positions: torch.Tensor, dim: int, theta: float, interpolation_factor: Optional[float] = None, dtype=torch.float32, scaling: Optional[dict] = None):
     """cos/sin tables [*positions.shape, dim/2] in fp32."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, device=positions.device, dtype=torch.float32) / dim))
+    inv_freq = rope_inverse_frequencies(dim, theta, scaling, device=positions.device)
     pos = positions.float()
     if interpolation_factor is not None:
         pos = pos / interpolation_factor

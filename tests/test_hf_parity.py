@@ -147,3 +147,39 @@ def test_mamba_example_matches_the_hugging_face_model(tmp_path):
     back = conv.to_hf(str(tmp_path / "nt"), str(tmp_path / "hf_back"))
     for name, p in hf.state_dict().items():
         assert torch.equal(back.state_dict()[name], p), name
+
+
+@pytest.mark.parametrize("kind", ["llama3", "linear"])
+def test_rope_frequency_scaling_matches_hugging_face(kind):
+    """Llama-3.1 checkpoints carry ``rope_scaling``: the frequencies, and the logits of a converted model at positions beyond the
+    original context, must equal the Hugging Face ones."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+
+    from convert_weights import build_single_process_model, hf_config_from_nanotron, hf_state_to_nanotron, load_state_into, nanotron_config_from_hf
+    from helpers import single_process_env
+    from nanotron_b200.ops.reference import rope_inverse_frequencies
+
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32} if kind == "llama3" else {"rope_type": "linear", "factor": 4.0}
+    cfg = LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=176, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256,
+                      rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=dict(scaling), attention_bias=False, mlp_bias=False)
+    expected, _ = ROPE_INIT_FUNCTIONS[kind](cfg, "cpu")
+    torch.testing.assert_close(rope_inverse_frequencies(32, 10000.0, scaling), expected.float(), rtol=1e-6, atol=0)
+    with pytest.raises(NotImplementedError):
+        rope_inverse_frequencies(32, 10000.0, {"rope_type": "yarn", "factor": 2.0})
+    torch.manual_seed(0)
+    hf = LlamaForCausalLM(cfg).eval().float()
+    single_process_env()
+    nt_cfg = nanotron_config_from_hf(hf.config)
+    assert nt_cfg.rope_scaling == scaling
+    back = hf_config_from_nanotron(nt_cfg)  # and the rule survives the way back
+    assert {k: v for k, v in back.rope_parameters.items() if k != "rope_theta"} == scaling
+    model, ctx = build_single_process_model(nt_cfg)
+    load_state_into(model, hf_state_to_nanotron(hf.state_dict(), nt_cfg))
+    model.eval()
+    ids = torch.randint(0, 320, (1, 150))  # well past the original 32 positions
+    with torch.no_grad():
+        exp = hf(input_ids=ids).logits
+        got = model.model(input_ids=ids, input_mask=torch.ones_like(ids, dtype=torch.bool)).reshape(1, 150, -1)
+    torch.testing.assert_close(got.float(), exp, atol=3e-4, rtol=1e-3)
+    ctx.destroy()
