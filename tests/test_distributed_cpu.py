@@ -385,3 +385,16 @@ def test_data_stages_may_change_the_sequence_length_under_pipeline_parallelism(t
     res = torch.load(out)
     assert res["seen"] == [(1, 16), (2, 16), (3, 32), (4, 32), (5, 32)]
     assert res["tokens"] == 2 * 4 * 16 + 3 * 4 * 32 and res["stages"] == [("short", 8, 16), ("long", 12, 32)]
+
+
+def test_training_without_the_fp32_accumulator_agrees_across_layouts(tmp_path):
+    """``accumulate_grad_in_fp32: false``: gradients live on the parameters, the data-parallel exchange and the ZeRO slices work on
+    them directly; same loss curve as one process, with clipping active and the invariant checks on."""
+    base = _losses_for(tmp_path, 1, "plain_base", fp32_accum=False, sanity=True, clip=0.05)
+    with_accumulator = _losses_for(tmp_path, 1, "accum_base", sanity=True, clip=0.05)
+    for a, b in zip(base, with_accumulator):
+        assert abs(a - b) < 1e-5  # float32 parameters: the two gradient paths are the same arithmetic
+    for name, world, kw in (("plain_dp2_zero1", 2, dict(dp=2, zero=1)), ("plain_tp2_pp2", 4, dict(tp=2, pp=2, tp_mode="reduce_scatter", pp_engine="1f1b"))):
+        got = _losses_for(tmp_path, world, name, fp32_accum=False, sanity=True, clip=0.05, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-4, (name, got, base)
