@@ -398,3 +398,16 @@ def test_training_without_the_fp32_accumulator_agrees_across_layouts(tmp_path):
         got = _losses_for(tmp_path, world, name, fp32_accum=False, sanity=True, clip=0.05, **kw)
         for a, b in zip(got, base):
             assert abs(a - b) < 2e-4, (name, got, base)
+
+
+def test_bfloat16_parameters_with_fp32_masters_agree_across_layouts(tmp_path):
+    """bf16 parameters, fp32 gradient accumulation and master weights (the production precision) on CPU ranks: sharding the
+    optimizer does not change the arithmetic; tensor / pipeline parallelism only reorders bf16 roundings."""
+    kw = dict(dtype="bfloat16", sanity=True, clip=0.05)
+    base = _losses_for(tmp_path, 1, "bf16_base", **kw)
+    zero = _losses_for(tmp_path, 2, "bf16_dp2_zero1", dp=2, zero=1, **kw)
+    for a, b in zip(zero, base):
+        assert abs(a - b) < 2e-4, (zero, base)
+    model_parallel = _losses_for(tmp_path, 4, "bf16_tp2_pp2", tp=2, pp=2, tp_mode="reduce_scatter", pp_engine="1f1b", **kw)
+    for a, b in zip(model_parallel, base):
+        assert abs(a - b) < 5e-3, (model_parallel, base)
