@@ -147,17 +147,16 @@ class Qwen2Attention(nn.Module, LogMixin):
         b, s = position_ids.shape
         if self.use_rope:
             q, k = self.rotary_emb(q, k, position_ids.reshape(-1), inplace=False)
+        doc_masking = cu_seqlens is not None  # under context parallelism the exchange cuts at the (global) document starts itself
         if cu_seqlens is None:
             cu_seqlens = regular_cu_seqlens(b, s, hidden_states.device)
-            max_len = s
-        else:
-            max_len = s
+        max_len = s
         if log_stats:
             # [local heads, tokens] log-sum-exp of the attention scores, collected by the trainer once per logged step
             self.tbi_logger({"attn_probs": ops.attention_lse(q, k, v, cu_seqlens, cu_seqlens, max_len, max_len, causal=True, softmax_scale=self.softmax_scale, window=self.sliding_window_size)})
         out = self.attention(
             q, k, v, cu_seqlens_q=cu_seqlens, cu_seqlens_k=cu_seqlens, max_seqlen_q=max_len, max_seqlen_k=max_len, causal=True,
-            softmax_scale=self.softmax_scale, sliding_window=self.sliding_window_size, cp_pg=self.cp_pg, position_ids=position_ids,
+            softmax_scale=self.softmax_scale, sliding_window=self.sliding_window_size, cp_pg=self.cp_pg, position_ids=position_ids, doc_masking=doc_masking,
             flex_attention_mask=getattr(self.config, "flex_attention_mask", None),
         )
         out = self.o_proj(out.reshape(T, self.local_q_size))

@@ -15,15 +15,14 @@ from nanotron_b200 import ops
 
 
 def get_attention_mask(position_ids: torch.Tensor, seq_length: int):
-    """Document boundaries from position ids: a 0 starts a new document.  Returns (mask or None, cu_seqlens int32).
-    position_ids: [b, s].  Padding positions must be -1."""
-    flat = position_ids.reshape(-1)
-    starts = torch.nonzero(flat == 0, as_tuple=False).flatten()
-    total = torch.tensor([flat.numel()], device=flat.device, dtype=starts.dtype)
-    cu = torch.cat([starts, total]).to(torch.int32)
-    if cu[0] != 0:
-        cu = torch.cat([torch.zeros(1, dtype=torch.int32, device=cu.device), cu])
-    return None, cu
+    """Document boundaries from position ids: a 0 starts a new document, and so does the first token of every batch row (a row
+    that begins in the middle of a document must not see the end of the previous row; the reference cuts at zeros only,
+    src/nanotron/nn/attention.py:227-238).  Returns (mask or None, cu_seqlens int32).  position_ids: [b, s]."""
+    is_start = position_ids == 0
+    is_start[:, 0] = True
+    starts = torch.nonzero(is_start.reshape(-1), as_tuple=False).flatten()
+    total = torch.tensor([position_ids.numel()], device=starts.device, dtype=starts.dtype)
+    return None, torch.cat([starts, total]).to(torch.int32)
 
 
 def regular_cu_seqlens(batch: int, seq: int, device) -> torch.Tensor:

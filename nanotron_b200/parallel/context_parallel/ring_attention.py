@@ -17,6 +17,11 @@ needs no mask beyond "causal" for the rank's own block: a block from a lower ran
 queries, a block from a higher rank is seen entirely by the second half of the local queries.  Partial results are merged
 with their log-sum-exp; the backward runs the ring again with the final (out, lse), dK / dV travelling with their block.
 
+Packed documents (``doc_masking``: a position id of 0 starts a document) are handled by the "allgather" variant: the position ids
+are gathered once per micro-batch, every local query chunk is cut at the document starts inside it, and each piece attends the
+keys from the start of its document up to its own end -- consecutive key ranges of the gathered K / V, so this is again one call
+of the variable-length kernel per chunk (what the reference does for contiguous shards: src/nanotron/nn/llama3_ring_attention.py:10-60).
+
 ``merge_attention_states`` combines partial results (out, lse) over disjoint key sets; it is the building block of the
 blockwise / ring schedule.
 """
@@ -28,7 +33,10 @@ import torch
 
 import nanotron_b200.distributed as dist
 from nanotron_b200 import ops
+from nanotron_b200.logging import get_logger
 from nanotron_b200.parallel.context_parallel.zigzag import zigzag_chunk_ids
+
+_logger = get_logger(__name__)
 
 
 class _AllGatherDim0(torch.autograd.Function):
@@ -236,9 +244,57 @@ def _merge_into(out, lse, o, l):
     return out * wa.to(out.dtype) + o.to(out.dtype) * wb.to(out.dtype), new
 
 
-def ring_attention(q, k, v, cp_pg, causal: bool = True, softmax_scale: Optional[float] = None, variant: str = "allgather", position_ids: Optional[torch.Tensor] = None, **_):
+def _global_order(cp: int):
+    """(source rank, half) of the 2cp chunks in global order: chunk i < cp is the first half of rank i, chunk i >= cp the second
+    half of rank 2cp-1-i."""
+    return [(chunk, 0) if chunk < cp else (2 * cp - 1 - chunk, 1) for chunk in range(2 * cp)]
+
+
+_PLAN_CACHE: dict = {}
+
+
+def _document_plan(position_ids: torch.Tensor, cp_pg, rank: int, cp: int, c: int):
+    """For each of the two local query chunks: (query piece lengths, key range lengths, per row (first key, end key)).
+
+    A piece is a run of queries of one document inside the chunk; its keys start where its document starts (possibly in an
+    earlier chunk, on another rank) and end with the piece.  The plan depends on the micro-batch only, so it is computed by the
+    first layer that asks and reused by the others (one small all-gather and one device -> host copy per micro-batch)."""
+    key = (position_ids.data_ptr(), tuple(position_ids.shape), position_ids._version, rank, cp)
+    if _PLAN_CACHE.get("key") == key:
+        return _PLAN_CACHE["plan"]
+    b = position_ids.shape[0]
+    local = position_ids.reshape(1, b, 2, c).contiguous()
+    gathered = local.new_empty((cp, b, 2, c))
+    dist.all_gather_into_tensor(gathered, local, group=cp_pg)
+    glob = torch.stack([gathered[src, :, half] for src, half in _global_order(cp)], dim=1).reshape(b, 2 * cp * c)
+    starts = (glob == 0).cpu()
+    starts[:, 0] = True  # a row may begin in the middle of a document
+    plan = []
+    for chunk in zigzag_chunk_ids(rank, cp):
+        lo, hi = chunk * c, (chunk + 1) * c
+        q_lens, k_lens, k_ranges = [], [], []
+        for row in range(b):
+            doc_starts = torch.nonzero(starts[row, :hi]).flatten().tolist()
+            first = max(s for s in doc_starts if s <= lo)
+            bounds = [lo] + [s for s in doc_starts if lo < s] + [hi]
+            for j in range(len(bounds) - 1):
+                q_lens.append(bounds[j + 1] - bounds[j])
+                k_lens.append(bounds[j + 1] - (first if j == 0 else bounds[j]))
+            k_ranges.append((first, hi))
+        plan.append((q_lens, k_lens, k_ranges))
+    _PLAN_CACHE["key"], _PLAN_CACHE["plan"] = key, plan
+    return plan
+
+
+def _cumulative(lengths, device) -> torch.Tensor:
+    return torch.tensor([0] + lengths, dtype=torch.int64).cumsum(0).to(torch.int32).to(device)
+
+
+def ring_attention(q, k, v, cp_pg, causal: bool = True, softmax_scale: Optional[float] = None, variant: str = "allgather", position_ids: Optional[torch.Tensor] = None,
+                   doc_masking: bool = False, **_):
     """q: [b*s_local, Hq, D]; k, v: [b*s_local, Hkv, D] with the local tokens of every batch row in zig-zag order
-    (first chunk ``r``, then chunk ``2cp-1-r``).  ``position_ids`` [b, s_local] gives the batch size."""
+    (first chunk ``r``, then chunk ``2cp-1-r``).  ``position_ids`` [b, s_local] gives the batch size and, with ``doc_masking``,
+    the document starts (position 0): attention then stays inside a document."""
     cp = cp_pg.size() if cp_pg is not None else 1
     assert position_ids is not None, "context-parallel attention needs position_ids to know the batch layout"
     b, s_local = position_ids.shape
@@ -246,7 +302,12 @@ def ring_attention(q, k, v, cp_pg, causal: bool = True, softmax_scale: Optional[
         cu = torch.arange(0, (b + 1) * s_local, s_local, dtype=torch.int32, device=q.device)
         return ops.flash_attn_varlen(q, k, v, cu, cu, s_local, s_local, causal=causal, softmax_scale=softmax_scale)
     assert causal, "zig-zag sharding is only meaningful for causal attention"
-    if variant == "fused" or ops._ATTN == "native":
+    if doc_masking and variant != "allgather":
+        from nanotron_b200.logging import warn_once
+
+        warn_once(logger=_logger, msg=f"context-parallel attention variant {variant!r} has no document masking: packed documents use the all-gather variant", rank=0)
+        variant = "allgather"
+    if not doc_masking and (variant == "fused" or ops._ATTN == "native"):
         from nanotron_b200.parallel.context_parallel import fused_ring
 
         if fused_ring.supported(q, k, cp_pg, s_local // 2):
@@ -263,14 +324,18 @@ def ring_attention(q, k, v, cp_pg, causal: bool = True, softmax_scale: Optional[
     # gather K and V: [cp, b, 2, c, Hkv, D] -> global order [b, 2cp*c, Hkv, D]
     kv = torch.stack([k, v], dim=0).reshape(2, b, 2, c, Hkv, D)
     gathered = _AllGatherDim0.apply(kv.reshape(1, *kv.shape), cp_pg)  # [cp, 2, b, 2, c, Hkv, D]
-    order = []
-    for chunk in range(2 * cp):
-        src = chunk if chunk < cp else 2 * cp - 1 - chunk
-        order.append((src, 0 if chunk < cp else 1))
-    glob = torch.stack([gathered[src, :, :, half] for src, half in order], dim=2)  # [2, b, 2cp, c, Hkv, D]
+    glob = torch.stack([gathered[src, :, :, half] for src, half in _global_order(cp)], dim=2)  # [2, b, 2cp, c, Hkv, D]
     glob = glob.reshape(2, b, 2 * cp * c, Hkv, D)
     qb = q.reshape(b, 2, c, Hq, D)
     outs = []
+    if doc_masking:
+        for half, (q_lens, k_lens, k_ranges) in enumerate(_document_plan(position_ids, cp_pg, rank, cp, c)):
+            qh = qb[:, half].reshape(b * c, Hq, D)
+            kh = torch.cat([glob[0, row, first:end] for row, (first, end) in enumerate(k_ranges)])
+            vh = torch.cat([glob[1, row, first:end] for row, (first, end) in enumerate(k_ranges)])
+            o = ops.flash_attn_varlen(qh, kh, vh, _cumulative(q_lens, q.device), _cumulative(k_lens, q.device), max(q_lens), max(k_lens), causal=True, softmax_scale=softmax_scale)
+            outs.append(o.reshape(b, c, Hq, D))
+        return torch.stack(outs, dim=1).reshape(b * s_local, Hq, D)
     for half, chunk in enumerate(zigzag_chunk_ids(rank, cp)):
         lk = (chunk + 1) * c
         qh = qb[:, half].reshape(b * c, Hq, D)

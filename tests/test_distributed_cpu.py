@@ -110,7 +110,19 @@ def test_vocab_parallel_cross_entropy():
 
 
 # --------------------------------------------------------------------------- trainer-level equivalences
-def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123):
+def _packed_positions(rows, seq, generator):
+    """Position ids of rows packed with several documents (a 0 starts one); the first document of a row may have begun earlier."""
+    out = []
+    for _ in range(rows):
+        cuts = sorted(set(torch.randint(1, seq, (3,), generator=generator).tolist()))
+        bounds = [0] + cuts + [seq]
+        pos = torch.cat([torch.arange(b - a) for a, b in zip(bounds[:-1], bounds[1:])])
+        pos[: bounds[1]] += int(torch.randint(0, 5, (1,), generator=generator))
+        out.append(pos)
+    return torch.stack(out)
+
+
+def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123, packed=False):
     """The same global batch for every topology: ``total_mbs`` sequences per step, this rank takes its dp slice."""
     import nanotron_b200.distributed as dist
     from nanotron_b200.parallel.pipeline_parallel.tensor_pointer import TensorPointer
@@ -124,6 +136,7 @@ def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123):
     out = []
     for _ in range(n):
         tokens = torch.randint(0, vocab, (total_mbs, seq + 1), generator=g)
+        positions = _packed_positions(total_mbs, seq, g) if packed else torch.arange(seq).unsqueeze(0).expand(total_mbs, -1)
         mine = tokens[dp_rank * per_rank : (dp_rank + 1) * per_rank]
         for i in range(0, per_rank, mbs):
             t = mine[i : i + mbs]
@@ -133,7 +146,7 @@ def _fixed_batches(trainer, n, total_mbs, seq, vocab, uses_mask=True, seed=123):
                 if uses_mask:
                     b["input_mask"] = torch.ones(mbs, seq, dtype=torch.bool)
                 else:
-                    b["position_ids"] = torch.arange(seq).unsqueeze(0).expand(mbs, -1).contiguous()
+                    b["position_ids"] = positions[dp_rank * per_rank + i : dp_rank * per_rank + i + mbs].contiguous()
             else:
                 b["input_ids"] = TensorPointer(trainer.unwrapped_model.input_pp_rank)
                 b["input_mask" if uses_mask else "position_ids"] = TensorPointer(trainer.unwrapped_model.input_pp_rank)
@@ -191,17 +204,18 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", norms_file=None
         topology["fp32_accum"] = True
     accum = total_mbs // (dp * mbs)
     tie = topology.pop("tie", False)
+    packed = topology.pop("packed", False)
     if model == "moe":
         import nanotron_b200.config as c
 
         moe = c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=16, shared_expert_intermediate_size=32, enable_shared_expert=True, router_aux_loss_coef=0.01)
         mc = tiny_qwen_config(tie_word_embeddings=tie, moe_config=moe)
     else:
-        mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie)
+        mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie, _use_doc_masking=packed)
     cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
     t = DistributedTrainer(cfg)
     t.prepare_training()
-    batches = iter(_fixed_batches(t, steps, total_mbs, 16, mc.vocab_size, uses_mask=(model == "llama")))
+    batches = iter(_fixed_batches(t, steps, total_mbs, 16, mc.vocab_size, uses_mask=(model == "llama"), packed=packed))
     losses, norms = [], []
     for _ in range(steps):
         _, loss, _ = t.training_step(batches)
@@ -411,3 +425,15 @@ def test_bfloat16_parameters_with_fp32_masters_agree_across_layouts(tmp_path):
     model_parallel = _losses_for(tmp_path, 4, "bf16_tp2_pp2", tp=2, pp=2, tp_mode="reduce_scatter", pp_engine="1f1b", **kw)
     for a, b in zip(model_parallel, base):
         assert abs(a - b) < 5e-3, (model_parallel, base)
+
+
+def test_packed_documents_train_the_same_under_context_parallelism(tmp_path):
+    """Qwen2 with document masking on rows packed with several documents: splitting every sequence over 2 ranks (alone, and
+    together with tensor parallelism) gives the loss curve of one process; without the masking the curve is a different one."""
+    base = _losses_for(tmp_path, 1, "docs_base", model="qwen", packed=True, sanity=True)
+    unmasked = _losses_for(tmp_path, 1, "docs_unmasked", model="qwen", sanity=True)
+    assert max(abs(a - b) for a, b in zip(base, unmasked)) > 1e-4
+    for name, world, kw in (("docs_cp2", 2, dict(cp=2)), ("docs_cp2_tp2", 4, dict(cp=2, tp=2, tp_mode="reduce_scatter"))):
+        got = _losses_for(tmp_path, world, name, model="qwen", packed=True, sanity=True, **kw)
+        for a, b in zip(got, base):
+            assert abs(a - b) < 2e-4, (name, got, base)
