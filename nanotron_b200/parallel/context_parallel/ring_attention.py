@@ -250,18 +250,17 @@ def _global_order(cp: int):
     return [(chunk, 0) if chunk < cp else (2 * cp - 1 - chunk, 1) for chunk in range(2 * cp)]
 
 
-_PLAN_CACHE: dict = {}
-
-
 def _document_plan(position_ids: torch.Tensor, cp_pg, rank: int, cp: int, c: int):
     """For each of the two local query chunks: (query piece lengths, key range lengths, per row (first key, end key)).
 
     A piece is a run of queries of one document inside the chunk; its keys start where its document starts (possibly in an
     earlier chunk, on another rank) and end with the piece.  The plan depends on the micro-batch only, so it is computed by the
     first layer that asks and reused by the others (one small all-gather and one device -> host copy per micro-batch)."""
-    key = (position_ids.data_ptr(), tuple(position_ids.shape), position_ids._version, rank, cp)
-    if _PLAN_CACHE.get("key") == key:
-        return _PLAN_CACHE["plan"]
+    # cached on the tensor object itself: the decoder layers of a stage hand the same object on, and a later micro-batch is a new
+    # object even when the allocator gives it the same address
+    cached = getattr(position_ids, "_ntb_document_plan", None)
+    if cached is not None and cached[0] == (position_ids._version, rank, cp, c):
+        return cached[1]
     b = position_ids.shape[0]
     local = position_ids.reshape(1, b, 2, c).contiguous()
     gathered = local.new_empty((cp, b, 2, c))
@@ -282,7 +281,7 @@ def _document_plan(position_ids: torch.Tensor, cp_pg, rank: int, cp: int, c: int
                 k_lens.append(bounds[j + 1] - (first if j == 0 else bounds[j]))
             k_ranges.append((first, hi))
         plan.append((q_lens, k_lens, k_ranges))
-    _PLAN_CACHE["key"], _PLAN_CACHE["plan"] = key, plan
+    position_ids._ntb_document_plan = ((position_ids._version, rank, cp, c), plan)
     return plan
 
 
