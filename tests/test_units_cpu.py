@@ -431,3 +431,63 @@ def test_learning_rate_schedules_have_the_documented_shapes():
     # default decay length: total steps minus the warm-up
     default = curve(total=12, lr_warmup_steps=2, lr_warmup_style="linear", lr_decay_style="linear", min_decay_lr=0.0)
     assert default[2] == pytest.approx(1.0) and default[12] == pytest.approx(0.0) and default[7] == pytest.approx(0.5)
+
+
+_FAKE_S5CMD = r'''#!/usr/bin/env python3
+"""Stands in for s5cmd: ``cp [--exclude P]... SRC DST`` where ``s3://bucket/key`` lives under $FAKE_S3_ROOT/bucket/key."""
+import fnmatch, os, shutil, sys
+root = os.environ["FAKE_S3_ROOT"]
+args = [a for a in sys.argv[1:]]
+local = lambda p: os.path.join(root, p[len("s3://"):]) if p.startswith("s3://") else p
+while args[0] != "cp":
+    args.pop(0) if args[0] == "--json" else (args.pop(0), args.pop(0))
+args.pop(0)
+exclude = []
+while args[0].startswith("--"):
+    flag, value = args.pop(0), args.pop(0)
+    if flag == "--exclude":
+        exclude.append(value)
+src, dst = local(args[0]), local(args[1])
+for folder, _, files in os.walk(src):
+    for name in files:
+        if any(fnmatch.fnmatch(name, pattern) for pattern in exclude):
+            continue
+        out = os.path.join(dst, os.path.relpath(os.path.join(folder, name), src))
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        shutil.copy(os.path.join(folder, name), out)
+        print('{"operation":"cp","success":true,"source":"%s","destination":"%s"}' % (os.path.join(folder, name), out))
+'''
+
+
+def _train_with_upload(ckpt, tool):
+    import nanotron_b200.config as c
+    import nanotron_b200.distributed as dist
+    from helpers import dummy_dataloader, make_config, tiny_llama_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    cfg = make_config(tiny_llama_config(), dp=2, seq=16, steps=4, ckpt_path=ckpt, ckpt_interval=2)
+    cfg.s3_upload = c.S3UploadArgs(upload_s3_path="s3://bucket/run1", remove_after_upload=True, s5cmd_numworkers=2, s5cmd_concurrency=2, s5cmd_path=tool)
+    t = DistributedTrainer(cfg)
+    t.train(dummy_dataloader(t))
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def test_trainer_uploads_every_checkpoint_and_removes_the_local_copy(tmp_path):
+    """``s3_upload`` in the configuration: after every save the checkpoint folder is copied to the bucket in the background (first
+    rank of the node only), the next save waits for it, the local step folders are removed, and training ends after the last copy."""
+    from helpers import run_distributed
+
+    tool = tmp_path / "s5cmd"
+    tool.write_text(_FAKE_S5CMD)
+    tool.chmod(tool.stat().st_mode | stat.S_IEXEC)
+    os.environ["FAKE_S3_ROOT"] = str(tmp_path / "object_store")
+    try:
+        run_distributed(_train_with_upload, 2, ckpt=str(tmp_path / "ckpt"), tool=str(tool))
+    finally:
+        os.environ.pop("FAKE_S3_ROOT")
+    remote = tmp_path / "object_store" / "bucket" / "run1"
+    assert sorted(os.listdir(remote)) == ["2", "4", "latest.txt"] and (remote / "latest.txt").read_text() == "4"
+    for step in ("2", "4"):
+        assert sorted(os.listdir(remote / step)) == ["checkpoint_metadata.json", "config.yaml", "lr_scheduler", "model", "model_config.json", "optimizer", "random"]
+    assert sorted(os.listdir(tmp_path / "ckpt")) == ["latest.txt"]  # the step folders are gone
