@@ -91,6 +91,27 @@ def load(model: nn.Module, optimizer: optim.BaseOptimizer, lr_scheduler, paralle
     return meta
 
 
+def _read_remote_step(url: str, s5cmd_path=None) -> Optional[int]:
+    """The step written in a remote ``latest.txt``, or None when there is no such object.  Read through fsspec when a driver for
+    the protocol is installed, else with the same ``s5cmd`` tool that moves the checkpoints (``s5cmd cat``)."""
+    from nanotron_b200.s3_checkpoints import fs_open
+
+    try:
+        with fs_open(url, mode="r") as fi:
+            return int(fi.read())
+    except FileNotFoundError:
+        return None
+    except (ImportError, ValueError, OSError) as e:
+        log_rank(f"{url}: not readable through fsspec ({type(e).__name__}); asking s5cmd", logger=logger, level=logging.INFO, rank=0)
+    import subprocess
+
+    try:
+        done = subprocess.run([str(s5cmd_path) if s5cmd_path is not None else "s5cmd", "cat", url], capture_output=True, text=True, timeout=300)
+    except FileNotFoundError as e:
+        raise RuntimeError(f"cannot read {url}: neither an fsspec driver for the protocol nor the s5cmd tool is available") from e
+    return int(done.stdout.strip()) if done.returncode == 0 and done.stdout.strip().isdigit() else None
+
+
 def parse_ckpt_path(config: Config, parallel_context: Optional[ParallelContext] = None) -> Optional[Path]:
     """Resolve ``checkpoints.resume_checkpoint_path`` to a concrete step folder.
 
@@ -106,12 +127,11 @@ def parse_ckpt_path(config: Config, parallel_context: Optional[ParallelContext] 
         s3_path = candidate if candidate.startswith("s3://") else candidate.replace("s3:/", "s3://", 1)
         local = Path(config.checkpoints.checkpoints_path)
         latest_meta = s3_path.rstrip("/") + "/" + LATEST_FILE_NAME
-        try:
-            with fs_open(latest_meta, mode="r") as fi:
-                step = int(fi.read())
+        step = _read_remote_step(latest_meta, config.s3_upload.s5cmd_path if config.s3_upload else None)
+        if step is not None:
             s3_path = s3_path.rstrip("/") + f"/{step}"
             local_dir = local / str(step)
-        except FileNotFoundError:
+        else:  # the path names a step folder itself
             local_dir = local / s3_path.rstrip("/").split("/")[-1]
         mover = S3Mover(local_path=str(local_dir), s3_path=s3_path, s5cmd_numworkers=config.s3_upload.s5cmd_numworkers if config.s3_upload else None, s5cmd_concurrency=config.s3_upload.s5cmd_concurrency if config.s3_upload else None, s5cmd_path=config.s3_upload.s5cmd_path if config.s3_upload else None, dummy=bool(int(os.environ.get("LOCAL_RANK", "0")) != 0))
         mover.distributed_wait_for_completion(parallel_context.world_pg if parallel_context is not None else None)

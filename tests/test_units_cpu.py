@@ -439,15 +439,22 @@ import fnmatch, os, shutil, sys
 root = os.environ["FAKE_S3_ROOT"]
 args = [a for a in sys.argv[1:]]
 local = lambda p: os.path.join(root, p[len("s3://"):]) if p.startswith("s3://") else p
-while args[0] != "cp":
+while args[0] not in ("cp", "cat"):
     args.pop(0) if args[0] == "--json" else (args.pop(0), args.pop(0))
-args.pop(0)
+if args.pop(0) == "cat":
+    path = local(args[0])
+    if not os.path.exists(path):
+        sys.exit(1)
+    sys.stdout.write(open(path).read())
+    sys.exit(0)
 exclude = []
 while args[0].startswith("--"):
     flag, value = args.pop(0), args.pop(0)
     if flag == "--exclude":
         exclude.append(value)
 src, dst = local(args[0]), local(args[1])
+if src.endswith("*"):  # everything under a prefix, hierarchy kept
+    src = os.path.dirname(src)
 for folder, _, files in os.walk(src):
     for name in files:
         if any(fnmatch.fnmatch(name, pattern) for pattern in exclude):
@@ -459,16 +466,20 @@ for folder, _, files in os.walk(src):
 '''
 
 
-def _train_with_upload(ckpt, tool):
+def _train_with_upload(ckpt, tool, steps=4, resume=None, out_file=None):
     import nanotron_b200.config as c
     import nanotron_b200.distributed as dist
     from helpers import dummy_dataloader, make_config, tiny_llama_config
     from nanotron_b200.trainer import DistributedTrainer
 
-    cfg = make_config(tiny_llama_config(), dp=2, seq=16, steps=4, ckpt_path=ckpt, ckpt_interval=2)
+    cfg = make_config(tiny_llama_config(), dp=2, seq=16, steps=steps, ckpt_path=ckpt, ckpt_interval=2)
     cfg.s3_upload = c.S3UploadArgs(upload_s3_path="s3://bucket/run1", remove_after_upload=True, s5cmd_numworkers=2, s5cmd_concurrency=2, s5cmd_path=tool)
+    cfg.checkpoints.resume_checkpoint_path = resume
     t = DistributedTrainer(cfg)
+    start = t.iteration_step
     t.train(dummy_dataloader(t))
+    if out_file is not None and dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save({"start": start, "end": t.iteration_step, "samples": t.metadata.consumed_train_samples}, out_file)
     dist.barrier()
     t.parallel_context.destroy()
 
@@ -482,12 +493,17 @@ def test_trainer_uploads_every_checkpoint_and_removes_the_local_copy(tmp_path):
     tool.write_text(_FAKE_S5CMD)
     tool.chmod(tool.stat().st_mode | stat.S_IEXEC)
     os.environ["FAKE_S3_ROOT"] = str(tmp_path / "object_store")
+    remote = tmp_path / "object_store" / "bucket" / "run1"
     try:
         run_distributed(_train_with_upload, 2, ckpt=str(tmp_path / "ckpt"), tool=str(tool))
+        assert sorted(os.listdir(remote)) == ["2", "4", "latest.txt"] and (remote / "latest.txt").read_text() == "4"
+        for step in ("2", "4"):
+            assert sorted(os.listdir(remote / step)) == ["checkpoint_metadata.json", "config.yaml", "lr_scheduler", "model", "model_config.json", "optimizer", "random"]
+        assert sorted(os.listdir(tmp_path / "ckpt")) == ["latest.txt"]  # the step folders are gone
+        # a new job on an empty disk resumes from the bucket: latest.txt is read remotely, step 4 is fetched, training goes on to 6
+        out = str(tmp_path / "resumed.pt")
+        run_distributed(_train_with_upload, 2, ckpt=str(tmp_path / "fresh_disk"), tool=str(tool), steps=6, resume="s3://bucket/run1", out_file=out)
     finally:
         os.environ.pop("FAKE_S3_ROOT")
-    remote = tmp_path / "object_store" / "bucket" / "run1"
-    assert sorted(os.listdir(remote)) == ["2", "4", "latest.txt"] and (remote / "latest.txt").read_text() == "4"
-    for step in ("2", "4"):
-        assert sorted(os.listdir(remote / step)) == ["checkpoint_metadata.json", "config.yaml", "lr_scheduler", "model", "model_config.json", "optimizer", "random"]
-    assert sorted(os.listdir(tmp_path / "ckpt")) == ["latest.txt"]  # the step folders are gone
+    assert torch.load(out) == {"start": 4, "end": 6, "samples": 6 * 4}
+    assert sorted(os.listdir(remote)) == ["2", "4", "6", "latest.txt"] and (remote / "latest.txt").read_text() == "6"
