@@ -267,3 +267,29 @@ def test_detailed_metrics_attention_statistics_and_diagnostics_reach_the_metric_
     # the two tensor-parallel ranks see different shards of a sharded matrix and the same replicated norm weight
     assert other[0]["weights/layer_0/attn/qkv_proj/l2"] != detailed["weights/layer_0/attn/qkv_proj/l2"]
     assert other[0]["weights/layer_0/input_layernorm/mean"] == detailed["weights/layer_0/input_layernorm/mean"]
+
+
+def test_benchmark_mode_appends_one_row_and_stops_after_four_steps(tmp_path, monkeypatch):
+    """``NANOTRON_BENCHMARK=1``: the throughput table is printed and appended to ``general.benchmark_csv_path`` at step 4, then the
+    run ends (a second run appends under the same header)."""
+    import csv
+
+    from helpers import dummy_dataloader, make_config, single_process_env, tiny_llama_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    monkeypatch.setenv("NANOTRON_BENCHMARK", "1")
+    monkeypatch.setenv("SLURM_JOB_ID", "4242")
+    path = tmp_path / "bench.csv"
+    for run in range(2):
+        single_process_env()
+        cfg = make_config(tiny_llama_config(), seq=16, steps=10)
+        cfg.general.benchmark_csv_path = str(path)
+        cfg.logging.iteration_step_info_interval = 1
+        t = DistributedTrainer(cfg)
+        with pytest.raises(SystemExit) as stop:
+            t.train(dummy_dataloader(t))
+        assert stop.value.code == 0 and t.iteration_step == 4
+        t.parallel_context.destroy()
+    rows = list(csv.DictReader(open(path)))
+    assert len(rows) == 2 and rows[0]["job_id"] == "4242" and rows[0]["seq_len"] == "16" and rows[0]["dp"] == rows[0]["tp"] == "1"
+    assert float(rows[0]["tok/s/gpu"]) > 0 and rows[0]["pp_engine"] == "AllForwardAllBackwardPipelineEngine" and rows[0]["Total Params"] == rows[0]["Local Params"]
