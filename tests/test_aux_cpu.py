@@ -293,3 +293,30 @@ def test_benchmark_mode_appends_one_row_and_stops_after_four_steps(tmp_path, mon
     rows = list(csv.DictReader(open(path)))
     assert len(rows) == 2 and rows[0]["job_id"] == "4242" and rows[0]["seq_len"] == "16" and rows[0]["dp"] == rows[0]["tp"] == "1"
     assert float(rows[0]["tok/s/gpu"]) > 0 and rows[0]["pp_engine"] == "AllForwardAllBackwardPipelineEngine" and rows[0]["Total Params"] == rows[0]["Local Params"]
+
+
+def test_profiler_section_writes_a_trace_with_the_named_regions(tmp_path):
+    import glob
+    import gzip
+    import json
+
+    import nanotron_b200.config as c
+    from helpers import dummy_dataloader, make_config, single_process_env, tiny_llama_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    single_process_env()
+    cfg = make_config(tiny_llama_config(), seq=16, steps=6)
+    cfg.profiler = c.ProfilerArgs(profiler_export_path=tmp_path / "traces", wait=1, warmup=1, active=1, repeat=1, skip_first=1)
+    t = DistributedTrainer(cfg)
+    t.train(dummy_dataloader(t))
+    t.parallel_context.destroy()
+    traces = glob.glob(str(tmp_path / "traces" / "*" / "*.json*"))
+    assert len(traces) == 1, traces  # one active window of one step
+    opener = gzip.open if traces[0].endswith(".gz") else open
+    with opener(traces[0], "rt") as f:
+        names = {e.get("name") for e in json.load(f)["traceEvents"]}
+    assert {"train_batch_iter", "micro_batch_forward", "micro_batch_backward", "optimizer_step"} <= names
+    # a schedule that does not fit into the run is rejected when the configuration is built
+    cfg.profiler = c.ProfilerArgs(profiler_export_path=tmp_path / "traces", wait=3, warmup=3, active=3, repeat=1, skip_first=3)
+    with pytest.raises((AssertionError, ValueError)):
+        c.Config(**{f.name: getattr(cfg, f.name) for f in __import__("dataclasses").fields(cfg)})
