@@ -320,3 +320,29 @@ def test_profiler_section_writes_a_trace_with_the_named_regions(tmp_path):
     cfg.profiler = c.ProfilerArgs(profiler_export_path=tmp_path / "traces", wait=3, warmup=3, active=3, repeat=1, skip_first=3)
     with pytest.raises((AssertionError, ValueError)):
         c.Config(**{f.name: getattr(cfg, f.name) for f in __import__("dataclasses").fields(cfg)})
+
+
+def test_wandb_receives_one_record_per_logged_step(monkeypatch):
+    """With ``WANDB_MODE`` set, the logger rank opens one run named after the configuration and logs every console step (the
+    package is replaced by a recorder here)."""
+    import sys
+    import types
+
+    from helpers import dummy_dataloader, make_config, single_process_env, tiny_llama_config
+    from nanotron_b200.trainer import DistributedTrainer
+
+    calls = {"init": [], "log": []}
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kw: calls["init"].append(kw)
+    fake.log = lambda record, **kw: calls["log"].append(record)
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.setenv("WANDB_MODE", "offline")
+    single_process_env()
+    cfg = make_config(tiny_llama_config(), seq=16, steps=5)
+    cfg.logging.iteration_step_info_interval = 2  # steps 1, 3, 5
+    t = DistributedTrainer(cfg)
+    t.train(dummy_dataloader(t))
+    t.parallel_context.destroy()
+    assert len(calls["init"]) == 1 and calls["init"][0]["project"] == "test" and calls["init"][0]["name"] == "t" and "nanotron_config" in calls["init"][0]["config"]
+    assert [r["iteration_step"] for r in calls["log"]] == [1, 3, 5]
+    assert all({"lm_loss", "tokens_per_sec", "lr", "consumed_tokens", "model_tflops_per_gpu"} <= set(r) for r in calls["log"])
