@@ -106,7 +106,7 @@ def _mamba_run(out_file, tp=1, pp=1, steps=80):
 
     os.chdir(os.path.dirname(out_file))
     cfg = create.build(d_model=32, layers=2, vocab=16, seq=32, mbs=8, steps=steps, tp=tp, pp=pp, lr=3e-2)
-    path = os.path.join(os.path.dirname(out_file), f"mamba_{dist.get_rank() if dist.is_initialized() else 0}.yaml")
+    path = os.path.join(os.path.dirname(out_file), f"mamba_{os.environ.get('RANK', '0')}.yaml")  # one file per rank: they are written concurrently
     cfg.save_as_yaml(path)  # the extended config survives the YAML round trip without naming its classes
     t = MambaTrainer(path)
     assert isinstance(t.unwrapped_model, mb.MambaForTraining) and t.model_config.ssm()["dt_rank"] == 2
@@ -206,7 +206,7 @@ def _llamoe_run(out_file):
 
     os.chdir(os.path.dirname(out_file))
     cfg = cfgmod.build(hidden_size=32, layers=2, heads=4, experts=4, top_k=2, expert_size=32, vocab=64, seq=32, mbs=2, dp=2, ep=2, steps=12, dtype="float32", lr=3e-3)
-    path = os.path.join(os.path.dirname(out_file), f"llamoe_{dist.get_rank() if dist.is_initialized() else 0}.yaml")
+    path = os.path.join(os.path.dirname(out_file), f"llamoe_{os.environ.get('RANK', '0')}.yaml")  # one file per rank: they are written concurrently
     cfg.save_as_yaml(path)
     t = train.make_trainer(path)  # from the YAML file: the extra model-config fields survive the round trip
     model = t.unwrapped_model
