@@ -252,4 +252,7 @@ def check_model_has_grad(model: NanotronModel, parallel_context: ParallelContext
         if dist.get_rank(parallel_context.pp_pg) != stage:
             continue
         if not any(p.requires_grad for p in model.parameters()):
-            raise ValueError(f"Can't use DDP because model in PP={stage} has no gradient. Consider moving to a previous stage")
+            raise ValueError(
+                f"pipeline stage {stage} of {parallel_context.pp_pg.size()} holds no trainable parameter: the model has too few blocks "
+                f"(or too uneven block costs) for this many stages; use fewer pipeline stages"
+            )

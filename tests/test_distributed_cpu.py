@@ -205,13 +205,14 @@ def _train_losses(out_file, steps=4, total_mbs=4, model="llama", norms_file=None
     accum = total_mbs // (dp * mbs)
     tie = topology.pop("tie", False)
     packed = topology.pop("packed", False)
+    layers = topology.pop("layers", 2)
     if model == "moe":
         import nanotron_b200.config as c
 
         moe = c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=16, shared_expert_intermediate_size=32, enable_shared_expert=True, router_aux_loss_coef=0.01)
         mc = tiny_qwen_config(tie_word_embeddings=tie, moe_config=moe)
     else:
-        mc = tiny_llama_config(tie_word_embeddings=tie) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie, _use_doc_masking=packed)
+        mc = tiny_llama_config(tie_word_embeddings=tie, num_hidden_layers=layers) if model == "llama" else tiny_qwen_config(tie_word_embeddings=tie, _use_doc_masking=packed, num_hidden_layers=layers)
     cfg = make_config(mc, seq=16, mbs=mbs, accum=accum, steps=steps, lr=1e-2, **topology)
     t = DistributedTrainer(cfg)
     t.prepare_training()
