@@ -10,11 +10,13 @@ token; without it the whole prefix is recomputed each step (what the reference d
 from __future__ import annotations
 
 import dataclasses
-from typing import Generator, Iterable, List, Optional, Union
+import time
+from typing import Dict, Generator, Iterable, List, Optional, Union
 
 import torch
 
 from nanotron_b200 import distributed as dist
+from nanotron_b200 import logging
 from nanotron_b200.config import GenerationArgs
 from nanotron_b200.config.utils_config import SamplerType
 from nanotron_b200.generation.generate_store import Store, attach_store
@@ -22,7 +24,10 @@ from nanotron_b200.generation.sampler import BasicSampler, GreedySampler, TopKSa
 from nanotron_b200.parallel import ParallelContext
 from nanotron_b200.parallel.pipeline_parallel.context_manager import attach_pipeline_state_to_model
 from nanotron_b200.parallel.pipeline_parallel.state import PipelineEvalBatchState
+from nanotron_b200.logging import log_rank
 from nanotron_b200.parallel.pipeline_parallel.tensor_pointer import TensorPointer
+
+logger = logging.get_logger(__name__)
 
 
 @dataclasses.dataclass
@@ -102,9 +107,11 @@ def decode_tokenized(
     use_cache: bool = False,
     eos_token_id: Optional[int] = None,
     returns_logits: bool = False,
+    is_bench: bool = False,
 ) -> GenerationOutput:
     """``model`` is the bare transformer (``trainer.unwrapped_model.model``).  Inputs are [b, s], left padded, present on
-    every rank (tiny).  Returns the generated ids [b, <= max_new_tokens] on every rank."""
+    every rank (tiny).  Returns the generated ids [b, <= max_new_tokens] on every rank.  ``is_bench`` logs the decoding
+    throughput of the call (the first step, which reads the whole prompt, is timed apart; reference generation/decode.py:277-449)."""
     ctx = parallel_context
     device = ctx.device
     input_ids, input_mask = input_ids.to(device), input_mask.to(device).bool()
@@ -125,7 +132,10 @@ def decode_tokenized(
     cur_ids, cur_mask = input_ids, input_mask
     state = PipelineEvalBatchState()
     with attach_pipeline_state_to_model(model, state), (attach_store(model, store) if use_cache else _null()):
+        clock = _DecodeClock(device) if is_bench else None
         for step in range(max_new_tokens):
+            if clock is not None:
+                clock.step_begins(step)
             if use_cache and step > 0:
                 step_ids, step_mask = generated[:, -1:], torch.ones((b, 1), dtype=torch.bool, device=device)
             else:
@@ -156,8 +166,44 @@ def decode_tokenized(
             cur_mask = torch.cat([cur_mask, torch.ones((b, 1), dtype=torch.bool, device=device)], dim=1)
             if eos_token_id is not None and bool(finished.all()):
                 break
+    if clock is not None:
+        clock.report(batch=b, steps=generated.shape[1], replicas=ctx.dp_pg.size(), world=ctx.world_pg.size(), use_cache=use_cache)
     model.train(was_training)
     return GenerationOutput(input_ids=input_ids, generation_ids=generated, return_logits=torch.stack(all_logits, 1) if all_logits else None)
+
+
+class _DecodeClock:
+    """Wall-clock of a decoding loop, synchronised with the device at the two points that are read."""
+
+    def __init__(self, device):
+        self.device = device
+        self.start = self.after_first = None
+        self.last: Optional[Dict[str, float]] = None
+
+    def _now(self) -> float:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        return time.perf_counter()
+
+    def step_begins(self, step: int):
+        if step == 0:
+            self.start = self._now()
+        elif step == 1:
+            self.after_first = self._now()
+
+    def report(self, batch: int, steps: int, replicas: int, world: int, use_cache: bool):
+        end = self._now()
+        first = (self.after_first if self.after_first is not None else end) - self.start
+        rest = end - (self.after_first if self.after_first is not None else end)
+        later_steps = max(steps - 1, 0)
+        tokens_per_sec = batch * replicas * later_steps / rest if rest > 0 and later_steps else 0.0
+        self.last = {"first_step_s": first, "later_steps_s": rest, "tokens_per_sec": tokens_per_sec, "tokens_per_sec_per_gpu": tokens_per_sec / world}
+        _DecodeClock.last_report = self.last
+        log_rank(
+            f"[decode bench] batch {batch} x {steps} new tokens ({'cached' if use_cache else 'recomputed'} keys / values): first step {first * 1e3:.1f} ms, "
+            f"{later_steps} later steps {rest * 1e3:.1f} ms -> {tokens_per_sec:.1f} tokens/s ({tokens_per_sec / world:.1f} per process)",
+            logger=logger, level=logging.INFO, rank=0,
+        )
 
 
 class _null:
@@ -180,6 +226,7 @@ def decode_text(
     tokenizer_config: Optional[TokenizerConfig] = None,
     returns_logits: bool = False,
     use_cache: bool = False,
+    is_bench: bool = False,
 ) -> Generator[GenerationOutput, None, None]:
     """Yields one ``GenerationOutput`` per input text (ids are trimmed of padding)."""
     if getattr(tokenizer, "pad_token_id", None) is None:
@@ -193,7 +240,7 @@ def decode_text(
         )
         out = decode_tokenized(
             enc["input_ids"], enc["attention_mask"], model=model, parallel_context=parallel_context, generation_config=generation_config,
-            max_new_tokens=max_new_tokens, use_cache=use_cache, eos_token_id=getattr(tokenizer, "eos_token_id", None), returns_logits=returns_logits,
+            max_new_tokens=max_new_tokens, use_cache=use_cache, eos_token_id=getattr(tokenizer, "eos_token_id", None), returns_logits=returns_logits, is_bench=is_bench,
         )
         mask = enc["attention_mask"].bool()
         for i in range(len(batch)):

@@ -74,6 +74,7 @@ def main():
         outputs = decode_text(
             input_iter=(GenerationInput(text=t) for t in prompts), tokenizer=tokenizer, model=model.model, parallel_context=ctx, max_new_tokens=args.max_new_tokens,
             max_micro_batch_size=2, generation_config=gen_cfg, tokenizer_config=TokenizerConfig(max_input_length=None), use_cache=args.use_cache,
+            is_bench=os.environ.get("USE_BENCH", "0") == "1",  # also logs the decoding throughput of every micro-batch
         )
         for out in outputs:
             log_rank(f"input: {tokenizer.decode(out.input_ids, clean_up_tokenization_spaces=False)[:1000]}", logger=logger, level=logging.INFO, rank=0)
@@ -82,7 +83,8 @@ def main():
     else:
         # no tokenizer in the config: generate from random token ids (smoke run)
         ids = torch.randint(0, model_config.vocab_size, (2, 8), generator=torch.Generator().manual_seed(0))
-        out = decode_tokenized(ids, torch.ones_like(ids, dtype=torch.bool), model=model.model, parallel_context=ctx, generation_config=gen_cfg, max_new_tokens=args.max_new_tokens, use_cache=args.use_cache)
+        out = decode_tokenized(ids, torch.ones_like(ids, dtype=torch.bool), model=model.model, parallel_context=ctx, generation_config=gen_cfg, max_new_tokens=args.max_new_tokens, use_cache=args.use_cache,
+                               is_bench=os.environ.get("USE_BENCH", "0") == "1")
         for i in range(ids.shape[0]):
             log_rank(f"input: {ids[i].tolist()}", logger=logger, level=logging.INFO, rank=0)
             log_rank(f"generation: {out.generation_ids[i].tolist()}", logger=logger, level=logging.INFO, rank=0)

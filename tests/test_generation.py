@@ -1,3 +1,4 @@
+import pytest
 import torch
 
 from helpers import make_config, single_process_env, tiny_llama_config, tiny_qwen_config
@@ -26,6 +27,13 @@ def test_greedy_decode_cache_matches_recompute():
     # a row decoded alone gives what it gives inside the padded batch
     alone = decode_tokenized(ids[1:, 3:], mask[1:, 3:], t.unwrapped_model.model, t.parallel_context, max_new_tokens=6, use_cache=True)
     assert torch.equal(alone.generation_ids[0], b.generation_ids[1])
+    # the timed mode changes nothing but reports the decoding rate of the call
+    from nanotron_b200.generation.decode import _DecodeClock
+
+    timed = decode_tokenized(ids, mask, t.unwrapped_model.model, t.parallel_context, max_new_tokens=6, use_cache=True, is_bench=True)
+    assert torch.equal(timed.generation_ids, b.generation_ids)
+    report = _DecodeClock.last_report
+    assert report["first_step_s"] > 0 and report["later_steps_s"] > 0 and report["tokens_per_sec"] == pytest.approx(2 * 5 / report["later_steps_s"])
     t.parallel_context.destroy()
 
 
