@@ -378,3 +378,52 @@ def test_rotary_options_layers_without_rope_and_frequency_scaling():
     if got is not None:
         assert torch.allclose(got[0], plain[0]) and torch.allclose(got[-1], plain[-1] / 8.0, rtol=1e-4)
     t.parallel_context.destroy()
+
+
+def test_fp32_accumulator_keeps_what_half_precision_would_lose():
+    """Gradients of bf16 parameters are summed in fp32 over the micro-batches, the optimizer works on fp32 masters, and the step
+    writes the masters back to the bf16 parameters: small updates that bf16 alone would round away survive."""
+    from nanotron_b200.optim.gradient_accumulator import FP32GradientAccumulator
+    from nanotron_b200.parallel.parameters import NanotronParameter
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(16, 8, bias=True).to(torch.bfloat16)
+    for name in ("weight", "bias"):
+        setattr(lin, name, NanotronParameter(getattr(lin, name).data))
+    named = list(lin.named_parameters())
+    acc = FP32GradientAccumulator(named)
+    reference = {n: p.detach().double().clone().requires_grad_(True) for n, p in named}
+    xs = [torch.randn(4, 16) for _ in range(3)]
+    for x in xs:  # three micro-batches
+        acc.backward(lin(x.to(torch.bfloat16)).float().pow(2).mean())
+        (x.double() @ reference["weight"].t() + reference["bias"]).pow(2).mean().backward()
+    for n, p in named:
+        assert p.grad is None  # the half-precision gradient is consumed at once
+        got, exp = acc.get_grad_buffer(n), reference[n].grad
+        assert got.dtype == torch.float32 and got.shape == p.shape
+        torch.testing.assert_close(got.double(), exp, rtol=0.05, atol=2e-2)  # bf16 forward, fp32 sum
+    # one flat buffer behind all slots
+    flat = acc._contiguous_fp32_grad_buffer
+    assert flat.numel() >= sum(p.numel() for _, p in named) and acc.get_grad_buffer("weight").data_ptr() == flat.data_ptr() + acc._grad_offsets["weight"] * 4
+    # an update far below bf16 resolution, applied 64 times: the masters move, and so (eventually) do the parameters
+    master = acc.get_parameter_for_optimizer("weight")
+    assert master.dtype == torch.float32 and master.grad is not None
+    before_master, before_half = master.detach().clone(), lin.weight.detach().clone()
+    for _ in range(64):
+        with torch.no_grad():
+            master.add_(1e-4)  # |w| ~ 0.1: one bf16 step there is ~5e-4
+        acc.step()
+    torch.testing.assert_close(master.detach(), before_master + 64e-4, rtol=0, atol=1e-6)
+    assert float((lin.weight.detach().float() - before_half.float()).mean()) == pytest.approx(64e-4, rel=0.2)
+    in_bf16 = before_half.clone()
+    for _ in range(64):
+        in_bf16 += 1e-4
+    assert float((in_bf16.float() - before_half.float()).abs().mean()) < 0.5 * 64e-4  # what accumulating in bf16 would have kept
+    acc.zero_grad()
+    assert float(flat.abs().sum()) == 0.0
+    # the masters are the state that a checkpoint carries
+    state = acc.state_dict()
+    assert set(state) == {"weight", "bias"} and state["weight"].dtype == torch.float32
+    fresh = FP32GradientAccumulator(named)
+    fresh.load_state_dict(state)
+    torch.testing.assert_close(fresh.get_parameter_for_optimizer("weight").detach(), master.detach(), rtol=0, atol=0)
