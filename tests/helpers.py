@@ -13,10 +13,27 @@ import torch
 import torch.multiprocessing as mp
 
 
+_USED_PORTS = set()
+
+
 def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+    """A port for a rendezvous that starts a moment later.  Taken from below the range the kernel hands out to outgoing connections
+    (32768 and up on Linux), so that neither the ranks' own connections nor another process can take it in between; each port is
+    tried at most once per process."""
+    import random
+
+    for _ in range(200):
+        port = random.randint(12000, 32000)
+        if port in _USED_PORTS:
+            continue
+        with socket.socket() as s:
+            try:
+                s.bind(("127.0.0.1", port))
+            except OSError:
+                continue
+        _USED_PORTS.add(port)
+        return port
+    raise RuntimeError("no free port found")
 
 
 def _worker(rank: int, world_size: int, port: int, fn: Callable, kwargs: dict, err_dir: str):

@@ -13,11 +13,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _free_port():
-    import socket
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import _free_port as pick
 
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+    return pick()
 
 
 def _write_datasets(tmp_path):
