@@ -24,7 +24,7 @@ def test_paths_named_in_the_guides_exist():
     tops = ("nanotron_b200/", "docs/", "examples/", "tests/", "tools/", "scripts/", "profiles/")
     missing = []
     measured = [os.path.join("profiles", f) for f in sorted(os.listdir(os.path.join(ROOT, "profiles"))) if f.endswith(".md")]
-    for doc in DOCS + measured + ["DESIGN.md"]:
+    for doc in DOCS + measured:
         for ref in re.findall(r"`([A-Za-z0-9_./{},*-]+)`", _text(doc)):
             if "<" in ref or not ref.startswith(tops):
                 continue
