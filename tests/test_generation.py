@@ -98,3 +98,38 @@ def test_decoding_through_pipeline_and_tensor_parallel_stages(tmp_path):
         outs[name] = torch.load(f)
     for name in ("pp2", "pp2_cache", "tp2pp2"):
         assert torch.equal(outs[name], outs["single"]), (name, outs[name], outs["single"])
+
+
+def _moe_decode(out_file, **topology):
+    import nanotron_b200.config as c
+    import nanotron_b200.distributed as dist
+    from nanotron_b200.generation.decode import decode_tokenized
+    from nanotron_b200.trainer import DistributedTrainer
+    from test_distributed_cpu import _deterministic_init
+
+    class T(DistributedTrainer):
+        def _load_model_checkpoint(self, model):
+            _deterministic_init(model)
+            return model
+
+    moe = c.MoEConfig(num_experts=4, top_k=2, moe_intermediate_size=16, shared_expert_intermediate_size=32, enable_shared_expert=True)
+    t = T(make_config(tiny_qwen_config(moe_config=moe), seq=16, **topology))
+    ids = torch.randint(0, 256, (2, 6), generator=torch.Generator().manual_seed(0))
+    out = decode_tokenized(ids, torch.ones_like(ids, dtype=torch.bool), t.unwrapped_model.model, t.parallel_context, max_new_tokens=5)
+    if dist.get_rank(t.parallel_context.world_pg) == 0:
+        torch.save(out.generation_ids.cpu(), out_file)
+    dist.barrier()
+    t.parallel_context.destroy()
+
+
+def test_mixture_of_experts_decodes_the_same_with_experts_split_over_ranks(tmp_path):
+    """Greedy decoding of a Qwen2 mixture-of-experts model: experts split over two expert-parallel ranks (tokens are dispatched
+    and combined at every step) and a tensor-parallel split give the tokens of one process."""
+    from helpers import run_distributed
+
+    outs = {}
+    for name, world, kw in (("single", 1, {}), ("ep2", 2, dict(dp=2, ep=2)), ("tp2", 2, dict(tp=2))):
+        f = str(tmp_path / f"{name}.pt")
+        run_distributed(_moe_decode, world, out_file=f, **kw)
+        outs[name] = torch.load(f)
+    assert torch.equal(outs["ep2"], outs["single"]) and torch.equal(outs["tp2"], outs["single"]), outs
