@@ -63,9 +63,12 @@ def dummy_infinite_data_generator(
     use_position_ids: bool = False,
     cp_zigzag: bool = True,
     host_pinned: bool = False,
+    skip_batches: int = 0,
 ):
     """Returns a generator factory.  ``host_pinned=True`` builds every batch in pinned host memory and copies it to
-    the device asynchronously (the end-to-end input path); otherwise tokens are drawn directly on the device."""
+    the device asynchronously (the end-to-end input path); otherwise tokens are drawn directly on the device.
+    ``skip_batches``: micro-batches this rank already consumed (a resumed run): they are drawn and dropped, so that the run
+    continues with the batch the interrupted one would have seen next (the reference restarts the stream)."""
 
     def data_generator() -> Generator[Dict[str, Union[torch.Tensor, TensorPointer]], None, None]:
         device = parallel_context.device
@@ -87,6 +90,8 @@ def dummy_infinite_data_generator(
                 return t.pin_memory().to(device, non_blocking=True)
             return t.to(device) if t.device != device else t
 
+        for _ in range(skip_batches):
+            torch.randint(0, vocab_size, (micro_batch_size, sequence_length + 1), dtype=torch.long, device=gen_device, generator=generator)
         while True:
             tokens = torch.randint(0, vocab_size, (micro_batch_size, sequence_length + 1), dtype=torch.long, device=gen_device, generator=generator)
             input_ids, label_ids = tokens[:, :-1], tokens[:, 1:]

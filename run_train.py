@@ -37,6 +37,7 @@ def get_dataloader_from_data_stage(trainer: DistributedTrainer, data: DataArgs, 
         return dummy_infinite_data_generator(
             micro_batch_size=trainer.micro_batch_size, sequence_length=seq, input_pp_rank=input_pp_rank, output_pp_rank=output_pp_rank,
             vocab_size=trainer.model_config.vocab_size, seed=data.seed, parallel_context=trainer.parallel_context, use_position_ids=not uses_mask,
+            skip_batches=consumed_train_samples_stage // (trainer.parallel_context.dp_pg.size() * trainer.micro_batch_size),
         )()
     if isinstance(data.dataset, (PretrainDatasetsArgs, SFTDatasetsArgs)):
         from transformers import AutoTokenizer

@@ -356,7 +356,7 @@ def test_expert_parallelism_with_pipeline_and_context_parallelism(tmp_path):
         assert abs(a - b) < 3e-4, (got, rep_cp)
 
 
-def _two_stage_lengths(out_file, **topology):
+def _two_stage_lengths(out_file, ckpt=None, resume=None, **topology):
     import importlib.util
 
     import nanotron_b200.config as c
@@ -368,7 +368,8 @@ def _two_stage_lengths(out_file, **topology):
     spec = importlib.util.spec_from_file_location("run_train_for_stage_test", os.path.join(root, "run_train.py"))
     run_train = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(run_train)
-    cfg = make_config(tiny_qwen_config(max_position_embeddings=64), seq=16, mbs=2, accum=2, steps=5, lr=1e-2, sanity=True, **topology)
+    cfg = make_config(tiny_qwen_config(max_position_embeddings=64), seq=16, mbs=2, accum=2, steps=5, lr=1e-2, sanity=True, ckpt_path=ckpt, ckpt_interval=4, **topology)
+    cfg.checkpoints.resume_checkpoint_path = resume
     cfg.data_stages = [
         c.DatasetStageArgs(name="short", start_training_step=1, data=c.DataArgs(dataset=None, seed=3)),
         c.DatasetStageArgs(name="long", start_training_step=3, data=c.DataArgs(dataset=None, seed=4), sequence_length=32),
@@ -379,7 +380,7 @@ def _two_stage_lengths(out_file, **topology):
 
     def spy(dataloader):
         result = step(dataloader)
-        seen.append((t.iteration_step, t.sequence_length))
+        seen.append((t.iteration_step, t.sequence_length) + ((round(float(result[1]), 5),) if result[1] is not None else ()))
         return result
 
     t.training_step = spy
@@ -393,11 +394,16 @@ def _two_stage_lengths(out_file, **topology):
 def test_data_stages_may_change_the_sequence_length_under_pipeline_parallelism(tmp_path):
     """The second stage doubles the sequence length: pipeline stages that replay learnt activation shapes must learn the new ones
     at the switch, and the token accounting follows the stage's length."""
-    out = str(tmp_path / "stages.pt")
-    run_distributed(_two_stage_lengths, 4, out_file=out, pp=2, tp=2, tp_mode="reduce_scatter", pp_engine="1f1b")
+    out, ckpt = str(tmp_path / "stages.pt"), str(tmp_path / "ckpt")
+    layout = dict(pp=2, tp=2, tp_mode="reduce_scatter", pp_engine="1f1b")
+    run_distributed(_two_stage_lengths, 4, out_file=out, ckpt=ckpt, **layout)
     res = torch.load(out)
-    assert res["seen"] == [(1, 16), (2, 16), (3, 32), (4, 32), (5, 32)]
+    assert [(step, length) for step, length, _ in res["seen"]] == [(1, 16), (2, 16), (3, 32), (4, 32), (5, 32)]
     assert res["tokens"] == 2 * 4 * 16 + 3 * 4 * 32 and res["stages"] == [("short", 8, 16), ("long", 12, 32)]
+    # resumed inside the second stage (checkpoint of step 4): the synthetic stream continues where it stopped, so step 5 repeats exactly
+    run_distributed(_two_stage_lengths, 4, out_file=out, ckpt=ckpt, resume=ckpt, **layout)
+    again = torch.load(out)
+    assert again["seen"] == res["seen"][4:] and again["tokens"] == res["tokens"] and again["stages"] == res["stages"]
 
 
 def test_training_without_the_fp32_accumulator_agrees_across_layouts(tmp_path):
