@@ -157,6 +157,21 @@ def set_logger_verbosity_format(logging_level: str, parallel_context) -> None:
     root.propagate = False
 
 
+def show_metric_lines(logging_level: str) -> None:
+    """Print the per-iteration metric line of THIS rank at ``logging_level`` whatever the rank's general verbosity: the line is
+    written by the rank that holds the loss (the last pipeline stage), which is a "replica" for every other message."""
+    root = get_library_root_logger()
+    own = get_logger(__name__)  # the logger of ``LoggerWriter``
+    handler = logging.StreamHandler(sys.stdout)
+    handler.setLevel(log_levels[logging_level])
+    if root.handlers:
+        handler.setFormatter(root.handlers[0].formatter)
+    own.handlers.clear()
+    own.addHandler(handler)
+    own.setLevel(log_levels[logging_level])
+    own.propagate = False
+
+
 def set_ranks_logging_level(parallel_context, logging_config) -> None:
     """World rank 0 uses ``log_level``; every other rank ``log_level_replica``."""
     import nanotron_b200.distributed as dist

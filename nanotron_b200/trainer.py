@@ -125,6 +125,12 @@ class DistributedTrainer:
         set_random_seed(self.config.general.seed + dist.get_rank(self.parallel_context.tp_pg) + 1000 * dist.get_rank(self.parallel_context.pp_pg))
         self.model = self.init_model()
         self.unwrapped_model: NanotronModel = self.model
+        if dist.get_rank(self.parallel_context.world_pg) in self.logger_ranks and dist.get_rank(self.parallel_context.world_pg) != 0:
+            # the metric line of every step is printed by the rank that holds the loss (the last pipeline stage): that line follows
+            # ``log_level`` like the rest of the run's console output, not ``log_level_replica``
+            from nanotron_b200.logging.base import show_metric_lines
+
+            show_metric_lines(self.config.logging.log_level or "info")
         self._configure_pipeline_p2p()
         parametrization_method = ParametrizationMethod.SPECTRAL_MUP if hasattr(self.config.model.init_method, "use_mup") else ParametrizationMethod.STANDARD
         symm_alloc = self._maybe_enable_symmetric_buffers()

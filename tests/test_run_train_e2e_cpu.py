@@ -149,7 +149,9 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
     cfg = c.Config(
         general=c.GeneralArgs(project="e2e", run=kind, seed=3),
         checkpoints=c.CheckpointsArgs(checkpoints_path=str(tmp_path / "ckpt"), checkpoint_interval=1000, save_final_state=kind == "text"),
-        parallelism=c.ParallelismArgs(dp=2, pp=1, tp=1),
+        # raw text: two data-parallel replicas; prompt / completion pairs: two pipeline stages (the collator hands pointers to the stage
+        # that does not consume a key, and the metric line comes from the last stage although replicas only log errors)
+        parallelism=c.ParallelismArgs(dp=2, pp=1, tp=1) if kind == "text" else c.ParallelismArgs(dp=1, pp=2, tp=1, pp_engine="1f1b"),
         model=c.ModelArgs(model_config=model, init_method=c.RandomInit(std=0.05), dtype="float32"),
         tokenizer=c.TokenizerArgs(tokenizer_name_or_path=str(tmp_path / "tok")),
         optimizer=c.OptimizerArgs(
@@ -157,7 +159,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
             accumulate_grad_in_fp32=True, learning_rate_scheduler=c.LRSchedulerArgs(learning_rate=1e-2, lr_warmup_steps=2, lr_decay_style="cosine", min_decay_lr=1e-3),
         ),
         logging=c.LoggingArgs(log_level="info", log_level_replica="error", iteration_step_info_interval=1),
-        tokens=c.TokensArgs(sequence_length=32, train_steps=steps, micro_batch_size=4, batch_accumulation_per_replica=1),
+        tokens=c.TokensArgs(sequence_length=32, train_steps=steps, micro_batch_size=4, batch_accumulation_per_replica=1 if kind == "text" else 2),
         data_stages=[c.DatasetStageArgs(name="only", start_training_step=1, data=c.DataArgs(dataset=dataset, seed=7, num_loading_workers=0))],
     )
     path = str(tmp_path / f"{kind}.yaml")
