@@ -14,6 +14,8 @@ import os
 import sys
 from typing import Dict, Optional
 
+import numpy as np
+
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from nanotron_b200 import logging  # noqa: E402
@@ -116,7 +118,41 @@ def get_dataloader_from_data_stage(trainer: DistributedTrainer, data: DataArgs, 
     raise ValueError(f"Unhandled case of `self.config.data.dataset`. Got: {data.dataset}")
 
 
-def get_dataloader(trainer: DistributedTrainer):
+def log_batches_every(dataloader, interval: int, tokenizer_path: Optional[str], stage_name: str):
+    """Pass the batches of ``dataloader`` through and describe every ``interval``-th one on rank 0: shapes, the first tokens of
+    the first row (decoded when the configuration names a tokenizer), where its documents start, how many labels count
+    (``--sanity-check-dataloader-interval``; capability parity: reference run_train.py:302-307).  Nothing is consumed twice."""
+    tokenizer = None
+    if tokenizer_path is not None:
+        try:
+            from transformers import AutoTokenizer
+
+            tokenizer = AutoTokenizer.from_pretrained(tokenizer_path)
+        except Exception as e:  # a debugging aid must not stop the run
+            log_rank(f"[dataloader sample] tokenizer {tokenizer_path} not usable ({type(e).__name__}): printing ids", logger=logger, level=logging.WARNING, rank=0)
+    for index, batch in enumerate(dataloader):
+        if index % interval == 0:
+            lines = [f"[dataloader sample] stage {stage_name!r}, micro-batch {index}"]
+            for key, value in batch.items():
+                if hasattr(value, "shape"):
+                    lines.append(f"  {key}: shape {tuple(value.shape)} dtype {getattr(value, 'dtype', '?')}")
+                else:
+                    lines.append(f"  {key}: {value}")
+            ids = batch.get("input_ids")
+            if hasattr(ids, "shape"):
+                row = [int(t) for t in ids[0][:32]]
+                lines.append("  first row: " + (repr(tokenizer.decode(row)) if tokenizer is not None else str(row)))
+            positions = batch.get("position_ids")
+            if hasattr(positions, "shape"):
+                lines.append(f"  documents of the first row start at {[i for i, p in enumerate(positions[0].tolist()) if p == 0][:16]}")
+            mask = batch.get("label_mask")
+            if hasattr(mask, "shape"):
+                lines.append(f"  labels that count: {int(mask.sum())} of {int(np.prod(mask.shape))}")  # (numpy from the collators, tensors from generators)
+            log_rank("\n".join(lines), logger=logger, level=logging.INFO, rank=0)
+        yield batch
+
+
+def get_dataloader(trainer: DistributedTrainer, sanity_check_dataloader_interval: Optional[int] = None):
     """{stage name: dataloader or zero-argument factory}.  The stage to resume is built now, later stages lazily."""
     dataloaders = {}
     stages = sorted(trainer.config.data_stages, key=lambda s: s.start_training_step)
@@ -129,11 +165,28 @@ def get_dataloader(trainer: DistributedTrainer):
         log_rank(f"[Training Plan] Stage {stage.name} has {remaining} remaining training steps and has consumed {consumed} samples", logger=logger, level=logging.INFO, rank=0)
 
         def build(stage=stage, consumed=consumed, remaining=remaining, meta_stage=meta_stage):
-            return get_dataloader_from_data_stage(trainer, stage.data, consumed_train_samples_stage=consumed, consumed_tokens_per_dataset_folder=meta_stage.consumed_tokens_per_dataset_folder, num_remaining_train_steps=remaining, sequence_length=stage.sequence_length)
+            dl = get_dataloader_from_data_stage(trainer, stage.data, consumed_train_samples_stage=consumed, consumed_tokens_per_dataset_folder=meta_stage.consumed_tokens_per_dataset_folder, num_remaining_train_steps=remaining, sequence_length=stage.sequence_length)
+            if sanity_check_dataloader_interval:
+                tokenizer_path = trainer.config.tokenizer.tokenizer_name_or_path if trainer.config.tokenizer is not None else None
+                return _Described(dl, sanity_check_dataloader_interval, tokenizer_path, stage.name)
+            return dl
 
         is_current = stage_idx == (trainer.metadata.last_stage_idx or 0)
         dataloaders[stage.name] = build() if is_current else build
     return dataloaders
+
+
+class _Described:
+    """A dataloader whose batches are described now and then; keeps ``dataset`` visible (the trainer reads consumption
+    statistics from it)."""
+
+    def __init__(self, dataloader, interval: int, tokenizer_path: Optional[str], stage_name: str):
+        self.dataloader, self.interval, self.tokenizer_path, self.stage_name = dataloader, interval, tokenizer_path, stage_name
+        if hasattr(dataloader, "dataset"):
+            self.dataset = dataloader.dataset
+
+    def __iter__(self):
+        return log_batches_every(self.dataloader, self.interval, self.tokenizer_path, self.stage_name)
 
 
 def get_args():
@@ -158,5 +211,5 @@ if __name__ == "__main__":
     args = get_args()
     wait_for_debugger_if_asked()
     trainer = DistributedTrainer(args.config_file)
-    dataloader = get_dataloader(trainer)
+    dataloader = get_dataloader(trainer, sanity_check_dataloader_interval=args.sanity_check_dataloader_interval)
     trainer.train(dataloader)

@@ -64,10 +64,10 @@ def _config(tmp_path, folders, resume=None, streamed=False):
     return path
 
 
-def _train(config_path):
+def _train(config_path, extra=()):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(ROOT, "run_train.py"), "--config-file", config_path]
+           os.path.join(ROOT, "run_train.py"), "--config-file", config_path, *extra]
     out = subprocess.run(cmd, capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     text = out.stdout + out.stderr
@@ -167,7 +167,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
     os.environ["HF_DATASETS_CACHE"] = str(tmp_path / "hf_cache")
     os.environ["HF_HUB_OFFLINE"] = "1"
     try:
-        losses, text = _train(path)
+        losses, text = _train(path, extra=("--sanity-check-dataloader-interval", "15") if kind == "text" else ())
         generations = []
         if kind == "text":
             # the checkpoint names its tokenizer: run_generate.py decodes text prompts, with and without the key / value cache
@@ -201,5 +201,7 @@ def test_run_train_on_raw_text_and_on_prompt_completion_pairs(tmp_path, kind):
     assert sorted(losses) == list(range(1, steps + 1)), text[-2000:]
     assert losses[20] < losses[1] - 1.0, losses
     if kind == "text":
+        # micro-batches 0, 15, 30 of rank 0 were described, decoded with the run's tokenizer
+        assert text.count("[dataloader sample] stage 'only'") == 3 and "first row: 'w" in text and "labels that count: 128 of 128" in text
         assert len(generations[0]) == 2 and all(len(g.split()) == 5 and all(w.startswith("w") for w in g.split()) for g in generations[0]), generations
         assert generations[0] == generations[1]
