@@ -157,7 +157,7 @@ def _stream_from_byte(path: str, start_byte: int, chunk: int):
 
 def _list_files(folder_path: str, pattern, recursive: bool) -> List[str]:
     if folder_path.startswith("s3://"):
-        return _get_s3_file_list(folder_path, pattern, recursive)
+        return _cached_s3_listing(folder_path, pattern, recursive)
     out = []
     for root, _, files in os.walk(folder_path):
         for f in files:
@@ -168,6 +168,34 @@ def _list_files(folder_path: str, pattern, recursive: bool) -> List[str]:
         if not recursive:
             break
     return sorted(out)
+
+
+def _cached_s3_listing(folder_path: str, pattern, recursive: bool) -> List[str]:
+    """Listing a large prefix takes minutes and every rank needs it: the result is kept in
+    ``$NANOTRON_CACHE (default ~/.cache/nanotron_b200)/s3_listings/<hash>.json`` and reused until ``FORCE_UPDATE_CACHE_S3=1`` asks for
+    a fresh one (capability parity: reference src/nanotron/data/tokenized_bytes.py:313-360)."""
+    import hashlib
+    import json
+
+    cache_dir = os.path.join(os.path.expanduser(os.environ.get("NANOTRON_CACHE", "~/.cache/nanotron_b200")), "s3_listings")
+    key = hashlib.md5(f"{folder_path}:{getattr(pattern, 'pattern', pattern)}:{recursive}".encode()).hexdigest()
+    cache_file = os.path.join(cache_dir, f"{key}.json")
+    if os.environ.get("FORCE_UPDATE_CACHE_S3", "0") != "1" and os.path.exists(cache_file):
+        try:
+            with open(cache_file) as f:
+                return json.load(f)["files"]
+        except (OSError, ValueError, KeyError):
+            pass  # unreadable cache: list again
+    files = _get_s3_file_list(folder_path, pattern, recursive)
+    try:
+        os.makedirs(cache_dir, exist_ok=True)
+        tmp = f"{cache_file}.{os.getpid()}.tmp"
+        with open(tmp, "w") as f:
+            json.dump({"folder": folder_path, "files": files}, f)
+        os.replace(tmp, cache_file)  # atomic: concurrent ranks never read a half-written file
+    except OSError:
+        pass
+    return files
 
 
 class OldTokenizedBytesFolderDataset(Dataset):

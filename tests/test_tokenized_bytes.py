@@ -184,3 +184,30 @@ def test_token_file_streams_from_an_object_store_and_survives_a_dropped_connecti
     fresh = TokenizedBytesFileDataset("s3://bucket/run/000.ds", seq_len=8)
     got = [fresh[i]["input_ids"].tolist() for i in range(5)]
     assert got == [list(range(9 * i, 9 * i + 9)) for i in range(5)] and state["opened"] == 2
+
+
+def test_object_store_listings_are_cached_until_a_refresh_is_asked_for(tmp_path, monkeypatch):
+    from nanotron_b200.data import s3_utils, tokenized_bytes
+
+    tokens = np.arange(90, dtype=np.uint16).tobytes()
+    store = {("bucket", "run/a/000.ds"): tokens, ("bucket", "run/a/001.ds"): tokens}
+    monkeypatch.setattr(s3_utils, "boto3", _FakeBoto3(store))
+    monkeypatch.setattr(s3_utils, "BOTO3_AVAILABLE", True)
+    monkeypatch.setenv("NANOTRON_CACHE", str(tmp_path / "cache"))
+    calls = {"n": 0}
+    real = tokenized_bytes._get_s3_file_list
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    monkeypatch.setattr(tokenized_bytes, "_get_s3_file_list", counting)
+    first = tokenized_bytes._list_files("s3://bucket/run", None, True)
+    assert first == ["s3://bucket/run/a/000.ds", "s3://bucket/run/a/001.ds"] and calls["n"] == 1
+    store[("bucket", "run/a/002.ds")] = tokens  # the bucket changes ...
+    assert tokenized_bytes._list_files("s3://bucket/run", None, True) == first and calls["n"] == 1  # ... the cached listing is used
+    monkeypatch.setenv("FORCE_UPDATE_CACHE_S3", "1")
+    assert len(tokenized_bytes._list_files("s3://bucket/run", None, True)) == 3 and calls["n"] == 2
+    monkeypatch.delenv("FORCE_UPDATE_CACHE_S3")
+    assert len(tokenized_bytes._list_files("s3://bucket/run", None, True)) == 3 and calls["n"] == 2  # the refreshed listing was stored
+    assert tokenized_bytes._list_files("s3://bucket/run", None, False) == [] and calls["n"] == 3  # another question, another entry
